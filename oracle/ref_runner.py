@@ -1,0 +1,84 @@
+"""TEST INFRASTRUCTURE — runs the compiled reference CPU engine harness (oracle/_ref/ref_gpt).
+
+Writes the binary input file ``oracle/ref_harness.cpp`` documents, executes the binary and parses
+its output.  Used to generate the golden vectors, to pin the numpy restatement and as the timed
+CPU baseline.  The product never imports this module.
+"""
+from __future__ import annotations
+
+import os
+import struct
+import subprocess
+import tempfile
+from typing import List, Optional
+
+import numpy as np
+
+from . import gpt_oracle as go
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_BIN = os.path.join(HERE, "_ref", "ref_gpt")
+
+
+def available() -> bool:
+    return os.path.isfile(REF_BIN) and os.access(REF_BIN, os.X_OK)
+
+
+def run_reference(cfg: go.GptConfig, params, micro_batches, *, steps, accum=1, lr=1e-3, wd=0.01,
+                  optimizer=go.OPT_ADAMW, muon_lr=0.02, clip=None, cosine=False, warmup=0,
+                  total_steps=1, min_lr=0.0, dump_grads=False, dump_logits=False,
+                  skip_params=False, threads: Optional[int] = None, timeout=3600):
+    """Returns dict(losses, grads|None, logits|None, params|None, seconds)."""
+    if not available():
+        raise RuntimeError("reference harness not built: run `make -C oracle` where the reference tree is present")
+    shapes = go.param_shapes(cfg)
+    use_doc = micro_batches[0].get("doc_ids") is not None
+    I = np.zeros(32, np.int32)
+    I[:21] = [cfg.vocab, cfg.d_model, cfg.heads, cfg.layers, cfg.d_ff, cfg.seq, cfg.batch, cfg.act,
+              cfg.norm, cfg.pos, int(use_doc), steps, accum, optimizer, int(clip is not None),
+              int(cosine), warmup, total_steps, int(dump_grads), int(dump_logits), int(skip_params)]
+    F = np.zeros(16, np.float32)
+    F[:5] = [lr, wd, clip if clip is not None else 0.0, min_lr, muon_lr]
+    with tempfile.TemporaryDirectory() as td:
+        fin, fout = os.path.join(td, "in.bin"), os.path.join(td, "out.bin")
+        with open(fin, "wb") as f:
+            f.write(struct.pack("<I", 0x3242424E))
+            f.write(I.tobytes())
+            f.write(F.tobytes())
+            f.write(struct.pack("<i", len(shapes)))
+            for p, (_, r, c) in zip(params, shapes):
+                f.write(struct.pack("<ii", r, c))
+                f.write(np.ascontiguousarray(p, np.float32).reshape(r, c).tobytes())
+            assert len(micro_batches) >= steps * accum
+            for mb in micro_batches[:steps * accum]:
+                f.write(np.asarray(mb["tokens"], np.int32).tobytes())
+                f.write(np.asarray(mb["labels"], np.int32).tobytes())
+                f.write(np.asarray(mb["mask"], np.float32).tobytes())
+                if use_doc:
+                    f.write(np.asarray(mb["doc_ids"], np.int32).tobytes())
+        cmd = [REF_BIN, fin, fout]
+        if threads:
+            cmd = ["taskset", "-c", "0-%d" % (threads - 1)] + cmd
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+        if r.returncode != 0:
+            raise RuntimeError("ref_gpt failed (%d): %s" % (r.returncode, r.stderr[-2000:]))
+        raw = open(fout, "rb").read()
+    off = 0
+
+    def take(n, dt=np.float32):
+        nonlocal off
+        a = np.frombuffer(raw, dt, n, off).copy()
+        off += a.nbytes
+        return a
+
+    out = {"losses": take(steps * accum), "grads": None, "logits": None, "params": None,
+           "stderr": r.stderr}
+    if dump_grads:
+        out["grads"] = [take(rr * cc).reshape(rr, cc) for _, rr, cc in shapes]
+    if dump_logits:
+        out["logits"] = take(cfg.vocab * cfg.tokens).reshape(cfg.vocab, cfg.tokens)
+    if not skip_params:
+        out["params"] = [take(rr * cc).reshape(rr, cc) for _, rr, cc in shapes]
+    out["seconds"] = take(steps, np.float64)
+    assert off == len(raw), (off, len(raw))
+    return out
