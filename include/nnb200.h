@@ -1,0 +1,234 @@
+/* nnb200.h — C ABI of the B200 (sm_100a) compute library for neuralnet.cpp's GPT training step.
+ *
+ * Conventions, the ones of the reference ABI (cuda/cuda_kernels.h:1-9, cuda/cuda_kernels.cu:24-55):
+ *   - every entry point returns int: 0 = success, positive = cudaError_t, -1 = shape/argument error,
+ *     -2 = driver service unavailable; a one-line message goes to stderr;
+ *   - the caller owns every buffer; nothing here allocates or frees device memory; results are
+ *     written to caller-provided outputs; all work is enqueued on `stream` and returns at once;
+ *   - pointers are device pointers unless a parameter says "host"; matrices are row-major.
+ * There is no CPU fallback: without a CUDA device every compute entry point fails.
+ *
+ * Section 1 re-exports, symbol for symbol, the fifteen kernels of cuda/cuda_kernels.h so the
+ * reference CudaBackend links against this library unchanged.  Sections 2-5 are new entry points in
+ * the same style for what the reference CudaEngine leaves unimplemented or composes from many
+ * primitive calls.
+ */
+#ifndef NNB200_H
+#define NNB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ===================================================================================== *
+ * 1. Engine primitives, fp32 — same signatures as cuda/cuda_kernels.h                    *
+ * ===================================================================================== */
+
+/* C = op(A) x op(B).  Replaces cuda_matmul (cuda_kernels.h:27-32). */
+int cuda_matmul(const float* A, const float* B, float* C, size_t A_rows, size_t A_cols, size_t B_rows, size_t B_cols,
+                int transA, int transB, void* stream);
+/* Same; `handle_ptr` is ignored (no cuBLAS handle is needed) and the stream is the one given to
+ * nnb200_set_handle_stream.  Replaces cuda_matmul_with_handle (cuda_kernels.h:37-42). */
+int cuda_matmul_with_handle(const float* A, const float* B, float* C, size_t A_rows, size_t A_cols, size_t B_rows,
+                            size_t B_cols, int transA, int transB, void* handle_ptr);
+int nnb200_set_handle_stream(void* stream);
+/* Per-batch C_b = op(A_b) x op(B_b), stacked vertically.  Replaces cuda_batched_matmul (:47-52). */
+int cuda_batched_matmul(const float* A, const float* B, float* C, size_t A_rows, size_t A_cols, size_t B_rows,
+                        size_t B_cols, unsigned int batch, int transA, int transB, void* stream);
+/* op: 0 Neg 1 Exp 2 Log 3 Sqrt 4 Rsqrt 5 Abs 6 Tanh.  Replaces cuda_elementwise_unary (:60-63). */
+int cuda_elementwise_unary(const float* A, float* out, unsigned int count, unsigned int op, void* stream);
+/* op: 0 Add 1 Sub 2 Mul 3 Div 4 Max 5 Min.  Replaces cuda_elementwise_binary (:67-70). */
+int cuda_elementwise_binary(const float* A, const float* B, float* out, unsigned int count, unsigned int op, void* stream);
+/* out = op(A, s) or op(s, A).  Replaces cuda_elementwise_binary_scalar (:74-78). */
+int cuda_elementwise_binary_scalar(const float* A, float* out, unsigned int count, unsigned int op, float scalar,
+                                   int scalar_first, void* stream);
+/* out = A + s*B.  Replaces cuda_axpy (:81-84). */
+int cuda_axpy(const float* A, const float* B, float* out, unsigned int count, float scalar, void* stream);
+/* out = cmp(A, b) ? then_v : else; cmp: 0 Lt 1 Le 2 Gt 3 Ge 4 Eq 5 Ne.  Replaces
+ * cuda_elementwise_select_scalar_cond (:88-92). */
+int cuda_elementwise_select_scalar_cond(const float* A, const float* then_v, float* out, unsigned int count,
+                                        unsigned int cmp, float scalar_b, float scalar_else, void* stream);
+/* (rows, cols) -> (rows, 1); mode 0 sum, 1 max, 2 min (2 is an extension).  Replaces cuda_reduce_row (:100-103). */
+int cuda_reduce_row(const float* A, float* out, unsigned int rows, unsigned int cols, unsigned int mode, void* stream);
+/* (rows, cols) -> (1, cols).  Replaces cuda_reduce_col (:107-110). */
+int cuda_reduce_col(const float* A, float* out, unsigned int rows, unsigned int cols, unsigned int mode, void* stream);
+/* out[r][c] = op(A[r][c], vec[r]).  Replaces cuda_broadcast_row (:118-121). */
+int cuda_broadcast_row(const float* A, const float* vec, float* out, unsigned int rows, unsigned int cols,
+                       unsigned int op, void* stream);
+/* out[r][c] = op(A[r][c], vec[c]).  Replaces cuda_broadcast_col (:124-127). */
+int cuda_broadcast_col(const float* A, const float* vec, float* out, unsigned int rows, unsigned int cols,
+                       unsigned int op, void* stream);
+/* (R, C) -> (C, R).  Replaces cuda_transpose (:134-137). */
+int cuda_transpose(const float* A, float* out, unsigned int R, unsigned int C, void* stream);
+/* inverse=0: (M, B*N) -> (B*M, N); inverse=1 the way back.  Replaces cuda_rearrange_3d (:142-146). */
+int cuda_rearrange_3d(const float* A, float* out, unsigned int M, unsigned int B, unsigned int N, unsigned int inverse,
+                      void* stream);
+/* out[i] = table[(int)indices[i]], zero row when out of range.  Replaces cuda_gather (:155-158). */
+int cuda_gather(const float* table, const float* indices, float* out, unsigned int vocab, unsigned int D,
+                unsigned int num, void* stream);
+/* dst[(int)indices[i]] += grad[i], rows added in ascending i — bit-identical to the CPU engine's
+ * sequential loop (cpu_engine.hpp:203-214), unlike the reference's atomicAdd kernel.  Replaces
+ * cuda_scatter_add (:162-165). */
+int cuda_scatter_add(float* dst, const float* indices, const float* grad, unsigned int vocab, unsigned int D,
+                     unsigned int num, void* stream);
+
+/* ===================================================================================== *
+ * 2. Dense contractions                                                                  *
+ * ===================================================================================== */
+
+/* D[M,N] = alpha * A[M,K] * B[N,K]^T (+ bias_n[n]) (+ residual[m,n]), or D += ... when accumulate.
+ * a_mn_major = 0: A stored (M, K), K contiguous, row stride lda; 1: stored (K, M), M contiguous.
+ * b_mn_major = 0: B stored (N, K), K contiguous, row stride ldb; 1: stored (K, N), N contiguous.
+ * bf16 version: TMA-fed tcgen05 tiles, fp32 accumulation in TMEM; A, B bf16; D bf16 (c_bf16=1) or
+ * fp32; residual has D's type and ldc; accumulate needs fp32 D and adds atomically (split-K).
+ * lda, ldb multiples of 8; A, B 16-byte aligned.  Replaces cublasSgemm + broadcast_row(Add) +
+ * add_inplace of Linear::forward/backward (compute_layer.hpp:151-195; cuda_kernels.cu:527-563). */
+int nnb200_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                     long long ldc, int a_mn_major, int b_mn_major, int c_bf16, float alpha, const float* bias_n,
+                     const void* residual, int accumulate, void* stream);
+/* Same contract, fp32 operands and fp32 SIMT arithmetic (the check mode). */
+int nnb200_gemm_f32(const float* A, const float* B, float* D, int M, int N, int K, long long lda, long long ldb,
+                    long long ldc, int a_mn_major, int b_mn_major, float alpha, const float* bias_n,
+                    const float* residual, int accumulate, void* stream);
+/* Reads (host) and clears the device-side status word of the tcgen05 GEMM: 0 = no wait ever gave up. */
+int nnb200_gemm_status(int* host_code);
+
+/* ===================================================================================== *
+ * 3. Fused attention and the fused memory-bound layers (token-major activations)         *
+ *    dtype: 0 = fp32, 1 = bf16 for every activation pointer; statistics are fp32.        *
+ * ===================================================================================== */
+
+/* Causal, optionally document-masked and ALiBi-biased attention over qkv (tokens, 3*d) = q|k|v,
+ * tokens = batch*seq in batch-major order; out (tokens, d); lse (batch*heads*seq).  doc_ids may be
+ * NULL.  One fused kernel replaces batched_matmul_reduce/_softmax_denom/_softmax_apply and the
+ * materialised-score path (compute_layer.hpp:1193-1252; compute_engine.hpp:217-243). */
+int nnb200_attention_forward(const void* qkv, void* out, float* lse, const int32_t* doc_ids, int batch, int seq,
+                             int heads, int head_dim, int alibi, int dtype, void* stream);
+/* dqkv (tokens, 3*d) from dout (tokens, d); dvec is scratch (batch*heads*seq floats).  Replaces
+ * batched_matmul_softmax_backward_q/_kv and the materialised backward (compute_layer.hpp:1296-1360). */
+int nnb200_attention_backward(const void* qkv, const void* out, const void* dout, const float* lse, float* dvec,
+                              void* dqkv, const int32_t* doc_ids, int batch, int seq, int heads, int head_dim, int alibi,
+                              int dtype, void* stream);
+
+/* y = norm(x) * gamma (+ beta); layer=1 LayerNorm, 0 RMSNorm; eps 1e-5; rinv (rows), mean (rows,
+ * LayerNorm only) are saved for backward.  Replaces LayerNorm/RMSNorm::forward
+ * (compute_layer.hpp:541-590, 722-755). */
+int nnb200_norm_forward(const void* x, const float* gamma, const float* beta, void* y, float* rinv, float* mean,
+                        int rows, int d, int layer, int dtype, void* stream);
+/* dx = norm-backward(g) (+ add); dgamma += sum g*gamma*n (the reference's formula, including gamma);
+ * dbeta += sum g.  scratch: nnb200_colsum_scratch_floats(rows, d) floats.  Replaces
+ * LayerNorm/RMSNorm::backward (compute_layer.hpp:592-654, 757-800). */
+int nnb200_norm_backward(const void* g, const void* x, const float* gamma, const float* rinv, const float* mean,
+                         const void* add, void* dx, float* dgamma, float* dbeta, float* scratch, int rows, int d,
+                         int layer, int dtype, void* stream);
+size_t nnb200_colsum_scratch_floats(int rows, int cols);
+/* out[c] += sum_r g[r][c] (bias gradient of Linear::backward, compute_layer.hpp:190-193). */
+int nnb200_bias_grad(const void* g, long long ldg, float* out, float* scratch, int rows, int cols, int dtype, void* stream);
+
+/* swiglu=0: h2 = h1*sigmoid(1.702*h1) on (rows, ff); swiglu=1: h1 (rows, 2ff) = gate|up,
+ * h2 = gate*sigmoid(gate)*up.  Replaces GeLU/SwiGLU::forward (compute_layer.hpp:266-295, 375-404). */
+int nnb200_activation_forward(const void* h1, void* h2, int rows, int ff, int swiglu, int dtype, void* stream);
+int nnb200_activation_backward(const void* g, const void* h1, void* dh1, int rows, int ff, int swiglu, int dtype,
+                               void* stream);
+
+/* Softmax cross-entropy over token rows: logits (rows, V) are overwritten by
+ * grad_scale*(softmax - onehot)/num_valid; rows with mask < 0.5 or label >= vocab get zero.
+ * stats (2 floats): number of valid rows and its reciprocal; loss_out[0] = -sum(loss_vec)/num_valid.
+ * Replaces CrossEntropyLoss::forward_sparse + col_softmax_sparse_forward (compute_loss.hpp:229-309;
+ * cpu_engine.hpp:948-1006). */
+int nnb200_cross_entropy(void* logits, const int32_t* labels, const float* mask, float grad_scale, float* loss_vec,
+                         float* stats, float* loss_out, int rows, int V, int vocab, int dtype, void* stream);
+
+/* x[i] = token_emb[tokens[i]] (+ pos_table[i % seq]); zero row for an id out of range.  Replaces
+ * the transpose/gather/transpose/add chain of GPTModel::forward (compute_layer.hpp:2792-2809). */
+int nnb200_embedding_forward(const float* token_emb, const float* pos_table, const int32_t* tokens, void* x, int tokens_n,
+                             int seq, int d, int vocab, int dtype, void* stream);
+/* token_grad[tokens[i]] += g[i] in ascending i (bit-exact against the sequential CPU loop);
+ * pos_grad[t] += sum_b g[b*seq+t] when pos_grad != NULL.  scratch: nnb200_embedding_scratch_bytes.
+ * Replaces scatter_add_rows in GPTModel::backward (compute_layer.hpp:2882-2891, 2573-2580). */
+int nnb200_embedding_backward(float* token_grad, float* pos_grad, const int32_t* tokens, const void* g, void* scratch,
+                              int batch, int seq, int d, int vocab, int dtype, void* stream);
+size_t nnb200_embedding_scratch_bytes(int tokens_n);
+
+/* ===================================================================================== *
+ * 4. Optimizers over flat fp32 ranges                                                    *
+ * ===================================================================================== */
+
+/* One fused AdamW update of n parameters: p *= (1 - lr*wd); m, v moments; p -= lr*m^/(sqrt(v^)+eps);
+ * the gradient is multiplied by *grad_scale_dev first (NULL = 1); shadow (bf16, may be NULL)
+ * receives the rounded parameters.  t_next is the 1-based step.  Replaces the sixteen engine
+ * calls per tensor of AdamW::step (compute_optimizer.hpp:252-304, 388-412). */
+int nnb200_adamw_step(float* p, const float* g, float* m, float* v, void* shadow_bf16, size_t n, float lr, float beta1,
+                      float beta2, float eps, float weight_decay, int t_next, const float* grad_scale_dev, void* stream);
+/* out[0] = pre_scale^2 * sum g^2, out[1] = its sqrt (the norm of pre_scale*g),
+ * out[2] = (max_norm > 0 && norm > max_norm ? max_norm/norm : 1) * pre_scale — the factor that
+ * turns g into the clipped, pre-scaled gradient; scratch: nnb200_sumsq_scratch_floats() floats.
+ * Deterministic two-stage reduction.  Replaces Optimizer::clip_grad_norm
+ * (compute_optimizer.hpp:90-140) without its host synchronisation. */
+int nnb200_grad_norm_clip(const float* g, size_t n, float pre_scale, float max_norm, float* scratch, float* out3,
+                          void* stream);
+size_t nnb200_sumsq_scratch_floats(void);
+/* Muon update of one (rows, cols) matrix: v = mu*v + g; u = g + mu*v; X = u/sqrt(|u|^2 + eps^2);
+ * ns_steps Newton-Schulz iterations (a,b,c) = (3.4445,-4.7750,2.0315) as GEMMs; p -= lr*X.
+ * precision 0: fp32 GEMMs in the stored orientation; 1: bf16 tcgen05 GEMMs on the short side
+ * (NS is an odd polynomial, so NS(X^T) = NS(X)^T).  scratch: nnb200_muon_scratch_bytes.  Replaces
+ * Muon::step + newton_schulz_orthogonalize (compute_optimizer.hpp:430-497, 517-590). */
+int nnb200_muon_step(float* p, const float* g, float* velocity, void* shadow_bf16, int rows, int cols, float lr,
+                     float momentum, int ns_steps, float ns_eps, int precision, void* scratch,
+                     const float* grad_scale_dev, void* stream);
+size_t nnb200_muon_scratch_bytes(int rows, int cols, int precision);
+int nnb200_f32_to_bf16(const float* in, void* out, size_t n, void* stream);
+int nnb200_bf16_to_f32(const void* in, float* out, size_t n, void* stream);
+
+/* ===================================================================================== *
+ * 5. The fused GPT training step                                                         *
+ * ===================================================================================== */
+
+typedef struct nnb200_gpt_config {
+    int32_t vocab, d_model, heads, layers, d_ff, seq, batch;
+    int32_t act;        /* 0 QuickGeLU, 1 SwiGLU          (ActivationType, model_spec.hpp:33-37) */
+    int32_t norm;       /* 0 LayerNorm, 1 RMSNorm         (NormType, model_spec.hpp:40-45)       */
+    int32_t pos;        /* 0 learned, 1 sinusoidal, 2 ALiBi (PosEncodingType, model_spec.hpp:24-30) */
+    int32_t precision;  /* 0 fp32 check mode, 1 bf16 tensor-core mode with fp32 master weights   */
+    int32_t reserved[5];
+} nnb200_gpt_config;
+
+/* Parameters live in one fp32 arena (gradients, moments and the bf16 shadow mirror it element for
+ * element).  The arena is [vectors and embeddings | hidden matrices]; within it wq|wk|wv are
+ * adjacent so the three projections run as one GEMM.  The table lists the tensors in the
+ * reference's parameter order (GPTModel::parameters, compute_layer.hpp:2739-2755): offset (in
+ * elements), rows, cols.  Returns the number of tensors; arrays may be NULL to query the count. */
+int nnb200_gpt_param_table(const nnb200_gpt_config* cfg, long long* offsets, int32_t* rows, int32_t* cols);
+long long nnb200_gpt_arena_elems(const nnb200_gpt_config* cfg);
+long long nnb200_gpt_matrix_region_begin(const nnb200_gpt_config* cfg);   /* first element of the hidden matrices */
+/* Start (elements) of layer l's matrices inside the arena; l = layers gives the end of the arena. */
+long long nnb200_gpt_layer_matrix_begin(const nnb200_gpt_config* cfg, int layer);
+long long nnb200_gpt_workspace_bytes(const nnb200_gpt_config* cfg);
+/* Byte offset of a named buffer inside the workspace, for inspection: 0 logits (tokens, vocab),
+ * 1 loss scalar (1 float), 2 gradient w.r.t. the embedded input (tokens, d), 3 CE stats. */
+long long nnb200_gpt_workspace_offset(const nnb200_gpt_config* cfg, int which);
+/* Fills the constant tables of the workspace (sinusoidal positions).  Call once, and again after
+ * the workspace moved. */
+int nnb200_gpt_init_workspace(const nnb200_gpt_config* cfg, void* workspace, void* stream);
+/* tokens, doc_ids (NULL = none): int32 (batch*seq), batch-major.  Logits are left in the workspace.
+ * Replaces GPTModel::forward (compute_layer.hpp:2783-2839). */
+int nnb200_gpt_forward(const nnb200_gpt_config* cfg, const float* params, const void* params_bf16, void* workspace,
+                       const int32_t* tokens, const int32_t* doc_ids, void* stream);
+/* Loss of the logits in the workspace; overwrites them by their gradient times grad_scale
+ * (1/accumulation steps, text_train.cpp:1253-1258).  The scalar loss lands in the workspace. */
+int nnb200_gpt_loss(const nnb200_gpt_config* cfg, void* workspace, const int32_t* labels, const float* loss_mask,
+                    float grad_scale, void* stream);
+/* Adds this micro-batch's parameter gradients into `grads` (arena layout).  layer_events (NULL or
+ * layers+1 cudaEvent_t): event[l] is recorded when layer l's matrix gradients are final, event
+ * [layers] when every gradient is.  Replaces GPTModel::backward (compute_layer.hpp:2841-2896). */
+int nnb200_gpt_backward(const nnb200_gpt_config* cfg, const float* params, const void* params_bf16, float* grads,
+                        void* workspace, const int32_t* tokens, const int32_t* doc_ids, void* const* layer_events,
+                        void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNB200_H */

@@ -1,0 +1,238 @@
+// extern "C" entry points that are thin type dispatchers over the templated launchers, and the
+// Muon update (Newton-Schulz iterations as GEMMs).
+#include "kernels.h"
+#include "nnb200.h"
+
+using namespace nnb;
+
+namespace nnb {
+
+// Bm = b*A + c*A2 + a*I on an (r, r) matrix: the polynomial of one Newton-Schulz step with the
+// "+ a*X" term (compute_optimizer.hpp:476-488) folded in as a*I, so X' = Bm X is one GEMM
+template <typename T>
+__global__ void ns_poly_kernel(const T* __restrict__ A, const T* __restrict__ A2, T* __restrict__ out, int r, float a,
+                               float b, float c)
+{
+    const size_t n = static_cast<size_t>(r) * r;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float v = b * to_f32(A[i]) + c * to_f32(A2[i]);
+        if (i / r == i % r) v += a;
+        out[i] = from_f32<T>(v);
+    }
+}
+
+static size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+
+template <typename T>
+static int muon_matrix(float* p, const float* u, bf16* shadow, int rows, int cols, float lr, int ns_steps, float eps,
+                       uint8_t* scratch, size_t off, cudaStream_t s)
+{
+    constexpr bool BF = sizeof(T) == 2;
+    const size_t n = static_cast<size_t>(rows) * cols;
+    const bool transposed = BF && rows > cols;          // bf16 mode iterates on the short side
+    const int r = transposed ? cols : rows;
+    float* partial = reinterpret_cast<float*>(scratch + off); off += up256(sumsq_scratch_floats() * 4);
+    float* out3 = reinterpret_cast<float*>(scratch + off); off += 256;
+    T* X = reinterpret_cast<T*>(scratch + off); off += up256(n * sizeof(T));
+    T* X2 = reinterpret_cast<T*>(scratch + off); off += up256(n * sizeof(T));
+    T* A = reinterpret_cast<T*>(scratch + off); off += up256(static_cast<size_t>(r) * r * sizeof(T));
+    T* A2 = reinterpret_cast<T*>(scratch + off); off += up256(static_cast<size_t>(r) * r * sizeof(T));
+    T* Bm = reinterpret_cast<T*>(scratch + off);
+    constexpr float ka = 3.4445f, kb = -4.7750f, kc = 2.0315f;   // compute_optimizer.hpp:433-435
+
+    NNB_TRY(sum_squares(u, n, 1.0f, 0.f, 1.0f, partial, out3, s));
+    NNB_TRY(muon_normalize<T>(u, out3, eps, X, n, s));
+    for (int it = 0; it < ns_steps; ++it) {
+        if constexpr (BF) {
+            const bf16* Xb = reinterpret_cast<const bf16*>(X);
+            if (!transposed) NNB_TRY(gemm_bf16(Xb, Xb, A, r, r, cols, cols, cols, r, 0, 0, 1, 1.0f, nullptr, nullptr, 0, s));
+            else NNB_TRY(gemm_bf16(Xb, Xb, A, r, r, rows, cols, cols, r, 1, 1, 1, 1.0f, nullptr, nullptr, 0, s));
+            NNB_TRY(gemm_bf16(reinterpret_cast<const bf16*>(A), reinterpret_cast<const bf16*>(A), A2, r, r, r, r, r, r, 0, 0, 1,
+                              1.0f, nullptr, nullptr, 0, s));
+        } else {
+            const float* Xf = reinterpret_cast<const float*>(X);
+            NNB_TRY(sgemm_strided(Xf, Xf, reinterpret_cast<float*>(A), r, r, cols, cols, 1, cols, 1, r, 1, 0, 0, 0, 1.0f,
+                                  nullptr, nullptr, nullptr, 0, s));
+            NNB_TRY(sgemm_strided(reinterpret_cast<const float*>(A), reinterpret_cast<const float*>(A),
+                                  reinterpret_cast<float*>(A2), r, r, r, r, 1, 1, r, r, 1, 0, 0, 0, 1.0f, nullptr, nullptr,
+                                  nullptr, 0, s));
+        }
+        ns_poly_kernel<T><<<grid_for(static_cast<long long>(r) * r, 256), 256, 0, s>>>(A, A2, Bm, r, ka, kb, kc);
+        NNB_CUDA_CHECK(cudaGetLastError());
+        if constexpr (BF) {
+            const bf16* Xb = reinterpret_cast<const bf16*>(X);
+            const bf16* Bb = reinterpret_cast<const bf16*>(Bm);
+            if (!transposed) NNB_TRY(gemm_bf16(Bb, Xb, X2, rows, cols, rows, rows, cols, cols, 0, 1, 1, 1.0f, nullptr, nullptr, 0, s));
+            else NNB_TRY(gemm_bf16(Xb, Bb, X2, rows, cols, cols, cols, cols, cols, 0, 0, 1, 1.0f, nullptr, nullptr, 0, s));
+        } else {
+            NNB_TRY(sgemm_strided(reinterpret_cast<const float*>(Bm), reinterpret_cast<const float*>(X),
+                                  reinterpret_cast<float*>(X2), rows, cols, rows, rows, 1, 1, cols, cols, 1, 0, 0, 0, 1.0f,
+                                  nullptr, nullptr, nullptr, 0, s));
+        }
+        T* t = X; X = X2; X2 = t;
+    }
+    return muon_apply<T>(p, X, shadow, lr, n, s);
+}
+
+}  // namespace nnb
+
+#define DT_CHECK(dtype) NNB_ARG_CHECK((dtype) == 0 || (dtype) == 1, "dtype must be 0 (fp32) or 1 (bf16)")
+
+extern "C" {
+
+int nnb200_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                     long long ldc, int a_mn_major, int b_mn_major, int c_bf16, float alpha, const float* bias_n,
+                     const void* residual, int accumulate, void* stream)
+{
+    return gemm_bf16(static_cast<const bf16*>(A), static_cast<const bf16*>(B), D, M, N, K, lda, ldb, ldc, a_mn_major,
+                     b_mn_major, c_bf16, alpha, bias_n, residual, accumulate, to_stream(stream));
+}
+
+int nnb200_gemm_status(int* host_code)
+{
+    NNB_ARG_CHECK(host_code != nullptr, "null output");
+    NNB_TRY(gemm_device_error(host_code));
+    if (*host_code) NNB_TRY(gemm_clear_device_error());
+    return 0;
+}
+
+int nnb200_attention_forward(const void* qkv, void* out, float* lse, const int32_t* doc_ids, int batch, int seq,
+                             int heads, int head_dim, int alibi, int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    cudaStream_t s = to_stream(stream);
+    if (dtype == 1) {
+        if (attention_mma_supported(head_dim, heads * head_dim))
+            return attention_fwd_mma(static_cast<const bf16*>(qkv), static_cast<bf16*>(out), lse, doc_ids, batch, seq, heads, head_dim, alibi, s);
+        return attention_fwd_simt<bf16>(static_cast<const bf16*>(qkv), static_cast<bf16*>(out), lse, doc_ids, batch, seq, heads, head_dim, alibi, s);
+    }
+    return attention_fwd_simt<float>(static_cast<const float*>(qkv), static_cast<float*>(out), lse, doc_ids, batch, seq, heads, head_dim, alibi, s);
+}
+
+int nnb200_attention_backward(const void* qkv, const void* out, const void* dout, const float* lse, float* dvec,
+                              void* dqkv, const int32_t* doc_ids, int batch, int seq, int heads, int head_dim, int alibi,
+                              int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    cudaStream_t s = to_stream(stream);
+    if (dtype == 1) {
+        if (attention_mma_supported(head_dim, heads * head_dim))
+            return attention_bwd_mma(static_cast<const bf16*>(qkv), static_cast<const bf16*>(out), static_cast<const bf16*>(dout), lse, dvec, static_cast<bf16*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);
+        return attention_bwd_simt<bf16>(static_cast<const bf16*>(qkv), static_cast<const bf16*>(out), static_cast<const bf16*>(dout), lse, dvec, static_cast<bf16*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);
+    }
+    return attention_bwd_simt<float>(static_cast<const float*>(qkv), static_cast<const float*>(out), static_cast<const float*>(dout), lse, dvec, static_cast<float*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);
+}
+
+int nnb200_norm_forward(const void* x, const float* gamma, const float* beta, void* y, float* rinv, float* mean,
+                        int rows, int d, int layer, int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    if (dtype == 1) return norm_fwd<bf16>(static_cast<const bf16*>(x), gamma, beta, static_cast<bf16*>(y), rinv, mean, rows, d, layer != 0, to_stream(stream));
+    return norm_fwd<float>(static_cast<const float*>(x), gamma, beta, static_cast<float*>(y), rinv, mean, rows, d, layer != 0, to_stream(stream));
+}
+
+int nnb200_norm_backward(const void* g, const void* x, const float* gamma, const float* rinv, const float* mean,
+                         const void* add, void* dx, float* dgamma, float* dbeta, float* scratch, int rows, int d,
+                         int layer, int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    if (dtype == 1)
+        return norm_bwd<bf16>(static_cast<const bf16*>(g), static_cast<const bf16*>(x), gamma, rinv, mean, static_cast<const bf16*>(add), static_cast<bf16*>(dx), dgamma, dbeta, scratch, rows, d, layer != 0, to_stream(stream));
+    return norm_bwd<float>(static_cast<const float*>(g), static_cast<const float*>(x), gamma, rinv, mean, static_cast<const float*>(add), static_cast<float*>(dx), dgamma, dbeta, scratch, rows, d, layer != 0, to_stream(stream));
+}
+
+size_t nnb200_colsum_scratch_floats(int rows, int cols) { return colsum_scratch_floats(rows, cols); }
+
+int nnb200_bias_grad(const void* g, long long ldg, float* out, float* scratch, int rows, int cols, int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    if (dtype == 1) return colsum_accumulate<bf16>(static_cast<const bf16*>(g), ldg, nullptr, nullptr, nullptr, nullptr, 0, out, scratch, rows, cols, to_stream(stream));
+    return colsum_accumulate<float>(static_cast<const float*>(g), ldg, nullptr, nullptr, nullptr, nullptr, 0, out, scratch, rows, cols, to_stream(stream));
+}
+
+int nnb200_activation_forward(const void* h1, void* h2, int rows, int ff, int swiglu, int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    if (dtype == 1) return act_fwd<bf16>(static_cast<const bf16*>(h1), static_cast<bf16*>(h2), rows, ff, swiglu != 0, to_stream(stream));
+    return act_fwd<float>(static_cast<const float*>(h1), static_cast<float*>(h2), rows, ff, swiglu != 0, to_stream(stream));
+}
+int nnb200_activation_backward(const void* g, const void* h1, void* dh1, int rows, int ff, int swiglu, int dtype,
+                               void* stream)
+{
+    DT_CHECK(dtype);
+    if (dtype == 1) return act_bwd<bf16>(static_cast<const bf16*>(g), static_cast<const bf16*>(h1), static_cast<bf16*>(dh1), rows, ff, swiglu != 0, to_stream(stream));
+    return act_bwd<float>(static_cast<const float*>(g), static_cast<const float*>(h1), static_cast<float*>(dh1), rows, ff, swiglu != 0, to_stream(stream));
+}
+
+int nnb200_cross_entropy(void* logits, const int32_t* labels, const float* mask, float grad_scale, float* loss_vec,
+                         float* stats, float* loss_out, int rows, int V, int vocab, int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    if (dtype == 1) return cross_entropy<bf16>(static_cast<bf16*>(logits), labels, mask, grad_scale, loss_vec, stats, loss_out, rows, V, vocab, to_stream(stream));
+    return cross_entropy<float>(static_cast<float*>(logits), labels, mask, grad_scale, loss_vec, stats, loss_out, rows, V, vocab, to_stream(stream));
+}
+
+int nnb200_embedding_forward(const float* token_emb, const float* pos_table, const int32_t* tokens, void* x, int tokens_n,
+                             int seq, int d, int vocab, int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    NNB_ARG_CHECK(seq > 0, "seq must be positive");
+    if (dtype == 1) return embed_fwd<bf16>(token_emb, pos_table, tokens, static_cast<bf16*>(x), tokens_n, seq, d, vocab, to_stream(stream));
+    return embed_fwd<float>(token_emb, pos_table, tokens, static_cast<float*>(x), tokens_n, seq, d, vocab, to_stream(stream));
+}
+int nnb200_embedding_backward(float* token_grad, float* pos_grad, const int32_t* tokens, const void* g, void* scratch,
+                              int batch, int seq, int d, int vocab, int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    if (dtype == 1) return embed_bwd<bf16>(token_grad, pos_grad, tokens, static_cast<const bf16*>(g), scratch, batch, seq, d, vocab, to_stream(stream));
+    return embed_bwd<float>(token_grad, pos_grad, tokens, static_cast<const float*>(g), scratch, batch, seq, d, vocab, to_stream(stream));
+}
+size_t nnb200_embedding_scratch_bytes(int tokens_n) { return embed_bwd_scratch_bytes(tokens_n); }
+
+int nnb200_adamw_step(float* p, const float* g, float* m, float* v, void* shadow_bf16, size_t n, float lr, float beta1,
+                      float beta2, float eps, float weight_decay, int t_next, const float* grad_scale_dev, void* stream)
+{
+    NNB_ARG_CHECK(t_next >= 1, "t_next is the 1-based step number");
+    return adamw_update(p, g, m, v, static_cast<bf16*>(shadow_bf16), n, lr, beta1, beta2, eps, weight_decay, t_next, grad_scale_dev, to_stream(stream));
+}
+
+int nnb200_grad_norm_clip(const float* g, size_t n, float pre_scale, float max_norm, float* scratch, float* out3,
+                          void* stream)
+{
+    return sum_squares(g, n, pre_scale, max_norm, pre_scale, scratch, out3, to_stream(stream));
+}
+size_t nnb200_sumsq_scratch_floats(void) { return sumsq_scratch_floats(); }
+
+size_t nnb200_muon_scratch_bytes(int rows, int cols, int precision)
+{
+    const size_t n = static_cast<size_t>(rows) * cols, esz = precision == 1 ? 2 : 4;
+    const size_t r = (precision == 1 && rows > cols) ? cols : rows;
+    return up256(n * 4) + up256(sumsq_scratch_floats() * 4) + 256 + 2 * up256(n * esz) + 3 * up256(r * r * esz);
+}
+
+int nnb200_muon_step(float* p, const float* g, float* velocity, void* shadow_bf16, int rows, int cols, float lr,
+                     float momentum, int ns_steps, float ns_eps, int precision, void* scratch,
+                     const float* grad_scale_dev, void* stream)
+{
+    NNB_ARG_CHECK(rows > 0 && cols > 0 && scratch != nullptr, "bad shape or scratch");
+    NNB_ARG_CHECK(precision == 0 || precision == 1, "precision must be 0 or 1");
+    cudaStream_t s = to_stream(stream);
+    const size_t n = static_cast<size_t>(rows) * cols;
+    uint8_t* sc = static_cast<uint8_t*>(scratch);
+    float* u = reinterpret_cast<float*>(sc);
+    NNB_TRY(muon_momentum(g, velocity, u, n, momentum, grad_scale_dev, s));
+    if (rows > 1 && cols > 1) {
+        if (precision == 1) {
+            NNB_ARG_CHECK(rows % 8 == 0 && cols % 8 == 0, "bf16 Newton-Schulz needs rows and cols multiples of 8");
+            return muon_matrix<bf16>(p, u, static_cast<bf16*>(shadow_bf16), rows, cols, lr, ns_steps, ns_eps, sc, up256(n * 4), s);
+        }
+        return muon_matrix<float>(p, u, static_cast<bf16*>(shadow_bf16), rows, cols, lr, ns_steps, ns_eps, sc, up256(n * 4), s);
+    }
+    return muon_apply<float>(p, u, static_cast<bf16*>(shadow_bf16), lr, n, s);     // non-2-D: p -= lr*u
+}
+
+int nnb200_f32_to_bf16(const float* in, void* out, size_t n, void* stream) { return f32_to_bf16(in, static_cast<bf16*>(out), n, to_stream(stream)); }
+int nnb200_bf16_to_f32(const void* in, float* out, size_t n, void* stream) { return bf16_to_f32(static_cast<const bf16*>(in), out, n, to_stream(stream)); }
+
+}  // extern "C"

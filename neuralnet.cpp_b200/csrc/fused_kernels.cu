@@ -1,0 +1,634 @@
+// Memory-bound kernels of the fused GPT training step, token-major layout: every activation is a
+// row-major (tokens, features) matrix, row i = b*seq + t.  Each kernel is templated on the
+// activation type (float = fp32 check mode, bf16 = tensor-core mode); statistics, reductions and
+// parameter gradients are always fp32.  They restate, fused, what the reference composes from
+// engine primitives:
+//   RMSNorm / LayerNorm      compute_layer.hpp:541-654, 722-800
+//   QuickGeLU / SwiGLU       compute_layer.hpp:256-339, 360-458
+//   softmax cross-entropy    compute_loss.hpp:229-309 + cpu_engine.hpp:948-1006
+//   AdamW / clip / Muon      compute_optimizer.hpp:90-140, 252-304, 388-412, 517-590
+#include "kernels.h"
+
+namespace nnb {
+
+constexpr float kNormEps = 1e-5f;     // compute_layer.hpp:495,687
+constexpr float kGeluBeta = 1.702f;   // compute_layer.hpp:259
+
+__device__ __forceinline__ float sigmoidf_ref(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ======================================================================================
+// normalisation: one warp per token row
+// ======================================================================================
+template <typename T, bool LAYER>
+__global__ void __launch_bounds__(256)
+norm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                T* __restrict__ y, float* __restrict__ rinv_out, float* __restrict__ mean_out, int rows, int d)
+{
+    constexpr int VN = Vec16<T>::N;
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const bool vec = (d % VN) == 0;
+    const float inv_d = 1.0f / static_cast<float>(d);
+    for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
+        const T* xr = x + static_cast<size_t>(r) * d;
+        T* yr = y + static_cast<size_t>(r) * d;
+        float mean = 0.f;
+        if (LAYER) {
+            float s = 0.f;
+            if (vec) for (int c = lane * VN; c < d; c += 32 * VN) { auto v = ld16(xr + c);
+#pragma unroll
+                for (int k = 0; k < VN; ++k) s += to_f32(v.v[k]); }
+            else for (int c = lane; c < d; c += 32) s += to_f32(xr[c]);
+            mean = warp_sum(s) * inv_d;
+        }
+        float ss = 0.f;
+        if (vec) for (int c = lane * VN; c < d; c += 32 * VN) { auto v = ld16(xr + c);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) { const float t = to_f32(v.v[k]) - mean; ss += t * t; } }
+        else for (int c = lane; c < d; c += 32) { const float t = to_f32(xr[c]) - mean; ss += t * t; }
+        const float rinv = 1.0f / sqrtf(warp_sum(ss) * inv_d + kNormEps);
+        if (lane == 0) { rinv_out[r] = rinv; if (LAYER) mean_out[r] = mean; }
+        if (vec) for (int c = lane * VN; c < d; c += 32 * VN) {
+            auto v = ld16(xr + c); Vec16<T> o;
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                float n = (to_f32(v.v[k]) - mean) * rinv;
+                n = n * gamma[c + k];
+                if (LAYER) n += beta[c + k];
+                o.v[k] = from_f32<T>(n);
+            }
+            st16(yr + c, o);
+        } else for (int c = lane; c < d; c += 32) {
+            float n = (to_f32(xr[c]) - mean) * rinv * gamma[c];
+            if (LAYER) n += beta[c];
+            yr[c] = from_f32<T>(n);
+        }
+    }
+}
+
+// dx = norm-backward(g) [+ add]; `add` is the gradient arriving over the residual connection
+template <typename T, bool LAYER>
+__global__ void __launch_bounds__(256)
+norm_bwd_dx_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ gamma,
+                   const float* __restrict__ rinv_in, const float* __restrict__ mean_in, const T* __restrict__ add,
+                   T* __restrict__ dx, int rows, int d)
+{
+    constexpr int VN = Vec16<T>::N;
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const bool vec = (d % VN) == 0;
+    const float inv_d = 1.0f / static_cast<float>(d);
+    for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
+        const size_t off = static_cast<size_t>(r) * d;
+        const float rinv = rinv_in[r], mean = LAYER ? mean_in[r] : 0.f;
+        float s_g = 0.f, s_gn = 0.f;
+        if (vec) for (int c = lane * VN; c < d; c += 32 * VN) {
+            auto gv = ld16(g + off + c); auto xv = ld16(x + off + c);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                const float gg = to_f32(gv.v[k]) * gamma[c + k];
+                const float n = (to_f32(xv.v[k]) - mean) * rinv;
+                s_g += gg; s_gn += gg * n;
+            }
+        } else for (int c = lane; c < d; c += 32) {
+            const float gg = to_f32(g[off + c]) * gamma[c];
+            const float n = (to_f32(x[off + c]) - mean) * rinv;
+            s_g += gg; s_gn += gg * n;
+        }
+        const float m_gn = warp_sum(s_gn) * inv_d;
+        const float m_g = LAYER ? warp_sum(s_g) * inv_d : 0.f;
+        if (vec) for (int c = lane * VN; c < d; c += 32 * VN) {
+            auto gv = ld16(g + off + c); auto xv = ld16(x + off + c); Vec16<T> o, av;
+            if (add) av = ld16(add + off + c);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                const float gg = to_f32(gv.v[k]) * gamma[c + k];
+                const float n = (to_f32(xv.v[k]) - mean) * rinv;
+                float v = (gg - m_g - n * m_gn) * rinv;
+                if (add) v += to_f32(av.v[k]);
+                o.v[k] = from_f32<T>(v);
+            }
+            st16(dx + off + c, o);
+        } else for (int c = lane; c < d; c += 32) {
+            const float gg = to_f32(g[off + c]) * gamma[c];
+            const float n = (to_f32(x[off + c]) - mean) * rinv;
+            float v = (gg - m_g - n * m_gn) * rinv;
+            if (add) v += to_f32(add[off + c]);
+            dx[off + c] = from_f32<T>(v);
+        }
+    }
+}
+
+// ======================================================================================
+// column sums over tokens (parameter gradients that reduce over the token dimension)
+//   MODE 0: sum_r g[r][c]                       (bias and LayerNorm-beta gradients)
+//   MODE 1: sum_r g[r][c]*gamma[c]*n[r][c]      (norm scale gradient; the reference multiplies by
+//                                                gamma — compute_layer.hpp:789-797, 636-644 — kept)
+// Stage 1 writes per-chunk partials, stage 2 folds them in fixed order and adds into the gradient.
+// ======================================================================================
+constexpr int CS_COLS = 64, CS_ROWLANES = 4, CS_CHUNK_ROWS = 256;
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ x, const float* __restrict__ gamma,
+                      const float* __restrict__ rinv, const float* __restrict__ mean, float* __restrict__ partial,
+                      int rows, int cols)
+{
+    __shared__ float red[CS_ROWLANES][CS_COLS];
+    const int tx = threadIdx.x % CS_COLS, ty = threadIdx.x / CS_COLS;
+    const int c = blockIdx.x * CS_COLS + tx;
+    const int r0 = blockIdx.y * CS_CHUNK_ROWS, r1 = min(rows, r0 + CS_CHUNK_ROWS);
+    float acc = 0.f;
+    if (c < cols) {
+        const float gm = (MODE == 1) ? gamma[c] : 0.f;
+        for (int r = r0 + ty; r < r1; r += CS_ROWLANES) {
+            const float gv = to_f32(g[static_cast<size_t>(r) * ldg + c]);
+            if (MODE == 0) acc += gv;
+            else {
+                const float mu = mean ? mean[r] : 0.f;
+                acc += gv * gm * ((to_f32(x[static_cast<size_t>(r) * cols + c]) - mu) * rinv[r]);
+            }
+        }
+    }
+    red[ty][tx] = acc;
+    __syncthreads();
+    if (ty == 0 && c < cols)
+        partial[static_cast<size_t>(blockIdx.y) * cols + c] = (red[0][tx] + red[1][tx]) + (red[2][tx] + red[3][tx]);
+}
+
+__global__ void colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int chunks, int cols)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float acc = 0.f;
+    for (int k = 0; k < chunks; ++k) acc += partial[static_cast<size_t>(k) * cols + c];
+    out[c] += acc;
+}
+
+// ======================================================================================
+// activations
+// ======================================================================================
+template <typename T>
+__global__ void gelu_fwd_kernel(const T* __restrict__ h1, T* __restrict__ h2, size_t n)
+{
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float x = to_f32(h1[i]);
+        h2[i] = from_f32<T>(x * sigmoidf_ref(kGeluBeta * x));
+    }
+}
+template <typename T>
+__global__ void gelu_bwd_kernel(const T* __restrict__ g, const T* __restrict__ h1, T* __restrict__ out, size_t n)
+{
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float x = to_f32(h1[i]);
+        const float s = sigmoidf_ref(kGeluBeta * x);
+        out[i] = from_f32<T>(to_f32(g[i]) * (s * (1.0f + (kGeluBeta * x) * (1.0f - s))));
+    }
+}
+
+// h1 (rows, 2*ff): columns [0,ff) gate, [ff,2ff) up  ->  h2 (rows, ff) = gate*sigmoid(gate)*up
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ h1, T* __restrict__ h2, int rows, int ff)
+{
+    constexpr int VN = Vec16<T>::N;
+    if ((ff % VN) == 0) {
+        const size_t nv = static_cast<size_t>(rows) * (ff / VN);
+        for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
+             i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+            const size_t r = i / (ff / VN);
+            const int c = static_cast<int>(i % (ff / VN)) * VN;
+            auto gv = ld16(h1 + r * 2 * ff + c); auto uv = ld16(h1 + r * 2 * ff + ff + c); Vec16<T> o;
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                const float gt = to_f32(gv.v[k]);
+                o.v[k] = from_f32<T>(gt * sigmoidf_ref(gt) * to_f32(uv.v[k]));
+            }
+            st16(h2 + r * ff + c, o);
+        }
+    } else {
+        const size_t n = static_cast<size_t>(rows) * ff;
+        for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+             i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+            const size_t r = i / ff; const int c = static_cast<int>(i % ff);
+            const float gt = to_f32(h1[r * 2 * ff + c]);
+            h2[i] = from_f32<T>(gt * sigmoidf_ref(gt) * to_f32(h1[r * 2 * ff + ff + c]));
+        }
+    }
+}
+// dh1 (rows, 2*ff) from g (rows, ff) and h1: compute_layer.hpp:436-445
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ g, const T* __restrict__ h1, T* __restrict__ dh1, int rows, int ff)
+{
+    constexpr int VN = Vec16<T>::N;
+    if ((ff % VN) == 0) {
+        const size_t nv = static_cast<size_t>(rows) * (ff / VN);
+        for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
+             i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+            const size_t r = i / (ff / VN);
+            const int c = static_cast<int>(i % (ff / VN)) * VN;
+            auto gv = ld16(g + r * ff + c);
+            auto gtv = ld16(h1 + r * 2 * ff + c); auto uv = ld16(h1 + r * 2 * ff + ff + c);
+            Vec16<T> og, ou;
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                const float go = to_f32(gv.v[k]), gt = to_f32(gtv.v[k]), up = to_f32(uv.v[k]);
+                const float s = sigmoidf_ref(gt);
+                og.v[k] = from_f32<T>(go * up * (s * (1.0f + gt * (1.0f - s))));
+                ou.v[k] = from_f32<T>(go * gt * s);
+            }
+            st16(dh1 + r * 2 * ff + c, og);
+            st16(dh1 + r * 2 * ff + ff + c, ou);
+        }
+    } else {
+        const size_t n = static_cast<size_t>(rows) * ff;
+        for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+             i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+            const size_t r = i / ff; const int c = static_cast<int>(i % ff);
+            const float go = to_f32(g[i]), gt = to_f32(h1[r * 2 * ff + c]), up = to_f32(h1[r * 2 * ff + ff + c]);
+            const float s = sigmoidf_ref(gt);
+            dh1[r * 2 * ff + c] = from_f32<T>(go * up * (s * (1.0f + gt * (1.0f - s))));
+            dh1[r * 2 * ff + ff + c] = from_f32<T>(go * gt * s);
+        }
+    }
+}
+
+// ======================================================================================
+// fused softmax cross-entropy over token rows: logits (rows, V) are overwritten by their gradient
+// ======================================================================================
+// stats[0] = number of valid rows, stats[1] = 1/num_valid (0 when none)
+__global__ void ce_count_kernel(const int* __restrict__ labels, const float* __restrict__ mask, int rows, int vocab,
+                                float* __restrict__ stats)
+{
+    __shared__ float red[32];
+    float c = 0.f;
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+        const bool ok = (!mask || mask[i] >= 0.5f) && labels[i] >= 0 && labels[i] < vocab;
+        c += ok ? 1.f : 0.f;
+    }
+    c = block_sum(c, red);
+    if (threadIdx.x == 0) { stats[0] = c; stats[1] = c > 0.f ? 1.0f / c : 0.f; }
+}
+
+template <typename T, int NV>   // NV 16-byte vectors cached per thread (0 = re-read from memory)
+__global__ void __launch_bounds__(512)
+ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const float* __restrict__ mask,
+                  const float* __restrict__ stats, float grad_scale, float* __restrict__ loss_vec, int rows, int V,
+                  int vocab)
+{
+    constexpr int VN = Vec16<T>::N;
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    T* row = logits + static_cast<size_t>(r) * V;
+    const int lbl = labels[r];
+    const bool valid = (!mask || mask[r] >= 0.5f) && lbl >= 0 && lbl < vocab;
+    const int nvec = V / VN;          // the launcher guarantees V % VN == 0 when NV > 0
+    if (!valid) {
+        if (NV > 0) { Vec16<T> z; for (int k = 0; k < VN; ++k) z.v[k] = from_f32<T>(0.f);
+            for (int i = threadIdx.x; i < nvec; i += blockDim.x) st16(row + i * VN, z); }
+        else for (int i = threadIdx.x; i < V; i += blockDim.x) row[i] = from_f32<T>(0.f);
+        if (threadIdx.x == 0) loss_vec[r] = 0.f;
+        return;
+    }
+    const float inv = stats[1] * grad_scale;   // inv_num_valid, times the accumulation scale (text_train.cpp:1253-1258)
+    Vec16<T> cache[NV > 0 ? NV : 1];
+    float mx = -INFINITY;
+    if (NV > 0) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < nvec) { cache[j] = ld16(row + i * VN);
+#pragma unroll
+                for (int k = 0; k < VN; ++k) mx = fmaxf(mx, to_f32(cache[j].v[k])); }
+        }
+    } else for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, to_f32(row[i]));
+    mx = block_max(mx, red);
+    float den = 0.f;
+    if (NV > 0) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < nvec) {
+#pragma unroll
+                for (int k = 0; k < VN; ++k) den += expf(to_f32(cache[j].v[k]) - mx); }
+        }
+    } else for (int i = threadIdx.x; i < V; i += blockDim.x) den += expf(to_f32(row[i]) - mx);
+    den = block_sum(den, red);
+    const float ll = to_f32(row[lbl]);
+    __syncthreads();                                  // everyone has read row[lbl] before it is overwritten
+    if (threadIdx.x == 0) loss_vec[r] = ll - mx - logf(den);
+    if (NV > 0) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < nvec) { Vec16<T> o;
+#pragma unroll
+                for (int k = 0; k < VN; ++k) {
+                    float gv = inv * expf(to_f32(cache[j].v[k]) - mx) / den;
+                    if (i * VN + k == lbl) gv -= inv;
+                    o.v[k] = from_f32<T>(gv);
+                }
+                st16(row + i * VN, o); }
+        }
+    } else for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        float gv = inv * expf(to_f32(row[i]) - mx) / den;
+        if (i == lbl) gv -= inv;
+        row[i] = from_f32<T>(gv);
+    }
+}
+
+// loss = -(sum loss_vec) / num_valid (compute_loss.hpp:300-307); single block, fixed order
+__global__ void ce_loss_kernel(const float* __restrict__ loss_vec, const float* __restrict__ stats, int rows,
+                               float* __restrict__ loss_out)
+{
+    __shared__ float red[32];
+    float s = 0.f;
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) s += loss_vec[i];
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) loss_out[0] = stats[0] > 0.f ? -s / stats[0] : 0.f;
+}
+
+// ======================================================================================
+// optimizers over flat parameter ranges
+// ======================================================================================
+// hyper[0] = gradient scale (clip * 1/world), read from device memory so no host sync is needed
+__global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                             float* __restrict__ v, bf16* __restrict__ shadow, size_t n, float lr, float beta1,
+                             float beta2, float eps, float decay, float inv_bc1, float inv_bc2,
+                             const float* __restrict__ gscale_ptr)
+{
+    const float gs = gscale_ptr ? gscale_ptr[0] : 1.0f;
+    const float omb1 = 1.0f - beta1, omb2 = 1.0f - beta2;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float gr = g[i] * gs;
+        float pv = p[i] * decay;                               // AdamW::step decay (compute_optimizer.hpp:397-404)
+        const float mv = m[i] * beta1 + omb1 * gr;             // adam_update_ (:262-265)
+        const float vv = v[i] * beta2 + (gr * gr) * omb2;      // (:267-274)
+        const float ratio = (mv * inv_bc1) / (sqrtf(vv * inv_bc2) + eps);
+        pv += ratio * (-lr);
+        p[i] = pv; m[i] = mv; v[i] = vv;
+        if (shadow) shadow[i] = __float2bfloat16_rn(pv);
+    }
+}
+
+// sum of squares, two stages, fixed order: partial[block] then one block folds
+__global__ void sumsq_partial_kernel(const float* __restrict__ g, size_t n, float* __restrict__ partial)
+{
+    __shared__ float red[32];
+    float s = 0.f;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) { const float x = g[i]; s += x * x; }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+// out[0] = total; when max_norm > 0 also out[1] = norm and out[2] = (norm > max_norm ? max_norm/norm : 1) * post_scale
+// (Optimizer::clip_grad_norm, compute_optimizer.hpp:128-138: no epsilon, applied only above the bound)
+__global__ void sumsq_final_kernel(const float* __restrict__ partial, int n, float pre_scale, float max_norm,
+                                   float post_scale, float* __restrict__ out)
+{
+    __shared__ float red[32];
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += partial[i];
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) {
+        s *= pre_scale * pre_scale;
+        out[0] = s;
+        const float norm = sqrtf(s);
+        out[1] = norm;
+        out[2] = ((max_norm > 0.f && norm > max_norm) ? max_norm / norm : 1.0f) * post_scale;
+    }
+}
+
+// Muon momentum (compute_optimizer.hpp:546-566): v = mu*v + g; u = g + mu*v (Nesterov)
+__global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ vel, float* __restrict__ u,
+                                     size_t n, float mu, const float* __restrict__ gscale_ptr)
+{
+    const float gs = gscale_ptr ? gscale_ptr[0] : 1.0f;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float gr = g[i] * gs;
+        const float vv = vel[i] * mu + gr;
+        vel[i] = vv;
+        u[i] = gr + mu * vv;
+    }
+}
+// X = u * 1/sqrt(|u|^2 + eps^2) (compute_optimizer.hpp:449-456), written as T for the NS GEMMs
+template <typename T>
+__global__ void muon_normalize_kernel(const float* __restrict__ u, const float* __restrict__ sumsq, float eps,
+                                      T* __restrict__ X, size_t n)
+{
+    const float inv = 1.0f / sqrtf(sumsq[0] + eps * eps);
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) X[i] = from_f32<T>(u[i] * inv);
+}
+// out = T(alpha*a + beta*b)
+template <typename T>
+__global__ void axpby_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, float alpha,
+                             float beta, size_t n)
+{
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        out[i] = from_f32<T>(alpha * to_f32(a[i]) + beta * to_f32(b[i]));
+}
+// p -= lr * X ; refresh the bf16 shadow
+template <typename T>
+__global__ void muon_apply_kernel(float* __restrict__ p, const T* __restrict__ X, bf16* __restrict__ shadow, float lr,
+                                  size_t n)
+{
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float pv = p[i] + (-lr) * to_f32(X[i]);
+        p[i] = pv;
+        if (shadow) shadow[i] = __float2bfloat16_rn(pv);
+    }
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ in, bf16* __restrict__ out, size_t n)
+{
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) out[i] = __float2bfloat16_rn(in[i]);
+}
+__global__ void bf16_to_f32_kernel(const bf16* __restrict__ in, float* __restrict__ out, size_t n)
+{
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) out[i] = __bfloat162float(in[i]);
+}
+
+// ======================================================================================
+// host launchers
+// ======================================================================================
+#define LAUNCH_CHECK() NNB_CUDA_CHECK(cudaGetLastError())
+
+template <typename T>
+int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rinv, float* mean, int rows, int d,
+             bool layer, cudaStream_t s)
+{
+    if (rows == 0) return 0;
+    const int grid = grid_for(rows, 8);
+    if (layer) norm_fwd_kernel<T, true><<<grid, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows, d);
+    else norm_fwd_kernel<T, false><<<grid, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows, d);
+    LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma, const float* rinv, const float* mean,
+                      int mode, float* out, float* scratch, int rows, int cols, cudaStream_t s)
+{
+    if (rows == 0 || cols == 0) return 0;
+    const int chunks = static_cast<int>(ceil_div(rows, CS_CHUNK_ROWS));
+    dim3 grid(static_cast<unsigned>(ceil_div(cols, CS_COLS)), chunks);
+    if (mode == 0) colsum_partial_kernel<T, 0><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, rows, cols);
+    else colsum_partial_kernel<T, 1><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, rows, cols);
+    LAUNCH_CHECK();
+    colsum_final_kernel<<<static_cast<unsigned>(ceil_div(cols, 128)), 128, 0, s>>>(scratch, out, chunks, cols);
+    LAUNCH_CHECK();
+    return 0;
+}
+size_t colsum_scratch_floats(int rows, int cols) { return static_cast<size_t>(ceil_div(rows, CS_CHUNK_ROWS)) * cols; }
+
+template <typename T>
+int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, const float* mean, const T* add, T* dx,
+             float* dgamma, float* dbeta, float* scratch, int rows, int d, bool layer, cudaStream_t s)
+{
+    if (rows == 0) return 0;
+    const int grid = grid_for(rows, 8);
+    // parameter gradients first: dx may alias g
+    NNB_TRY(colsum_accumulate<T>(g, d, x, gamma, rinv, layer ? mean : nullptr, 1, dgamma, scratch, rows, d, s));
+    if (layer) NNB_TRY(colsum_accumulate<T>(g, d, nullptr, nullptr, nullptr, nullptr, 0, dbeta, scratch, rows, d, s));
+    if (layer) norm_bwd_dx_kernel<T, true><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
+    else norm_bwd_dx_kernel<T, false><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
+    LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+int act_fwd(const T* h1, T* h2, int rows, int ff, bool swiglu, cudaStream_t s)
+{
+    const size_t n = static_cast<size_t>(rows) * ff;
+    if (n == 0) return 0;
+    if (swiglu) swiglu_fwd_kernel<T><<<grid_for(static_cast<long long>(n / Vec16<T>::N + 1), 256), 256, 0, s>>>(h1, h2, rows, ff);
+    else gelu_fwd_kernel<T><<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(h1, h2, n);
+    LAUNCH_CHECK();
+    return 0;
+}
+template <typename T>
+int act_bwd(const T* g, const T* h1, T* dh1, int rows, int ff, bool swiglu, cudaStream_t s)
+{
+    const size_t n = static_cast<size_t>(rows) * ff;
+    if (n == 0) return 0;
+    if (swiglu) swiglu_bwd_kernel<T><<<grid_for(static_cast<long long>(n / Vec16<T>::N + 1), 256), 256, 0, s>>>(g, h1, dh1, rows, ff);
+    else gelu_bwd_kernel<T><<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(g, h1, dh1, n);
+    LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+int cross_entropy(T* logits, const int* labels, const float* mask, float grad_scale, float* loss_vec, float* stats,
+                  float* loss_out, int rows, int V, int vocab, cudaStream_t s)
+{
+    NNB_ARG_CHECK(rows > 0 && V > 0, "empty input");            // compute_loss.hpp:243-244
+    NNB_ARG_CHECK(vocab <= V, "vocab_size > classes");          // cpu_engine.hpp:966-967
+    ce_count_kernel<<<1, 1024, 0, s>>>(labels, mask, rows, vocab, stats);
+    LAUNCH_CHECK();
+    constexpr int VN = Vec16<T>::N;
+    const bool vec_ok = (V % VN) == 0;
+    const int nvec = V / VN;
+    if (vec_ok && nvec <= 512 * 2) ce_fwd_bwd_kernel<T, 2><<<rows, 512, 0, s>>>(logits, labels, mask, stats, grad_scale, loss_vec, rows, V, vocab);
+    else if (vec_ok && nvec <= 512 * 4) ce_fwd_bwd_kernel<T, 4><<<rows, 512, 0, s>>>(logits, labels, mask, stats, grad_scale, loss_vec, rows, V, vocab);
+    else if (vec_ok && nvec <= 512 * 8) ce_fwd_bwd_kernel<T, 8><<<rows, 512, 0, s>>>(logits, labels, mask, stats, grad_scale, loss_vec, rows, V, vocab);
+    else ce_fwd_bwd_kernel<T, 0><<<rows, 512, 0, s>>>(logits, labels, mask, stats, grad_scale, loss_vec, rows, V, vocab);
+    LAUNCH_CHECK();
+    ce_loss_kernel<<<1, 1024, 0, s>>>(loss_vec, stats, rows, loss_out);
+    LAUNCH_CHECK();
+    return 0;
+}
+
+int adamw_update(float* p, const float* g, float* m, float* v, bf16* shadow, size_t n, float lr, float beta1,
+                 float beta2, float eps, float wd, int t_next, const float* gscale, cudaStream_t s)
+{
+    if (n == 0) return 0;
+    // bias_correction_ (compute_optimizer.hpp:312-317): float pow on the host
+    const float bc1 = 1.0f - powf(beta1, static_cast<float>(t_next));
+    const float bc2 = 1.0f - powf(beta2, static_cast<float>(t_next));
+    const float decay = (wd != 0.f) ? 1.0f - lr * wd : 1.0f;
+    adamw_kernel<<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(p, g, m, v, shadow, n, lr, beta1, beta2, eps,
+                                                                         decay, 1.0f / bc1, 1.0f / bc2, gscale);
+    LAUNCH_CHECK();
+    return 0;
+}
+
+constexpr int SUMSQ_BLOCKS = kSmCount * 4;
+size_t sumsq_scratch_floats() { return SUMSQ_BLOCKS; }
+
+int sum_squares(const float* g, size_t n, float pre_scale, float max_norm, float post_scale, float* scratch, float* out,
+                cudaStream_t s)
+{
+    const int blocks = n == 0 ? 1 : grid_for(static_cast<long long>(n), 256, 4);
+    sumsq_partial_kernel<<<blocks, 256, 0, s>>>(g, n, scratch);
+    LAUNCH_CHECK();
+    sumsq_final_kernel<<<1, 1024, 0, s>>>(scratch, blocks, pre_scale, max_norm, post_scale, out);
+    LAUNCH_CHECK();
+    return 0;
+}
+
+int muon_momentum(const float* g, float* vel, float* u, size_t n, float mu, const float* gscale, cudaStream_t s)
+{
+    if (n == 0) return 0;
+    muon_momentum_kernel<<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(g, vel, u, n, mu, gscale);
+    LAUNCH_CHECK();
+    return 0;
+}
+template <typename T>
+int muon_normalize(const float* u, const float* sumsq, float eps, T* X, size_t n, cudaStream_t s)
+{
+    muon_normalize_kernel<T><<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(u, sumsq, eps, X, n);
+    LAUNCH_CHECK();
+    return 0;
+}
+template <typename T>
+int axpby(const T* a, const T* b, T* out, float alpha, float beta, size_t n, cudaStream_t s)
+{
+    axpby_kernel<T><<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(a, b, out, alpha, beta, n);
+    LAUNCH_CHECK();
+    return 0;
+}
+template <typename T>
+int muon_apply(float* p, const T* X, bf16* shadow, float lr, size_t n, cudaStream_t s)
+{
+    muon_apply_kernel<T><<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(p, X, shadow, lr, n);
+    LAUNCH_CHECK();
+    return 0;
+}
+int f32_to_bf16(const float* in, bf16* out, size_t n, cudaStream_t s)
+{
+    if (n == 0) return 0;
+    f32_to_bf16_kernel<<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(in, out, n);
+    LAUNCH_CHECK();
+    return 0;
+}
+int bf16_to_f32(const bf16* in, float* out, size_t n, cudaStream_t s)
+{
+    if (n == 0) return 0;
+    bf16_to_f32_kernel<<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(in, out, n);
+    LAUNCH_CHECK();
+    return 0;
+}
+
+#define INSTANTIATE(T)                                                                                                 \
+    template int norm_fwd<T>(const T*, const float*, const float*, T*, float*, float*, int, int, bool, cudaStream_t);  \
+    template int norm_bwd<T>(const T*, const T*, const float*, const float*, const float*, const T*, T*, float*,       \
+                             float*, float*, int, int, bool, cudaStream_t);                                            \
+    template int colsum_accumulate<T>(const T*, long long, const T*, const float*, const float*, const float*, int,    \
+                                      float*, float*, int, int, cudaStream_t);                                         \
+    template int act_fwd<T>(const T*, T*, int, int, bool, cudaStream_t);                                               \
+    template int act_bwd<T>(const T*, const T*, T*, int, int, bool, cudaStream_t);                                     \
+    template int cross_entropy<T>(T*, const int*, const float*, float, float*, float*, float*, int, int, int,          \
+                                  cudaStream_t);                                                                       \
+    template int muon_normalize<T>(const float*, const float*, float, T*, size_t, cudaStream_t);                       \
+    template int axpby<T>(const T*, const T*, T*, float, float, size_t, cudaStream_t);                                 \
+    template int muon_apply<T>(float*, const T*, bf16*, float, size_t, cudaStream_t);
+INSTANTIATE(float)
+INSTANTIATE(bf16)
+
+}  // namespace nnb

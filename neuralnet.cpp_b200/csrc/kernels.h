@@ -1,0 +1,67 @@
+// Internal C++ interface between the translation units of the library (not part of the C ABI).
+#pragma once
+#include "common.cuh"
+
+namespace nnb {
+
+// ---- gemm_simt.cu : fp32, arbitrary strides, optional batch
+int sgemm_strided(const float* A, const float* B, float* C, int M, int N, int K, long long sam, long long sak,
+                  long long sbn, long long sbk, long long ldc, int batch, long long batch_a, long long batch_b,
+                  long long batch_c, float alpha, const float* bias_n, const float* bias_m, const float* residual,
+                  int accumulate, cudaStream_t stream);
+
+// ---- gemm_tcgen05.cu : bf16 operands, fp32 accumulate in TMEM
+int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+              int a_mn, int b_mn, int c_bf16, float alpha, const float* bias_n, const void* residual, int accumulate,
+              cudaStream_t stream);
+int gemm_device_error(int* code);
+int gemm_clear_device_error();
+
+// ---- fused_kernels.cu
+template <typename T> int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rinv, float* mean,
+                                   int rows, int d, bool layer, cudaStream_t s);
+template <typename T> int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, const float* mean,
+                                   const T* add, T* dx, float* dgamma, float* dbeta, float* scratch, int rows, int d,
+                                   bool layer, cudaStream_t s);
+template <typename T> int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma, const float* rinv,
+                                            const float* mean, int mode, float* out, float* scratch, int rows, int cols,
+                                            cudaStream_t s);
+size_t colsum_scratch_floats(int rows, int cols);
+template <typename T> int act_fwd(const T* h1, T* h2, int rows, int ff, bool swiglu, cudaStream_t s);
+template <typename T> int act_bwd(const T* g, const T* h1, T* dh1, int rows, int ff, bool swiglu, cudaStream_t s);
+template <typename T> int cross_entropy(T* logits, const int* labels, const float* mask, float grad_scale,
+                                        float* loss_vec, float* stats, float* loss_out, int rows, int V, int vocab,
+                                        cudaStream_t s);
+int adamw_update(float* p, const float* g, float* m, float* v, bf16* shadow, size_t n, float lr, float beta1, float beta2,
+                 float eps, float wd, int t_next, const float* gscale, cudaStream_t s);
+size_t sumsq_scratch_floats();
+int sum_squares(const float* g, size_t n, float pre_scale, float max_norm, float post_scale, float* scratch, float* out,
+                cudaStream_t s);
+int muon_momentum(const float* g, float* vel, float* u, size_t n, float mu, const float* gscale, cudaStream_t s);
+template <typename T> int muon_normalize(const float* u, const float* sumsq, float eps, T* X, size_t n, cudaStream_t s);
+template <typename T> int axpby(const T* a, const T* b, T* out, float alpha, float beta, size_t n, cudaStream_t s);
+template <typename T> int muon_apply(float* p, const T* X, bf16* shadow, float lr, size_t n, cudaStream_t s);
+int f32_to_bf16(const float* in, bf16* out, size_t n, cudaStream_t s);
+int bf16_to_f32(const bf16* in, float* out, size_t n, cudaStream_t s);
+
+// ---- embedding.cu
+template <typename T> int embed_fwd(const float* tok_emb, const float* pos_table, const int* tokens, T* x, int n_tok,
+                                    int seq, int d, int vocab, cudaStream_t s);
+template <typename T> int embed_bwd(float* tok_grad, float* pos_grad, const int* tokens, const T* g, void* scratch,
+                                    int batch, int seq, int d, int vocab, cudaStream_t s);
+size_t embed_bwd_scratch_bytes(int n_tok);
+
+// ---- attention_simt.cu / attention_mma.cu
+template <typename T> int attention_fwd_simt(const T* qkv, T* out, float* lse, const int* doc, int B, int S, int H, int dk,
+                                             int alibi, cudaStream_t s);
+template <typename T> int attention_bwd_simt(const T* qkv, const T* out, const T* dout, const float* lse, float* dvec,
+                                             T* dqkv, const int* doc, int B, int S, int H, int dk, int alibi,
+                                             cudaStream_t s);
+int attention_dvec_bf16(const bf16* out, const bf16* dout, float* dvec, int B, int S, int H, int dk, cudaStream_t s);
+bool attention_mma_supported(int dk, int d);
+int attention_fwd_mma(const bf16* qkv, bf16* out, float* lse, const int* doc, int B, int S, int H, int dk, int alibi,
+                      cudaStream_t s);
+int attention_bwd_mma(const bf16* qkv, const bf16* out, const bf16* dout, const float* lse, float* dvec, bf16* dqkv,
+                      const int* doc, int B, int S, int H, int dk, int alibi, cudaStream_t s);
+
+}  // namespace nnb

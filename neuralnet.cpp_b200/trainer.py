@@ -1,0 +1,239 @@
+"""Host-side driver of the fused GPT training step (the call a user makes).
+
+Mirrors the training-loop order of the reference driver (src/text_train.cpp:1107-1334): per
+micro-batch forward -> CrossEntropyLoss.forward_sparse -> backward with the logit gradient scaled
+by 1/accum; per optimizer step an optional global-norm clip, the optimizer update and zero_grad.
+PyTorch is used for device memory, streams and torch.distributed only; every computation is a call
+into libnnb200.so.
+
+Data parallelism: one process per GPU, identical replicas, each rank runs its own micro-batches;
+the gradient arena is summed over ranks with NCCL all-reduces issued on a side stream, per layer
+bucket, as soon as the backward pass has recorded that bucket's event; 1/world is folded into the
+optimizer's gradient scale.
+"""
+import ctypes as C
+import dataclasses
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import GptConfigC, call
+
+ACT_GELU, ACT_SWIGLU = 0, 1
+NORM_LAYER, NORM_RMS = 0, 1
+POS_LEARNED, POS_SINUSOIDAL, POS_ALIBI = 0, 1, 2
+FP32, BF16 = 0, 1
+
+
+@dataclasses.dataclass
+class GptConfig:
+    """nn::GptConfig (include/neuralnet.cpp/domain_gpt.hpp:29-39) plus batch and precision."""
+    vocab: int
+    d_model: int
+    heads: int
+    layers: int
+    d_ff: int
+    seq: int
+    batch: int
+    act: int = ACT_GELU
+    norm: int = NORM_LAYER
+    pos: int = POS_LEARNED
+    precision: int = FP32
+
+    def c_struct(self) -> GptConfigC:
+        return GptConfigC(vocab=self.vocab, d_model=self.d_model, heads=self.heads, layers=self.layers,
+                          d_ff=self.d_ff, seq=self.seq, batch=self.batch, act=self.act, norm=self.norm,
+                          pos=self.pos, precision=self.precision)
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class GptTrainer:
+    """Owns the parameter/gradient/moment arenas and the activation workspace of one replica."""
+
+    def __init__(self, cfg: GptConfig, device: Optional[torch.device] = None, *, lr=1e-3, weight_decay=0.01,
+                 beta1=0.9, beta2=0.999, eps=1e-8, muon: bool = False, muon_lr=0.02, muon_momentum=0.95,
+                 ns_steps=5, ns_eps=1e-7, process_group=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("GptTrainer needs a CUDA device: there is no CPU path")
+        self.cfg = cfg
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self._c = cfg.c_struct()
+        cp = C.byref(self._c)
+        n = call("nnb200_gpt_param_table", cp, None, None, None)
+        offs, rows, cols = (C.c_longlong * n)(), (C.c_int32 * n)(), (C.c_int32 * n)()
+        call("nnb200_gpt_param_table", cp, offs, rows, cols)
+        self.table = [(int(offs[i]), int(rows[i]), int(cols[i])) for i in range(n)]
+        self.arena_elems = int(call("nnb200_gpt_arena_elems", cp))
+        self.matrix_begin = int(call("nnb200_gpt_matrix_region_begin", cp))
+        self.layer_begin = [int(call("nnb200_gpt_layer_matrix_begin", cp, l)) for l in range(cfg.layers + 1)]
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self.params = torch.zeros(self.arena_elems, **f32)
+        self.grads = torch.zeros(self.arena_elems, **f32)
+        self.m = torch.zeros(self.arena_elems, **f32)
+        self.v = torch.zeros(self.arena_elems, **f32)
+        self.shadow = (torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=self.device)
+                       if cfg.precision == BF16 else None)
+        self.ws_bytes = int(call("nnb200_gpt_workspace_bytes", cp))
+        self.workspace = torch.empty(self.ws_bytes, dtype=torch.uint8, device=self.device)
+        call("nnb200_gpt_init_workspace", cp, _ptr(self.workspace), _stream())
+        self._off = {k: int(call("nnb200_gpt_workspace_offset", cp, i))
+                     for i, k in enumerate(("logits", "loss", "grad_x0", "ce_stats"))}
+        self.scal = torch.zeros(8, **f32)                                  # [0..2] clip outputs
+        self.sumsq_scratch = torch.empty(int(call("nnb200_sumsq_scratch_floats")), **f32)
+        self.lr, self.wd, self.b1, self.b2, self.eps = lr, weight_decay, beta1, beta2, eps
+        self.t = 0
+        self.muon = muon
+        self.muon_lr, self.muon_mu, self.ns_steps, self.ns_eps = muon_lr, muon_momentum, ns_steps, ns_eps
+        if muon:
+            worst = max(int(call("nnb200_muon_scratch_bytes", r, c, cfg.precision))
+                        for o, r, c in self.table if o >= self.matrix_begin)
+            self.muon_scratch = torch.empty(worst, dtype=torch.uint8, device=self.device)
+        # data parallel state
+        self.pg = process_group
+        self.world = torch.distributed.get_world_size(process_group) if process_group is not None else 1
+        self.side = torch.cuda.Stream(device=self.device) if self.world > 1 else None
+        self.events = [torch.cuda.Event() for _ in range(cfg.layers + 1)]
+        self._event_handles = (C.c_void_p * (cfg.layers + 1))()
+        self.launches = 0
+
+    # -------------------------------------------------------------- parameters
+    def load_params(self, tensors: Sequence[np.ndarray]):
+        """Copies parameters given in the reference order (GPTModel::parameters) into the arena —
+        the analogue of engine.copy_from(param, Matrix) on every parameter."""
+        assert len(tensors) == len(self.table)
+        host = np.zeros(self.arena_elems, np.float32)
+        for (off, r, c), t in zip(self.table, tensors):
+            host[off:off + r * c] = np.asarray(t, np.float32).reshape(-1)
+        self.params.copy_(torch.from_numpy(host))
+        self.refresh_shadow()
+
+    def refresh_shadow(self):
+        if self.shadow is not None:
+            call("nnb200_f32_to_bf16", _ptr(self.params), _ptr(self.shadow), self.arena_elems, _stream())
+
+    def _split(self, arena: torch.Tensor) -> List[np.ndarray]:
+        host = arena.detach().cpu().numpy()
+        return [host[off:off + r * c].reshape(r, c).copy() for off, r, c in self.table]
+
+    def get_params(self) -> List[np.ndarray]:
+        return self._split(self.params)
+
+    def get_grads(self) -> List[np.ndarray]:
+        return self._split(self.grads)
+
+    # -------------------------------------------------------------- step pieces
+    def _ints(self, a):
+        if isinstance(a, torch.Tensor):
+            return a.to(device=self.device, dtype=torch.int32, non_blocking=True)
+        return torch.from_numpy(np.ascontiguousarray(a, np.int32)).to(self.device, non_blocking=True)
+
+    def forward(self, tokens, doc_ids=None):
+        self._tokens = self._ints(tokens)
+        self._docs = self._ints(doc_ids) if doc_ids is not None else None
+        call("nnb200_gpt_forward", C.byref(self._c), _ptr(self.params), _ptr(self.shadow), _ptr(self.workspace),
+             _ptr(self._tokens), _ptr(self._docs), _stream())
+
+    def loss_and_grad(self, labels, mask=None, grad_scale=1.0):
+        self._labels = self._ints(labels)
+        if mask is not None and not isinstance(mask, torch.Tensor):
+            mask = torch.from_numpy(np.ascontiguousarray(mask, np.float32)).to(self.device, non_blocking=True)
+        self._mask = mask
+        call("nnb200_gpt_loss", C.byref(self._c), _ptr(self.workspace), _ptr(self._labels), _ptr(self._mask),
+             C.c_float(grad_scale), _stream())
+
+    def backward(self, record_events=False):
+        ev = None
+        if record_events:
+            for i, e in enumerate(self.events):
+                e.record()            # materialises the underlying cudaEvent_t
+                self._event_handles[i] = e.cuda_event
+            ev = self._event_handles
+        call("nnb200_gpt_backward", C.byref(self._c), _ptr(self.params), _ptr(self.shadow), _ptr(self.grads),
+             _ptr(self.workspace), _ptr(self._tokens), _ptr(self._docs), ev, _stream())
+
+    def loss_tensor(self) -> torch.Tensor:
+        """Device view of the scalar loss of the last loss_and_grad call."""
+        o = self._off["loss"]
+        return self.workspace[o:o + 4].view(torch.float32)
+
+    def logits(self) -> torch.Tensor:
+        """(tokens, vocab) view of the logits (their gradient after loss_and_grad)."""
+        c = self.cfg
+        n = c.batch * c.seq * c.vocab
+        o = self._off["logits"]
+        dt = torch.bfloat16 if c.precision == BF16 else torch.float32
+        return self.workspace[o:o + n * dt.itemsize].view(dt).view(c.batch * c.seq, c.vocab)
+
+    def micro_step(self, tokens, labels, mask=None, doc_ids=None, grad_scale=1.0, last=True):
+        """forward + loss + backward of one micro-batch; gradients accumulate."""
+        self.forward(tokens, doc_ids)
+        self.loss_and_grad(labels, mask, grad_scale)
+        self.backward(record_events=last and self.world > 1)
+        if last and self.world > 1:
+            self._all_reduce_buckets()
+
+    # -------------------------------------------------------------- data parallel
+    def _all_reduce_buckets(self):
+        """Sum-all-reduce of the gradient arena, one bucket per layer's matrices (in the order the
+        backward pass completes them) and a final bucket for embeddings, head and vectors; issued
+        on the side stream behind the events the backward pass recorded."""
+        import torch.distributed as dist
+        L = self.cfg.layers
+        with torch.cuda.stream(self.side):
+            for l in range(L - 1, -1, -1):
+                self.side.wait_event(self.events[l])
+                dist.all_reduce(self.grads[self.layer_begin[l]:self.layer_begin[l + 1]], group=self.pg)
+            self.side.wait_event(self.events[L])
+            dist.all_reduce(self.grads[:self.matrix_begin], group=self.pg)
+        torch.cuda.current_stream().wait_stream(self.side)
+
+    # -------------------------------------------------------------- optimizer
+    def optimizer_step(self, clip: Optional[float] = None, lr: Optional[float] = None,
+                       muon_lr: Optional[float] = None):
+        """clip_grad_norm (optional) + AdamW (+ Muon on the hidden matrices) + zero_grad.
+        Optimizer::clip_grad_norm / AdamW::step / Muon::step (compute_optimizer.hpp:90-140,
+        388-412, 517-590).  The clip factor and 1/world stay on the device: no host sync."""
+        lr = self.lr if lr is None else lr
+        s = _stream()
+        pre = 1.0 / self.world
+        gscale = None
+        if clip is not None or self.world > 1:
+            call("nnb200_grad_norm_clip", _ptr(self.grads), self.arena_elems, C.c_float(pre),
+                 C.c_float(clip if clip is not None else 0.0), _ptr(self.sumsq_scratch), _ptr(self.scal), s)
+            gscale = C.c_void_p(self.scal.data_ptr() + 8)
+        self.t += 1
+        n_adam = self.matrix_begin if self.muon else self.arena_elems
+        call("nnb200_adamw_step", _ptr(self.params), _ptr(self.grads), _ptr(self.m), _ptr(self.v), _ptr(self.shadow),
+             n_adam, C.c_float(lr), C.c_float(self.b1), C.c_float(self.b2), C.c_float(self.eps), C.c_float(self.wd),
+             self.t, gscale, s)
+        if self.muon:
+            mlr = self.muon_lr if muon_lr is None else muon_lr
+            base = self.params.data_ptr()
+            for off, r, c in self.table:
+                if off < self.matrix_begin:
+                    continue
+                sh = C.c_void_p(self.shadow.data_ptr() + 2 * off) if self.shadow is not None else None
+                call("nnb200_muon_step", C.c_void_p(base + 4 * off), C.c_void_p(self.grads.data_ptr() + 4 * off),
+                     C.c_void_p(self.m.data_ptr() + 4 * off), sh, r, c, C.c_float(mlr), C.c_float(self.muon_mu),
+                     self.ns_steps, C.c_float(self.ns_eps), self.cfg.precision, _ptr(self.muon_scratch), gscale, s)
+        self.grads.zero_()
+
+    def grad_norm(self) -> float:
+        """Norm computed by the last optimizer_step that clipped (host read; synchronises)."""
+        return float(self.scal[1].item())
+
+    def check_device_status(self):
+        """Raises if a bounded wait inside the tcgen05 GEMM ever gave up."""
+        code = C.c_int(0)
+        call("nnb200_gemm_status", C.byref(code))
+        if code.value:
+            raise _lib.NnbError(f"tcgen05 GEMM reported a timed-out wait (code {code.value >> 16}, block {code.value & 0xffff})")

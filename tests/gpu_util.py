@@ -1,0 +1,39 @@
+"""Helpers for the GPU parity tests: device buffers through torch, calls through the C ABI."""
+import ctypes as C
+
+import numpy as np
+import torch
+
+import __graft_entry__ as entry
+
+nnb = entry.load_package()
+call = nnb.call
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def host(t):
+    torch.cuda.synchronize()
+    return t.detach().float().cpu().numpy() if t.dtype == torch.bfloat16 else t.detach().cpu().numpy()
+
+
+def bf16_round(a):
+    """fp32 array rounded to bf16 and back (what a bf16 kernel sees of an fp32 input)."""
+    return torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(torch.bfloat16).float().numpy()
+
+
+def gemm_status():
+    code = C.c_int(0)
+    call("nnb200_gemm_status", C.byref(code))
+    return code.value
