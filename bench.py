@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Benchmark of the GPT training step (forward + backward + optimizer) on B200.
+
+  python bench.py --gpus N --steps K --warmup W            this repository's CUDA path
+  python bench.py --impl reference --gpus N --steps K ...  the reference CPU engine on the host cores
+
+Workload: BASELINE configuration 3 — vocab 8192, d_model 768, 12 heads, 12 layers, SwiGLU FFN 2048,
+RMSNorm, ALiBi, seq 1024, micro-batch 16 per GPU, gradient accumulation 2, AdamW with a cosine
+schedule, fp32 master weights, bf16 tensor-core GEMM/attention; token ids Zipf(1.1) from a per-rank
+seed; weights N(0, 0.02) from seed 42.  One step = one optimizer step = 2 micro-batches = 32768
+tokens per GPU.  Prints ONE JSON line on rank 0.
+"""
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(vocab=8192, d_model=768, heads=12, layers=12, d_ff=2048, seq=1024, batch=16, accum=2)
+BASE_LR, MIN_LR, WARMUP_STEPS, TOTAL_STEPS, WEIGHT_DECAY = 6e-4, 6e-5, 2, 1000, 0.01
+METRIC = "gpt_train_tokens_per_sec"
+
+
+def flops_per_token(w, mean_keys):
+    """Algorithmic training FLOPs per token: 3 * (2*[L*(4d^2 + 3*d*ff) + d*V] + 4*d*L*mean_keys)."""
+    d, ff, L, V = w["d_model"], w["d_ff"], w["layers"], w["vocab"]
+    return 3.0 * (2.0 * (L * (4 * d * d + 3 * d * ff) + d * V) + 4.0 * d * L * mean_keys)
+
+
+def step_lr(step):
+    """compute_step_lr of the reference (cli/lr_scheduler.hpp:89-114): linear warm-up, cosine decay."""
+    if WARMUP_STEPS > 0 and step < WARMUP_STEPS:
+        return BASE_LR * (step + 1) / WARMUP_STEPS
+    p = min(max((step - WARMUP_STEPS) / max(TOTAL_STEPS - WARMUP_STEPS, 1), 0.0), 1.0)
+    return MIN_LR + 0.5 * (BASE_LR - MIN_LR) * (1.0 + math.cos(math.pi * p))
+
+
+def zipf_tokens(rng, vocab, n, s=1.1):
+    import numpy as np
+    w = 1.0 / np.power(np.arange(1, vocab + 1, dtype=np.float64), s)
+    cdf = np.cumsum(w) / w.sum()
+    return np.minimum(np.searchsorted(cdf, rng.random(n)), vocab - 1).astype(np.int32)
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], bf16_tflops_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.path = tempfile.mktemp(prefix="nnb200_clocks_", suffix=".csv")
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 7:
+                    continue
+                try:
+                    sm.append(float(f[0]))
+                    mx.append(float(f[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, f[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            busy = sorted(x for x in sm if x > 0.5 * max(sm)) or sorted(sm)
+            out.update(sm_mhz=busy[len(busy) // 2], sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# --------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's own CpuEngine (oracle/_ref/ref_gpt)
+# --------------------------------------------------------------------------------------
+def run_cpu_reference(steps):
+    """Times the unmodified reference CPU engine (GPTModel + CrossEntropyLoss::forward_sparse + AdamW on
+    CpuEngine, all host threads) on a bounded sample of the workload: the full model shape, one
+    sequence of 1024 tokens per step (batch 1 instead of 16, no accumulation)."""
+    import numpy as np
+    from oracle import gpt_oracle as go
+    from oracle import ref_runner as rr
+    w = WORKLOAD
+    cfg = go.GptConfig(w["vocab"], w["d_model"], w["heads"], w["layers"], w["d_ff"], w["seq"], 1,
+                       go.ACT_SWIGLU, go.NORM_RMS, go.POS_ALIBI)
+    params = go.init_params(cfg, 42)
+    mbs = go.make_batches(cfg, steps, seed=1000, dist="zipf")
+    out = rr.run_reference(cfg, params, mbs, steps=steps, lr=BASE_LR, wd=WEIGHT_DECAY, cosine=True, warmup=WARMUP_STEPS,
+                           total_steps=TOTAL_STEPS, min_lr=MIN_LR, skip_params=True)
+    secs = out["seconds"]
+    tokens = cfg.tokens
+    return dict(value=tokens * len(secs) / float(secs.sum()), unit="tokens/s", cores=os.cpu_count(), kind="reference",
+                sample=f"{len(secs)} step(s) of 1 sequence x {w['seq']} tokens (batch 1, no accumulation) at the full "
+                       f"model shape: forward + backward + AdamW on the reference CpuEngine",
+                ms_per_step=1e3 * float(secs.mean()), last_loss=float(out["losses"][-1]))
+
+
+def reference_arm(args, rank):
+    if rank != 0:
+        return 0
+    steps = max(1, min(args.steps, 3))      # ~1 minute of CPU work per step: bounded so the arm ends in minutes
+    w = WORKLOAD
+    line = {"impl": "reference", "metric": METRIC, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
+            "warmup": 0, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": config_dict(args.gpus)}
+    try:
+        cb = run_cpu_reference(steps)
+    except Exception as e:  # the harness binary is built where the reference tree is present
+        print(json.dumps({"impl": "reference", "unavailable": f"reference CPU harness not runnable: {e}"[:300]}))
+        return 0
+    line.update(value=cb["value"], ms_per_step=cb["ms_per_step"],
+                cpu_baseline={k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                e2e={"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                gpu_launches=0)
+    print(json.dumps(line))
+    return 0
+
+
+def config_dict(n_gpus):
+    w = WORKLOAD
+    return {"workload": "BASELINE configs[2]: GPT-small-class data-parallel training step",
+            "vocab": w["vocab"], "d_model": w["d_model"], "heads": w["heads"], "layers": w["layers"], "d_ff": w["d_ff"],
+            "activation": "SwiGLU", "norm": "RMSNorm", "positions": "ALiBi", "seq_len": w["seq"],
+            "micro_batch_per_gpu": w["batch"], "grad_accum": w["accum"],
+            "global_batch": w["batch"] * w["accum"] * n_gpus, "optimizer": "AdamW, cosine LR, fp32 master weights",
+            "parallelism": f"dp{n_gpus}", "l2": "working set per step (>5 GB of activations) exceeds the 126 MB L2"}
+
+
+# --------------------------------------------------------------------------------------
+# this repository's arm
+# --------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (rank 0, N=1 only)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        return reference_arm(args, rank)
+
+    import numpy as np
+    import torch
+    import __graft_entry__ as entry
+    nnb = entry.load_package()          # raises if libnnb200.so is missing: there is no fallback
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local_rank)
+    pg = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+        pg = dist.group.WORLD
+    w = WORKLOAD
+    K, W = max(1, args.steps), max(3, args.warmup)
+    cfg = nnb.GptConfig(w["vocab"], w["d_model"], w["heads"], w["layers"], w["d_ff"], w["seq"], w["batch"],
+                        nnb.ACT_SWIGLU, nnb.NORM_RMS, nnb.POS_ALIBI, nnb.BF16)
+    tr = nnb.GptTrainer(cfg, lr=BASE_LR, weight_decay=WEIGHT_DECAY, process_group=pg)
+    tr.init_params_normal(seed=42, std=0.02)
+    ntok, accum = w["batch"] * w["seq"], w["accum"]
+
+    # synthetic data: per-rank seed, S+1 ids per row, x = ids[:S], y = ids[1:], mask of ones
+    rng = np.random.default_rng(1000 + rank)
+    n_micro = accum * 4                   # a small pool of distinct micro-batches, cycled
+    ids = zipf_tokens(rng, w["vocab"], n_micro * w["batch"] * (w["seq"] + 1)).reshape(n_micro, w["batch"], w["seq"] + 1)
+    host_tok = torch.from_numpy(np.ascontiguousarray(ids[:, :, :-1]).reshape(n_micro, ntok)).pin_memory()
+    host_lab = torch.from_numpy(np.ascontiguousarray(ids[:, :, 1:]).reshape(n_micro, ntok)).pin_memory()
+    host_mask = torch.ones(n_micro, ntok, dtype=torch.float32).pin_memory()
+    dev_tok, dev_lab, dev_mask = host_tok.cuda(), host_lab.cuda(), host_mask.cuda()
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def run_step(step, resident):
+        last = None
+        for a in range(accum):
+            i = (step * accum + a) % n_micro
+            if resident:
+                t, l, m = dev_tok[i], dev_lab[i], dev_mask[i]
+            else:   # the user's call: host buffers in, loss out
+                t = host_tok[i].cuda(non_blocking=True)
+                l = host_lab[i].cuda(non_blocking=True)
+                m = host_mask[i].cuda(non_blocking=True)
+            tr.micro_step(t, l, m, None, grad_scale=1.0 / accum, last=(a == accum - 1))
+            if not resident:
+                loss_host.copy_(tr.loss_tensor(), non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                last = float(loss_host[0])
+        tr.optimizer_step(lr=step_lr(step))
+        return last
+
+    def timed(resident, first_step):
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        last = None
+        for s in range(K):
+            last = run_step(first_step + s, resident)
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+        return float(ms.item()), last
+
+    for s in range(W):
+        run_step(s, True)
+    torch.cuda.synchronize()
+    nnb.call("nnb200_launch_count", 1)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms_resident, _ = timed(True, W)
+    launches = int(nnb.call("nnb200_launch_count", 1))
+    clocks = sampler.stop() if sampler else None
+    run_step(W + K, False)                 # warm the host-buffer path
+    ms_e2e, last_loss = timed(False, W + K + 1)
+
+    # roofline of the dominant kernel (tcgen05 GEMM): event pairs around every launch of one more step
+    nnb.call("nnb200_gemm_profile", 1)
+    run_step(W + 2 * K + 1, True)
+    nnb.call("nnb200_gemm_profile", 0)
+    tms, tfl, nl = C.c_double(0), C.c_double(0), C.c_int(0)
+    nnb.call("nnb200_gemm_profile_read", C.byref(tms), C.byref(tfl), C.byref(nl))
+    torch.cuda.synchronize()
+    tr.check_device_status()
+
+    if rank != 0:
+        return 0
+    peaks = load_peaks()
+    tokens_per_step = ntok * accum * world
+    value = tokens_per_step * K / (ms_resident * 1e-3)
+    e2e_value = tokens_per_step * K / (ms_e2e * 1e-3)
+    fpt = flops_per_token(w, (w["seq"] + 1) / 2.0)
+    achieved_tf = (tfl.value / (tms.value * 1e-3)) / 1e12 if tms.value > 0 else 0.0
+    peak_tf = peaks["bf16_tflops_sustained"]
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_resident / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": config_dict(world),
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / K,
+                "h2d_bytes_per_step": accum * ntok * (4 + 4 + 4), "d2h_bytes_per_step": accum * 4,
+                "last_loss": last_loss},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "model_flops_per_token": fpt,
+        "mfu": {"of_nominal_2250": value / world * fpt / 2.25e15, "of_measured_burst": value / world * fpt / (peaks["bf16_tflops"] * 1e12),
+                "of_measured_sustained": value / world * fpt / (peaks["bf16_tflops_sustained"] * 1e12)},
+        "roofline": {"kernel": "gemm_bf16_kernel (tcgen05)", "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf,
+                     "unit": "TFLOP/s", "frac": achieved_tf / peak_tf, "traffic": None,
+                     "peak_source": peaks["source"] + " cuBLAS bf16, sustained (kernel timed inside a long step)",
+                     "launches_timed": nl.value, "share_of_step": tms.value / (ms_resident / K) if ms_resident else None},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        try:
+            cb = run_cpu_reference(1)
+            line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        except Exception as e:
+            line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "reference",
+                                    "sample": f"not run: {e}"[:200]}
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

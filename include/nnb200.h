@@ -93,6 +93,14 @@ int nnb200_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K,
 int nnb200_gemm_f32(const float* A, const float* B, float* D, int M, int N, int K, long long lda, long long ldb,
                     long long ldc, int a_mn_major, int b_mn_major, float alpha, const float* bias_n,
                     const float* residual, int accumulate, void* stream);
+/* Per-launch timing of the tcgen05 GEMM: enable=1 starts recording a CUDA event pair around every
+ * GEMM kernel on its launching stream (and resets the totals), enable=0 stops.  _read synchronises
+ * on the recorded events and returns (host) the summed kernel time, the summed algorithmic FLOPs
+ * (2*M*N*K per launch) and the number of launches. */
+int nnb200_gemm_profile(int enable);
+int nnb200_gemm_profile_read(double* host_total_ms, double* host_total_flops, int* host_launches);
+/* Kernels launched by this library since the last reset (host-side counter). */
+unsigned long long nnb200_launch_count(int reset);
 /* Reads (host) and clears the device-side status word of the tcgen05 GEMM: 0 = no wait ever gave up. */
 int nnb200_gemm_status(int* host_code);
 

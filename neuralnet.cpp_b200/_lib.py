@@ -55,6 +55,9 @@ SIGNATURES = {
     "nnb200_gemm_bf16": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _f, _p, _p, _i, _p],
     "nnb200_gemm_f32": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _f, _p, _p, _i, _p],
     "nnb200_gemm_status": [C.POINTER(C.c_int)],
+    "nnb200_gemm_profile": [_i],
+    "nnb200_gemm_profile_read": [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)],
+    "nnb200_launch_count": [_i],
     "nnb200_attention_forward": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "nnb200_attention_backward": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "nnb200_norm_forward": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
@@ -86,6 +89,7 @@ SIGNATURES = {
     "nnb200_gpt_backward": [_cfgp, _p, _p, _p, _p, _p, _p, _p, _p],
 }
 _RET = {
+    "nnb200_launch_count": C.c_ulonglong,
     "nnb200_colsum_scratch_floats": _sz, "nnb200_embedding_scratch_bytes": _sz, "nnb200_sumsq_scratch_floats": _sz,
     "nnb200_muon_scratch_bytes": _sz, "nnb200_gpt_arena_elems": _ll, "nnb200_gpt_matrix_region_begin": _ll,
     "nnb200_gpt_layer_matrix_begin": _ll, "nnb200_gpt_workspace_bytes": _ll, "nnb200_gpt_workspace_offset": _ll,

@@ -7,6 +7,8 @@ using namespace nnb;
 
 namespace nnb {
 
+unsigned long long g_launches = 0;
+
 // Bm = b*A + c*A2 + a*I on an (r, r) matrix: the polynomial of one Newton-Schulz step with the
 // "+ a*X" term (compute_optimizer.hpp:476-488) folded in as a*I, so X' = Bm X is one GEMM
 template <typename T>
@@ -59,7 +61,7 @@ static int muon_matrix(float* p, const float* u, bf16* shadow, int rows, int col
                                   nullptr, 0, s));
         }
         ns_poly_kernel<T><<<grid_for(static_cast<long long>(r) * r, 256), 256, 0, s>>>(A, A2, Bm, r, ka, kb, kc);
-        NNB_CUDA_CHECK(cudaGetLastError());
+        NNB_LAUNCH_CHECK();
         if constexpr (BF) {
             const bf16* Xb = reinterpret_cast<const bf16*>(X);
             const bf16* Bb = reinterpret_cast<const bf16*>(Bm);
@@ -230,6 +232,20 @@ int nnb200_muon_step(float* p, const float* g, float* velocity, void* shadow_bf1
         return muon_matrix<float>(p, u, static_cast<bf16*>(shadow_bf16), rows, cols, lr, ns_steps, ns_eps, sc, up256(n * 4), s);
     }
     return muon_apply<float>(p, u, static_cast<bf16*>(shadow_bf16), lr, n, s);     // non-2-D: p -= lr*u
+}
+
+unsigned long long nnb200_launch_count(int reset)
+{
+    const unsigned long long v = g_launches;
+    if (reset) g_launches = 0;
+    return v;
+}
+
+int nnb200_gemm_profile(int enable) { return gemm_profile_enable(enable); }
+int nnb200_gemm_profile_read(double* host_total_ms, double* host_total_flops, int* host_launches)
+{
+    NNB_ARG_CHECK(host_total_ms && host_total_flops && host_launches, "null output");
+    return gemm_profile_read(host_total_ms, host_total_flops, host_launches);
 }
 
 int nnb200_f32_to_bf16(const float* in, void* out, size_t n, void* stream) { return f32_to_bf16(in, static_cast<bf16*>(out), n, to_stream(stream)); }

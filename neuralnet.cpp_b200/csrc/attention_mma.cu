@@ -385,7 +385,7 @@ static int run_fwd(const AttnArgs& a, cudaStream_t s)
 {
     dim3 grid(static_cast<unsigned>(ceil_div(a.S, 64)), a.H, a.B);
     attn_fwd_mma_kernel<DK><<<grid, 128, 0, s>>>(a);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 template <int DK>
@@ -393,9 +393,9 @@ static int run_bwd(const AttnArgs& a, cudaStream_t s)
 {
     dim3 grid(static_cast<unsigned>(ceil_div(a.S, 64)), a.H, a.B);
     attn_bwd_dq_mma_kernel<DK><<<grid, 128, 0, s>>>(a);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     attn_bwd_dkv_mma_kernel<DK><<<grid, 128, 0, s>>>(a);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 

@@ -185,7 +185,7 @@ static int fwd_dk(const T* qkv, T* out, float* lse, const int* doc, int B, int S
     const long long rows = static_cast<long long>(B) * H * S;
     attn_fwd_simt_kernel<T, DK><<<static_cast<unsigned>(ceil_div(rows, 4)), 128, 0, s>>>(
         qkv, out, lse, doc, B, S, H, alibi, 1.0f / sqrtf(static_cast<float>(DK)));
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 template <typename T, int DK>
@@ -195,12 +195,12 @@ static int bwd_dk(const T* qkv, const T* out, const T* dout, const float* lse, f
     const long long rows = static_cast<long long>(B) * H * S;
     const float scale = 1.0f / sqrtf(static_cast<float>(DK));
     attn_dvec_kernel<T><<<static_cast<unsigned>(ceil_div(rows * 32, 256)), 256, 0, s>>>(out, dout, dvec, B, S, H, DK);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     const unsigned grid = static_cast<unsigned>(ceil_div(rows, 4));
     attn_bwd_dq_simt_kernel<T, DK><<<grid, 128, 0, s>>>(qkv, dout, lse, dvec, dqkv, doc, B, S, H, alibi, scale);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     attn_bwd_dkv_simt_kernel<T, DK><<<grid, 128, 0, s>>>(qkv, dout, lse, dvec, dqkv, doc, B, S, H, alibi, scale);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -233,7 +233,7 @@ int attention_dvec_bf16(const bf16* out, const bf16* dout, float* dvec, int B, i
 {
     const long long rows = static_cast<long long>(B) * H * S;
     attn_dvec_kernel<bf16><<<static_cast<unsigned>(ceil_div(rows * 32, 256)), 256, 0, s>>>(out, dout, dvec, B, S, H, dk);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 

@@ -18,6 +18,14 @@
         }                                                                                     \
     } while (0)
 
+// after every kernel launch: counts it (the host-side launch counter the benchmark reports) and
+// surfaces launch-configuration errors
+#define NNB_LAUNCH_CHECK()                                                                    \
+    do {                                                                                      \
+        ++nnb::g_launches;                                                                    \
+        NNB_CUDA_CHECK(cudaGetLastError());                                                   \
+    } while (0)
+
 #define NNB_ARG_CHECK(cond, msg)                                                              \
     do {                                                                                      \
         if (!(cond)) {                                                                        \
@@ -33,6 +41,8 @@
     } while (0)
 
 namespace nnb {
+
+extern unsigned long long g_launches;   // kernels launched by this library since the last reset
 
 using bf16 = __nv_bfloat16;
 

@@ -147,7 +147,7 @@ int embed_fwd(const float* tok_emb, const float* pos_table, const int* tokens, T
 {
     if (n_tok == 0) return 0;
     embed_fwd_kernel<T><<<grid_for(n_tok, 8), 256, 0, s>>>(tok_emb, pos_table, tokens, x, n_tok, seq, d, vocab);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -163,26 +163,26 @@ int embed_bwd(float* tok_grad, float* pos_grad, const int* tokens, const T* g, v
     int* flags = reinterpret_cast<int*>(keys + n_pad);
     const unsigned blocks = static_cast<unsigned>(ceil_div(n_pad, 256));
     make_keys_kernel<<<blocks, 256, 0, s>>>(tokens, keys, n_tok, n_pad, vocab);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     // bitonic network: k = 2..2048 entirely in shared memory, then global stages for j >= 2048 and
     // a shared-memory tail for j < 2048 of each larger k
     bitonic_local_kernel<<<n_pad / 2048, 1024, 0, s>>>(keys, n_pad, 2, 2048);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     for (int k = 4096; k <= n_pad; k <<= 1) {
         for (int j = k >> 1; j >= 2048; j >>= 1) {
             bitonic_stage_kernel<<<blocks, 256, 0, s>>>(keys, n_pad, k, j);
-            NNB_CUDA_CHECK(cudaGetLastError());
+            NNB_LAUNCH_CHECK();
         }
         bitonic_local_kernel<<<n_pad / 2048, 1024, 0, s>>>(keys, n_pad, k, k);
-        NNB_CUDA_CHECK(cudaGetLastError());
+        NNB_LAUNCH_CHECK();
     }
     segment_heads_kernel<<<blocks, 256, 0, s>>>(keys, n_pad, flags);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     scatter_segments_kernel<T><<<kSmCount * 8, 256, 0, s>>>(tok_grad, keys, flags, g, n_pad, d);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     if (pos_grad) {
         pos_bwd_kernel<T><<<grid_for(static_cast<long long>(seq) * d, 256), 256, 0, s>>>(pos_grad, g, batch, seq, d);
-        NNB_CUDA_CHECK(cudaGetLastError());
+        NNB_LAUNCH_CHECK();
     }
     return 0;
 }

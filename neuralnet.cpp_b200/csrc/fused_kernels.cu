@@ -457,7 +457,7 @@ __global__ void bf16_to_f32_kernel(const bf16* __restrict__ in, float* __restric
 // ======================================================================================
 // host launchers
 // ======================================================================================
-#define LAUNCH_CHECK() NNB_CUDA_CHECK(cudaGetLastError())
+#define LAUNCH_CHECK() NNB_LAUNCH_CHECK()
 
 template <typename T>
 int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rinv, float* mean, int rows, int d,

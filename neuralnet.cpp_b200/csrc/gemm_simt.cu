@@ -83,7 +83,7 @@ int sgemm_strided(const float* A, const float* B, float* C, int M, int N, int K,
     NNB_ARG_CHECK(grid.y <= 65535, "M too large for one launch");
     sgemm_strided_kernel<<<grid, 256, 0, stream>>>(A, B, C, M, N, K, sam, sak, sbn, sbk, ldc, batch_a, batch_b,
                                                    batch_c, alpha, bias_n, bias_m, residual, accumulate);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 

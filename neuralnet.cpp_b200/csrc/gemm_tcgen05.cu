@@ -19,6 +19,7 @@
 
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 
 #include "kernels.h"
 
@@ -375,6 +376,28 @@ static int sm_count()
     return n;
 }
 
+// Optional per-launch timing: CUDA events recorded on the launching stream around each GEMM kernel,
+// so a benchmark can report achieved FLOP/s of this kernel from inside a real training step.
+struct GemmProfile {
+    bool on = false;
+    std::vector<cudaEvent_t> events;     // pairs: start, stop
+    size_t used = 0;
+    double flops = 0.0;
+};
+static GemmProfile g_prof;
+
+static cudaEvent_t prof_event(cudaStream_t s)
+{
+    if (g_prof.used == g_prof.events.size()) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) return nullptr;
+        g_prof.events.push_back(e);
+    }
+    cudaEvent_t e = g_prof.events[g_prof.used++];
+    cudaEventRecord(e, s);
+    return e;
+}
+
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t s)
 {
@@ -387,8 +410,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     }
     const int units = p.tiles_m * p.tiles_n * p.splits;
     const int grid = units < sm_count() ? units : sm_count();
+    if (g_prof.on) prof_event(s);
     gemm_bf16_kernel<BN, A_MN, B_MN, STAGES><<<grid, 192, SMEM, s>>>(ta, tb, p);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    if (g_prof.on) { prof_event(s); g_prof.flops += 2.0 * p.M * p.N * p.K; }
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -446,6 +471,25 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
         GO(128, true, true);
     }
 #undef GO
+}
+
+int gemm_profile_enable(int enable)
+{
+    g_prof.on = enable != 0;
+    if (g_prof.on) { g_prof.used = 0; g_prof.flops = 0.0; }
+    return 0;
+}
+int gemm_profile_read(double* total_ms, double* total_flops, int* launches)
+{
+    double ms = 0.0;
+    for (size_t i = 0; i + 1 < g_prof.used; i += 2) {
+        NNB_CUDA_CHECK(cudaEventSynchronize(g_prof.events[i + 1]));
+        float t = 0.f;
+        NNB_CUDA_CHECK(cudaEventElapsedTime(&t, g_prof.events[i], g_prof.events[i + 1]));
+        ms += t;
+    }
+    *total_ms = ms; *total_flops = g_prof.flops; *launches = static_cast<int>(g_prof.used / 2);
+    return 0;
 }
 
 int gemm_device_error(int* code)

@@ -16,6 +16,8 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
               cudaStream_t stream);
 int gemm_device_error(int* code);
 int gemm_clear_device_error();
+int gemm_profile_enable(int enable);
+int gemm_profile_read(double* total_ms, double* total_flops, int* launches);
 
 // ---- fused_kernels.cu
 template <typename T> int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rinv, float* mean,

@@ -88,14 +88,14 @@ template <typename F> static int launch_map1(const float* a, float* out, size_t 
 {
     if (n == 0) return 0;
     map1_kernel<<<grid_for(static_cast<long long>(n / 4 + 1), 256), 256, 0, s>>>(a, out, n, f);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 template <typename F> static int launch_map2(const float* a, const float* b, float* out, size_t n, F f, cudaStream_t s)
 {
     if (n == 0) return 0;
     map2_kernel<<<grid_for(static_cast<long long>(n / 4 + 1), 256), 256, 0, s>>>(a, b, out, n, f);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -347,7 +347,7 @@ int cuda_reduce_row(const float* A, float* out, unsigned int rows, unsigned int 
     if (mode > 2) return -1;
     if (rows == 0) return 0;
     reduce_row_kernel<<<grid_for(rows, 8), 256, 0, to_stream(stream)>>>(A, out, rows, cols, mode);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -356,7 +356,7 @@ int cuda_reduce_col(const float* A, float* out, unsigned int rows, unsigned int 
     if (mode > 2) return -1;
     if (cols == 0) return 0;
     reduce_col_kernel<<<static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, to_stream(stream)>>>(A, out, rows, cols, mode);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -367,7 +367,7 @@ int cuda_broadcast_row(const float* A, const float* vec, float* out, unsigned in
     if (static_cast<size_t>(rows) * cols == 0) return 0;
     broadcast_kernel<<<grid_for(static_cast<long long>(rows) * cols, 256), 256, 0, to_stream(stream)>>>(A, vec, out, rows,
                                                                                                       cols, op, 1);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -378,7 +378,7 @@ int cuda_broadcast_col(const float* A, const float* vec, float* out, unsigned in
     if (static_cast<size_t>(rows) * cols == 0) return 0;
     broadcast_kernel<<<grid_for(static_cast<long long>(rows) * cols, 256), 256, 0, to_stream(stream)>>>(A, vec, out, rows,
                                                                                                       cols, op, 0);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -388,7 +388,7 @@ int cuda_transpose(const float* A, float* out, unsigned int R, unsigned int C, v
     dim3 grid(static_cast<unsigned>(ceil_div(C, 32)), static_cast<unsigned>(ceil_div(R, 32)));
     if (grid.y > 65535) return -1;
     transpose_kernel<<<grid, dim3(32, 8), 0, to_stream(stream)>>>(A, out, R, C);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -398,7 +398,7 @@ int cuda_rearrange_3d(const float* A, float* out, unsigned int M, unsigned int B
     const long long total = static_cast<long long>(M) * B * N;
     if (total == 0) return 0;
     rearrange3d_kernel<<<grid_for(total, 256), 256, 0, to_stream(stream)>>>(A, out, M, B, N, inverse);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -407,7 +407,7 @@ int cuda_gather(const float* table, const float* indices, float* out, unsigned i
 {
     if (static_cast<size_t>(num) * D == 0) return 0;
     gather_kernel<<<grid_for(num, 8), 256, 0, to_stream(stream)>>>(table, indices, out, vocab, D, num);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 
@@ -416,7 +416,7 @@ int cuda_scatter_add(float* dst, const float* indices, const float* grad, unsign
 {
     if (static_cast<size_t>(num) * D == 0 || vocab == 0) return 0;
     scatter_add_ordered_kernel<<<vocab, 128, 0, to_stream(stream)>>>(dst, indices, grad, vocab, D, num);
-    NNB_CUDA_CHECK(cudaGetLastError());
+    NNB_LAUNCH_CHECK();
     return 0;
 }
 

@@ -116,6 +116,35 @@ class GptTrainer:
         self.params.copy_(torch.from_numpy(host))
         self.refresh_shadow()
 
+    def param_names(self) -> List[str]:
+        """Names of the tensors in the reference's parameter order (GPTModel::parameters,
+        compute_layer.hpp:2739-2755; GPTBlock :2336-2346)."""
+        c = self.cfg
+        norm = lambda p: [p + ".gamma"] + ([p + ".beta"] if c.norm == NORM_LAYER else [])
+        names = ["token_emb"] + (["pos_emb"] if c.pos == POS_LEARNED else [])
+        for l in range(c.layers):
+            p = f"blk{l}."
+            for w in ("wq", "wk", "wv", "wo"):
+                names += [p + w + ".W", p + w + ".b"]
+            names += norm(p + "norm1") + [p + "fc1.W", p + "fc1.b", p + "fc2.W", p + "fc2.b"] + norm(p + "norm2")
+        names += norm("ln_f") + ["lm_head.W", "lm_head.b"]
+        assert len(names) == len(self.table)
+        return names
+
+    def init_params_normal(self, seed=42, std=0.02):
+        """Synthetic weights: matrices and embeddings ~ N(0, std), biases 0, norm scales 1 — the same
+        on every rank for the same seed."""
+        rng = np.random.default_rng(seed)
+        tensors = []
+        for name, (_, r, c) in zip(self.param_names(), self.table):
+            if name.endswith(".gamma"):
+                tensors.append(np.ones((r, c), np.float32))
+            elif c == 1:
+                tensors.append(np.zeros((r, c), np.float32))
+            else:
+                tensors.append((rng.standard_normal((r, c)) * std).astype(np.float32))
+        self.load_params(tensors)
+
     def refresh_shadow(self):
         if self.shadow is not None:
             call("nnb200_f32_to_bf16", _ptr(self.params), _ptr(self.shadow), self.arena_elems, _stream())

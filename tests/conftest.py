@@ -24,3 +24,11 @@ def pytest_collection_modifyitems(config, items):
     for it in items:
         if "gpu" in it.keywords:
             it.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _release_device_buffers():
+    yield
+    mod = sys.modules.get("tests.gpu_util")
+    if mod is not None:
+        mod.release()

@@ -9,10 +9,22 @@ import __graft_entry__ as entry
 nnb = entry.load_package()
 call = nnb.call
 
+# Device tensors made by dev() stay referenced until the test ends (tests/conftest.py clears the
+# list): a temporary passed as `ptr(dev(x))` would otherwise be freed, and its memory handed to the
+# next allocation, before the kernel that reads it has even been enqueued.
+_keep = []
+
 
 def dev(a, dtype=None):
     t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
-    return t.to(dtype) if dtype is not None else t
+    if dtype is not None:
+        t = t.to(dtype)
+    _keep.append(t)
+    return t
+
+
+def release():
+    _keep.clear()
 
 
 def ptr(t):
