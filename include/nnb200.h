@@ -136,6 +136,17 @@ size_t nnb200_colsum_scratch_floats(int rows, int cols);
 /* out[c] += sum_r g[r][c] (bias gradient of Linear::backward, compute_layer.hpp:190-193). */
 int nnb200_bias_grad(const void* g, long long ldg, float* out, float* scratch, int rows, int cols, int dtype, void* stream);
 
+/* Same result as nnb200_bias_grad for callers that cannot supply scratch memory (no counterpart in
+ * the reference: its CudaBackend allocates op outputs only and offers kernels no workspace, and
+ * hosts with a device-memory budget fixed at start-up must not call cudaMalloc).  The partial sums
+ * go to a buffer built into the library — NNB200_BIAS_GRAD_STATIC_MAX_FLOATS floats (1 MiB) that
+ * each GPU holds from library load to exit; shapes needing more (ceil(rows/256)*cols floats) are
+ * rejected with -1.  Allocates nothing.  The first call on a device looks the buffer's address up;
+ * make that call before any stream capture.  All calls on a device share the buffer, so two calls
+ * whose kernels may overlap on the GPU (different streams) race: serialise them. */
+#define NNB200_BIAS_GRAD_STATIC_MAX_FLOATS 262144
+int nnb200_bias_grad_static(const void* g, long long ldg, float* out, int rows, int cols, int dtype, void* stream);
+
 /* swiglu=0: h2 = h1*sigmoid(1.702*h1) on (rows, ff); swiglu=1: h1 (rows, 2ff) = gate|up,
  * h2 = gate*sigmoid(gate)*up.  Replaces GeLU/SwiGLU::forward (compute_layer.hpp:266-295, 375-404). */
 int nnb200_activation_forward(const void* h1, void* h2, int rows, int ff, int swiglu, int dtype, void* stream);

@@ -64,6 +64,7 @@ SIGNATURES = {
     "nnb200_norm_backward": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
     "nnb200_colsum_scratch_floats": [_i, _i],
     "nnb200_bias_grad": [_p, _ll, _p, _p, _i, _i, _i, _p],
+    "nnb200_bias_grad_static": [_p, _ll, _p, _i, _i, _i, _p],
     "nnb200_activation_forward": [_p, _p, _i, _i, _i, _i, _p],
     "nnb200_activation_backward": [_p, _p, _p, _i, _i, _i, _i, _p],
     "nnb200_cross_entropy": [_p, _p, _p, _f, _p, _p, _p, _i, _i, _i, _i, _p],

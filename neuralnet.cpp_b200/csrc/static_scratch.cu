@@ -1,0 +1,61 @@
+// A bias-gradient entry point for callers that cannot provide scratch memory.
+//
+// nnb200_bias_grad needs a caller-allocated buffer for its per-chunk partial sums.  Some hosts of
+// this library have nowhere to get one: the reference's CudaBackend allocates op *outputs* only
+// and has no hook through which a kernel could ask for workspace, and services that fix their
+// device-memory budget at start-up (or run inside latency-critical loops) must not call cudaMalloc,
+// which synchronises the whole device.  For them the partial sums live in a file-scope device
+// array that every GPU loading the library holds from load to exit.
+#include "kernels.h"
+#include "nnb200.h"
+
+namespace nnb {
+
+// 1 MiB per GPU.  Enough for e.g. 16384 rows x 4096 columns (64 chunks of 256 rows x 4096).
+static __device__ __align__(256) float g_bias_grad_scratch[NNB200_BIAS_GRAD_STATIC_MAX_FLOATS];
+
+constexpr int kMaxDevices = 64;
+static float* g_scratch_addr[kMaxDevices] = {};
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel can use:
+// the device address is looked up once per device, with that device current, and cached.
+static int static_scratch(float** out)
+{
+    int dev = 0;
+    NNB_CUDA_CHECK(cudaGetDevice(&dev));
+    NNB_ARG_CHECK(dev >= 0 && dev < kMaxDevices, "device ordinal out of range");
+    if (!g_scratch_addr[dev]) {
+        void* p = nullptr;
+        NNB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_bias_grad_scratch));
+        g_scratch_addr[dev] = static_cast<float*>(p);
+    }
+    *out = g_scratch_addr[dev];
+    return 0;
+}
+
+}  // namespace nnb
+
+using namespace nnb;
+
+extern "C" int nnb200_bias_grad_static(const void* g, long long ldg, float* out, int rows, int cols, int dtype,
+                                       void* stream)
+{
+    NNB_ARG_CHECK(dtype == 0 || dtype == 1, "dtype must be 0 (fp32) or 1 (bf16)");
+    NNB_ARG_CHECK(rows >= 0 && cols >= 0, "negative shape");
+    if (colsum_scratch_floats(rows, cols) > static_cast<size_t>(NNB200_BIAS_GRAD_STATIC_MAX_FLOATS)) {
+        fprintf(stderr,
+                "nnb200_bias_grad_static: %d x %d needs %zu scratch floats, the built-in buffer holds %d; "
+                "use nnb200_bias_grad with caller scratch\n",
+                rows, cols, colsum_scratch_floats(rows, cols), NNB200_BIAS_GRAD_STATIC_MAX_FLOATS);
+        return -1;
+    }
+    float* scratch = nullptr;
+    NNB_TRY(static_scratch(&scratch));
+    // Every partial the second stage reads is written by the first stage of the same call, so the
+    // buffer needs no clearing between calls even though it keeps the previous call's contents.
+    if (dtype == 1)
+        return colsum_accumulate<bf16>(static_cast<const bf16*>(g), ldg, nullptr, nullptr, nullptr, nullptr, 0, out, scratch,
+                                       rows, cols, to_stream(stream));
+    return colsum_accumulate<float>(static_cast<const float*>(g), ldg, nullptr, nullptr, nullptr, nullptr, 0, out, scratch,
+                                    rows, cols, to_stream(stream));
+}
