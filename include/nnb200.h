@@ -140,7 +140,7 @@ int nnb200_bias_grad(const void* g, long long ldg, float* out, float* scratch, i
  * the reference: its CudaBackend allocates op outputs only and offers kernels no workspace, and
  * hosts with a device-memory budget fixed at start-up must not call cudaMalloc).  The partial sums
  * go to a buffer built into the library — NNB200_BIAS_GRAD_STATIC_MAX_FLOATS floats (1 MiB) that
- * each GPU holds from library load to exit; shapes needing more (ceil(rows/256)*cols floats) are
+ * each GPU holds from library load to exit; shapes needing more (ceil(rows/128)*cols floats) are
  * rejected with -1.  Allocates nothing.  The first call on a device looks the buffer's address up;
  * make that call before any stream capture.  All calls on a device share the buffer, so two calls
  * whose kernels may overlap on the GPU (different streams) race: serialise them. */

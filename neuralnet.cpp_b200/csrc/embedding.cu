@@ -92,30 +92,51 @@ __global__ void segment_heads_kernel(const unsigned long long* __restrict__ keys
     flags[i] = (valid && (i == 0 || (keys[i - 1] >> 32) != (k >> 32))) ? 1 : 0;
 }
 
-// one block per sorted position that heads a segment; threads own columns; rows are added in ascending i
+// Work item = (segment head, 128-column slice): a block adds the rows of one token id, in ascending
+// position order, into 128 columns of its destination row.  Threads own columns, so every thread
+// performs the same sequential fp32 sum as the CPU loop; the segment's positions are staged through
+// shared memory and the row loads of 8 positions are issued together, ahead of the ordered adds.
+// Long segments (frequent tokens) are spread over d/128 blocks instead of serialising one block.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 scatter_segments_kernel(float* __restrict__ dst, const unsigned long long* __restrict__ keys, const int* __restrict__ flags,
                         const T* __restrict__ g, int n_pad, int d)
 {
-    for (int h = blockIdx.x; h < n_pad; h += gridDim.x) {
-        if (!flags[h]) continue;
+    __shared__ unsigned spos[256];
+    const int nchunk = (d + 127) / 128;
+    const long long work_total = static_cast<long long>(n_pad) * nchunk;
+    for (long long w = blockIdx.x; w < work_total; w += gridDim.x) {
+        const int h = static_cast<int>(w / nchunk), cc = static_cast<int>(w % nchunk);
+        if (!flags[h]) continue;                                   // block-uniform
         const unsigned id = static_cast<unsigned>(keys[h] >> 32);
-        int end = h + 1;
-        while (end < n_pad && keys[end] != ~0ull && static_cast<unsigned>(keys[end] >> 32) == id) ++end;
-        for (int c = threadIdx.x; c < d; c += blockDim.x) {
-            float acc = dst[static_cast<size_t>(id) * d + c];
-            int p = h;
-            for (; p + 4 <= end; p += 4) {      // independent loads, dependent adds kept in order
-                const float v0 = to_f32(g[static_cast<size_t>(static_cast<unsigned>(keys[p])) * d + c]);
-                const float v1 = to_f32(g[static_cast<size_t>(static_cast<unsigned>(keys[p + 1])) * d + c]);
-                const float v2 = to_f32(g[static_cast<size_t>(static_cast<unsigned>(keys[p + 2])) * d + c]);
-                const float v3 = to_f32(g[static_cast<size_t>(static_cast<unsigned>(keys[p + 3])) * d + c]);
-                acc += v0; acc += v1; acc += v2; acc += v3;
+        const int c = cc * 128 + threadIdx.x;
+        const bool col_ok = c < d;
+        float acc = col_ok ? dst[static_cast<size_t>(id) * d + c] : 0.f;
+        for (int base = h;; base += 256) {
+            __syncthreads();
+            for (int t = threadIdx.x; t < 256; t += 128) {
+                const int pidx = base + t;
+                unsigned v = 0xffffffffu;
+                if (pidx < n_pad) { const unsigned long long k = keys[pidx]; if (k != ~0ull && static_cast<unsigned>(k >> 32) == id) v = static_cast<unsigned>(k); }
+                spos[t] = v;
             }
-            for (; p < end; ++p) acc += to_f32(g[static_cast<size_t>(static_cast<unsigned>(keys[p])) * d + c]);
-            dst[static_cast<size_t>(id) * d + c] = acc;
+            __syncthreads();
+            if (col_ok) {
+                for (int t = 0; t < 256; t += 8) {
+                    if (spos[t] == 0xffffffffu) break;
+                    float v[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const unsigned pz = spos[t + k];
+                        v[k] = (pz != 0xffffffffu) ? to_f32(g[static_cast<size_t>(pz) * d + c]) : 0.f;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) if (spos[t + k] != 0xffffffffu) acc += v[k];
+                }
+            }
+            if (spos[255] == 0xffffffffu) break;                    // segment ended inside this batch (block-uniform)
         }
+        if (col_ok) dst[static_cast<size_t>(id) * d + c] = acc;
     }
 }
 
@@ -178,7 +199,7 @@ int embed_bwd(float* tok_grad, float* pos_grad, const int* tokens, const T* g, v
     }
     segment_heads_kernel<<<blocks, 256, 0, s>>>(keys, n_pad, flags);
     NNB_LAUNCH_CHECK();
-    scatter_segments_kernel<T><<<kSmCount * 8, 256, 0, s>>>(tok_grad, keys, flags, g, n_pad, d);
+    scatter_segments_kernel<T><<<kSmCount * 16, 128, 0, s>>>(tok_grad, keys, flags, g, n_pad, d);
     NNB_LAUNCH_CHECK();
     if (pos_grad) {
         pos_bwd_kernel<T><<<grid_for(static_cast<long long>(seq) * d, 256), 256, 0, s>>>(pos_grad, g, batch, seq, d);

@@ -124,7 +124,7 @@ norm_bwd_dx_kernel(const T* __restrict__ g, const T* __restrict__ x, const float
 //                                                gamma — compute_layer.hpp:789-797, 636-644 — kept)
 // Stage 1 writes per-chunk partials, stage 2 folds them in fixed order and adds into the gradient.
 // ======================================================================================
-constexpr int CS_COLS = 64, CS_ROWLANES = 4, CS_CHUNK_ROWS = 256;
+constexpr int CS_COLS = 64, CS_ROWLANES = 4, CS_CHUNK_ROWS = 128;
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
@@ -152,6 +152,75 @@ colsum_partial_kernel(const T* __restrict__ g, long long ldg, const T* __restric
     __syncthreads();
     if (ty == 0 && c < cols)
         partial[static_cast<size_t>(blockIdx.y) * cols + c] = (red[0][tx] + red[1][tx]) + (red[2][tx] + red[3][tx]);
+}
+
+// Vectorised variant (16-byte loads; needs cols, ldg multiples of the vector width and aligned
+// pointers): a block owns 32 vectors of columns x 8 row lanes over one 128-row chunk.  With
+// `counters` (one zero-initialised int per column block, reset by the kernel after use) the block
+// that finishes last folds all chunk partials in fixed order and adds them into `out`, so the
+// second launch disappears while the summation order stays deterministic.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+colsum_vec_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ x, const float* __restrict__ gamma,
+                  const float* __restrict__ rinv, const float* __restrict__ mean, float* __restrict__ partial,
+                  int* __restrict__ counters, float* __restrict__ out, int rows, int cols, int chunks)
+{
+    constexpr int VN = Vec16<T>::N;
+    constexpr int BW = 32 * VN;                                   // columns per block
+    __shared__ float red[8][BW];
+    __shared__ int is_last;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c0 = (blockIdx.x * 32 + tx) * VN;
+    const int r0 = blockIdx.y * CS_CHUNK_ROWS, r1 = min(rows, r0 + CS_CHUNK_ROWS);
+    float acc[VN];
+#pragma unroll
+    for (int k = 0; k < VN; ++k) acc[k] = 0.f;
+    if (c0 < cols) {
+        float gm[VN];
+#pragma unroll
+        for (int k = 0; k < VN; ++k) gm[k] = (MODE == 1) ? gamma[c0 + k] : 0.f;
+#pragma unroll 4
+        for (int r = r0 + ty; r < r1; r += 8) {
+            const Vec16<T> gv = ld16(g + static_cast<size_t>(r) * ldg + c0);
+            if (MODE == 0) {
+#pragma unroll
+                for (int k = 0; k < VN; ++k) acc[k] += to_f32(gv.v[k]);
+            } else {
+                const Vec16<T> xv = ld16(x + static_cast<size_t>(r) * cols + c0);
+                const float mu = mean ? mean[r] : 0.f, ri = rinv[r];
+#pragma unroll
+                for (int k = 0; k < VN; ++k) acc[k] += to_f32(gv.v[k]) * gm[k] * ((to_f32(xv.v[k]) - mu) * ri);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < VN; ++k) red[ty][tx * VN + k] = acc[k];
+    __syncthreads();
+    for (int j = threadIdx.x; j < BW; j += 256) {
+        const int c = blockIdx.x * BW + j;
+        if (c < cols) {
+            float s = red[0][j];
+#pragma unroll
+            for (int k = 1; k < 8; ++k) s += red[k][j];
+            partial[static_cast<size_t>(blockIdx.y) * cols + c] = s;
+        }
+    }
+    if (!counters) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = (atomicAdd(&counters[blockIdx.x], 1) == chunks - 1);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int j = threadIdx.x; j < BW; j += 256) {
+        const int c = blockIdx.x * BW + j;
+        if (c < cols) {
+            float s = 0.f;
+            for (int k = 0; k < chunks; ++k) s += __ldcg(partial + static_cast<size_t>(k) * cols + c);
+            out[c] += s;
+        }
+    }
+    if (threadIdx.x == 0) counters[blockIdx.x] = 0;
 }
 
 __global__ void colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int chunks, int cols)
@@ -473,14 +542,26 @@ int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rin
 
 template <typename T>
 int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma, const float* rinv, const float* mean,
-                      int mode, float* out, float* scratch, int rows, int cols, cudaStream_t s)
+                      int mode, float* out, float* scratch, int rows, int cols, cudaStream_t s, int* counters)
 {
     if (rows == 0 || cols == 0) return 0;
+    constexpr int VN = Vec16<T>::N;
     const int chunks = static_cast<int>(ceil_div(rows, CS_CHUNK_ROWS));
-    dim3 grid(static_cast<unsigned>(ceil_div(cols, CS_COLS)), chunks);
-    if (mode == 0) colsum_partial_kernel<T, 0><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, rows, cols);
-    else colsum_partial_kernel<T, 1><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, rows, cols);
-    LAUNCH_CHECK();
+    const bool vec = (cols % VN) == 0 && (ldg % VN) == 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0 &&
+                     (mode == 0 || (reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    if (vec) {
+        dim3 grid(static_cast<unsigned>(ceil_div(cols, 32 * VN)), chunks);
+        if (counters && grid.x > 1024) counters = nullptr;        // the counter array holds 1024 entries
+        if (mode == 0) colsum_vec_kernel<T, 0><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks);
+        else colsum_vec_kernel<T, 1><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks);
+        LAUNCH_CHECK();
+        if (counters) return 0;
+    } else {
+        dim3 grid(static_cast<unsigned>(ceil_div(cols, CS_COLS)), chunks);
+        if (mode == 0) colsum_partial_kernel<T, 0><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, rows, cols);
+        else colsum_partial_kernel<T, 1><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, rows, cols);
+        LAUNCH_CHECK();
+    }
     colsum_final_kernel<<<static_cast<unsigned>(ceil_div(cols, 128)), 128, 0, s>>>(scratch, out, chunks, cols);
     LAUNCH_CHECK();
     return 0;
@@ -489,13 +570,13 @@ size_t colsum_scratch_floats(int rows, int cols) { return static_cast<size_t>(ce
 
 template <typename T>
 int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, const float* mean, const T* add, T* dx,
-             float* dgamma, float* dbeta, float* scratch, int rows, int d, bool layer, cudaStream_t s)
+             float* dgamma, float* dbeta, float* scratch, int rows, int d, bool layer, cudaStream_t s, int* counters)
 {
     if (rows == 0) return 0;
     const int grid = grid_for(rows, 8);
     // parameter gradients first: dx may alias g
-    NNB_TRY(colsum_accumulate<T>(g, d, x, gamma, rinv, layer ? mean : nullptr, 1, dgamma, scratch, rows, d, s));
-    if (layer) NNB_TRY(colsum_accumulate<T>(g, d, nullptr, nullptr, nullptr, nullptr, 0, dbeta, scratch, rows, d, s));
+    NNB_TRY(colsum_accumulate<T>(g, d, x, gamma, rinv, layer ? mean : nullptr, 1, dgamma, scratch, rows, d, s, counters));
+    if (layer) NNB_TRY(colsum_accumulate<T>(g, d, nullptr, nullptr, nullptr, nullptr, 0, dbeta, scratch, rows, d, s, counters));
     if (layer) norm_bwd_dx_kernel<T, true><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
     else norm_bwd_dx_kernel<T, false><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
     LAUNCH_CHECK();
@@ -618,9 +699,9 @@ int bf16_to_f32(const bf16* in, float* out, size_t n, cudaStream_t s)
 #define INSTANTIATE(T)                                                                                                 \
     template int norm_fwd<T>(const T*, const float*, const float*, T*, float*, float*, int, int, bool, cudaStream_t);  \
     template int norm_bwd<T>(const T*, const T*, const float*, const float*, const float*, const T*, T*, float*,       \
-                             float*, float*, int, int, bool, cudaStream_t);                                            \
+                             float*, float*, int, int, bool, cudaStream_t, int*);                                      \
     template int colsum_accumulate<T>(const T*, long long, const T*, const float*, const float*, const float*, int,    \
-                                      float*, float*, int, int, cudaStream_t);                                         \
+                                      float*, float*, int, int, cudaStream_t, int*);                                   \
     template int act_fwd<T>(const T*, T*, int, int, bool, cudaStream_t);                                               \
     template int act_bwd<T>(const T*, const T*, T*, int, int, bool, cudaStream_t);                                     \
     template int cross_entropy<T>(T*, const int*, const float*, float, float*, float*, float*, int, int, int,          \

@@ -68,7 +68,7 @@ struct Workspace {
     size_t sin_table, stats, loss, loss_vec;
     std::vector<LayerActs> layers;
     size_t x_final, xnf, rinvf, meanf, logits;
-    size_t g_a, g_b, d_xn, d_h2, d_h1, d_attn, d_qkv, dvec, colsum, embed_scratch;
+    size_t g_a, g_b, d_xn, d_h2, d_h1, d_attn, d_qkv, dvec, colsum, counters, embed_scratch;
     size_t total;
 };
 
@@ -96,6 +96,7 @@ static Workspace make_workspace(const nnb200_gpt_config& c)
     W.dvec = take(static_cast<size_t>(c.batch) * c.heads * c.seq * 4);
     const size_t widest = std::max(std::max(fc1, 3 * d), V);
     W.colsum = take(colsum_scratch_floats(static_cast<int>(N), static_cast<int>(widest)) * 4);
+    W.counters = take(kColsumCounters * sizeof(int));
     W.embed_scratch = take(embed_bwd_scratch_bytes(static_cast<int>(N)));
     W.total = off;
     return W;
@@ -127,8 +128,8 @@ static int linear_bwd_input(const T* dY, const float* Wf, const bf16* Wh, T* dX,
 }
 // dW[out, in] += dY^T X ; db[out] += column sums of dY
 template <typename T>
-static int linear_bwd_params(const T* dY, const T* X, float* dW, float* db, float* scratch, int ntok, int in, int out,
-                             cudaStream_t s)
+static int linear_bwd_params(const T* dY, const T* X, float* dW, float* db, float* scratch, int* counters, int ntok, int in,
+                             int out, cudaStream_t s)
 {
     if (Mode<T>::bf)
         NNB_TRY(gemm_bf16(reinterpret_cast<const bf16*>(dY), reinterpret_cast<const bf16*>(X), dW, out, in, ntok, out, in, in,
@@ -136,7 +137,7 @@ static int linear_bwd_params(const T* dY, const T* X, float* dW, float* db, floa
     else
         NNB_TRY(sgemm_strided(reinterpret_cast<const float*>(dY), reinterpret_cast<const float*>(X), dW, out, in, ntok, 1,
                               out, 1, in, in, 1, 0, 0, 0, 1.0f, nullptr, nullptr, nullptr, 1, s));
-    return colsum_accumulate<T>(dY, out, nullptr, nullptr, nullptr, nullptr, 0, db, scratch, ntok, out, s);
+    return colsum_accumulate<T>(dY, out, nullptr, nullptr, nullptr, nullptr, 0, db, scratch, ntok, out, s, counters);
 }
 
 template <typename T>
@@ -207,37 +208,38 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
     auto GB = [&](long long off) { return off >= 0 ? G + off : nullptr; };
     auto Hh = [&](long long off) { return H ? H + off : nullptr; };
     float* cs = F(W.colsum);
+    int* cn = reinterpret_cast<int*>(ws + W.counters);
 
     // LM head and final norm (GPTModel::backward, compute_layer.hpp:2849-2856)
     T* dlogits = A(W.logits);
-    NNB_TRY(linear_bwd_params<T>(dlogits, A(W.xnf), G + L.lm_w, G + L.lm_b, cs, N, d, c.vocab, s));
+    NNB_TRY(linear_bwd_params<T>(dlogits, A(W.xnf), G + L.lm_w, G + L.lm_b, cs, cn, N, d, c.vocab, s));
     NNB_TRY(linear_bwd_input<T>(dlogits, P + L.lm_w, Hh(L.lm_w), A(W.d_xn), N, d, c.vocab, s));
     T* g = A(W.g_a);
     T* g_other = A(W.g_b);
     NNB_TRY(norm_bwd<T>(A(W.d_xn), A(W.x_final), P + L.lnf_g, F(W.rinvf), F(W.meanf), nullptr, g, G + L.lnf_g, GB(L.lnf_b),
-                        cs, N, d, ln, s));
+                        cs, N, d, ln, s, cn));
 
     for (int l = c.layers - 1; l >= 0; --l) {
         const LayerParams& lp = L.layers[l];
         const LayerActs& a = W.layers[l];
         // FeedForward::backward (compute_layer.hpp:1674-1688)
-        NNB_TRY(linear_bwd_params<T>(g, A(a.h2), G + lp.w2, G + lp.b2, cs, N, ff, d, s));
+        NNB_TRY(linear_bwd_params<T>(g, A(a.h2), G + lp.w2, G + lp.b2, cs, cn, N, ff, d, s));
         NNB_TRY(linear_bwd_input<T>(g, P + lp.w2, Hh(lp.w2), A(W.d_h2), N, ff, d, s));
         NNB_TRY(act_bwd<T>(A(W.d_h2), A(a.h1), A(W.d_h1), N, ff, swiglu, s));
-        NNB_TRY(linear_bwd_params<T>(A(W.d_h1), A(a.xn2), G + lp.w1, G + lp.b1, cs, N, d, fc1, s));
+        NNB_TRY(linear_bwd_params<T>(A(W.d_h1), A(a.xn2), G + lp.w1, G + lp.b1, cs, cn, N, d, fc1, s));
         NNB_TRY(linear_bwd_input<T>(A(W.d_h1), P + lp.w1, Hh(lp.w1), A(W.d_xn), N, d, fc1, s));
         // grad_r1 = grad_output + norm2.backward (GPTBlock::backward, compute_layer.hpp:2388-2404)
         NNB_TRY(norm_bwd<T>(A(W.d_xn), A(a.x_mid), P + lp.g2, F(a.rinv2), F(a.mean2), g, g_other, G + lp.g2, GB(lp.be2), cs,
-                            N, d, ln, s));
+                            N, d, ln, s, cn));
         std::swap(g, g_other);
         // AttentionBase::backward (compute_layer.hpp:1271-1412)
-        NNB_TRY(linear_bwd_params<T>(g, A(a.attn), G + lp.wo, G + lp.bo, cs, N, d, d, s));
+        NNB_TRY(linear_bwd_params<T>(g, A(a.attn), G + lp.wo, G + lp.bo, cs, cn, N, d, d, s));
         NNB_TRY(linear_bwd_input<T>(g, P + lp.wo, Hh(lp.wo), A(W.d_attn), N, d, d, s));
         NNB_TRY(attention_bwd<T>(A(a.qkv), A(a.attn), A(W.d_attn), F(a.lse), F(W.dvec), A(W.d_qkv), doc, c, s));
-        NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, N, d, 3 * d, s));
+        NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, cn, N, d, 3 * d, s));
         NNB_TRY(linear_bwd_input<T>(A(W.d_qkv), P + lp.wqkv, Hh(lp.wqkv), A(W.d_xn), N, d, 3 * d, s));
         NNB_TRY(norm_bwd<T>(A(W.d_xn), A(a.x_in), P + lp.g1, F(a.rinv1), F(a.mean1), g, g_other, G + lp.g1, GB(lp.be1), cs, N,
-                            d, ln, s));
+                            d, ln, s, cn));
         std::swap(g, g_other);
         if (events && events[l]) NNB_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(events[l]), s));
     }
@@ -309,6 +311,9 @@ long long nnb200_gpt_workspace_offset(const nnb200_gpt_config* cfg, int which)
 int nnb200_gpt_init_workspace(const nnb200_gpt_config* cfg, void* workspace, void* stream)
 {
     if (!config_ok(cfg) || !workspace) { fprintf(stderr, "nnb200: invalid GPT configuration or workspace\n"); return -1; }
+    // the column-sum kernels expect their completion counters to start at zero (they reset them after use)
+    NNB_CUDA_CHECK(cudaMemsetAsync(static_cast<uint8_t*>(workspace) + make_workspace(*cfg).counters, 0,
+                                   kColsumCounters * sizeof(int), to_stream(stream)));
     if (cfg->pos != 1) return 0;
     // SinusoidalPositionEncoder (compute_layer.hpp:2604-2622): built on the host with the same
     // float pow/sin/cos calls as the reference, so the table is bit-identical to the CPU engine's

@@ -11,7 +11,7 @@
 
 namespace nnb {
 
-// 1 MiB per GPU.  Enough for e.g. 16384 rows x 4096 columns (64 chunks of 256 rows x 4096).
+// 1 MiB per GPU.  Enough for e.g. 8192 rows x 4096 columns (64 chunks of 128 rows x 4096).
 static __device__ __align__(256) float g_bias_grad_scratch[NNB200_BIAS_GRAD_STATIC_MAX_FLOATS];
 
 constexpr int kMaxDevices = 64;
