@@ -96,6 +96,12 @@ int nnb200_gemm_status(int* host_code)
     NNB_ARG_CHECK(host_code != nullptr, "null output");
     NNB_TRY(gemm_device_error(host_code));
     if (*host_code) NNB_TRY(gemm_clear_device_error());
+    int attn = 0;
+    NNB_TRY(attention_device_error(&attn));                 // reads and clears
+    if (!*host_code && attn) *host_code = attn | 0x40000000;  // bit 30 marks the attention forward kernel
+    int attn_b = 0;
+    NNB_TRY(attention_bwd_device_error(&attn_b));
+    if (!*host_code && attn_b) *host_code = attn_b | 0x20000000;   // bit 29: attention backward kernels
     return 0;
 }
 
@@ -105,6 +111,8 @@ int nnb200_attention_forward(const void* qkv, void* out, float* lse, const int32
     DT_CHECK(dtype);
     cudaStream_t s = to_stream(stream);
     if (dtype == 1) {
+        if (attention_tc_supported(head_dim, seq, heads * head_dim))
+            return attention_fwd_tc(static_cast<const bf16*>(qkv), static_cast<bf16*>(out), lse, doc_ids, batch, seq, heads, head_dim, alibi, s);
         if (attention_mma_supported(head_dim, heads * head_dim))
             return attention_fwd_mma(static_cast<const bf16*>(qkv), static_cast<bf16*>(out), lse, doc_ids, batch, seq, heads, head_dim, alibi, s);
         return attention_fwd_simt<bf16>(static_cast<const bf16*>(qkv), static_cast<bf16*>(out), lse, doc_ids, batch, seq, heads, head_dim, alibi, s);
@@ -119,6 +127,8 @@ int nnb200_attention_backward(const void* qkv, const void* out, const void* dout
     DT_CHECK(dtype);
     cudaStream_t s = to_stream(stream);
     if (dtype == 1) {
+        if (attention_tc_supported(head_dim, seq, heads * head_dim))
+            return attention_bwd_tc(static_cast<const bf16*>(qkv), static_cast<const bf16*>(out), static_cast<const bf16*>(dout), lse, dvec, static_cast<bf16*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);
         if (attention_mma_supported(head_dim, heads * head_dim))
             return attention_bwd_mma(static_cast<const bf16*>(qkv), static_cast<const bf16*>(out), static_cast<const bf16*>(dout), lse, dvec, static_cast<bf16*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);
         return attention_bwd_simt<bf16>(static_cast<const bf16*>(qkv), static_cast<const bf16*>(out), static_cast<const bf16*>(dout), lse, dvec, static_cast<bf16*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);

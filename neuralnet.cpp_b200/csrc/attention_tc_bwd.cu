@@ -1,0 +1,495 @@
+// Attention backward on the 5th-generation tensor cores: two kernels, no atomics.
+//
+//   dQ kernel   CTA = 128 queries, loop over 64-key blocks up to the diagonal:
+//                 S = Q K^T, dP = dO V^T (TMEM, double-buffered) -> workers: P = exp2(S*scale+bias-lse),
+//                 dS = P o (dP - D) as bf16 into a K-major shared tile -> dQ += dS K (TMEM accumulator)
+//   dK/dV kernel CTA = 128 keys, loop over 64-query blocks from the diagonal to the end:
+//                 S^T = K Q^T, dP^T = V dO^T -> workers: P^T, dS^T as bf16 tiles ->
+//                 dV += P^T dO, dK += dS^T Q (TMEM accumulators)
+// Ten warps per CTA: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 workers; worker (row, half)
+// owns one TMEM lane (query resp. key) and 32 of the 64 columns of each block, so workers never
+// synchronise with each other.  K/V resp. Q/dO tiles are consumed both K-major (first MMAs) and
+// MN-major (second MMAs) from the same shared-memory tile.  Recomputing S in both kernels keeps the
+// gradients deterministic (the reference's backward_q / backward_kv split, cpu_engine.hpp:702-915).
+#include <type_traits>
+
+#include "kernels.h"
+#include "tc_ptx.cuh"
+
+namespace nnb {
+
+__device__ int g_attn_bwd_error = 0;
+
+constexpr int BT = 128 * 128;          // bytes of a 128-row x 64-bf16 tile
+constexpr int HT = 64 * 128;           // bytes of a 64-row tile
+constexpr int B_STAGES = 3;
+constexpr float kL2e = 1.4426950408889634f;
+
+struct AttnBwdArgs {
+    bf16* dqkv; const float* lse; const float* dvec; const int* doc;
+    int B, S, H;
+    float scale;
+};
+
+__device__ __forceinline__ float ex2a(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// fp32 accumulate, bf16 operands, M = 128, N = 64; B operand K-major or MN-major
+constexpr uint32_t IDESC_KK = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(64 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+constexpr uint32_t IDESC_KM = IDESC_KK | (1u << 16);
+
+// ======================================================================================
+// dQ
+// ======================================================================================
+// shared memory: Q | dO | ring of (K, V) 64-key tiles | dS (2 buffers) | barriers
+constexpr int DQ_OFF_RING = 2 * BT, DQ_OFF_DS = DQ_OFF_RING + B_STAGES * 2 * HT, DQ_OFF_BAR = DQ_OFF_DS + 2 * BT,
+              DQ_SMEM = DQ_OFF_BAR + 256;
+
+template <bool DOC, bool ALIBI>
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_constant__ CUtensorMap tmKV64,
+                      const __grid_constant__ CUtensorMap tmDO128, const AttnBwdArgs a)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sQ = smem;
+    uint8_t* sDO = smem + BT;
+    uint8_t* sRing = smem + DQ_OFF_RING;           // stage s: K at +s*2*HT, V right after
+    uint8_t* sDS = smem + DQ_OFF_DS;               // buffer b at +b*BT
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DQ_OFF_BAR);
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t q_full = bar0, kv_full0 = bar0 + 8, kv_empty0 = bar0 + 32, sp_full0 = bar0 + 56, sp_empty0 = bar0 + 72,
+                   ds_full0 = bar0 + 88, ds_empty0 = bar0 + 104, done_bar = bar0 + 120;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int d = a.H * 64;
+    const int q0 = qb * 128, nkb = 2 * (qb + 1);   // 64-key blocks up to and including the diagonal
+    const int row_base = b * a.S;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < B_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(sp_full0 + 8 * s, 1); mbar_init(sp_empty0 + 8 * s, 8);
+            mbar_init(ds_full0 + 8 * s, 8); mbar_init(ds_empty0 + 8 * s, 1);
+        }
+        mbar_init(done_bar, 1);
+        *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;
+        if (*abort_flag) atomicCAS(&g_attn_bwd_error, 0, (9 << 16));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // TMEM columns: S buffers at 0 / 64, dP buffers at 128 / 192, dQ accumulator at 256
+    const uint32_t tmem_dQ = tmem_base + 256;
+
+    if (warp == 0) {
+        if (lane == 0 && !*abort_flag) {
+            mbar_expect_tx(q_full, 2 * BT);
+            tma_load_2d(smem_u32(sQ), &tmQ128, q_full, h * 64, row_base + q0);
+            tma_load_2d(smem_u32(sDO), &tmDO128, q_full, h * 64, row_base + q0);
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int st = kb % B_STAGES;
+                if (!mbar_wait(kv_empty0 + 8 * st, ((kb / B_STAGES) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) break;
+                mbar_expect_tx(kv_full0 + 8 * st, 2 * HT);
+                const uint32_t dst = smem_u32(sRing + st * 2 * HT);
+                tma_load_2d(dst, &tmKV64, kv_full0 + 8 * st, d + h * 64, row_base + kb * 64);
+                tma_load_2d(dst + HT, &tmKV64, kv_full0 + 8 * st, 2 * d + h * 64, row_base + kb * 64);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && !*abort_flag) {
+            bool ok = mbar_wait(q_full, 0, abort_flag, 2, &g_attn_bwd_error);
+            const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+            auto issue_sdp = [&](int kb) -> bool {
+                const int st = kb % B_STAGES, sb = kb & 1, u = kb >> 1;
+                if (!mbar_wait(kv_full0 + 8 * st, (kb / B_STAGES) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
+                if (u >= 1 && !mbar_wait(sp_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 4, &g_attn_bwd_error)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(sRing + st * 2 * HT), v_addr = k_addr + HT;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem_base + sb * 64, smem_desc(q_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem_base + 128 + sb * 64, smem_desc(do_addr + k * 32, 16, 1024), smem_desc(v_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
+                umma_commit(sp_full0 + 8 * sb);
+                return true;
+            };
+            auto issue_dq = [&](int kb) -> bool {
+                const int st = kb % B_STAGES, sb = kb & 1;
+                if (!mbar_wait(ds_full0 + 8 * sb, (kb >> 1) & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
+                tc_fence_after();
+                const uint32_t ds_addr = smem_u32(sDS + sb * BT), k_addr = smem_u32(sRing + st * 2 * HT);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem_dQ, smem_desc(ds_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 2048, HT, 1024), IDESC_KM, (kb > 0 || k > 0));
+                umma_commit(ds_empty0 + 8 * sb);
+                umma_commit(kv_empty0 + 8 * st);
+                return true;
+            };
+            if (ok) ok = issue_sdp(0);
+            for (int kb = 0; ok && kb < nkb; ++kb) {
+                if (kb + 1 < nkb) ok = issue_sdp(kb + 1);
+                if (ok) ok = issue_dq(kb);
+            }
+            if (ok) umma_commit(done_bar);
+        }
+    } else {
+        const int q = warp & 3, hf = (warp - 2) >> 2;
+        const int row = q * 32 + lane;
+        const int i = q0 + row;
+        const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+        const float scale2 = a.scale * kL2e;
+        const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kL2e : 0.f;
+        const int my_doc = DOC ? a.doc[row_base + i] : 0;
+        const size_t stat = (static_cast<size_t>(b) * a.H + h) * a.S + i;
+        const float lse2 = a.lse[stat] * kL2e, Dv = a.dvec[stat];
+        const int sw = row & 7;
+        bool ok = !*abort_flag;
+
+        auto block = [&](auto diag_tag, int kb) -> bool {
+            constexpr bool DIAG = decltype(diag_tag)::value;
+            const int sb = kb & 1, u = kb >> 1;
+            if (!mbar_wait(sp_full0 + 8 * sb, u & 1, abort_flag, 6, &g_attn_bwd_error)) return false;
+            tc_fence_after();
+            const int k0 = kb * 64 + hf * 32;                     // first key of this thread's 32 columns
+            uint32_t rs[32], rp[32];
+            tmem_ld32(tmem_base + sb * 64 + lane_addr + hf * 32, rs);
+            tmem_ld32(tmem_base + 128 + sb * 64 + lane_addr + hf * 32, rp);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sp_empty0 + 8 * sb);
+            const int* dk_ptr = DOC ? a.doc + row_base + k0 : nullptr;
+            const float base = (ALIBI ? -slope2 * static_cast<float>(i - k0) : 0.f) - lse2;
+            uint32_t pk[16];
+#pragma unroll
+            for (int cj = 0; cj < 32; cj += 2) {
+                float dsv[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int c = cj + e;
+                    const float t = ALIBI ? fmaf(slope2, static_cast<float>(c), base) : base;
+                    float p = ex2a(fmaf(__uint_as_float(rs[c]), scale2, t));
+                    if (DIAG && k0 + c > i) p = 0.f;
+                    if (DOC && dk_ptr[c] != my_doc) p = 0.f;
+                    dsv[e] = p * (__uint_as_float(rp[c]) - Dv);
+                }
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(dsv[0], dsv[1]);
+                pk[cj >> 1] = *reinterpret_cast<uint32_t*>(&t2);
+            }
+            if (u >= 1 && !mbar_wait(ds_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 7, &g_attn_bwd_error)) return false;
+            uint8_t* drow = sDS + sb * BT + row * 128;
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+                *reinterpret_cast<uint4*>(drow + (((hf * 4 + g) ^ sw) << 4)) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ds_full0 + 8 * sb);
+            return true;
+        };
+        for (int kb = 0; ok && kb < nkb - 2; ++kb) ok = block(std::false_type{}, kb);
+        for (int kb = nkb - 2; ok && kb < nkb; ++kb) ok = block(std::true_type{}, kb);
+        if (ok) ok = mbar_wait(done_bar, 0, abort_flag, 8, &g_attn_bwd_error);
+        if (ok) {
+            tc_fence_after();
+            uint32_t r[32];
+            tmem_ld32(tmem_dQ + lane_addr + hf * 32, r);
+            tmem_ld_wait();
+            bf16* op = a.dqkv + (static_cast<size_t>(row_base) + i) * (3 * d) + h * 64 + hf * 32;
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+                Vec16<bf16> o;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(__uint_as_float(r[c + k]) * a.scale);
+                st16(op + c, o);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ======================================================================================
+// dK, dV
+// ======================================================================================
+// shared memory: K | V | ring of (Q, dO) 64-query tiles | P^T (2) | dS^T (2) | lse, D per stage | barriers
+constexpr int KV_OFF_RING = 2 * BT, KV_OFF_PT = KV_OFF_RING + B_STAGES * 2 * HT, KV_OFF_DST = KV_OFF_PT + 2 * BT,
+              KV_OFF_STAT = KV_OFF_DST + 2 * BT, KV_OFF_BAR = KV_OFF_STAT + B_STAGES * 512, KV_SMEM = KV_OFF_BAR + 256;
+
+template <bool DOC, bool ALIBI>
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid_constant__ CUtensorMap tmQ64,
+                       const __grid_constant__ CUtensorMap tmDO64, const AttnBwdArgs a)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sK = smem;
+    uint8_t* sV = smem + BT;
+    uint8_t* sRing = smem + KV_OFF_RING;           // stage s: Q at +s*2*HT, dO right after
+    uint8_t* sPT = smem + KV_OFF_PT;
+    uint8_t* sDST = smem + KV_OFF_DST;
+    float* sStat = reinterpret_cast<float*>(smem + KV_OFF_STAT);   // [stage][lse(64) | D(64)]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + KV_OFF_BAR);
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t kv_full = bar0, q_full0 = bar0 + 8, q_empty0 = bar0 + 32, sp_full0 = bar0 + 56, sp_empty0 = bar0 + 72,
+                   pd_full0 = bar0 + 88, pd_empty0 = bar0 + 104, done_bar = bar0 + 120;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;   // key tile 0 has the most query blocks: heavy first
+    const int d = a.H * 64;
+    const int k0 = kt * 128;
+    const int qi0 = kt * 2, nit = a.S / 64 - qi0;                  // 64-query blocks from the diagonal to the end
+    const int row_base = b * a.S;
+    const size_t stat_base = (static_cast<size_t>(b) * a.H + h) * a.S;
+
+    if (threadIdx.x == 0) {
+        mbar_init(kv_full, 1);
+        for (int s = 0; s < B_STAGES; ++s) { mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1); }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(sp_full0 + 8 * s, 1); mbar_init(sp_empty0 + 8 * s, 8);
+            mbar_init(pd_full0 + 8 * s, 8); mbar_init(pd_empty0 + 8 * s, 1);
+        }
+        mbar_init(done_bar, 1);
+        *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;
+        if (*abort_flag) atomicCAS(&g_attn_bwd_error, 0, (9 << 16));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // TMEM columns: S^T buffers at 0 / 64, dP^T at 128 / 192, dV at 256, dK at 320
+    const uint32_t tmem_dV = tmem_base + 256, tmem_dK = tmem_base + 320;
+
+    if (warp == 0) {
+        if (lane == 0 && !*abort_flag) {
+            mbar_expect_tx(kv_full, 2 * BT);
+            tma_load_2d(smem_u32(sK), &tmKV128, kv_full, d + h * 64, row_base + k0);
+            tma_load_2d(smem_u32(sV), &tmKV128, kv_full, 2 * d + h * 64, row_base + k0);
+            for (int it = 0; it < nit; ++it) {
+                const int st = it % B_STAGES, qs = (qi0 + it) * 64;
+                if (!mbar_wait(q_empty0 + 8 * st, ((it / B_STAGES) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) break;
+                mbar_expect_tx(q_full0 + 8 * st, 2 * HT + 512);
+                const uint32_t dst = smem_u32(sRing + st * 2 * HT);
+                tma_load_2d(dst, &tmQ64, q_full0 + 8 * st, h * 64, row_base + qs);
+                tma_load_2d(dst + HT, &tmDO64, q_full0 + 8 * st, h * 64, row_base + qs);
+                bulk_load_1d(smem_u32(sStat + st * 128), a.lse + stat_base + qs, 256, q_full0 + 8 * st);
+                bulk_load_1d(smem_u32(sStat + st * 128 + 64), a.dvec + stat_base + qs, 256, q_full0 + 8 * st);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && !*abort_flag) {
+            bool ok = mbar_wait(kv_full, 0, abort_flag, 2, &g_attn_bwd_error);
+            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+            auto issue_st = [&](int it) -> bool {
+                const int st = it % B_STAGES, sb = it & 1, u = it >> 1;
+                if (!mbar_wait(q_full0 + 8 * st, (it / B_STAGES) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
+                if (u >= 1 && !mbar_wait(sp_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 4, &g_attn_bwd_error)) return false;
+                tc_fence_after();
+                const uint32_t q_addr = smem_u32(sRing + st * 2 * HT), do_addr = q_addr + HT;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem_base + sb * 64, smem_desc(k_addr + k * 32, 16, 1024), smem_desc(q_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem_base + 128 + sb * 64, smem_desc(v_addr + k * 32, 16, 1024), smem_desc(do_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
+                umma_commit(sp_full0 + 8 * sb);
+                return true;
+            };
+            auto issue_dkv = [&](int it) -> bool {
+                const int st = it % B_STAGES, sb = it & 1;
+                if (!mbar_wait(pd_full0 + 8 * sb, (it >> 1) & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
+                tc_fence_after();
+                const uint32_t pt_addr = smem_u32(sPT + sb * BT), dst_addr = smem_u32(sDST + sb * BT);
+                const uint32_t q_addr = smem_u32(sRing + st * 2 * HT), do_addr = q_addr + HT;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem_dV, smem_desc(pt_addr + k * 32, 16, 1024), smem_desc(do_addr + k * 2048, HT, 1024), IDESC_KM, (it > 0 || k > 0));
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem_dK, smem_desc(dst_addr + k * 32, 16, 1024), smem_desc(q_addr + k * 2048, HT, 1024), IDESC_KM, (it > 0 || k > 0));
+                umma_commit(pd_empty0 + 8 * sb);
+                umma_commit(q_empty0 + 8 * st);
+                return true;
+            };
+            if (ok) ok = issue_st(0);
+            for (int it = 0; ok && it < nit; ++it) {
+                if (it + 1 < nit) ok = issue_st(it + 1);
+                if (ok) ok = issue_dkv(it);
+            }
+            if (ok) umma_commit(done_bar);
+        }
+    } else {
+        const int q = warp & 3, hf = (warp - 2) >> 2;
+        const int row = q * 32 + lane;
+        const int j = k0 + row;                                   // key position
+        const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+        const float scale2 = a.scale * kL2e;
+        const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kL2e : 0.f;
+        const int my_doc = DOC ? a.doc[row_base + j] : 0;
+        const int sw = row & 7;
+        bool ok = !*abort_flag;
+
+        auto block = [&](auto diag_tag, int it) -> bool {
+            constexpr bool DIAG = decltype(diag_tag)::value;
+            const int st = it % B_STAGES, sb = it & 1, u = it >> 1;
+            if (!mbar_wait(sp_full0 + 8 * sb, u & 1, abort_flag, 6, &g_attn_bwd_error)) return false;
+            tc_fence_after();
+            const int qs = (qi0 + it) * 64 + hf * 32;              // first query of this thread's 32 columns
+            uint32_t rs[32], rp[32];
+            tmem_ld32(tmem_base + sb * 64 + lane_addr + hf * 32, rs);
+            tmem_ld32(tmem_base + 128 + sb * 64 + lane_addr + hf * 32, rp);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sp_empty0 + 8 * sb);
+            const float4* lse4 = reinterpret_cast<const float4*>(sStat + st * 128 + hf * 32);
+            const float4* dv4 = reinterpret_cast<const float4*>(sStat + st * 128 + 64 + hf * 32);
+            const int* dq_ptr = DOC ? a.doc + row_base + qs : nullptr;
+            const float base = ALIBI ? -slope2 * static_cast<float>(qs - j) : 0.f;
+            uint32_t pk[16], dk[16];
+#pragma unroll
+            for (int c4 = 0; c4 < 8; ++c4) {
+                const float4 l4 = lse4[c4], d4 = dv4[c4];
+                const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+                float pv[4], dsv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c = c4 * 4 + e;
+                    const float t = (ALIBI ? fmaf(-slope2, static_cast<float>(c), base) : 0.f) - ls[e] * kL2e;
+                    float p = ex2a(fmaf(__uint_as_float(rs[c]), scale2, t));
+                    if (DIAG && j > qs + c) p = 0.f;
+                    if (DOC && dq_ptr[c] != my_doc) p = 0.f;
+                    pv[e] = p;
+                    dsv[e] = p * (__uint_as_float(rp[c]) - dd[e]);
+                }
+                __nv_bfloat162 t0 = __floats2bfloat162_rn(pv[0], pv[1]), t1 = __floats2bfloat162_rn(pv[2], pv[3]);
+                __nv_bfloat162 u0 = __floats2bfloat162_rn(dsv[0], dsv[1]), u1 = __floats2bfloat162_rn(dsv[2], dsv[3]);
+                pk[c4 * 2] = *reinterpret_cast<uint32_t*>(&t0); pk[c4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&t1);
+                dk[c4 * 2] = *reinterpret_cast<uint32_t*>(&u0); dk[c4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&u1);
+            }
+            if (u >= 1 && !mbar_wait(pd_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 7, &g_attn_bwd_error)) return false;
+            uint8_t* prow = sPT + sb * BT + row * 128;
+            uint8_t* drow = sDST + sb * BT + row * 128;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int off = ((hf * 4 + g) ^ sw) << 4;
+                *reinterpret_cast<uint4*>(prow + off) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                *reinterpret_cast<uint4*>(drow + off) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pd_full0 + 8 * sb);
+            return true;
+        };
+        for (int it = 0; ok && it < 2; ++it) ok = block(std::true_type{}, it);
+        for (int it = 2; ok && it < nit; ++it) ok = block(std::false_type{}, it);
+        if (ok) ok = mbar_wait(done_bar, 0, abort_flag, 8, &g_attn_bwd_error);
+        if (ok) {
+            tc_fence_after();
+            uint32_t rv[32], rk[32];
+            tmem_ld32(tmem_dV + lane_addr + hf * 32, rv);
+            tmem_ld32(tmem_dK + lane_addr + hf * 32, rk);
+            tmem_ld_wait();
+            bf16* kp = a.dqkv + (static_cast<size_t>(row_base) + j) * (3 * d) + d + h * 64 + hf * 32;
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+                Vec16<bf16> ok8, ov8;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    ok8.v[k] = __float2bfloat16_rn(__uint_as_float(rk[c + k]) * a.scale);
+                    ov8.v[k] = __float2bfloat16_rn(__uint_as_float(rv[c + k]));
+                }
+                st16(kp + c, ok8);
+                st16(kp + d + c, ov8);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ======================================================================================
+// host
+// ======================================================================================
+template <bool DOC, bool ALIBI>
+static int launch_bwd_tc(const CUtensorMap& q128, const CUtensorMap& q64, const CUtensorMap& do128, const CUtensorMap& do64,
+                         const AttnBwdArgs& a, dim3 grid, cudaStream_t s)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        NNB_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<DOC, ALIBI>, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM));
+        NNB_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<DOC, ALIBI>, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM));
+        attr_set = true;
+    }
+    attn_bwd_dq_tc_kernel<DOC, ALIBI><<<grid, 320, DQ_SMEM, s>>>(q128, q64, do128, a);
+    NNB_LAUNCH_CHECK();
+    attn_bwd_dkv_tc_kernel<DOC, ALIBI><<<grid, 320, KV_SMEM, s>>>(q128, q64, do64, a);
+    NNB_LAUNCH_CHECK();
+    return 0;
+}
+
+int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const float* lse, float* dvec, bf16* dqkv,
+                     const int* doc, int B, int S, int H, int dk, int alibi, cudaStream_t s)
+{
+    if (static_cast<long long>(B) * S * H == 0) return 0;
+    NNB_ARG_CHECK(attention_tc_supported(dk, S, H * dk), "shape not supported by the tcgen05 attention kernels");
+    NNB_ARG_CHECK(B <= 65535 && H <= 65535, "batch / heads exceed the grid limits");
+    NNB_TRY(attention_dvec_bf16(out, dout, dvec, B, S, H, dk, s));
+    const int d = H * dk;
+    const long long rows = static_cast<long long>(B) * S;
+    CUtensorMap q128, q64, do128, do64;
+    NNB_TRY(tensor_map_2d(qkv, 3LL * d, rows, 3LL * d, 64, 128, &q128, 2));
+    NNB_TRY(tensor_map_2d(qkv, 3LL * d, rows, 3LL * d, 64, 64, &q64, 2));
+    NNB_TRY(tensor_map_2d(dout, d, rows, d, 64, 128, &do128, 2));
+    NNB_TRY(tensor_map_2d(dout, d, rows, d, 64, 64, &do64, 2));
+    AttnBwdArgs a{dqkv, lse, dvec, doc, B, S, H, 1.0f / sqrtf(static_cast<float>(dk))};
+    dim3 grid(S / 128, H, B);
+    if (doc && alibi) return launch_bwd_tc<true, true>(q128, q64, do128, do64, a, grid, s);
+    if (doc) return launch_bwd_tc<true, false>(q128, q64, do128, do64, a, grid, s);
+    if (alibi) return launch_bwd_tc<false, true>(q128, q64, do128, do64, a, grid, s);
+    return launch_bwd_tc<false, false>(q128, q64, do128, do64, a, grid, s);
+}
+
+int attention_bwd_device_error(int* code)
+{
+    NNB_CUDA_CHECK(cudaMemcpyFromSymbol(code, g_attn_bwd_error, sizeof(int)));
+    if (*code) { const int z = 0; NNB_CUDA_CHECK(cudaMemcpyToSymbol(g_attn_bwd_error, &z, sizeof(int))); }
+    return 0;
+}
+
+}  // namespace nnb

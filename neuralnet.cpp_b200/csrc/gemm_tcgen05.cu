@@ -347,8 +347,8 @@ struct MapKeyHash {
 
 // 2-D tensor map (bf16 when esz = 2, fp32 when esz = 4): `inner` contiguous elements per row, `outer`
 // rows `ld` elements apart; 128-byte swizzle
-static int get_tensor_map(const void* ptr, long long inner, long long outer, long long ld, int box_inner, int box_outer,
-                          CUtensorMap* out, int esz = 2)
+int tensor_map_2d(const void* ptr, long long inner, long long outer, long long ld, int box_inner, int box_outer,
+                  CUtensorMap* out, int esz)
 {
     static std::mutex mu;
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
@@ -457,13 +457,13 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
     p.splits = static_cast<int>(ceil_div(p.kb_total, p.kb_per_split));
 
     CUtensorMap ta, tb;
-    if (!a_mn) NNB_TRY(get_tensor_map(A, K, M, lda, BK, BM, &ta));
-    else NNB_TRY(get_tensor_map(A, M, K, lda, 64, BK, &ta));
-    if (!b_mn) NNB_TRY(get_tensor_map(B, K, N, ldb, BK, BN, &tb));
-    else NNB_TRY(get_tensor_map(B, N, K, ldb, 64, BK, &tb));
+    if (!a_mn) NNB_TRY(tensor_map_2d(A, K, M, lda, BK, BM, &ta, 2));
+    else NNB_TRY(tensor_map_2d(A, M, K, lda, 64, BK, &ta, 2));
+    if (!b_mn) NNB_TRY(tensor_map_2d(B, K, N, ldb, BK, BN, &tb, 2));
+    else NNB_TRY(tensor_map_2d(B, N, K, ldb, 64, BK, &tb, 2));
     CUtensorMap tcm = ta;                      // unused placeholder when the direct epilogue runs
     p.tma_store = p.vec_ok;
-    if (p.tma_store) NNB_TRY(get_tensor_map(C, N, M, ldc, c_bf16 ? 64 : 32, BM, &tcm, esz));
+    if (p.tma_store) NNB_TRY(tensor_map_2d(C, N, M, ldc, c_bf16 ? 64 : 32, BM, &tcm, esz));
 
 #define GO(bn, am, bm) return launch_gemm<bn, am, bm>(ta, tb, tcm, p, stream)
     if (BN == 256) {

@@ -145,6 +145,7 @@ static int attention_fwd(const T* qkv, T* out, float* lse, const int* doc, const
 {
     const int dk = c.d_model / c.heads, alibi = c.pos == 2;
     if constexpr (Mode<T>::bf) {
+        if (attention_tc_supported(dk, c.seq, c.d_model)) return attention_fwd_tc(qkv, out, lse, doc, c.batch, c.seq, c.heads, dk, alibi, s);
         if (attention_mma_supported(dk, c.d_model)) return attention_fwd_mma(qkv, out, lse, doc, c.batch, c.seq, c.heads, dk, alibi, s);
     }
     return attention_fwd_simt<T>(qkv, out, lse, doc, c.batch, c.seq, c.heads, dk, alibi, s);
@@ -155,6 +156,8 @@ static int attention_bwd(const T* qkv, const T* out, const T* dout, const float*
 {
     const int dk = c.d_model / c.heads, alibi = c.pos == 2;
     if constexpr (Mode<T>::bf) {
+        if (attention_tc_supported(dk, c.seq, c.d_model))
+            return attention_bwd_tc(qkv, out, dout, lse, dvec, dqkv, doc, c.batch, c.seq, c.heads, dk, alibi, s);
         if (attention_mma_supported(dk, c.d_model))
             return attention_bwd_mma(qkv, out, dout, lse, dvec, dqkv, doc, c.batch, c.seq, c.heads, dk, alibi, s);
     }

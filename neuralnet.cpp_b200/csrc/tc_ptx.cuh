@@ -109,4 +109,8 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
 }
 
 
+// host: cached 2-D tensor map with 128-byte swizzle (esz 2 = bf16, 4 = fp32); defined in gemm_tcgen05.cu
+int tensor_map_2d(const void* ptr, long long inner, long long outer, long long ld, int box_inner, int box_outer,
+                  CUtensorMap* out, int esz);
+
 }  // namespace nnb

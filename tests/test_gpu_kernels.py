@@ -117,7 +117,8 @@ def _attention_reference(q, k, v, dout, B, S, H, dk, alibi, doc):
 @pytest.mark.parametrize("dtype", [0, 1])
 @pytest.mark.parametrize("B,S,H,dk,alibi,docs", [
     (2, 64, 2, 32, 0, False), (2, 128, 2, 64, 1, False), (3, 96, 4, 64, 0, True), (2, 200, 2, 64, 1, True),
-    (2, 24, 4, 8, 0, True), (1, 256, 1, 128, 1, False)])
+    (2, 24, 4, 8, 0, True), (1, 256, 1, 128, 1, False), (2, 512, 3, 64, 1, True), (1, 1024, 2, 64, 0, False),
+    (2, 384, 2, 64, 0, True)])
 def test_attention_forward_backward(g, dtype, B, S, H, dk, alibi, docs):
     import torch
     from oracle import gpt_oracle as go
