@@ -91,6 +91,48 @@ __global__ void attn_dvec_kernel(const T* __restrict__ out, const T* __restrict_
     if (lane == 0) dvec[row] = s;
 }
 
+// Vectorised variant: a warp walks a whole token row (all heads) with 16-byte loads; the lanes that
+// share a head fold their partial dot products with shuffles.  Needs dk a multiple of the vector
+// width with dk/width a power of two <= 32.
+template <typename T>
+__global__ void __launch_bounds__(256)
+attn_dvec_vec_kernel(const T* __restrict__ out, const T* __restrict__ dout, float* __restrict__ dvec, int B, int S,
+                     int H, int dk)
+{
+    constexpr int VN = Vec16<T>::N;
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const int d = H * dk, nvec = d / VN, L = dk / VN;
+    const int nvec_pad = (nvec + 31) & ~31;
+    const long long ntok = static_cast<long long>(B) * S;
+    for (long long t = static_cast<long long>(blockIdx.x) * wpb + (threadIdx.x >> 5); t < ntok; t += static_cast<long long>(gridDim.x) * wpb) {
+        const int b = static_cast<int>(t / S), i = static_cast<int>(t % S);
+        for (int v = lane; v < nvec_pad; v += 32) {
+            float sacc = 0.f;
+            if (v < nvec) {
+                const Vec16<T> ov = ld16(out + t * d + v * VN), gv = ld16(dout + t * d + v * VN);
+#pragma unroll
+                for (int k = 0; k < VN; ++k) sacc += to_f32(ov.v[k]) * to_f32(gv.v[k]);
+            }
+            for (int off = L >> 1; off > 0; off >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, off);
+            if (v < nvec && (lane & (L - 1)) == 0) dvec[(static_cast<size_t>(b) * H + v / L) * S + i] = sacc;
+        }
+    }
+}
+
+template <typename T>
+static int launch_dvec(const T* out, const T* dout, float* dvec, int B, int S, int H, int dk, cudaStream_t s)
+{
+    constexpr int VN = Vec16<T>::N;
+    const long long rows = static_cast<long long>(B) * H * S;
+    const int L = dk / VN;
+    const bool vec = (dk % VN) == 0 && L >= 1 && L <= 32 && (L & (L - 1)) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout)) & 15) == 0;
+    if (vec) attn_dvec_vec_kernel<T><<<grid_for(static_cast<long long>(B) * S, 8), 256, 0, s>>>(out, dout, dvec, B, S, H, dk);
+    else attn_dvec_kernel<T><<<static_cast<unsigned>(ceil_div(rows * 32, 256)), 256, 0, s>>>(out, dout, dvec, B, S, H, dk);
+    NNB_LAUNCH_CHECK();
+    return 0;
+}
+
 // dQ: one warp per query row, lanes over keys
 template <typename T, int DK>
 __global__ void __launch_bounds__(128)
@@ -194,8 +236,7 @@ static int bwd_dk(const T* qkv, const T* out, const T* dout, const float* lse, f
 {
     const long long rows = static_cast<long long>(B) * H * S;
     const float scale = 1.0f / sqrtf(static_cast<float>(DK));
-    attn_dvec_kernel<T><<<static_cast<unsigned>(ceil_div(rows * 32, 256)), 256, 0, s>>>(out, dout, dvec, B, S, H, DK);
-    NNB_LAUNCH_CHECK();
+    NNB_TRY(launch_dvec<T>(out, dout, dvec, B, S, H, DK, s));
     const unsigned grid = static_cast<unsigned>(ceil_div(rows, 4));
     attn_bwd_dq_simt_kernel<T, DK><<<grid, 128, 0, s>>>(qkv, dout, lse, dvec, dqkv, doc, B, S, H, alibi, scale);
     NNB_LAUNCH_CHECK();
@@ -231,10 +272,7 @@ int attention_bwd_simt(const T* qkv, const T* out, const T* dout, const float* l
 
 int attention_dvec_bf16(const bf16* out, const bf16* dout, float* dvec, int B, int S, int H, int dk, cudaStream_t s)
 {
-    const long long rows = static_cast<long long>(B) * H * S;
-    attn_dvec_kernel<bf16><<<static_cast<unsigned>(ceil_div(rows * 32, 256)), 256, 0, s>>>(out, dout, dvec, B, S, H, dk);
-    NNB_LAUNCH_CHECK();
-    return 0;
+    return launch_dvec<bf16>(out, dout, dvec, B, S, H, dk, s);
 }
 
 template int attention_fwd_simt<float>(const float*, float*, float*, const int*, int, int, int, int, int, cudaStream_t);

@@ -95,7 +95,7 @@ __global__ void segment_heads_kernel(const unsigned long long* __restrict__ keys
 // Work item = (segment head, 128-column slice): a block adds the rows of one token id, in ascending
 // position order, into 128 columns of its destination row.  Threads own columns, so every thread
 // performs the same sequential fp32 sum as the CPU loop; the segment's positions are staged through
-// shared memory and the row loads of 8 positions are issued together, ahead of the ordered adds.
+// shared memory and the row loads of 32 positions are issued together, ahead of the ordered adds.
 // Long segments (frequent tokens) are spread over d/128 blocks instead of serialising one block.
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -122,16 +122,16 @@ scatter_segments_kernel(float* __restrict__ dst, const unsigned long long* __res
             }
             __syncthreads();
             if (col_ok) {
-                for (int t = 0; t < 256; t += 8) {
+                for (int t = 0; t < 256; t += 32) {
                     if (spos[t] == 0xffffffffu) break;
-                    float v[8];
+                    float v[32];
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
+                    for (int k = 0; k < 32; ++k) {
                         const unsigned pz = spos[t + k];
                         v[k] = (pz != 0xffffffffu) ? to_f32(g[static_cast<size_t>(pz) * d + c]) : 0.f;
                     }
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) if (spos[t + k] != 0xffffffffu) acc += v[k];
+                    for (int k = 0; k < 32; ++k) if (spos[t + k] != 0xffffffffu) acc += v[k];
                 }
             }
             if (spos[255] == 0xffffffffu) break;                    // segment ended inside this batch (block-uniform)

@@ -117,6 +117,109 @@ norm_bwd_dx_kernel(const T* __restrict__ g, const T* __restrict__ x, const float
     }
 }
 
+// Register-resident variants for d == 32 * NV * (elements per 16 bytes): a lane keeps its NV vectors of
+// the row and of gamma/beta in registers, so every activation is read once and the parameters once per warp.
+template <typename T, bool LAYER, int NV>
+__global__ void __launch_bounds__(256)
+norm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                    T* __restrict__ y, float* __restrict__ rinv_out, float* __restrict__ mean_out, int rows)
+{
+    constexpr int VN = Vec16<T>::N, D = 32 * NV * VN;
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    float gm[NV][VN], bt[NV][VN];
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+#pragma unroll
+        for (int k = 0; k < VN; ++k) {
+            const int c = (v * 32 + lane) * VN + k;
+            gm[v][k] = gamma[c];
+            bt[v][k] = LAYER ? beta[c] : 0.f;
+        }
+    const float inv_d = 1.0f / static_cast<float>(D);
+    for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
+        const T* xr = x + static_cast<size_t>(r) * D;
+        float xv[NV][VN];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) { const Vec16<T> t = ld16(xr + (v * 32 + lane) * VN);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) xv[v][k] = to_f32(t.v[k]); }
+        float mean = 0.f;
+        if (LAYER) {
+            float sm = 0.f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+                for (int k = 0; k < VN; ++k) sm += xv[v][k];
+            mean = warp_sum(sm) * inv_d;
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+            for (int k = 0; k < VN; ++k) { const float t = xv[v][k] - mean; ss += t * t; }
+        const float rinv = 1.0f / sqrtf(warp_sum(ss) * inv_d + kNormEps);
+        if (lane == 0) { rinv_out[r] = rinv; if (LAYER) mean_out[r] = mean; }
+        T* yr = y + static_cast<size_t>(r) * D;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            Vec16<T> o;
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                float n = (xv[v][k] - mean) * rinv * gm[v][k];
+                if (LAYER) n += bt[v][k];
+                o.v[k] = from_f32<T>(n);
+            }
+            st16(yr + (v * 32 + lane) * VN, o);
+        }
+    }
+}
+
+template <typename T, bool LAYER, int NV>
+__global__ void __launch_bounds__(256)
+norm_bwd_dx_reg_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ gamma,
+                       const float* __restrict__ rinv_in, const float* __restrict__ mean_in, const T* __restrict__ add,
+                       T* __restrict__ dx, int rows)
+{
+    constexpr int VN = Vec16<T>::N, D = 32 * NV * VN;
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    float gm[NV][VN];
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+#pragma unroll
+        for (int k = 0; k < VN; ++k) gm[v][k] = gamma[(v * 32 + lane) * VN + k];
+    const float inv_d = 1.0f / static_cast<float>(D);
+    for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
+        const size_t off = static_cast<size_t>(r) * D;
+        const float rinv = rinv_in[r], mean = LAYER ? mean_in[r] : 0.f;
+        float gg[NV][VN], nn[NV][VN];
+        float s_g = 0.f, s_gn = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const Vec16<T> gv = ld16(g + off + (v * 32 + lane) * VN), xv = ld16(x + off + (v * 32 + lane) * VN);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                gg[v][k] = to_f32(gv.v[k]) * gm[v][k];
+                nn[v][k] = (to_f32(xv.v[k]) - mean) * rinv;
+                s_g += gg[v][k]; s_gn += gg[v][k] * nn[v][k];
+            }
+        }
+        const float m_gn = warp_sum(s_gn) * inv_d;
+        const float m_g = LAYER ? warp_sum(s_g) * inv_d : 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            Vec16<T> o, av;
+            if (add) av = ld16(add + off + (v * 32 + lane) * VN);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                float t = (gg[v][k] - m_g - nn[v][k] * m_gn) * rinv;
+                if (add) t += to_f32(av.v[k]);
+                o.v[k] = from_f32<T>(t);
+            }
+            st16(dx + off + (v * 32 + lane) * VN, o);
+        }
+    }
+}
+
 // ======================================================================================
 // column sums over tokens (parameter gradients that reduce over the token dimension)
 //   MODE 0: sum_r g[r][c]                       (bias and LayerNorm-beta gradients)
@@ -179,7 +282,7 @@ colsum_vec_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ 
         float gm[VN];
 #pragma unroll
         for (int k = 0; k < VN; ++k) gm[k] = (MODE == 1) ? gamma[c0 + k] : 0.f;
-#pragma unroll 4
+#pragma unroll 8
         for (int r = r0 + ty; r < r1; r += 8) {
             const Vec16<T> gv = ld16(g + static_cast<size_t>(r) * ldg + c0);
             if (MODE == 0) {
@@ -212,12 +315,31 @@ colsum_vec_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ 
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int j = threadIdx.x; j < BW; j += 256) {
-        const int c = blockIdx.x * BW + j;
-        if (c < cols) {
-            float s = 0.f;
-            for (int k = 0; k < chunks; ++k) s += __ldcg(partial + static_cast<size_t>(k) * cols + c);
-            out[c] += s;
+    // final fold by the last block: 4 chunk groups x (BW/4) float4 columns, 8 loads in flight per
+    // thread; group g sums chunks g, g+4, ... in order and the groups are combined in fixed order
+    constexpr int QW = BW / 4;                                    // float4 columns per block
+    float4* red4 = reinterpret_cast<float4*>(&red[0][0]);        // reuse: 8*BW floats >= 4*QW float4
+    for (int j0 = 0; j0 < QW; j0 += 64) {
+        const int jq = j0 + (threadIdx.x & 63), grp = threadIdx.x >> 6;
+        const int c = blockIdx.x * BW + jq * 4;
+        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (jq < QW && c < cols) {
+#pragma unroll 8
+            for (int k = grp; k < chunks; k += 4) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(partial + static_cast<size_t>(k) * cols + c));
+                s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+            }
+        }
+        __syncthreads();
+        red4[grp * 64 + (threadIdx.x & 63)] = s4;
+        __syncthreads();
+        if (grp == 0 && jq < QW && c < cols) {
+            float4 t = red4[threadIdx.x & 63];
+#pragma unroll
+            for (int gq = 1; gq < 4; ++gq) { const float4 v = red4[gq * 64 + (threadIdx.x & 63)]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+            float4 o = *reinterpret_cast<float4*>(out + c);
+            o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
+            *reinterpret_cast<float4*>(out + c) = o;
         }
     }
     if (threadIdx.x == 0) counters[blockIdx.x] = 0;
@@ -534,6 +656,17 @@ int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rin
 {
     if (rows == 0) return 0;
     const int grid = grid_for(rows, 8);
+    constexpr int VN = Vec16<T>::N;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+#define NNB_NORM_FWD_REG(nv)                                                                                          \
+    if (aligned && d == 32 * VN * nv) {                                                                               \
+        if (layer) norm_fwd_reg_kernel<T, true, nv><<<grid, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows);         \
+        else norm_fwd_reg_kernel<T, false, nv><<<grid, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows);              \
+        LAUNCH_CHECK();                                                                                               \
+        return 0;                                                                                                     \
+    }
+    NNB_NORM_FWD_REG(1) NNB_NORM_FWD_REG(2) NNB_NORM_FWD_REG(3) NNB_NORM_FWD_REG(4)
+#undef NNB_NORM_FWD_REG
     if (layer) norm_fwd_kernel<T, true><<<grid, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows, d);
     else norm_fwd_kernel<T, false><<<grid, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows, d);
     LAUNCH_CHECK();
@@ -577,6 +710,18 @@ int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, cons
     // parameter gradients first: dx may alias g
     NNB_TRY(colsum_accumulate<T>(g, d, x, gamma, rinv, layer ? mean : nullptr, 1, dgamma, scratch, rows, d, s, counters));
     if (layer) NNB_TRY(colsum_accumulate<T>(g, d, nullptr, nullptr, nullptr, nullptr, 0, dbeta, scratch, rows, d, s, counters));
+    constexpr int VN = Vec16<T>::N;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) |
+                           reinterpret_cast<uintptr_t>(add)) & 15) == 0;
+#define NNB_NORM_BWD_REG(nv)                                                                                          \
+    if (aligned && d == 32 * VN * nv) {                                                                               \
+        if (layer) norm_bwd_dx_reg_kernel<T, true, nv><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows);   \
+        else norm_bwd_dx_reg_kernel<T, false, nv><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows);        \
+        LAUNCH_CHECK();                                                                                               \
+        return 0;                                                                                                     \
+    }
+    NNB_NORM_BWD_REG(1) NNB_NORM_BWD_REG(2) NNB_NORM_BWD_REG(3) NNB_NORM_BWD_REG(4)
+#undef NNB_NORM_BWD_REG
     if (layer) norm_bwd_dx_kernel<T, true><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
     else norm_bwd_dx_kernel<T, false><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
     LAUNCH_CHECK();
