@@ -70,7 +70,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             pass
@@ -196,7 +196,7 @@ def main():
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
         pg = dist.group.WORLD
     w = WORKLOAD
-    K, W = max(1, args.steps), max(3, args.warmup)
+    K, W = max(1, args.steps), max(int(os.environ.get("NNB200_BENCH_MIN_WARMUP", "3")), args.warmup)   # the override is for profiling captures only
     cfg = nnb.GptConfig(w["vocab"], w["d_model"], w["heads"], w["layers"], w["d_ff"], w["seq"], w["batch"],
                         nnb.ACT_SWIGLU, nnb.NORM_RMS, nnb.POS_ALIBI, nnb.BF16)
     tr = nnb.GptTrainer(cfg, lr=BASE_LR, weight_decay=WEIGHT_DECAY, process_group=pg)
@@ -249,11 +249,13 @@ def main():
             torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
         return float(ms.item()), last
 
+    # the sampler starts before the warm-up (nvidia-smi needs a moment before its first sample); samples taken
+    # while the SMs idle are filtered out in ClockSampler.stop
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     for s in range(W):
         run_step(s, True)
     torch.cuda.synchronize()
     nnb.call("nnb200_launch_count", 1)
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     ms_resident, _ = timed(True, W)
     launches = int(nnb.call("nnb200_launch_count", 1))
     clocks = sampler.stop() if sampler else None
@@ -303,6 +305,8 @@ def main():
             line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "reference",
                                     "sample": f"not run: {e}"[:200]}
     print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
     return 0
 
 

@@ -15,6 +15,12 @@ constexpr float kNormEps = 1e-5f;     // compute_layer.hpp:495,687
 constexpr float kGeluBeta = 1.702f;   // compute_layer.hpp:259
 
 __device__ __forceinline__ float sigmoidf_ref(float x) { return 1.0f / (1.0f + expf(-x)); }
+// bf16 mode rounds every activation to 8 mantissa bits anyway: use the fast exp / reciprocal there
+template <typename T> __device__ __forceinline__ float sigmoid_t(float x)
+{
+    if constexpr (sizeof(T) == 2) return __frcp_rn(1.0f + __expf(-x));
+    else return sigmoidf_ref(x);
+}
 
 // ======================================================================================
 // normalisation: one warp per token row
@@ -220,6 +226,122 @@ norm_bwd_dx_reg_kernel(const T* __restrict__ g, const T* __restrict__ x, const f
     }
 }
 
+// norm backward with its parameter gradients fused in.  A lane owns the same columns for every row
+// its warp visits, so  dgamma += sum g*gamma*n,  dbeta += sum g  and (optionally) the column sums
+// of the produced dx — the bias gradient of the Linear layer that fed this point — accumulate in
+// registers.  Warps fold through shared memory, blocks write partials, and the block that finishes
+// last adds the partials up in fixed order: deterministic, no extra pass over the activations.
+constexpr int kNormFusedBlocks = 296;   // two per SM
+
+template <typename T, bool LAYER, int NV>
+__global__ void __launch_bounds__(256, 2)
+norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ gamma,
+                      const float* __restrict__ rinv_in, const float* __restrict__ mean_in, const T* __restrict__ add,
+                      T* __restrict__ dx, float* __restrict__ partial, int* __restrict__ counter,
+                      float* __restrict__ dgamma, float* __restrict__ dbeta, float* __restrict__ osum, int rows)
+{
+    constexpr int VN = Vec16<T>::N, D = 32 * NV * VN, NQ = 3;
+    __shared__ float red[8][D];
+    __shared__ int is_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    float gm[NV][VN], a_dg[NV][VN], a_db[NV][VN], a_os[NV][VN];
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+#pragma unroll
+        for (int k = 0; k < VN; ++k) { gm[v][k] = gamma[(v * 32 + lane) * VN + k]; a_dg[v][k] = 0.f; a_db[v][k] = 0.f; a_os[v][k] = 0.f; }
+    const float inv_d = 1.0f / static_cast<float>(D);
+    for (int r = blockIdx.x * wpb + warp; r < rows; r += gridDim.x * wpb) {
+        const size_t off = static_cast<size_t>(r) * D;
+        const float rinv = rinv_in[r], mean = LAYER ? mean_in[r] : 0.f;
+        float gg[NV][VN], nn[NV][VN];
+        float s_g = 0.f, s_gn = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const Vec16<T> gv = ld16(g + off + (v * 32 + lane) * VN), xv = ld16(x + off + (v * 32 + lane) * VN);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                const float graw = to_f32(gv.v[k]);
+                gg[v][k] = graw * gm[v][k];
+                nn[v][k] = (to_f32(xv.v[k]) - mean) * rinv;
+                s_g += gg[v][k]; s_gn += gg[v][k] * nn[v][k];
+                a_dg[v][k] += gg[v][k] * nn[v][k];
+                if (LAYER) a_db[v][k] += graw;
+            }
+        }
+        const float m_gn = warp_sum(s_gn) * inv_d;
+        const float m_g = LAYER ? warp_sum(s_g) * inv_d : 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            Vec16<T> o, av;
+            if (add) av = ld16(add + off + (v * 32 + lane) * VN);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                float t = (gg[v][k] - m_g - nn[v][k] * m_gn) * rinv;
+                if (add) t += to_f32(av.v[k]);
+                o.v[k] = from_f32<T>(t);
+                a_os[v][k] += to_f32(o.v[k]);             // the rounded value: what the next kernel reads
+            }
+            st16(dx + off + (v * 32 + lane) * VN, o);
+        }
+    }
+    // block fold, one quantity at a time, then this block's partial row
+    const size_t pstride = static_cast<size_t>(gridDim.x) * D;
+#pragma unroll 1
+    for (int qn = 0; qn < NQ; ++qn) {
+        if ((qn == 1 && !LAYER) || (qn == 2 && !osum)) continue;
+        __syncthreads();
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+            for (int k = 0; k < VN; ++k)
+                red[warp][(v * 32 + lane) * VN + k] = qn == 0 ? a_dg[v][k] : (qn == 1 ? a_db[v][k] : a_os[v][k]);
+        __syncthreads();
+        for (int c = threadIdx.x; c < D; c += 256) {
+            float sacc = red[0][c];
+#pragma unroll
+            for (int w = 1; w < 8; ++w) sacc += red[w][c];
+            partial[qn * pstride + static_cast<size_t>(blockIdx.x) * D + c] = sacc;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = (atomicAdd(counter, 1) == static_cast<int>(gridDim.x) - 1);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    float4* red4 = reinterpret_cast<float4*>(&red[0][0]);
+    const int nb = gridDim.x;
+#pragma unroll 1
+    for (int qn = 0; qn < NQ; ++qn) {
+        if ((qn == 1 && !LAYER) || (qn == 2 && !osum)) continue;
+        float* dst = qn == 0 ? dgamma : (qn == 1 ? dbeta : osum);
+        const float* src = partial + qn * pstride;
+        for (int j0 = 0; j0 < D / 4; j0 += 64) {
+            const int jq = j0 + (threadIdx.x & 63), grp = threadIdx.x >> 6;
+            float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (jq < D / 4) {
+#pragma unroll 8
+                for (int k = grp; k < nb; k += 4) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * D + jq * 4));
+                    s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+                }
+            }
+            __syncthreads();
+            red4[grp * 64 + (threadIdx.x & 63)] = s4;
+            __syncthreads();
+            if (grp == 0 && jq < D / 4) {
+                float4 t = red4[threadIdx.x & 63];
+#pragma unroll
+                for (int gq = 1; gq < 4; ++gq) { const float4 v = red4[gq * 64 + (threadIdx.x & 63)]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+                float4 o = *reinterpret_cast<float4*>(dst + jq * 4);
+                o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
+                *reinterpret_cast<float4*>(dst + jq * 4) = o;
+            }
+        }
+    }
+    if (threadIdx.x == 0) *counter = 0;
+}
+
 // ======================================================================================
 // column sums over tokens (parameter gradients that reduce over the token dimension)
 //   MODE 0: sum_r g[r][c]                       (bias and LayerNorm-beta gradients)
@@ -363,7 +485,7 @@ __global__ void gelu_fwd_kernel(const T* __restrict__ h1, T* __restrict__ h2, si
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const float x = to_f32(h1[i]);
-        h2[i] = from_f32<T>(x * sigmoidf_ref(kGeluBeta * x));
+        h2[i] = from_f32<T>(x * sigmoid_t<T>(kGeluBeta * x));
     }
 }
 template <typename T>
@@ -372,7 +494,7 @@ __global__ void gelu_bwd_kernel(const T* __restrict__ g, const T* __restrict__ h
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const float x = to_f32(h1[i]);
-        const float s = sigmoidf_ref(kGeluBeta * x);
+        const float s = sigmoid_t<T>(kGeluBeta * x);
         out[i] = from_f32<T>(to_f32(g[i]) * (s * (1.0f + (kGeluBeta * x) * (1.0f - s))));
     }
 }
@@ -392,7 +514,7 @@ __global__ void swiglu_fwd_kernel(const T* __restrict__ h1, T* __restrict__ h2, 
 #pragma unroll
             for (int k = 0; k < VN; ++k) {
                 const float gt = to_f32(gv.v[k]);
-                o.v[k] = from_f32<T>(gt * sigmoidf_ref(gt) * to_f32(uv.v[k]));
+                o.v[k] = from_f32<T>(gt * sigmoid_t<T>(gt) * to_f32(uv.v[k]));
             }
             st16(h2 + r * ff + c, o);
         }
@@ -402,7 +524,7 @@ __global__ void swiglu_fwd_kernel(const T* __restrict__ h1, T* __restrict__ h2, 
              i += static_cast<size_t>(gridDim.x) * blockDim.x) {
             const size_t r = i / ff; const int c = static_cast<int>(i % ff);
             const float gt = to_f32(h1[r * 2 * ff + c]);
-            h2[i] = from_f32<T>(gt * sigmoidf_ref(gt) * to_f32(h1[r * 2 * ff + ff + c]));
+            h2[i] = from_f32<T>(gt * sigmoid_t<T>(gt) * to_f32(h1[r * 2 * ff + ff + c]));
         }
     }
 }
@@ -423,7 +545,7 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ g, const T* __restrict__
 #pragma unroll
             for (int k = 0; k < VN; ++k) {
                 const float go = to_f32(gv.v[k]), gt = to_f32(gtv.v[k]), up = to_f32(uv.v[k]);
-                const float s = sigmoidf_ref(gt);
+                const float s = sigmoid_t<T>(gt);
                 og.v[k] = from_f32<T>(go * up * (s * (1.0f + gt * (1.0f - s))));
                 ou.v[k] = from_f32<T>(go * gt * s);
             }
@@ -436,7 +558,7 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ g, const T* __restrict__
              i += static_cast<size_t>(gridDim.x) * blockDim.x) {
             const size_t r = i / ff; const int c = static_cast<int>(i % ff);
             const float go = to_f32(g[i]), gt = to_f32(h1[r * 2 * ff + c]), up = to_f32(h1[r * 2 * ff + ff + c]);
-            const float s = sigmoidf_ref(gt);
+            const float s = sigmoid_t<T>(gt);
             dh1[r * 2 * ff + c] = from_f32<T>(go * up * (s * (1.0f + gt * (1.0f - s))));
             dh1[r * 2 * ff + ff + c] = from_f32<T>(go * gt * s);
         }
@@ -684,7 +806,7 @@ int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma,
                      (mode == 0 || (reinterpret_cast<uintptr_t>(x) & 15) == 0);
     if (vec) {
         dim3 grid(static_cast<unsigned>(ceil_div(cols, 32 * VN)), chunks);
-        if (counters && grid.x > 1024) counters = nullptr;        // the counter array holds 1024 entries
+        if (counters && grid.x > 1000) counters = nullptr;        // the counter array holds 1024 entries (the last is the norm kernel's)
         if (mode == 0) colsum_vec_kernel<T, 0><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks);
         else colsum_vec_kernel<T, 1><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks);
         LAUNCH_CHECK();
@@ -701,30 +823,55 @@ int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma,
 }
 size_t colsum_scratch_floats(int rows, int cols) { return static_cast<size_t>(ceil_div(rows, CS_CHUNK_ROWS)) * cols; }
 
+size_t norm_bwd_scratch_floats(int rows, int d)
+{
+    const size_t a = colsum_scratch_floats(rows, d), b = static_cast<size_t>(3) * kNormFusedBlocks * d;
+    return a > b ? a : b;
+}
+
 template <typename T>
 int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, const float* mean, const T* add, T* dx,
-             float* dgamma, float* dbeta, float* scratch, int rows, int d, bool layer, cudaStream_t s, int* counters)
+             float* dgamma, float* dbeta, float* scratch, int rows, int d, bool layer, cudaStream_t s, int* counters,
+             float* out_colsum)
 {
     if (rows == 0) return 0;
     const int grid = grid_for(rows, 8);
-    // parameter gradients first: dx may alias g
-    NNB_TRY(colsum_accumulate<T>(g, d, x, gamma, rinv, layer ? mean : nullptr, 1, dgamma, scratch, rows, d, s, counters));
-    if (layer) NNB_TRY(colsum_accumulate<T>(g, d, nullptr, nullptr, nullptr, nullptr, 0, dbeta, scratch, rows, d, s, counters));
     constexpr int VN = Vec16<T>::N;
     const bool aligned = ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) |
                            reinterpret_cast<uintptr_t>(add)) & 15) == 0;
-#define NNB_NORM_BWD_REG(nv)                                                                                          \
-    if (aligned && d == 32 * VN * nv) {                                                                               \
-        if (layer) norm_bwd_dx_reg_kernel<T, true, nv><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows);   \
-        else norm_bwd_dx_reg_kernel<T, false, nv><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows);        \
+    const bool out_ok = ((reinterpret_cast<uintptr_t>(dgamma) | reinterpret_cast<uintptr_t>(dbeta) |
+                          reinterpret_cast<uintptr_t>(out_colsum)) & 15) == 0;
+    // fused path: needs the caller's zero-initialised completion counter and norm_bwd_scratch_floats of scratch
+#define NNB_NORM_BWD_FUSED(nv)                                                                                        \
+    if (counters && aligned && out_ok && d == 32 * VN * nv) {                                                         \
+        if (layer) norm_bwd_fused_kernel<T, true, nv><<<kNormFusedBlocks, 256, 0, s>>>(                                \
+            g, x, gamma, rinv, mean, add, dx, scratch, counters + kColsumCounters - 1, dgamma, dbeta, out_colsum, rows); \
+        else norm_bwd_fused_kernel<T, false, nv><<<kNormFusedBlocks, 256, 0, s>>>(                                     \
+            g, x, gamma, rinv, mean, add, dx, scratch, counters + kColsumCounters - 1, dgamma, dbeta, out_colsum, rows); \
         LAUNCH_CHECK();                                                                                               \
         return 0;                                                                                                     \
     }
+    NNB_NORM_BWD_FUSED(1) NNB_NORM_BWD_FUSED(2) NNB_NORM_BWD_FUSED(3) NNB_NORM_BWD_FUSED(4)
+#undef NNB_NORM_BWD_FUSED
+    // parameter gradients first: dx may alias g
+    NNB_TRY(colsum_accumulate<T>(g, d, x, gamma, rinv, layer ? mean : nullptr, 1, dgamma, scratch, rows, d, s, counters));
+    if (layer) NNB_TRY(colsum_accumulate<T>(g, d, nullptr, nullptr, nullptr, nullptr, 0, dbeta, scratch, rows, d, s, counters));
+    bool done = false;
+#define NNB_NORM_BWD_REG(nv)                                                                                          \
+    if (!done && aligned && d == 32 * VN * nv) {                                                                      \
+        if (layer) norm_bwd_dx_reg_kernel<T, true, nv><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows);   \
+        else norm_bwd_dx_reg_kernel<T, false, nv><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows);        \
+        LAUNCH_CHECK();                                                                                               \
+        done = true;                                                                                                  \
+    }
     NNB_NORM_BWD_REG(1) NNB_NORM_BWD_REG(2) NNB_NORM_BWD_REG(3) NNB_NORM_BWD_REG(4)
 #undef NNB_NORM_BWD_REG
-    if (layer) norm_bwd_dx_kernel<T, true><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
-    else norm_bwd_dx_kernel<T, false><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
-    LAUNCH_CHECK();
+    if (!done) {
+        if (layer) norm_bwd_dx_kernel<T, true><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
+        else norm_bwd_dx_kernel<T, false><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
+        LAUNCH_CHECK();
+    }
+    if (out_colsum) NNB_TRY(colsum_accumulate<T>(dx, d, nullptr, nullptr, nullptr, nullptr, 0, out_colsum, scratch, rows, d, s, counters));
     return 0;
 }
 
@@ -739,16 +886,19 @@ int act_fwd(const T* h1, T* h2, int rows, int ff, bool swiglu, cudaStream_t s)
     return 0;
 }
 template <typename T>
-int act_bwd(const T* g, const T* h1, T* dh1, int rows, int ff, bool swiglu, cudaStream_t s)
+int act_bwd(const T* g, const T* h1, T* dh1, int rows, int ff, bool swiglu, cudaStream_t s, float* dbias, float* scratch,
+            int* counters)
 {
     const size_t n = static_cast<size_t>(rows) * ff;
     if (n == 0) return 0;
-    if (swiglu) swiglu_bwd_kernel<T><<<grid_for(static_cast<long long>(n / Vec16<T>::N + 1), 256), 256, 0, s>>>(g, h1, dh1, rows, ff);
+    constexpr int VN = Vec16<T>::N;
+    const int width = swiglu ? 2 * ff : ff;
+    if (swiglu) swiglu_bwd_kernel<T><<<grid_for(static_cast<long long>(n / VN + 1), 256), 256, 0, s>>>(g, h1, dh1, rows, ff);
     else gelu_bwd_kernel<T><<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(g, h1, dh1, n);
     LAUNCH_CHECK();
+    if (dbias) NNB_TRY(colsum_accumulate<T>(dh1, width, nullptr, nullptr, nullptr, nullptr, 0, dbias, scratch, rows, width, s, counters));
     return 0;
 }
-
 template <typename T>
 int cross_entropy(T* logits, const int* labels, const float* mask, float grad_scale, float* loss_vec, float* stats,
                   float* loss_out, int rows, int V, int vocab, cudaStream_t s)
@@ -844,11 +994,11 @@ int bf16_to_f32(const bf16* in, float* out, size_t n, cudaStream_t s)
 #define INSTANTIATE(T)                                                                                                 \
     template int norm_fwd<T>(const T*, const float*, const float*, T*, float*, float*, int, int, bool, cudaStream_t);  \
     template int norm_bwd<T>(const T*, const T*, const float*, const float*, const float*, const T*, T*, float*,       \
-                             float*, float*, int, int, bool, cudaStream_t, int*);                                      \
+                             float*, float*, int, int, bool, cudaStream_t, int*, float*);                              \
     template int colsum_accumulate<T>(const T*, long long, const T*, const float*, const float*, const float*, int,    \
                                       float*, float*, int, int, cudaStream_t, int*);                                   \
     template int act_fwd<T>(const T*, T*, int, int, bool, cudaStream_t);                                               \
-    template int act_bwd<T>(const T*, const T*, T*, int, int, bool, cudaStream_t);                                     \
+    template int act_bwd<T>(const T*, const T*, T*, int, int, bool, cudaStream_t, float*, float*, int*);               \
     template int cross_entropy<T>(T*, const int*, const float*, float, float*, float*, float*, int, int, int,          \
                                   cudaStream_t);                                                                       \
     template int muon_normalize<T>(const float*, const float*, float, T*, size_t, cudaStream_t);                       \

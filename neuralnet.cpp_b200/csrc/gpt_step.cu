@@ -95,7 +95,8 @@ static Workspace make_workspace(const nnb200_gpt_config& c)
     W.d_h2 = take(N * ff * esz); W.d_h1 = take(N * fc1 * esz); W.d_attn = take(N * d * esz); W.d_qkv = take(N * 3 * d * esz);
     W.dvec = take(static_cast<size_t>(c.batch) * c.heads * c.seq * 4);
     const size_t widest = std::max(std::max(fc1, 3 * d), V);
-    W.colsum = take(colsum_scratch_floats(static_cast<int>(N), static_cast<int>(widest)) * 4);
+    W.colsum = take(std::max(colsum_scratch_floats(static_cast<int>(N), static_cast<int>(widest)),
+                             norm_bwd_scratch_floats(static_cast<int>(N), static_cast<int>(d))) * 4);
     W.counters = take(kColsumCounters * sizeof(int));
     W.embed_scratch = take(embed_bwd_scratch_bytes(static_cast<int>(N)));
     W.total = off;
@@ -137,6 +138,7 @@ static int linear_bwd_params(const T* dY, const T* X, float* dW, float* db, floa
     else
         NNB_TRY(sgemm_strided(reinterpret_cast<const float*>(dY), reinterpret_cast<const float*>(X), dW, out, in, ntok, 1,
                               out, 1, in, in, 1, 0, 0, 0, 1.0f, nullptr, nullptr, nullptr, 1, s));
+    if (!db) return 0;                       // the bias gradient was already summed by the kernel that produced dY
     return colsum_accumulate<T>(dY, out, nullptr, nullptr, nullptr, nullptr, 0, db, scratch, ntok, out, s, counters);
 }
 
@@ -219,30 +221,32 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
     NNB_TRY(linear_bwd_input<T>(dlogits, P + L.lm_w, Hh(L.lm_w), A(W.d_xn), N, d, c.vocab, s));
     T* g = A(W.g_a);
     T* g_other = A(W.g_b);
+    // each norm backward also sums the columns of the gradient it produces: that is the bias gradient
+    // of the Linear layer whose output this gradient belongs to (fc2 of the layer below, or wo)
     NNB_TRY(norm_bwd<T>(A(W.d_xn), A(W.x_final), P + L.lnf_g, F(W.rinvf), F(W.meanf), nullptr, g, G + L.lnf_g, GB(L.lnf_b),
-                        cs, N, d, ln, s, cn));
+                        cs, N, d, ln, s, cn, G + L.layers[c.layers - 1].b2));
 
     for (int l = c.layers - 1; l >= 0; --l) {
         const LayerParams& lp = L.layers[l];
         const LayerActs& a = W.layers[l];
         // FeedForward::backward (compute_layer.hpp:1674-1688)
-        NNB_TRY(linear_bwd_params<T>(g, A(a.h2), G + lp.w2, G + lp.b2, cs, cn, N, ff, d, s));
+        NNB_TRY(linear_bwd_params<T>(g, A(a.h2), G + lp.w2, nullptr, cs, cn, N, ff, d, s));
         NNB_TRY(linear_bwd_input<T>(g, P + lp.w2, Hh(lp.w2), A(W.d_h2), N, ff, d, s));
-        NNB_TRY(act_bwd<T>(A(W.d_h2), A(a.h1), A(W.d_h1), N, ff, swiglu, s));
-        NNB_TRY(linear_bwd_params<T>(A(W.d_h1), A(a.xn2), G + lp.w1, G + lp.b1, cs, cn, N, d, fc1, s));
+        NNB_TRY(act_bwd<T>(A(W.d_h2), A(a.h1), A(W.d_h1), N, ff, swiglu, s, G + lp.b1, cs, cn));   // also sums fc1's bias gradient
+        NNB_TRY(linear_bwd_params<T>(A(W.d_h1), A(a.xn2), G + lp.w1, nullptr, cs, cn, N, d, fc1, s));
         NNB_TRY(linear_bwd_input<T>(A(W.d_h1), P + lp.w1, Hh(lp.w1), A(W.d_xn), N, d, fc1, s));
         // grad_r1 = grad_output + norm2.backward (GPTBlock::backward, compute_layer.hpp:2388-2404)
         NNB_TRY(norm_bwd<T>(A(W.d_xn), A(a.x_mid), P + lp.g2, F(a.rinv2), F(a.mean2), g, g_other, G + lp.g2, GB(lp.be2), cs,
-                            N, d, ln, s, cn));
+                            N, d, ln, s, cn, G + lp.bo));
         std::swap(g, g_other);
         // AttentionBase::backward (compute_layer.hpp:1271-1412)
-        NNB_TRY(linear_bwd_params<T>(g, A(a.attn), G + lp.wo, G + lp.bo, cs, cn, N, d, d, s));
+        NNB_TRY(linear_bwd_params<T>(g, A(a.attn), G + lp.wo, nullptr, cs, cn, N, d, d, s));
         NNB_TRY(linear_bwd_input<T>(g, P + lp.wo, Hh(lp.wo), A(W.d_attn), N, d, d, s));
         NNB_TRY(attention_bwd<T>(A(a.qkv), A(a.attn), A(W.d_attn), F(a.lse), F(W.dvec), A(W.d_qkv), doc, c, s));
         NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, cn, N, d, 3 * d, s));
         NNB_TRY(linear_bwd_input<T>(A(W.d_qkv), P + lp.wqkv, Hh(lp.wqkv), A(W.d_xn), N, d, 3 * d, s));
         NNB_TRY(norm_bwd<T>(A(W.d_xn), A(a.x_in), P + lp.g1, F(a.rinv1), F(a.mean1), g, g_other, G + lp.g1, GB(lp.be1), cs, N,
-                            d, ln, s, cn));
+                            d, ln, s, cn, l >= 1 ? G + L.layers[l - 1].b2 : nullptr));
         std::swap(g, g_other);
         if (events && events[l]) NNB_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(events[l]), s));
     }

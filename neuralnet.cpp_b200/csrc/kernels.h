@@ -24,14 +24,16 @@ template <typename T> int norm_fwd(const T* x, const float* gamma, const float* 
                                    int rows, int d, bool layer, cudaStream_t s);
 template <typename T> int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, const float* mean,
                                    const T* add, T* dx, float* dgamma, float* dbeta, float* scratch, int rows, int d,
-                                   bool layer, cudaStream_t s, int* counters = nullptr);
+                                   bool layer, cudaStream_t s, int* counters = nullptr, float* out_colsum = nullptr);
+size_t norm_bwd_scratch_floats(int rows, int d);
 template <typename T> int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma, const float* rinv,
                                             const float* mean, int mode, float* out, float* scratch, int rows, int cols,
                                             cudaStream_t s, int* counters = nullptr);
 constexpr int kColsumCounters = 1024;   // ints a caller-provided, zero-initialised counter array must hold
 size_t colsum_scratch_floats(int rows, int cols);
 template <typename T> int act_fwd(const T* h1, T* h2, int rows, int ff, bool swiglu, cudaStream_t s);
-template <typename T> int act_bwd(const T* g, const T* h1, T* dh1, int rows, int ff, bool swiglu, cudaStream_t s);
+template <typename T> int act_bwd(const T* g, const T* h1, T* dh1, int rows, int ff, bool swiglu, cudaStream_t s,
+                                  float* dbias = nullptr, float* scratch = nullptr, int* counters = nullptr);
 template <typename T> int cross_entropy(T* logits, const int* labels, const float* mask, float grad_scale,
                                         float* loss_vec, float* stats, float* loss_out, int rows, int V, int vocab,
                                         cudaStream_t s);
