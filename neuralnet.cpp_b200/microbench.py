@@ -1,0 +1,202 @@
+#!/usr/bin/env python
+"""Kernel microbenchmarks through the C ABI (BASELINE configuration 5): bf16 inputs, values N(0,1) from a seed.
+
+  python neuralnet.cpp_b200/microbench.py                   the whole sweep, one JSON line per case
+  python neuralnet.cpp_b200/microbench.py --only gemm        one family: gemm | attention | ce | rmsnorm | step_gemms
+  python neuralnet.cpp_b200/microbench.py --only gemm --shape 16384,4096,768 --iters 3 --no-time
+                                                             a few launches of one shape (for an ncu capture)
+
+Each case is timed with CUDA events on the launching stream after 3 warm-up launches; inputs are larger than L2
+or L2 is flushed between launches (--flush-l2).  `frac` is achieved / measured peak (MEASURED_PEAKS.json at the
+repository root: cuBLAS bf16 burst for tensor-bound kernels, copy bandwidth for HBM-bound ones).
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+import torch  # noqa: E402
+
+nnb = entry.load_package()
+call = nnb.call
+
+
+def P(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def S():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush = None
+
+
+def timed(fn, iters, flush):
+    global _flush
+    if flush and _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            _flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def run_gemm(M, N, K, args, a_mn=0, b_mn=0, c_bf16=1, bias=False, acc=0, tag="gemm"):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    A = torch.randn((K, M) if a_mn else (M, K), device="cuda", generator=g).bfloat16()
+    B = torch.randn((K, N) if b_mn else (N, K), device="cuda", generator=g).bfloat16()
+    Cm = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16 if c_bf16 else torch.float32)
+    bv = torch.randn(N, device="cuda", generator=g) if bias else None
+    fn = lambda: call("nnb200_gemm_bf16", P(A), P(B), P(Cm), M, N, K, A.shape[1], B.shape[1], N, a_mn, b_mn, c_bf16,
+                      C.c_float(1.0), P(bv), None, acc, S())
+    if args.no_time:
+        for _ in range(args.iters):
+            fn()
+        torch.cuda.synchronize()
+        return
+    ms = timed(fn, args.iters, args.flush_l2)
+    hbm, tf, src = peaks()
+    ach = 2.0 * M * N * K / ms / 1e9
+    emit(kernel=tag, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, us=ms * 1e3, bound="tensor", achieved=ach, peak=tf, unit="TFLOP/s",
+         frac=ach / tf, peak_source=src)
+
+
+def run_attention(B, S_, H, dk, args):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    d, N = H * dk, B * S_
+    qkv = torch.randn(N, 3 * d, device="cuda", generator=g).bfloat16()
+    dout = torch.randn(N, d, device="cuda", generator=g).bfloat16()
+    out = torch.zeros(N, d, device="cuda", dtype=torch.bfloat16)
+    dqkv = torch.zeros_like(qkv)
+    lse = torch.zeros(B * H * S_, device="cuda")
+    dvec = torch.zeros_like(lse)
+    fwd = lambda: call("nnb200_attention_forward", P(qkv), P(out), P(lse), None, B, S_, H, dk, 0, 1, S())
+    bwd = lambda: call("nnb200_attention_backward", P(qkv), P(out), P(dout), P(lse), P(dvec), P(dqkv), None, B, S_, H, dk, 0, 1, S())
+    if args.no_time:
+        for _ in range(args.iters):
+            fwd()
+            bwd()
+        torch.cuda.synchronize()
+        return
+    hbm, tf, src = peaks()
+    fl = 4.0 * B * H * S_ * S_ * dk * 0.5
+    for name, fn, flops in (("attention_fwd", fwd, fl), ("attention_bwd", bwd, 2.5 * fl)):
+        ms = timed(fn, args.iters, args.flush_l2)
+        ach = flops / ms / 1e9
+        emit(kernel=name, batch=B, seq=S_, heads=H, head_dim=dk, us=ms * 1e3, bound="tensor", achieved=ach, peak=tf,
+             unit="TFLOP/s", frac=ach / tf, peak_source=src)
+
+
+def run_ce(rows, V, args):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    logits = torch.randn(rows, V, device="cuda", generator=g).bfloat16()
+    work = torch.empty_like(logits)
+    labels = torch.randint(0, V, (rows,), device="cuda", generator=g, dtype=torch.int32)
+    lv, st, lo = torch.zeros(rows, device="cuda"), torch.zeros(2, device="cuda"), torch.zeros(1, device="cuda")
+
+    def fn():
+        work.copy_(logits)          # the kernel overwrites its input; the copy is outside the timed kernel below
+    fn()
+    ce = lambda: call("nnb200_cross_entropy", P(work), P(labels), None, C.c_float(1.0), P(lv), P(st), P(lo), rows, V, V, 1, S())
+    if args.no_time:
+        for _ in range(args.iters):
+            ce()
+        torch.cuda.synchronize()
+        return
+    ms = timed(ce, args.iters, args.flush_l2)
+    hbm, tf, src = peaks()
+    ach = 2.0 * rows * V * 2 / ms / 1e6
+    emit(kernel="cross_entropy", rows=rows, vocab=V, us=ms * 1e3, bound="hbm", achieved=ach, peak=hbm, unit="GB/s",
+         frac=ach / hbm, peak_source=src)
+
+
+def run_rmsnorm(rows, d, args):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(rows, d, device="cuda", generator=g).bfloat16()
+    gy = torch.randn(rows, d, device="cuda", generator=g).bfloat16()
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    gamma, dgamma = torch.ones(d, device="cuda"), torch.zeros(d, device="cuda")
+    rinv = torch.zeros(rows, device="cuda")
+    scratch = torch.zeros(int(call("nnb200_colsum_scratch_floats", rows, d)), device="cuda")
+    fwd = lambda: call("nnb200_norm_forward", P(x), P(gamma), None, P(y), P(rinv), None, rows, d, 0, 1, S())
+    bwd = lambda: call("nnb200_norm_backward", P(gy), P(x), P(gamma), P(rinv), None, None, P(dx), P(dgamma), None, P(scratch),
+                       rows, d, 0, 1, S())
+    if args.no_time:
+        for _ in range(args.iters):
+            fwd()
+            bwd()
+        torch.cuda.synchronize()
+        return
+    hbm, tf, src = peaks()
+    for name, fn, nbytes in (("rmsnorm_fwd", fwd, 2.0 * rows * d * 2 + rows * 4), ("rmsnorm_bwd", bwd, 3.0 * rows * d * 2)):
+        ms = timed(fn, args.iters, args.flush_l2)
+        ach = nbytes / ms / 1e6
+        emit(kernel=name, rows=rows, d=d, us=ms * 1e3, bound="hbm", achieved=ach, peak=hbm, unit="GB/s", frac=ach / hbm,
+             peak_source=src)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="all")
+    ap.add_argument("--shape", default=None, help="comma-separated override: gemm M,N,K | attention B,S,H,dk | ce rows,V | rmsnorm rows,d")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--no-time", action="store_true", help="just launch --iters times (for profiler captures)")
+    args = ap.parse_args()
+    shape = [int(v) for v in args.shape.split(",")] if args.shape else None
+    fam = args.only
+    if fam in ("all", "gemm"):
+        for s in ([shape] if shape else [(n, n, n) for n in (1024, 2048, 4096, 8192)]):
+            run_gemm(*s, args)
+    if fam in ("all", "step_gemms"):
+        # the GEMMs of one config-3 layer: forward (K-major x K-major), input gradient, weight gradient (split-K)
+        T = 16384
+        for n, k, tag in ((2304, 768, "qkv"), (768, 768, "out_proj"), (4096, 768, "fc1"), (768, 2048, "fc2"), (8192, 768, "lm_head")):
+            run_gemm(T, n, k, args, bias=True, tag=tag + ".fwd")
+            run_gemm(T, k, n, args, b_mn=1, tag=tag + ".dx")
+            run_gemm(n, k, T, args, a_mn=1, b_mn=1, c_bf16=0, acc=1, tag=tag + ".dw")
+    if fam in ("all", "attention"):
+        for s in ([shape] if shape else [(4, sq, 16, dk) for dk in (64, 128) for sq in (512, 1024, 2048, 4096, 8192)]):
+            if s[3] == 128 and s[1] > 2048:
+                continue        # head size 128 runs the SIMT fallback: too slow to be worth timing at long sequences
+            run_attention(*s, args)
+    if fam in ("all", "ce"):
+        run_ce(*(shape or (16384, 32768)), args)
+    if fam in ("all", "rmsnorm"):
+        run_rmsnorm(*(shape or (65536, 4096)), args)
+    code = C.c_int(0)
+    call("nnb200_gemm_status", C.byref(code))
+    if code.value:
+        raise SystemExit(f"device status word set: {code.value:#x}")
+
+
+if __name__ == "__main__":
+    main()
