@@ -56,6 +56,17 @@ def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def gradient_buckets(layer_begin: Sequence[int], matrix_begin: int):
+    """All-reduce buckets of the gradient arena as (start, end) element ranges, in issue order: the hidden
+    matrices of the last layer first (the backward pass finishes them first), down to layer 0, then the
+    vectors-and-embeddings region, which is final only when the embedding scatter-add has run.  `layer_begin`
+    has layers+1 entries (nnb200_gpt_layer_matrix_begin); the buckets tile [0, layer_begin[-1]) exactly."""
+    n = len(layer_begin) - 1
+    out = [(layer_begin[l], layer_begin[l + 1]) for l in range(n - 1, -1, -1)]
+    out.append((0, matrix_begin))
+    return out
+
+
 class GptTrainer:
     """Owns the parameter/gradient/moment arenas and the activation workspace of one replica."""
 
@@ -217,12 +228,11 @@ class GptTrainer:
         on the side stream behind the events the backward pass recorded."""
         import torch.distributed as dist
         L = self.cfg.layers
+        order = list(range(L - 1, -1, -1)) + [L]            # event index behind which each bucket is final
         with torch.cuda.stream(self.side):
-            for l in range(L - 1, -1, -1):
-                self.side.wait_event(self.events[l])
-                dist.all_reduce(self.grads[self.layer_begin[l]:self.layer_begin[l + 1]], group=self.pg)
-            self.side.wait_event(self.events[L])
-            dist.all_reduce(self.grads[:self.matrix_begin], group=self.pg)
+            for ev, (lo, hi) in zip(order, gradient_buckets(self.layer_begin, self.matrix_begin)):
+                self.side.wait_event(self.events[ev])
+                dist.all_reduce(self.grads[lo:hi], group=self.pg)
         torch.cuda.current_stream().wait_stream(self.side)
 
     # -------------------------------------------------------------- optimizer
