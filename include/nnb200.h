@@ -3,8 +3,8 @@
  * Conventions, the ones of the reference ABI (cuda/cuda_kernels.h:1-9, cuda/cuda_kernels.cu:24-55):
  *   - every entry point returns int: 0 = success, positive = cudaError_t, -1 = shape/argument error,
  *     -2 = driver service unavailable; a one-line message goes to stderr;
- *   - the caller owns every buffer; nothing here allocates or frees device memory; results are
- *     written to caller-provided outputs; all work is enqueued on `stream` and returns at once;
+ *   - the caller owns every buffer; nothing here allocates or frees device memory (the nnb200_rt_*
+ *     runtime family at the end is the one exception); results are written to caller-provided outputs; all work is enqueued on `stream` and returns at once;
  *   - pointers are device pointers unless a parameter says "host"; matrices are row-major.
  * There is no CPU fallback: without a CUDA device every compute entry point fails.
  *
@@ -246,6 +246,88 @@ int nnb200_gpt_loss(const nnb200_gpt_config* cfg, void* workspace, const int32_t
 int nnb200_gpt_backward(const nnb200_gpt_config* cfg, const float* params, const void* params_bf16, float* grads,
                         void* workspace, const int32_t* tokens, const int32_t* doc_ids, void* const* layer_events,
                         void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Engine primitives in the reference's own layouts (fp32; matrices row-major, batch blocks stacked
+ * along rows).  These are the ComputeEngine virtuals the reference's CudaEngine answers "not
+ * implemented" to (cuda_engine.hpp:213-261, 461-469); with them the unchanged reference layers run
+ * on the device one primitive at a time.  Semantics follow the CPU engine.
+ * A_b is (M,K) (stored (K,M) when transA), B_b is (K,N) (stored (N,K) when transB); S = alpha*A_b*B_b
+ * + mask, mask (M,N) shared by the batch or NULL. */
+
+/* cuda_batched_matmul with the alpha factor of ComputeEngine::batched_matmul (compute_engine.hpp:72-79). */
+int nnb200_batched_matmul(const float* A, const float* B, float* C, size_t A_rows, size_t A_cols, size_t B_rows, size_t B_cols,
+                          unsigned int batch, int transA, int transB, float alpha, void* stream);
+/* op 0 Sum, 1 Max, 2 Min over the columns (reduce_cols=1, out (batch*M)) or rows (0, out (batch*N)) of S;
+ * entries whose mask is -inf are skipped for Sum and Min.  cpu_engine.hpp:426-515. */
+int nnb200_bmm_reduce(const float* A, const float* B, const float* mask, float* out, int batch, int M, int N, int K, int op,
+                      int transA, int transB, float alpha, int reduce_cols, void* stream);
+/* out[b*M+i] = sum_j exp(S_ij - row_max[b*M+i]) over unmasked j.  cpu_engine.hpp:517-590. */
+int nnb200_bmm_softmax_denom(const float* A, const float* B, const float* row_max, const float* mask, float* out, int batch,
+                             int M, int N, int K, int transA, int transB, float alpha, void* stream);
+/* out (batch*M, D) = softmax(S) * V, V (batch*N, D).  cpu_engine.hpp:592-680. */
+int nnb200_bmm_softmax_apply(const float* A, const float* B, const float* V, const float* row_max, const float* denom,
+                             const float* mask, float* out, int batch, int M, int N, int K, int D, int transA, int transB,
+                             float alpha, void* stream);
+/* P (batch*M, N) is the gradient w.r.t. the weights.  r_out[b*M+i] = sum_j W_ij P_ij;
+ * grad_q (batch*K, M) = alpha * B_b * (W o (P - R))^T.  cpu_engine.hpp:682-790. */
+int nnb200_bmm_softmax_backward_q(const float* A, const float* B, const float* P, const float* row_max, const float* denom,
+                                  const float* mask, float* grad_q, float* r_out, int batch, int M, int N, int K, int transA,
+                                  int transB, float alpha, void* stream);
+/* grad_k (batch*K, N) = alpha * A_b^T * (W o (P - R)); grad_v (batch*K, N) = (W^T * G[:, :K])^T with
+ * G (batch*M, D), D >= K (the reference sizes grad_v by K).  cpu_engine.hpp:792-915. */
+int nnb200_bmm_softmax_backward_kv(const float* A, const float* B, const float* P, const float* G, const float* R,
+                                   const float* row_max, const float* denom, const float* mask, float* grad_k, float* grad_v,
+                                   int batch, int M, int N, int K, int D, int transA, int transB, float alpha, void* stream);
+/* logits (classes, tokens): out[n] = sum_r exp(logits[r][n] - col_max[n]).  cpu_engine.hpp:922-946. */
+int nnb200_col_softmax_denom(const float* logits, const float* col_max, float* out, int classes, int tokens, void* stream);
+/* Fused sparse cross-entropy on (classes, tokens) logits with float labels: grad (classes, tokens) =
+ * inv_num_valid*(softmax - onehot), loss_vec[n] = log-probability of the label; a column whose mask
+ * is < 0.5 or whose label is >= vocab_size gets zeros.  cpu_engine.hpp:948-1006. */
+int nnb200_col_softmax_sparse_forward(const float* logits, const float* labels, const float* mask, float* grad, float* loss_vec,
+                                      int classes, int tokens, int vocab_size, float inv_num_valid, void* stream);
+
+/* Element-wise expression programs: the flat form of the reference's ExprSpec (expr_spec.hpp:30-180).
+ * instrs[i] = {op, dst, a.kind, a.idx, b.kind, b.idx, c.kind, c.idx} with the reference's numbering of
+ * operators (0-23), operand kinds (0-4) and view kinds (0-8). */
+#define NNB200_EXPR_MAX_INPUTS 8
+#define NNB200_EXPR_MAX_CONSTS 16
+#define NNB200_EXPR_MAX_REGS 16
+#define NNB200_EXPR_MAX_INSTRS 64
+typedef struct nnb200_expr_program {
+    uint32_t num_instrs, num_regs, num_inputs, num_consts;
+    uint8_t instrs[NNB200_EXPR_MAX_INSTRS][8];
+    uint8_t view_kind[NNB200_EXPR_MAX_INPUTS];
+    uint8_t view_negate[NNB200_EXPR_MAX_INPUTS];
+    uint32_t view_param[NNB200_EXPR_MAX_INPUTS];
+    float consts[NNB200_EXPR_MAX_CONSTS];
+} nnb200_expr_program;
+/* -1 element-wise, 0 all reductions by row, 1 all by column, -2 mixed (expr_spec_reduce_axis). */
+int nnb200_expr_reduce_axis(const nnb200_expr_program* prog);
+size_t nnb200_eval_expr_scratch_floats(int rows, int cols);
+/* ComputeEngine::eval_expr (vector_out=0: out (rows, cols)) and eval_expr_reduce (vector_out=1: out
+ * (rows,1) for a row reduction, (1,cols) for a column reduction).  inputs[k] has shape
+ * (input_rows[k], input_cols[k]), checked against views as the CPU engine does; an invalid program or
+ * shape prints the reason and returns -1.  cpu_engine.hpp:1280-1659. */
+int nnb200_eval_expr(const nnb200_expr_program* prog, const float* const* inputs, const int* input_rows, const int* input_cols,
+                     float* out, float* scratch, int rows, int cols, int vector_out, void* stream);
+
+/* Device runtime of the C++ drop-in engine (the one family of entry points that owns memory): device
+ * selection, one compute stream, stream-ordered blocks from the device's default memory pool, blocking
+ * host<->device copies.  Replaces CudaBackend::initialize, CudaBuffer::allocate/~CudaBuffer,
+ * upload_blocking, download_blocking and sync_stream (backend/cuda_backend.hpp:66-125, 207-337).
+ * device < 0 picks LOCAL_RANK (one process per GPU) or 0.  The first call wins; later calls only
+ * report the device's name, memory and SM count. */
+int nnb200_rt_init(int device, char* name_out, size_t name_len, size_t* total_mem, int* sm_count);
+int nnb200_rt_device(void);                     /* -1 before nnb200_rt_init */
+void* nnb200_rt_stream(void);
+int nnb200_rt_alloc(size_t bytes, void** out);  /* valid for work queued on the runtime's stream */
+int nnb200_rt_free(void* p);                    /* returns the block once the work queued so far has run */
+int nnb200_rt_upload(void* dst, const void* host_src, size_t bytes);
+int nnb200_rt_download(void* host_dst, const void* src, size_t bytes);
+int nnb200_rt_copy(void* dst, const void* src, size_t bytes);
+int nnb200_rt_zero(void* dst, size_t bytes);
+int nnb200_rt_sync(void);
 
 #ifdef __cplusplus
 }

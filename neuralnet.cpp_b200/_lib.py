@@ -88,15 +88,41 @@ SIGNATURES = {
     "nnb200_gpt_forward": [_cfgp, _p, _p, _p, _p, _p, _p],
     "nnb200_gpt_loss": [_cfgp, _p, _p, _p, _f, _p],
     "nnb200_gpt_backward": [_cfgp, _p, _p, _p, _p, _p, _p, _p, _p],
+    # engine primitives in the reference's layouts
+    "nnb200_batched_matmul": [_p, _p, _p, _sz, _sz, _sz, _sz, _u, _i, _i, _f, _p],
+    "nnb200_bmm_reduce": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
+    "nnb200_bmm_softmax_denom": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p],
+    "nnb200_bmm_softmax_apply": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _p],
+    "nnb200_bmm_softmax_backward_q": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p],
+    "nnb200_bmm_softmax_backward_kv": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _p],
+    "nnb200_col_softmax_denom": [_p, _p, _p, _i, _i, _p],
+    "nnb200_col_softmax_sparse_forward": [_p, _p, _p, _p, _p, _i, _i, _i, _f, _p],
+    "nnb200_expr_reduce_axis": [_p],
+    "nnb200_eval_expr_scratch_floats": [_i, _i],
+    "nnb200_eval_expr": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p],
+    # device runtime of the C++ engine
+    "nnb200_rt_init": [_i, _p, _sz, _p, _p],
+    "nnb200_rt_device": [],
+    "nnb200_rt_stream": [],
+    "nnb200_rt_alloc": [_sz, _p],
+    "nnb200_rt_free": [_p],
+    "nnb200_rt_upload": [_p, _p, _sz],
+    "nnb200_rt_download": [_p, _p, _sz],
+    "nnb200_rt_copy": [_p, _p, _sz],
+    "nnb200_rt_zero": [_p, _sz],
+    "nnb200_rt_sync": [],
 }
 _RET = {
     "nnb200_launch_count": C.c_ulonglong,
     "nnb200_colsum_scratch_floats": _sz, "nnb200_embedding_scratch_bytes": _sz, "nnb200_sumsq_scratch_floats": _sz,
     "nnb200_muon_scratch_bytes": _sz, "nnb200_gpt_arena_elems": _ll, "nnb200_gpt_matrix_region_begin": _ll,
     "nnb200_gpt_layer_matrix_begin": _ll, "nnb200_gpt_workspace_bytes": _ll, "nnb200_gpt_workspace_offset": _ll,
+    "nnb200_eval_expr_scratch_floats": _sz, "nnb200_rt_stream": C.c_void_p,
 }
 # functions whose int return value is a count, not a status
 _COUNT = {"nnb200_gpt_param_table"}
+# functions that return a plain value (negative values are answers, not errors)
+_VALUE = {"nnb200_expr_reduce_axis", "nnb200_rt_device", "nnb200_rt_stream"}
 
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)
@@ -107,6 +133,8 @@ for _name, _args in SIGNATURES.items():
 def call(name, *args):
     """Calls a status-returning entry point and raises NnbError on failure."""
     rc = getattr(lib, name)(*args)
+    if name in _VALUE:
+        return rc
     if name in _RET or name in _COUNT:
         if rc < 0:
             raise NnbError(f"{name} rejected its arguments ({rc})")

@@ -1,0 +1,115 @@
+// Device runtime behind the C++ drop-in engine: device selection, one compute stream, stream-ordered
+// memory from the device's default pool, and blocking host<->device copies.  It is the counterpart of
+// the reference's CudaBackend::initialize / CudaBuffer::allocate / upload_blocking / download_blocking /
+// sync_stream (backend/cuda_backend.hpp:66-125, 207-337), behind plain C entry points so that the
+// engine headers need no CUDA header.  Unlike the reference (cudaMalloc + cudaFree around every op
+// output, each a device-wide synchronisation) blocks come from and return to a pool in stream order:
+// an op's output can be released while kernels that read it are still queued.
+#include <cstdlib>
+#include <cstring>
+
+#include "kernels.h"
+#include "nnb200.h"
+
+namespace {
+struct Runtime {
+    bool ready = false;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+};
+Runtime g_rt;
+}  // namespace
+
+extern "C" {
+
+int nnb200_rt_init(int device, char* name_out, size_t name_len, size_t* total_mem, int* sm_count)
+{
+    if (!g_rt.ready) {
+        int count = 0;
+        NNB_CUDA_CHECK(cudaGetDeviceCount(&count));
+        if (count <= 0) { fprintf(stderr, "nnb200_rt_init: no CUDA device\n"); return -2; }
+        if (device < 0) {                                    // one process per GPU: the launcher's local rank picks it
+            const char* lr = std::getenv("LOCAL_RANK");
+            device = lr ? std::atoi(lr) % count : 0;
+        }
+        if (device >= count) { fprintf(stderr, "nnb200_rt_init: device %d of %d\n", device, count); return -1; }
+        NNB_CUDA_CHECK(cudaSetDevice(device));
+        NNB_CUDA_CHECK(cudaStreamCreateWithFlags(&g_rt.stream, cudaStreamNonBlocking));
+        cudaMemPool_t pool;
+        NNB_CUDA_CHECK(cudaDeviceGetDefaultMemPool(&pool, device));
+        unsigned long long keep = ~0ull;                     // never hand freed blocks back to the driver
+        NNB_CUDA_CHECK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        NNB_TRY(nnb200_set_handle_stream(g_rt.stream));
+        g_rt.device = device;
+        g_rt.ready = true;
+    }
+    cudaDeviceProp prop;
+    NNB_CUDA_CHECK(cudaGetDeviceProperties(&prop, g_rt.device));
+    if (name_out && name_len) { std::strncpy(name_out, prop.name, name_len - 1); name_out[name_len - 1] = 0; }
+    if (total_mem) *total_mem = prop.totalGlobalMem;
+    if (sm_count) *sm_count = prop.multiProcessorCount;
+    return 0;
+}
+
+int nnb200_rt_device(void) { return g_rt.ready ? g_rt.device : -1; }
+void* nnb200_rt_stream(void) { return g_rt.stream; }
+
+int nnb200_rt_alloc(size_t bytes, void** out)
+{
+    if (!g_rt.ready || !out) return -1;
+    *out = nullptr;
+    if (bytes == 0) return 0;
+    NNB_CUDA_CHECK(cudaMallocAsync(out, bytes, g_rt.stream));
+    return 0;
+}
+
+int nnb200_rt_free(void* p)
+{
+    if (!p) return 0;
+    if (!g_rt.ready) return -1;
+    NNB_CUDA_CHECK(cudaFreeAsync(p, g_rt.stream));
+    return 0;
+}
+
+int nnb200_rt_upload(void* dst, const void* host_src, size_t bytes)
+{
+    if (!g_rt.ready) return -1;
+    if (bytes == 0) return 0;
+    NNB_CUDA_CHECK(cudaMemcpyAsync(dst, host_src, bytes, cudaMemcpyHostToDevice, g_rt.stream));
+    NNB_CUDA_CHECK(cudaStreamSynchronize(g_rt.stream));
+    return 0;
+}
+
+int nnb200_rt_download(void* host_dst, const void* src, size_t bytes)
+{
+    if (!g_rt.ready) return -1;
+    if (bytes == 0) return 0;
+    NNB_CUDA_CHECK(cudaMemcpyAsync(host_dst, src, bytes, cudaMemcpyDeviceToHost, g_rt.stream));
+    NNB_CUDA_CHECK(cudaStreamSynchronize(g_rt.stream));
+    return 0;
+}
+
+int nnb200_rt_copy(void* dst, const void* src, size_t bytes)
+{
+    if (!g_rt.ready) return -1;
+    if (bytes == 0) return 0;
+    NNB_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, g_rt.stream));
+    return 0;
+}
+
+int nnb200_rt_zero(void* dst, size_t bytes)
+{
+    if (!g_rt.ready) return -1;
+    if (bytes == 0) return 0;
+    NNB_CUDA_CHECK(cudaMemsetAsync(dst, 0, bytes, g_rt.stream));
+    return 0;
+}
+
+int nnb200_rt_sync(void)
+{
+    if (!g_rt.ready) return -1;
+    NNB_CUDA_CHECK(cudaStreamSynchronize(g_rt.stream));
+    return 0;
+}
+
+}  // extern "C"

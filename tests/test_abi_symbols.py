@@ -15,7 +15,7 @@ HEADER = os.path.join(entry.ROOT, "include", "nnb200.h")
 def declared_functions():
     src = open(HEADER).read()
     src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
-    return sorted(set(re.findall(r"\b(?:int|size_t|long long|unsigned long long)\s+((?:cuda|nnb200)_\w+)\s*\(", src)))
+    return sorted(set(re.findall(r"(?:\b(?:int|size_t|long long|unsigned long long)\s+|\bvoid\s*\*\s*)((?:cuda|nnb200)_\w+)\s*\(", src)))
 
 
 def test_library_exports_every_declared_symbol():
