@@ -137,7 +137,8 @@ static void check_contractions(Pair& P)
             P.run("batched_matmul tA=" + std::to_string(ta) + " tB=" + std::to_string(tb), kTol,
                   [&](nn::ComputeEngine& e, const Mk& mk) { return e.batched_matmul(mk(Ab), mk(Bb), batch, ta, tb, 0.37f); });
         }
-    P.run("matmul K mismatch", kTol, [&](nn::ComputeEngine& e, const Mk& mk) { return e.matmul(mk(rnd(4, 5)), mk(rnd(6, 3)), false, false); });
+    const Matrix m45 = rnd(4, 5), m63 = rnd(6, 3);
+    P.run("matmul K mismatch", kTol, [&](nn::ComputeEngine& e, const Mk& mk) { return e.matmul(mk(m45), mk(m63), false, false); });
 
     // attention-shaped: A = Q^T stored (batch*dk, S) with transA, B = K stored (batch*dk, S); S = alpha Q K^T + mask
     const std::size_t batch = 6, S = 45, dk = 16;
@@ -329,8 +330,9 @@ static void check_index_ops(Pair& P)
     P.run("rearrange_3d forward", 0, [&](nn::ComputeEngine& e, const Mk& mk) { return e.rearrange_3d(mk(x), M, B, N, false); });
     P.run("rearrange_3d inverse", 0, [&](nn::ComputeEngine& e, const Mk& mk) { return e.rearrange_3d(mk(y), M, B, N, true); });
     P.run("rearrange_3d element count mismatch", 0, [&](nn::ComputeEngine& e, const Mk& mk) { return e.rearrange_3d(mk(x), M, B, N + 1, false); });
-    P.run("transpose", 0, [&](nn::ComputeEngine& e, const Mk& mk) { return e.transpose(mk(rnd(33, 65))); });
-    const Matrix big = rnd(40, 9), part = rnd(6, 9);
+    const Matrix wide = rnd(33, 65);
+    P.run("transpose", 0, [&](nn::ComputeEngine& e, const Mk& mk) { return e.transpose(mk(wide)); });
+    const Matrix big = rnd(40, 9), part = rnd(6, 9), fresh = rnd(40, 9);
     P.run("slice_rows", 0, [&](nn::ComputeEngine& e, const Mk& mk) { return e.slice_rows(mk(big), 11, 17); });
     P.run("slice_rows out of bounds", 0, [&](nn::ComputeEngine& e, const Mk& mk) { return e.slice_rows(mk(big), 30, 11); });
     P.run("insert_rows", 0, [&](nn::ComputeEngine& e, const Mk& mk) -> Result<Tensor> {
@@ -352,7 +354,7 @@ static void check_index_ops(Pair& P)
     });
     P.run("copy_from", 0, [&](nn::ComputeEngine& e, const Mk& mk) -> Result<Tensor> {
         Tensor a = mk(big);
-        if (auto r = e.copy_from(a, rnd(40, 9)); !r) return std::unexpected(r.error());
+        if (auto r = e.copy_from(a, fresh); !r) return std::unexpected(r.error());
         return a;
     });
     // a reshape() view must be read with the view's shape, and an in-place op through the original must show in it
@@ -453,12 +455,14 @@ static void check_expr(Pair& P)
         r.views = {ex::linear(), ex::row_reduce_max(), ex::row_reduce_sum()};
         r.num_regs = 2;
         r.instrs = {ins(Op::Sub, 0, ex::input(0), ex::input(1)), ins(Op::Div, 1, ex::reg(0), ex::input(2))};
-        eval("eval_expr row reduce views", r, {x, x, x}, F, T);
+        Matrix xpos = x;   // a sum that stays away from zero, so that the quotient is well conditioned
+        for (auto& v : xpos.span()) v = std::fabs(v) + 0.1f;
+        eval("eval_expr row reduce views", r, {x, x, xpos}, F, T);
         nn::ExprSpec cv;
         cv.views = {ex::linear(), ex::col_broadcast(), ex::col_reduce_sum()};
         cv.num_regs = 2;
         cv.instrs = {ins(Op::Mul, 0, ex::input(0), ex::input(1)), ins(Op::Sub, 1, ex::reg(0), ex::input(2))};
-        eval("eval_expr ColBroadcast + ColReduceSum views", cv, {x, rnd(1, T), x}, F, T);
+        eval("eval_expr ColBroadcast + ColReduceSum views", cv, {x, rnd(1, T), x}, F, T);   // inputs are built once, before both runs
     }
     {   // comparisons, select, min/max, the remaining unary operators
         const Matrix y = rnd(F, T, -2.f, 2.f);
