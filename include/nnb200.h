@@ -99,6 +99,9 @@ int nnb200_gemm_f32(const float* A, const float* B, float* D, int M, int N, int 
  * (2*M*N*K per launch) and the number of launches. */
 int nnb200_gemm_profile(int enable);
 int nnb200_gemm_profile_read(double* host_total_ms, double* host_total_flops, int* host_launches);
+/* CTA pairs (two SMs running one 256 x 256 tile with tcgen05.mma.cta_group::2) the device keeps resident at once;
+ * 0 when the pair kernel is unavailable or switched off (environment NNB200_GEMM_PAIR=0). */
+int nnb200_gemm_pair_capacity(void);
 /* Kernels launched by this library since the last reset (host-side counter). */
 unsigned long long nnb200_launch_count(int reset);
 /* Reads (host) and clears the device-side status word of the tcgen05 GEMM: 0 = no wait ever gave up. */

@@ -111,6 +111,7 @@ SIGNATURES = {
     "nnb200_rt_copy": [_p, _p, _sz],
     "nnb200_rt_zero": [_p, _sz],
     "nnb200_rt_sync": [],
+    "nnb200_gemm_pair_capacity": [],
 }
 _RET = {
     "nnb200_launch_count": C.c_ulonglong,
@@ -122,7 +123,7 @@ _RET = {
 # functions whose int return value is a count, not a status
 _COUNT = {"nnb200_gpt_param_table"}
 # functions that return a plain value (negative values are answers, not errors)
-_VALUE = {"nnb200_expr_reduce_axis", "nnb200_rt_device", "nnb200_rt_stream"}
+_VALUE = {"nnb200_gemm_pair_capacity", "nnb200_expr_reduce_axis", "nnb200_rt_device", "nnb200_rt_stream"}
 
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)

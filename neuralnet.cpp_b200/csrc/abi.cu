@@ -91,6 +91,7 @@ int nnb200_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K,
                      b_mn_major, c_bf16, alpha, bias_n, residual, accumulate, to_stream(stream));
 }
 
+int nnb200_gemm_pair_capacity(void) { return nnb::gemm_pair_capacity(); }
 int nnb200_gemm_status(int* host_code)
 {
     NNB_ARG_CHECK(host_code != nullptr, "null output");

@@ -41,6 +41,7 @@ struct GemmParams {
     const float* bias_n;
     const void* residual;
     float alpha;
+    int debug;          // timing experiments only (NNB200_GEMM_DEBUG): bit 0 = skip the TMA loads, bit 1 = skip the MMAs, bit 2 = skip the stores; results are garbage
 };
 
 // ---------------------------------------------------------------- kernel
@@ -154,12 +155,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // clipped by the tensor map.  Two staging tiles alternate so a store drains while the next fills.
             const int CB = p.c_bf16 ? 64 : 32;            // columns per 128-byte row
             for (int u = blockIdx.x; u < units; u += gridDim.x, ++tc) {
-                if (*abort_flag) break;
                 const int split = u / tiles, t = u - split * tiles;
                 const int tile_n = t / p.tiles_m, tile_m = t - tile_n * p.tiles_m;
                 const int acc = tc & 1;
                 const uint32_t acc_ph = (tc >> 1) & 1;
-                if (!mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag, 4, &g_gemm_error)) break;
+                const bool arrived = mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag, 4, &g_gemm_error);
+                if (epi_any(!arrived || *abort_flag)) break;
                 tc_fence_after();
                 const bool add_extra = (split == 0);      // bias / residual enter once when K is split
                 const bool use_bias = p.bias_n && add_extra;
@@ -314,6 +315,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
 }
 
+}  // namespace nnb
+#include "gemm_tcgen05_2cta.cuh"
+namespace nnb {
+
 // ---------------------------------------------------------------- host side
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -421,6 +426,70 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     return 0;
 }
 
+constexpr int PAIR_THREADS = 320;
+// CTA pairs that can be resident at once (GPCs with an odd SM count strand one SM each)
+template <typename Kernel>
+static int max_pairs(Kernel kernel, int smem)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * sm_count());
+    cfg.blockDim = dim3(PAIR_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 0; }
+    return n;
+}
+
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + 2 * C_STAGE_BYTES + 256 * 4 + 1024 + 256;
+static_assert(PAIR_SMEM <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
+
+// number of CTA pairs the machine runs at once; 0 = the pair kernel cannot be used (or is switched off by
+// NNB200_GEMM_PAIR=0, which exists for A/B timing)
+static int pair_capacity()
+{
+    static int n = [] {
+        const char* e = getenv("NNB200_GEMM_PAIR");
+        if (e && e[0] == '0') return 0;
+        if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<false, false, PAIR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM) != cudaSuccess) { cudaGetLastError(); return 0; }
+        return max_pairs(gemm_bf16_pair_kernel<false, false, PAIR_STAGES>, PAIR_SMEM);
+    }();
+    return n;
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tcm, const GemmParams& p, cudaStream_t s)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        NNB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, PAIR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM));
+        attr_set = true;
+    }
+    const int units = p.tiles_m * p.tiles_n * p.splits;
+    const int pairs = units < pair_capacity() ? units : pair_capacity();
+    static const int debug = [] { const char* e = getenv("NNB200_GEMM_DEBUG"); return e ? atoi(e) : 0; }();
+    GemmParams pd = p;
+    pd.debug = debug;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(PAIR_THREADS);
+    cfg.dynamicSmemBytes = PAIR_SMEM;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (g_prof.on) prof_event(s);
+    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, PAIR_STAGES>, ta, tb, tcm, pd));
+    if (g_prof.on) { prof_event(s); g_prof.flops += 2.0 * p.M * p.N * p.K; }
+    NNB_LAUNCH_CHECK();
+    return 0;
+}
+
 int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
               int a_mn, int b_mn, int c_bf16, float alpha, const float* bias_n, const void* residual, int accumulate,
               cudaStream_t stream)
@@ -440,13 +509,16 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
     p.vec_ok = ((ldc * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) &&
                (!residual || (reinterpret_cast<uintptr_t>(residual) & 15) == 0);
     const int BN = (N > 128) ? 256 : 128;
-    p.tiles_m = static_cast<int>(ceil_div(M, BM));
+    // 256 x 256 tiles on CTA pairs when the output has more than one 128-row and one 128-column block and
+    // the coalesced (TMA-store) epilogue applies
+    const bool pair = p.vec_ok && M > 128 && N > 128 && pair_capacity() > 0;
+    p.tiles_m = static_cast<int>(ceil_div(M, pair ? 256 : BM));
     p.tiles_n = static_cast<int>(ceil_div(N, BN));
     p.kb_total = static_cast<int>(ceil_div(K, BK));
     p.splits = 1;
     if (accumulate) {
         // split K so the work units fill whole waves of the machine: minimise waves/splits
-        const int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
+        const int tiles = p.tiles_m * p.tiles_n, sms = pair ? pair_capacity() : sm_count();
         double best = 1e30;
         for (int sp = 1; sp <= 32 && p.kb_total / sp >= 4; ++sp) {
             const double cost = static_cast<double>(ceil_div(static_cast<long long>(tiles) * sp, sms)) / sp + 0.02 * sp;
@@ -459,12 +531,18 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
     CUtensorMap ta, tb;
     if (!a_mn) NNB_TRY(tensor_map_2d(A, K, M, lda, BK, BM, &ta, 2));
     else NNB_TRY(tensor_map_2d(A, M, K, lda, 64, BK, &ta, 2));
-    if (!b_mn) NNB_TRY(tensor_map_2d(B, K, N, ldb, BK, BN, &tb, 2));
+    if (!b_mn) NNB_TRY(tensor_map_2d(B, K, N, ldb, BK, pair ? PAIR_BN_HALF : BN, &tb, 2));
     else NNB_TRY(tensor_map_2d(B, N, K, ldb, 64, BK, &tb, 2));
     CUtensorMap tcm = ta;                      // unused placeholder when the direct epilogue runs
     p.tma_store = p.vec_ok;
     if (p.tma_store) NNB_TRY(tensor_map_2d(C, N, M, ldc, c_bf16 ? 64 : 32, BM, &tcm, esz));
 
+    if (pair) {
+        if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(ta, tb, tcm, p, stream);
+        if (!a_mn && b_mn) return launch_gemm_pair<false, true>(ta, tb, tcm, p, stream);
+        if (a_mn && !b_mn) return launch_gemm_pair<true, false>(ta, tb, tcm, p, stream);
+        return launch_gemm_pair<true, true>(ta, tb, tcm, p, stream);
+    }
 #define GO(bn, am, bm) return launch_gemm<bn, am, bm>(ta, tb, tcm, p, stream)
     if (BN == 256) {
         if (!a_mn && !b_mn) GO(256, false, false);
@@ -479,6 +557,8 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
     }
 #undef GO
 }
+
+int gemm_pair_capacity() { return pair_capacity(); }
 
 int gemm_profile_enable(int enable)
 {

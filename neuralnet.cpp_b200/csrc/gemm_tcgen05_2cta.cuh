@@ -1,0 +1,249 @@
+// CTA-pair variant of the bf16 GEMM (included by gemm_tcgen05.cu): a cluster of two CTAs on two SMs works
+// on one 256 x 256 output tile with tcgen05.mma.cta_group::2.  Each CTA loads 128 rows of A and 128 rows of
+// B per k-block (32 KB instead of the 48 KB a lone CTA needs for its 128 x 256 tile), which is what lifts
+// the shared-memory bandwidth ceiling of the one-CTA kernel; each keeps the 128 accumulator rows it will
+// store in its own TMEM.
+//
+//   rank 0 (leader)  warp 0: TMA producer for its halves      warp 1: issues every MMA of the pair
+//   rank 1           warp 0: TMA producer for its halves      warp 1: idle after the TMEM allocation
+//   both             warps 2..9: epilogue of the CTA's own 128 rows (TMEM -> registers -> swizzled shared
+//                    memory -> TMA store / reduce-add) in two independent groups of four warps that take
+//                    alternate 128-byte column blocks, so the drain of a tile keeps pace with a main loop
+//                    that is as short as 12 k-blocks (K = 768)
+// Barriers: full[s] lives in the leader and counts the bytes of all four loads of a stage (the peer's loads
+// name it through its shared::cluster address); empty[s] and tfull[a] exist in both CTAs and are signalled
+// together by a multicast tcgen05.commit; tempty[a] lives in the leader and takes one arrival from each of
+// the sixteen epilogue warps of the pair.  All TMA loads are plain (no cluster multicast).  Every wait is
+// bounded as in the one-CTA kernel; a CTA that gives up still joins the cluster barrier at the end, so its
+// shared memory and TMEM outlive anything the peer may still send to them.
+#pragma once
+
+namespace nnb {
+
+constexpr int PAIR_BN_HALF = 128;                                // rows of B each CTA stages per k-block
+constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_BN_HALF * BK * 2;
+
+template <bool A_MN, bool B_MN, int STAGES>
+__global__ void __launch_bounds__(320, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmC, const GemmParams p)
+{
+    constexpr int BN = 256;                                      // accumulator columns per CTA
+    constexpr int B_STAGE_BYTES = PAIR_BN_HALF * BK * 2;
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    // instruction descriptor of the pair MMA: fp32 accumulate, bf16 x bf16, operand majors, N = 256, M = 256
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(A_MN) << 15) | (uint32_t(B_MN) << 16) |
+                               (uint32_t(256 >> 3) << 17) | (uint32_t(256 >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    // the same offsets in both CTAs: the dynamic shared window starts at the same address in every CTA of a kernel
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+    uint8_t* sC = sB + STAGES * B_STAGE_BYTES;
+    float* sBias = reinterpret_cast<float*>(sC + 2 * C_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + BN);             // each epilogue group keeps the bias of its own 128 columns
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
+    const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16, drain_bar = tempty0 + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                     // 0 = leader
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 16); }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                          // the peer's barriers exist before anything is sent to them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int units = tiles * p.splits;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t leader_full0 = mapa_shared(full0, 0);
+            int it = 0;
+            for (int u = pair; u < units && !*abort_flag; u += pairs) {
+                const int split = u / tiles, t = u - split * tiles;
+                const int tile_n = t / p.tiles_m, tile_m = t - tile_n * p.tiles_m;
+                const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const int row_a = tile_m * 256 + static_cast<int>(rank) * 128;      // this CTA's rows of A (and of D)
+                const int row_b = tile_n * 256 + static_cast<int>(rank) * 128;      // this CTA's rows of B (columns of D)
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, 1, &g_gemm_error)) break;
+                    if (p.debug & 1) { if (rank == 0) mbar_arrive(full0 + 8 * s); continue; }
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);
+                    const uint32_t fb = leader_full0 + 8 * s;
+                    const uint32_t a_dst = smem_u32(sA + s * A_STAGE_BYTES), b_dst = smem_u32(sB + s * B_STAGE_BYTES);
+                    if (!A_MN) tma_load_2d_pair(a_dst, &tmA, fb, kb * BK, row_a);
+                    else
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * (BK * 128), &tmA, fb, row_a + j * 64, kb * BK);
+                    if (!B_MN) tma_load_2d_pair(b_dst, &tmB, fb, kb * BK, row_b);
+                    else
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(b_dst + j * (BK * 128), &tmB, fb, row_b + j * 64, kb * BK);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            int it = 0, tc = 0;
+            for (int u = pair; u < units && !*abort_flag; u += pairs, ++tc) {
+                const int split = u / tiles;
+                const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const int acc = tc & 1;
+                const uint32_t acc_ph = (tc >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, abort_flag, 2, &g_gemm_error)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                bool ok = true;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(full0 + 8 * s, ph, abort_flag, 3, &g_gemm_error)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES), b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t da = A_MN ? smem_desc(a_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                                                 : smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+                        const uint64_t db = B_MN ? smem_desc(b_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                                                 : smem_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
+                        if (!(p.debug & 2)) umma_bf16_pair(d_tmem, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit_pair(empty0 + 8 * s, 3);         // frees the stage in both CTAs
+                }
+                if (!ok) break;
+                umma_commit_pair(tfull0 + 8 * acc, 3);           // accumulators complete in both CTAs
+            }
+            // nothing issued above may still be reading the peer's shared memory or writing its TMEM when
+            // the pair leaves: wait (bounded) for the tensor cores to drain
+            umma_commit_pair(drain_bar, 1);
+            mbar_wait(drain_bar, 0, abort_flag, 5, &g_gemm_error);
+        }
+    } else {
+        // Two epilogue groups of four warps; group g takes the column blocks cb with (cb & 1) == g, has its own
+        // staging tile, bias copy, named barrier and bulk-store queue, and never synchronises with the other.
+        const int q = warp & 3;                                  // TMEM lane quadrant this warp may read
+        const int grp = (warp - 2) >> 2;
+        const int bar_id = 1 + grp;
+        const int grp_tid = threadIdx.x - 64 - grp * 128;        // 0..127 inside the group
+        const bool elected = grp_tid == 0;
+        const int r_local = q * 32 + lane;
+        const uint32_t leader_tempty0 = mapa_shared(tempty0, 0);
+        const int CB = p.c_bf16 ? 64 : 32;                       // columns per 128-byte staging row
+        uint8_t* stage = sC + grp * C_STAGE_BYTES;
+        uint8_t* srow = stage + r_local * 128;
+        float* bias_s = sBias + grp * (BN / 2);
+        int tc = 0;
+        for (int u = pair; u < units; u += pairs, ++tc) {
+            const int split = u / tiles, t = u - split * tiles;
+            const int tile_n = t / p.tiles_m, tile_m = t - tile_n * p.tiles_m;
+            const int acc = tc & 1;
+            const uint32_t acc_ph = (tc >> 1) & 1;
+            const bool add_extra = (split == 0);
+            const bool use_bias = p.bias_n && add_extra;
+            float bias_reg = 0.f;                                // fetched while the accumulators are still being computed
+            if (use_bias) {                                      // slot j of the group: column block 2*(j/CB)+grp, column j%CB of it
+                const int col = tile_n * BN + (2 * (grp_tid / CB) + grp) * CB + grp_tid % CB;
+                if (col < p.N) bias_reg = p.bias_n[col];
+            }
+            const bool arrived = mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag, 4, &g_gemm_error);
+            if (group_any(bar_id, !arrived || *abort_flag)) break;
+            tc_fence_after();
+            if (use_bias) bias_s[grp_tid] = bias_reg;            // the previous tile's readers are past their last group_bar
+            const int m0 = tile_m * 256 + static_cast<int>(rank) * 128;
+            const int m = m0 + r_local;
+            const bool row_ok = m < p.M;
+            const long long row_off = static_cast<long long>(m) * p.ldc;
+            if (m0 < p.M) {
+#pragma unroll 1
+            for (int cb = grp; cb * CB < BN; cb += 2) {
+                const int n0 = tile_n * BN + cb * CB;
+                if (n0 >= p.N) break;
+                if (elected) tma_wait_read0();                   // the group's previous store has read the staging tile
+                group_bar(bar_id);
+                uint32_t ra[32], rb[32];
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + cb * CB;
+                tmem_ld32(taddr, ra);
+                if (CB == 64) tmem_ld32(taddr + 32, rb);
+                tmem_ld_wait();
+                auto emit = [&](const uint32_t (&r)[32], int half) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+                    if (use_bias) {
+                        const float4* b4 = reinterpret_cast<const float4*>(bias_s + (cb >> 1) * CB + half * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) { const float4 b = b4[j]; v[4 * j] += b.x; v[4 * j + 1] += b.y; v[4 * j + 2] += b.z; v[4 * j + 3] += b.w; }
+                    }
+                    const int nh = n0 + half * 32;
+                    if (p.c_bf16) {
+                        const bf16* rp = (p.residual && add_extra && row_ok) ? static_cast<const bf16*>(p.residual) + row_off + nh : nullptr;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (rp && nh + j + 8 <= p.N) { const Vec16<bf16> rr = ld16(rp + j);
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) v[j + k] += __bfloat162float(rr.v[k]); }
+                            else if (rp) { for (int k = 0; k < 8; ++k) if (nh + j + k < p.N) v[j + k] += __bfloat162float(rp[j + k]); }
+                            Vec16<bf16> o;
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(v[j + k]);
+                            const int chunk = half * 4 + (j >> 3);
+                            *reinterpret_cast<uint4*>(srow + ((chunk ^ (r_local & 7)) << 4)) = *reinterpret_cast<const uint4*>(&o);
+                        }
+                    } else {
+                        const float* rp = (p.residual && add_extra && row_ok) ? static_cast<const float*>(p.residual) + row_off + nh : nullptr;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            if (rp && nh + j + 4 <= p.N) { const float4 rr = *reinterpret_cast<const float4*>(rp + j); o.x += rr.x; o.y += rr.y; o.z += rr.z; o.w += rr.w; }
+                            else if (rp) { if (nh + j < p.N) o.x += rp[j]; if (nh + j + 1 < p.N) o.y += rp[j + 1]; if (nh + j + 2 < p.N) o.z += rp[j + 2]; }
+                            const int chunk = j >> 2;
+                            *reinterpret_cast<float4*>(srow + ((chunk ^ (r_local & 7)) << 4)) = o;
+                        }
+                    }
+                };
+                emit(ra, 0);
+                if (CB == 64) emit(rb, 1);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                group_bar(bar_id);
+                if (elected && !(p.debug & 4)) {
+                    if (p.accumulate) tma_reduce_add_2d(&tmC, smem_u32(stage), n0, m0);
+                    else tma_store_2d(&tmC, smem_u32(stage), n0, m0);
+                    tma_commit();
+                }
+            }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8 * acc);
+        }
+        if (elected) tma_wait_all();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                          // nobody leaves while the peer may still address this CTA
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace nnb

@@ -15,6 +15,7 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
               int a_mn, int b_mn, int c_bf16, float alpha, const float* bias_n, const void* residual, int accumulate,
               cudaStream_t stream);
 int gemm_device_error(int* code);
+int gemm_pair_capacity();
 int gemm_clear_device_error();
 int gemm_profile_enable(int enable);
 int gemm_profile_read(double* total_ms, double* total_flops, int* launches);

@@ -65,6 +65,21 @@ def test_gemm_bf16_ragged_shapes(g, M, N, K):
     _gemm_case(g, M, N, K, 1, 1, c_bf16=False, bias=False, residual=False, accumulate=True, seed=N)
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(640, 768, 512), (304, 520, 136), (1000, 264, 1032), (8192, 2304, 64), (4096, 2560, 192)])
+def test_gemm_bf16_cta_pair_tiles(g, a_mn, b_mn, M, N, K):
+    """Outputs larger than one 128 x 128 block run 256 x 256 tiles on CTA pairs: ragged rows where the second
+    CTA of a pair has nothing to store (304, 1000), ragged columns, several tiles per pair (both TMEM
+    accumulator buffers and every pipeline stage wrap around), all operand layouts."""
+    _gemm_case(g, M, N, K, a_mn, b_mn, c_bf16=True, bias=True, residual=True, accumulate=False, seed=M + a_mn)
+    _gemm_case(g, M, N, K, a_mn, b_mn, c_bf16=False, bias=True, residual=False, accumulate=False, seed=N + b_mn)
+
+
+def test_gemm_bf16_cta_pair_split_k(g):
+    _gemm_case(g, 768, 2048, 16384, 1, 1, c_bf16=False, bias=False, residual=False, accumulate=True, seed=3)
+    _gemm_case(g, 2304, 768, 4096, 1, 1, c_bf16=False, bias=False, residual=False, accumulate=True, seed=4)
+
+
 def test_gemm_bf16_split_k_weight_gradient_shape(g):
     # dW = dY^T X with K = tokens: both operands MN-major, fp32 accumulate into an existing gradient
     _gemm_case(g, 384, 256, 8192, 1, 1, c_bf16=False, bias=False, residual=False, accumulate=True)
