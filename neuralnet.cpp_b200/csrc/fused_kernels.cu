@@ -199,6 +199,11 @@ norm_bwd_dx_reg_kernel(const T* __restrict__ g, const T* __restrict__ x, const f
         const float rinv = rinv_in[r], mean = LAYER ? mean_in[r] : 0.f;
         float gg[NV][VN], nn[NV][VN];
         float s_g = 0.f, s_gn = 0.f;
+        Vec16<T> av[NV];
+        if (add) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) av[v] = ld16(add + off + (v * 32 + lane) * VN);
+        }
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
             const Vec16<T> gv = ld16(g + off + (v * 32 + lane) * VN), xv = ld16(x + off + (v * 32 + lane) * VN);
@@ -213,12 +218,11 @@ norm_bwd_dx_reg_kernel(const T* __restrict__ g, const T* __restrict__ x, const f
         const float m_g = LAYER ? warp_sum(s_g) * inv_d : 0.f;
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-            Vec16<T> o, av;
-            if (add) av = ld16(add + off + (v * 32 + lane) * VN);
+            Vec16<T> o;
 #pragma unroll
             for (int k = 0; k < VN; ++k) {
                 float t = (gg[v][k] - m_g - nn[v][k] * m_gn) * rinv;
-                if (add) t += to_f32(av.v[k]);
+                if (add) t += to_f32(av[v].v[k]);
                 o.v[k] = from_f32<T>(t);
             }
             st16(dx + off + (v * 32 + lane) * VN, o);
@@ -232,6 +236,8 @@ norm_bwd_dx_reg_kernel(const T* __restrict__ g, const T* __restrict__ x, const f
 // registers.  Warps fold through shared memory, blocks write partials, and the block that finishes
 // last adds the partials up in fixed order: deterministic, no extra pass over the activations.
 constexpr int kNormFusedBlocks = 296;   // two per SM
+constexpr int kNormFoldGroup = 8;       // blocks per first-level fold group
+constexpr int kNormFoldCounters = 64;   // ints at the end of the counter array: one per group, the last for the groups
 
 template <typename T, bool LAYER, int NV>
 __global__ void __launch_bounds__(256, 2)
@@ -255,6 +261,11 @@ norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const fl
         const float rinv = rinv_in[r], mean = LAYER ? mean_in[r] : 0.f;
         float gg[NV][VN], nn[NV][VN];
         float s_g = 0.f, s_gn = 0.f;
+        Vec16<T> av[NV];
+        if (add) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) av[v] = ld16(add + off + (v * 32 + lane) * VN);
+        }
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
             const Vec16<T> gv = ld16(g + off + (v * 32 + lane) * VN), xv = ld16(x + off + (v * 32 + lane) * VN);
@@ -272,12 +283,11 @@ norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const fl
         const float m_g = LAYER ? warp_sum(s_g) * inv_d : 0.f;
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-            Vec16<T> o, av;
-            if (add) av = ld16(add + off + (v * 32 + lane) * VN);
+            Vec16<T> o;
 #pragma unroll
             for (int k = 0; k < VN; ++k) {
                 float t = (gg[v][k] - m_g - nn[v][k] * m_gn) * rinv;
-                if (add) t += to_f32(av.v[k]);
+                if (add) t += to_f32(av[v].v[k]);
                 o.v[k] = from_f32<T>(t);
                 a_os[v][k] += to_f32(o.v[k]);             // the rounded value: what the next kernel reads
             }
@@ -303,43 +313,64 @@ norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const fl
             partial[qn * pstride + static_cast<size_t>(blockIdx.x) * D + c] = sacc;
         }
     }
+    // Two-level fold in fixed order (deterministic, whatever order the blocks finish in): the last block of each
+    // group of kNormFoldGroup consecutive blocks adds that group's rows into one group row; the last group to
+    // finish adds the group rows into the gradients.  One block folding all 296 rows alone took longer than
+    // the pass over the activations.
+    const int nb = gridDim.x, ngroups = (nb + kNormFoldGroup - 1) / kNormFoldGroup;
+    const int grp_id = blockIdx.x / kNormFoldGroup, grp_first = grp_id * kNormFoldGroup;
+    const int grp_size = min(kNormFoldGroup, nb - grp_first);
+    float* gpartial = partial + NQ * pstride;                                // [NQ][ngroups][D]
+    const size_t gstride = static_cast<size_t>(ngroups) * D;
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) is_last = (atomicAdd(counter, 1) == static_cast<int>(gridDim.x) - 1);
+    if (threadIdx.x == 0) is_last = (atomicAdd(counter + grp_id, 1) == grp_size - 1);
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    float4* red4 = reinterpret_cast<float4*>(&red[0][0]);
-    const int nb = gridDim.x;
+#pragma unroll 1
+    for (int qn = 0; qn < NQ; ++qn) {
+        if ((qn == 1 && !LAYER) || (qn == 2 && !osum)) continue;
+        const float* src = partial + qn * pstride + static_cast<size_t>(grp_first) * D;
+        for (int c4 = threadIdx.x; c4 < D / 4; c4 += 256) {
+            float4 v[kNormFoldGroup];
+#pragma unroll
+            for (int k = 0; k < kNormFoldGroup; ++k)
+                if (k < grp_size) v[k] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * D) + c4);
+            float4 t = v[0];
+#pragma unroll
+            for (int k = 1; k < kNormFoldGroup; ++k)
+                if (k < grp_size) { t.x += v[k].x; t.y += v[k].y; t.z += v[k].z; t.w += v[k].w; }
+            reinterpret_cast<float4*>(gpartial + qn * gstride + static_cast<size_t>(grp_id) * D)[c4] = t;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        counter[grp_id] = 0;
+        is_last = (atomicAdd(counter + kNormFoldCounters - 1, 1) == ngroups - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
 #pragma unroll 1
     for (int qn = 0; qn < NQ; ++qn) {
         if ((qn == 1 && !LAYER) || (qn == 2 && !osum)) continue;
         float* dst = qn == 0 ? dgamma : (qn == 1 ? dbeta : osum);
-        const float* src = partial + qn * pstride;
-        for (int j0 = 0; j0 < D / 4; j0 += 64) {
-            const int jq = j0 + (threadIdx.x & 63), grp = threadIdx.x >> 6;
-            float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (jq < D / 4) {
+        const float* src = gpartial + qn * gstride;
+        for (int c4 = threadIdx.x; c4 < D / 4; c4 += 256) {
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
-                for (int k = grp; k < nb; k += 4) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * D + jq * 4));
-                    s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
-                }
+            for (int k = 0; k < ngroups; ++k) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * D) + c4);
+                t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
             }
-            __syncthreads();
-            red4[grp * 64 + (threadIdx.x & 63)] = s4;
-            __syncthreads();
-            if (grp == 0 && jq < D / 4) {
-                float4 t = red4[threadIdx.x & 63];
-#pragma unroll
-                for (int gq = 1; gq < 4; ++gq) { const float4 v = red4[gq * 64 + (threadIdx.x & 63)]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
-                float4 o = *reinterpret_cast<float4*>(dst + jq * 4);
-                o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
-                *reinterpret_cast<float4*>(dst + jq * 4) = o;
-            }
+            float4 o = reinterpret_cast<float4*>(dst)[c4];
+            o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
+            reinterpret_cast<float4*>(dst)[c4] = o;
         }
     }
-    if (threadIdx.x == 0) *counter = 0;
+    if (threadIdx.x == 0) counter[kNormFoldCounters - 1] = 0;
 }
 
 // ======================================================================================
@@ -806,7 +837,7 @@ int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma,
                      (mode == 0 || (reinterpret_cast<uintptr_t>(x) & 15) == 0);
     if (vec) {
         dim3 grid(static_cast<unsigned>(ceil_div(cols, 32 * VN)), chunks);
-        if (counters && grid.x > 1000) counters = nullptr;        // the counter array holds 1024 entries (the last is the norm kernel's)
+        if (counters && grid.x > static_cast<unsigned>(kColsumCounters - kNormFoldCounters)) counters = nullptr;   // the last 64 of the 1024 counters are the norm kernel's
         if (mode == 0) colsum_vec_kernel<T, 0><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks);
         else colsum_vec_kernel<T, 1><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks);
         LAUNCH_CHECK();
@@ -825,7 +856,8 @@ size_t colsum_scratch_floats(int rows, int cols) { return static_cast<size_t>(ce
 
 size_t norm_bwd_scratch_floats(int rows, int d)
 {
-    const size_t a = colsum_scratch_floats(rows, d), b = static_cast<size_t>(3) * kNormFusedBlocks * d;
+    const size_t a = colsum_scratch_floats(rows, d);
+    const size_t b = static_cast<size_t>(3) * (kNormFusedBlocks + (kNormFusedBlocks + kNormFoldGroup - 1) / kNormFoldGroup) * d;
     return a > b ? a : b;
 }
 
@@ -845,9 +877,9 @@ int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, cons
 #define NNB_NORM_BWD_FUSED(nv)                                                                                        \
     if (counters && aligned && out_ok && d == 32 * VN * nv) {                                                         \
         if (layer) norm_bwd_fused_kernel<T, true, nv><<<kNormFusedBlocks, 256, 0, s>>>(                                \
-            g, x, gamma, rinv, mean, add, dx, scratch, counters + kColsumCounters - 1, dgamma, dbeta, out_colsum, rows); \
+            g, x, gamma, rinv, mean, add, dx, scratch, counters + kColsumCounters - kNormFoldCounters, dgamma, dbeta, out_colsum, rows); \
         else norm_bwd_fused_kernel<T, false, nv><<<kNormFusedBlocks, 256, 0, s>>>(                                     \
-            g, x, gamma, rinv, mean, add, dx, scratch, counters + kColsumCounters - 1, dgamma, dbeta, out_colsum, rows); \
+            g, x, gamma, rinv, mean, add, dx, scratch, counters + kColsumCounters - kNormFoldCounters, dgamma, dbeta, out_colsum, rows); \
         LAUNCH_CHECK();                                                                                               \
         return 0;                                                                                                     \
     }
