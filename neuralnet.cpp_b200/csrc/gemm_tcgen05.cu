@@ -41,7 +41,7 @@ struct GemmParams {
     const float* bias_n;
     const void* residual;
     float alpha;
-    int debug;          // timing experiments only (NNB200_GEMM_DEBUG): bit 0 = skip the TMA loads, bit 1 = skip the MMAs, bit 2 = skip the stores; results are garbage
+    int debug;          // timing experiments only (NNB200_GEMM_DEBUG): bit 0 = skip the TMA loads, bit 1 = skip the MMAs, bit 2 = skip the stores, bit 3 = skip the TMEM loads; results are garbage
 };
 
 // ---------------------------------------------------------------- kernel

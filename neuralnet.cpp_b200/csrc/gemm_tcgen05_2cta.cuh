@@ -180,9 +180,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 group_bar(bar_id);
                 uint32_t ra[32], rb[32];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + cb * CB;
-                tmem_ld32(taddr, ra);
-                if (CB == 64) tmem_ld32(taddr + 32, rb);
-                tmem_ld_wait();
+                if (!(p.debug & 8)) {
+                    tmem_ld32(taddr, ra);
+                    if (CB == 64) tmem_ld32(taddr + 32, rb);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) { ra[j] = 0u; rb[j] = 0u; }
+                }
                 auto emit = [&](const uint32_t (&r)[32], int half) {
                     float v[32];
 #pragma unroll
