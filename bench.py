@@ -292,7 +292,7 @@ def main():
         "model_flops_per_token": fpt,
         "mfu": {"of_nominal_2250": value / world * fpt / 2.25e15, "of_measured_burst": value / world * fpt / (peaks["bf16_tflops"] * 1e12),
                 "of_measured_sustained": value / world * fpt / (peaks["bf16_tflops_sustained"] * 1e12)},
-        "roofline": {"kernel": "gemm_bf16_kernel (tcgen05)", "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf,
+        "roofline": {"kernel": "gemm_bf16_pair_kernel (tcgen05.mma.cta_group::2)", "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf,
                      "unit": "TFLOP/s", "frac": achieved_tf / peak_tf, "traffic": None,
                      "peak_source": peaks["source"] + " cuBLAS bf16, sustained (kernel timed inside a long step)",
                      "launches_timed": nl.value, "share_of_step": tms.value / (ms_resident / K) if ms_resident else None},
