@@ -82,59 +82,145 @@ __global__ void __launch_bounds__(1024) bitonic_local_kernel(unsigned long long*
     for (int t = threadIdx.x; t < 2048; t += 1024) if (base + t < n_pad) keys[base + t] = s[t];
 }
 
-// segment heads: seg_start[s] = first sorted position of the s-th distinct id; count in n_seg[0]
-__global__ void segment_heads_kernel(const unsigned long long* __restrict__ keys, int n_pad, int* __restrict__ flags)
+// Segment heads of the sorted keys.  flags[i] = 0: not the first row of its token id; 1: head of a short segment
+// (at most SC_SHORT rows, added by one warp); 2: head of a long segment, whose position is also appended to
+// long_list (the order of the list does not matter: each entry is an independent sum).  long_count must be zero.
+constexpr int SC_SHORT = 8;
+__global__ void segment_heads_kernel(const unsigned long long* __restrict__ keys, int n_pad, int* __restrict__ flags,
+                                     int* __restrict__ long_list, int* __restrict__ long_count)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_pad) return;
     const unsigned long long k = keys[i];
     const bool valid = k != ~0ull;
-    flags[i] = (valid && (i == 0 || (keys[i - 1] >> 32) != (k >> 32))) ? 1 : 0;
+    const bool head = valid && (i == 0 || (keys[i - 1] >> 32) != (k >> 32));
+    int f = 0;
+    if (head) {
+        const bool is_long = i + SC_SHORT < n_pad && (keys[i + SC_SHORT] >> 32) == (k >> 32);   // sorted: same id there = more than SC_SHORT rows
+        f = is_long ? 2 : 1;
+        if (is_long) long_list[atomicAdd(long_count, 1)] = i;
+    }
+    flags[i] = f;
 }
 
-// Work item = (segment head, 128-column slice): a block adds the rows of one token id, in ascending
-// position order, into 128 columns of its destination row.  Threads own columns, so every thread
-// performs the same sequential fp32 sum as the CPU loop; the segment's positions are staged through
-// shared memory and the row loads of 32 positions are issued together, ahead of the ordered adds.
-// Long segments (frequent tokens) are spread over d/128 blocks instead of serialising one block.
+// Short segments: one warp per sorted position; a head's warp adds its at most SC_SHORT rows, in ascending
+// position order, into the whole destination row (lanes own 16-byte column chunks).
 template <typename T>
-__global__ void __launch_bounds__(128)
-scatter_segments_kernel(float* __restrict__ dst, const unsigned long long* __restrict__ keys, const int* __restrict__ flags,
-                        const T* __restrict__ g, int n_pad, int d)
+__global__ void __launch_bounds__(256)
+scatter_short_kernel(float* __restrict__ dst, const unsigned long long* __restrict__ keys, const int* __restrict__ flags,
+                     const T* __restrict__ g, int n_pad, int d, int rows_aligned)
 {
-    __shared__ unsigned spos[256];
-    const int nchunk = (d + 127) / 128;
-    const long long work_total = static_cast<long long>(n_pad) * nchunk;
-    for (long long w = blockIdx.x; w < work_total; w += gridDim.x) {
-        const int h = static_cast<int>(w / nchunk), cc = static_cast<int>(w % nchunk);
-        if (!flags[h]) continue;                                   // block-uniform
-        const unsigned id = static_cast<unsigned>(keys[h] >> 32);
-        const int c = cc * 128 + threadIdx.x;
-        const bool col_ok = c < d;
-        float acc = col_ok ? dst[static_cast<size_t>(id) * d + c] : 0.f;
-        for (int base = h;; base += 256) {
-            __syncthreads();
-            for (int t = threadIdx.x; t < 256; t += 128) {
-                const int pidx = base + t;
-                unsigned v = 0xffffffffu;
-                if (pidx < n_pad) { const unsigned long long k = keys[pidx]; if (k != ~0ull && static_cast<unsigned>(k >> 32) == id) v = static_cast<unsigned>(k); }
-                spos[t] = v;
+    constexpr int VN = Vec16<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int h = static_cast<int>((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5);
+    if (h >= n_pad || flags[h] != 1) return;
+    const unsigned id = static_cast<unsigned>(keys[h] >> 32);
+    unsigned pos[SC_SHORT];
+    int count = 0;
+#pragma unroll
+    for (int r = 0; r < SC_SHORT; ++r) {
+        pos[r] = 0;
+        if (h + r < n_pad) { const unsigned long long k = keys[h + r]; if (k != ~0ull && static_cast<unsigned>(k >> 32) == id) { pos[r] = static_cast<unsigned>(k); count = r + 1; } }
+    }
+    float* drow = dst + static_cast<size_t>(id) * d;
+    for (int c0 = lane * VN; c0 < d; c0 += 32 * VN) {
+        const bool vec_ok = rows_aligned && c0 + VN <= d;
+        Vec16<T> v[SC_SHORT];
+#pragma unroll
+        for (int r = 0; r < SC_SHORT; ++r)
+            if (r < count) {
+                const T* src = g + static_cast<size_t>(pos[r]) * d + c0;
+                if (vec_ok) v[r] = ld16(src);
+                else
+#pragma unroll
+                    for (int k = 0; k < VN; ++k) v[r].v[k] = (c0 + k < d) ? src[k] : from_f32<T>(0.f);
             }
+        float acc[VN];
+#pragma unroll
+        for (int k = 0; k < VN; ++k) acc[k] = (c0 + k < d) ? drow[c0 + k] : 0.f;
+#pragma unroll
+        for (int r = 0; r < SC_SHORT; ++r)
+            if (r < count) {
+#pragma unroll
+                for (int k = 0; k < VN; ++k) acc[k] += to_f32(v[r].v[k]);
+            }
+#pragma unroll
+        for (int k = 0; k < VN; ++k) if (c0 + k < d) drow[c0 + k] = acc[k];
+    }
+}
+
+// Long segments.  Work item = (entry of long_list, 128-column slice): a block adds the rows of one token id, in ascending
+// position order, into 128 columns of its destination row.  The rows of a segment are fetched 256 at a
+// time by all 256 threads (every 16-byte load of the batch in flight together) into shared memory; then
+// one thread per column adds the staged values in order, which is the same sequential fp32 sum as the
+// CPU loop.  A frequent token (thousands of rows under a Zipf distribution) costs a handful of such
+// rounds instead of a serial chain of global-memory round trips.
+constexpr int SC_COLS = 128, SC_TILE_BYTES = 65536;   // rows per round = 64 KB / row slice: 256 (bf16) or 128 (fp32)
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+scatter_segments_kernel(float* __restrict__ dst, const unsigned long long* __restrict__ keys, const int* __restrict__ long_list,
+                        const int* __restrict__ long_count, const T* __restrict__ g, int n_pad, int d, int rows_aligned)
+{
+    constexpr int SC_ROWS = SC_TILE_BYTES / (SC_COLS * static_cast<int>(sizeof(T)));
+    constexpr int VN = Vec16<T>::N;                   // elements per 16-byte load
+    constexpr int CHUNKS = SC_COLS / VN;              // 16-byte chunks per staged row
+    constexpr int ROWS_PER_PASS = 256 / CHUNKS;
+    constexpr int PASSES = SC_ROWS / ROWS_PER_PASS;
+    extern __shared__ uint8_t sc_smem[];
+    T* tile = reinterpret_cast<T*>(sc_smem);          // [SC_ROWS][SC_COLS]
+    __shared__ unsigned spos[SC_ROWS];
+    __shared__ int s_count;
+    static_assert(SC_ROWS <= 256 && SC_ROWS % ROWS_PER_PASS == 0, "one position per thread");
+    const int nchunk = (d + SC_COLS - 1) / SC_COLS;
+    const long long work_total = static_cast<long long>(*long_count) * nchunk;
+    const int my_chunk = threadIdx.x % CHUNKS, my_row = threadIdx.x / CHUNKS;
+    for (long long w = blockIdx.x; w < work_total; w += gridDim.x) {
+        const int h = long_list[w / nchunk], cc = static_cast<int>(w % nchunk);
+        const unsigned id = static_cast<unsigned>(keys[h] >> 32);
+        const int c0 = cc * SC_COLS;
+        const int c = c0 + threadIdx.x;                            // the column thread t < 128 accumulates
+        const bool col_ok = threadIdx.x < SC_COLS && c < d;
+        float acc = col_ok ? dst[static_cast<size_t>(id) * d + c] : 0.f;
+        const int cv = c0 + my_chunk * VN;                         // first column of the chunk this thread fetches
+        const bool vec_ok = rows_aligned && cv + VN <= d;
+        for (int base = h;; base += SC_ROWS) {
+            __syncthreads();                                       // the previous round's adds are done
+            if (threadIdx.x == 0) s_count = SC_ROWS;
             __syncthreads();
-            if (col_ok) {
-                for (int t = 0; t < 256; t += 32) {
-                    if (spos[t] == 0xffffffffu) break;
-                    float v[32];
-#pragma unroll
-                    for (int k = 0; k < 32; ++k) {
-                        const unsigned pz = spos[t + k];
-                        v[k] = (pz != 0xffffffffu) ? to_f32(g[static_cast<size_t>(pz) * d + c]) : 0.f;
-                    }
-#pragma unroll
-                    for (int k = 0; k < 32; ++k) if (spos[t + k] != 0xffffffffu) acc += v[k];
+            {
+                const int pidx = base + threadIdx.x;
+                unsigned v = 0xffffffffu;
+                if (threadIdx.x < SC_ROWS && pidx < n_pad) { const unsigned long long k = keys[pidx]; if (k != ~0ull && static_cast<unsigned>(k >> 32) == id) v = static_cast<unsigned>(k); }
+                if (threadIdx.x < SC_ROWS) {
+                    spos[threadIdx.x] = v;
+                    // the segment is contiguous in the sorted keys: the first slot that is not ours ends it
+                    if (v == 0xffffffffu) atomicMin(&s_count, static_cast<int>(threadIdx.x));
                 }
             }
-            if (spos[255] == 0xffffffffu) break;                    // segment ended inside this batch (block-uniform)
+            __syncthreads();
+            const int count = s_count;
+            Vec16<T> v[PASSES];
+#pragma unroll
+            for (int ps = 0; ps < PASSES; ++ps) {
+                const int r = ps * ROWS_PER_PASS + my_row;
+                if (r < count) {
+                    const T* src = g + static_cast<size_t>(spos[r]) * d + cv;
+                    if (vec_ok) v[ps] = ld16(src);
+                    else
+#pragma unroll
+                        for (int k = 0; k < VN; ++k) v[ps].v[k] = (cv + k < d) ? src[k] : from_f32<T>(0.f);
+                }
+            }
+#pragma unroll
+            for (int ps = 0; ps < PASSES; ++ps) {
+                const int r = ps * ROWS_PER_PASS + my_row;
+                if (r < count) st16(tile + r * SC_COLS + my_chunk * VN, v[ps]);
+            }
+            __syncthreads();
+            if (col_ok)
+                for (int r = 0; r < count; ++r) acc += to_f32(tile[r * SC_COLS + threadIdx.x]);
+            if (count < SC_ROWS) break;                            // block-uniform
         }
         if (col_ok) dst[static_cast<size_t>(id) * d + c] = acc;
     }
@@ -159,7 +245,7 @@ static int next_pow2(int n) { int p = 1; while (p < n) p <<= 1; return p; }
 size_t embed_bwd_scratch_bytes(int n_tok)
 {
     const size_t n_pad = static_cast<size_t>(next_pow2(n_tok < 2048 ? 2048 : n_tok));
-    return n_pad * sizeof(unsigned long long) + n_pad * sizeof(int);
+    return n_pad * sizeof(unsigned long long) + 2 * n_pad * sizeof(int) + 16;   // keys, flags, long-segment list, its counter
 }
 
 template <typename T>
@@ -197,9 +283,21 @@ int embed_bwd(float* tok_grad, float* pos_grad, const int* tokens, const T* g, v
         bitonic_local_kernel<<<n_pad / 2048, 1024, 0, s>>>(keys, n_pad, k, k);
         NNB_LAUNCH_CHECK();
     }
-    segment_heads_kernel<<<blocks, 256, 0, s>>>(keys, n_pad, flags);
+    int* long_list = flags + n_pad;
+    int* long_count = long_list + n_pad;
+    NNB_CUDA_CHECK(cudaMemsetAsync(long_count, 0, sizeof(int), s));
+    segment_heads_kernel<<<blocks, 256, 0, s>>>(keys, n_pad, flags, long_list, long_count);
     NNB_LAUNCH_CHECK();
-    scatter_segments_kernel<T><<<kSmCount * 16, 128, 0, s>>>(tok_grad, keys, flags, g, n_pad, d);
+    constexpr int sc_smem = SC_TILE_BYTES;
+    static bool sc_attr = false;
+    if (!sc_attr) {
+        NNB_CUDA_CHECK(cudaFuncSetAttribute(scatter_segments_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, sc_smem));
+        sc_attr = true;
+    }
+    const int rows_aligned = ((reinterpret_cast<uintptr_t>(g) & 15) == 0 && (static_cast<size_t>(d) * sizeof(T)) % 16 == 0) ? 1 : 0;
+    scatter_short_kernel<T><<<static_cast<unsigned>(ceil_div(static_cast<long long>(n_pad) * 32, 256)), 256, 0, s>>>(tok_grad, keys, flags, g, n_pad, d, rows_aligned);
+    NNB_LAUNCH_CHECK();
+    scatter_segments_kernel<T><<<kSmCount * 3, 256, sc_smem, s>>>(tok_grad, keys, long_list, long_count, g, n_pad, d, rows_aligned);
     NNB_LAUNCH_CHECK();
     if (pos_grad) {
         pos_bwd_kernel<T><<<grid_for(static_cast<long long>(seq) * d, 256), 256, 0, s>>>(pos_grad, g, batch, seq, d);
