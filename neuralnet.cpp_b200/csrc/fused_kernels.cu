@@ -419,7 +419,7 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 colsum_vec_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ x, const float* __restrict__ gamma,
                   const float* __restrict__ rinv, const float* __restrict__ mean, float* __restrict__ partial,
-                  int* __restrict__ counters, float* __restrict__ out, int rows, int cols, int chunks)
+                  int* __restrict__ counters, float* __restrict__ out, int rows, int cols, int chunks, int chunk_rows)
 {
     constexpr int VN = Vec16<T>::N;
     constexpr int BW = 32 * VN;                                   // columns per block
@@ -427,7 +427,7 @@ colsum_vec_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ 
     __shared__ int is_last;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int c0 = (blockIdx.x * 32 + tx) * VN;
-    const int r0 = blockIdx.y * CS_CHUNK_ROWS, r1 = min(rows, r0 + CS_CHUNK_ROWS);
+    const int r0 = blockIdx.y * chunk_rows, r1 = min(rows, r0 + chunk_rows);
     float acc[VN];
 #pragma unroll
     for (int k = 0; k < VN; ++k) acc[k] = 0.f;
@@ -647,19 +647,21 @@ ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const 
     } else for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, to_f32(row[i]));
     mx = block_max(mx, red);
     float den = 0.f;
+    float ex[NV > 0 ? NV : 1][VN];                    // exp(x - max) of the cached row: computed once, used for the sum and the gradient
     if (NV > 0) {
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
             if (i < nvec) {
 #pragma unroll
-                for (int k = 0; k < VN; ++k) den += expf(to_f32(cache[j].v[k]) - mx); }
+                for (int k = 0; k < VN; ++k) { ex[j][k] = expf(to_f32(cache[j].v[k]) - mx); den += ex[j][k]; } }
         }
     } else for (int i = threadIdx.x; i < V; i += blockDim.x) den += expf(to_f32(row[i]) - mx);
     den = block_sum(den, red);
     const float ll = to_f32(row[lbl]);
     __syncthreads();                                  // everyone has read row[lbl] before it is overwritten
     if (threadIdx.x == 0) loss_vec[r] = ll - mx - logf(den);
+    const float inv_den = inv / den;
     if (NV > 0) {
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
@@ -667,7 +669,7 @@ ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const 
             if (i < nvec) { Vec16<T> o;
 #pragma unroll
                 for (int k = 0; k < VN; ++k) {
-                    float gv = inv * expf(to_f32(cache[j].v[k]) - mx) / den;
+                    float gv = ex[j][k] * inv_den;
                     if (i * VN + k == lbl) gv -= inv;
                     o.v[k] = from_f32<T>(gv);
                 }
@@ -832,14 +834,20 @@ int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma,
 {
     if (rows == 0 || cols == 0) return 0;
     constexpr int VN = Vec16<T>::N;
-    const int chunks = static_cast<int>(ceil_div(rows, CS_CHUNK_ROWS));
+    int chunks = static_cast<int>(ceil_div(rows, CS_CHUNK_ROWS));
     const bool vec = (cols % VN) == 0 && (ldg % VN) == 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0 &&
                      (mode == 0 || (reinterpret_cast<uintptr_t>(x) & 15) == 0);
     if (vec) {
-        dim3 grid(static_cast<unsigned>(ceil_div(cols, 32 * VN)), chunks);
+        // row chunks sized so that the grid is about four blocks per SM: wide matrices get long chunks (more loads
+        // in flight per thread, fewer partial rows for the last block to fold), narrow ones keep 128 rows
+        const long long col_blocks = ceil_div(cols, 32 * VN);
+        int chunk_rows = static_cast<int>(ceil_div(static_cast<long long>(rows) * col_blocks, 4 * kSmCount));
+        chunk_rows = static_cast<int>(ceil_div(chunk_rows < CS_CHUNK_ROWS ? CS_CHUNK_ROWS : chunk_rows, 8) * 8);
+        chunks = static_cast<int>(ceil_div(rows, chunk_rows));
+        dim3 grid(static_cast<unsigned>(col_blocks), chunks);
         if (counters && grid.x > static_cast<unsigned>(kColsumCounters - kNormFoldCounters)) counters = nullptr;   // the last 64 of the 1024 counters are the norm kernel's
-        if (mode == 0) colsum_vec_kernel<T, 0><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks);
-        else colsum_vec_kernel<T, 1><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks);
+        if (mode == 0) colsum_vec_kernel<T, 0><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks, chunk_rows);
+        else colsum_vec_kernel<T, 1><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks, chunk_rows);
         LAUNCH_CHECK();
         if (counters) return 0;
     } else {
