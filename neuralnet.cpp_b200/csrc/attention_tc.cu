@@ -28,8 +28,8 @@ __device__ int g_attn_error = 0;
 constexpr int AQ = 128, AK = 128, ADK = 64;
 constexpr int A_TILE = 128 * 128;                  // bytes of a 128-row x 64-bf16 tile
 constexpr int A_KV_STAGES = 3;
-// Q | K,V ring | P (2 buffers x two 64-key halves) | row-max exchange | barriers
-constexpr int A_OFF_KV = A_TILE, A_OFF_P = A_OFF_KV + A_KV_STAGES * 2 * A_TILE, A_OFF_X = A_OFF_P + 4 * A_TILE,
+// Q (2 tiles) | K,V ring | P (2 buffers x two 64-key halves) | row-max exchange | barriers
+constexpr int A_OFF_KV = 2 * A_TILE, A_OFF_P = A_OFF_KV + A_KV_STAGES * 2 * A_TILE, A_OFF_X = A_OFF_P + 4 * A_TILE,
               A_OFF_BAR = A_OFF_X + 2 * 2 * 128 * 4, A_SMEM = A_OFF_BAR + 256;
 constexpr uint32_t A_TMEM_COLS = 512;
 constexpr float kLog2eF = 1.4426950408889634f, kLn2F = 0.6931471805599453f;
@@ -46,33 +46,55 @@ __device__ __forceinline__ float ex2_approx(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+// Barrier of the 256 softmax threads that also ORs a flag over them.  Every wait a softmax thread gives up on is
+// carried to the next of these barriers, where all eight warps leave together; nobody is left alone at one.
+__device__ __forceinline__ bool softmax_any(bool pred)
+{
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, 2, 256, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r) : "r"(static_cast<uint32_t>(pred)) : "memory");
+    return r != 0;
+}
+
+// work item w of a persistent CTA: query tiles in descending length, heads and batches inside
+struct AttnTile { int qb, h, b; };
+__device__ __forceinline__ AttnTile attn_tile(int w, int nq, int H, int HB)
+{
+    AttnTile t;
+    const int hb = w % HB;
+    t.qb = nq - 1 - w / HB;
+    t.h = hb % H;
+    t.b = hb / H;
+    return t;
+}
 
 template <bool DOC, bool ALIBI>
 __global__ void __launch_bounds__(320, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sQ = smem;
+    uint8_t* sQ = smem;                            // two query tiles: the next one is fetched while this one is in use
     uint8_t* sKV = smem + A_OFF_KV;                // stage s: K at sKV + s*2*A_TILE, V right after it
     uint8_t* sP = smem + A_OFF_P;                  // buffer b at sP + b*2*A_TILE (two 64-key halves)
     float* sX = reinterpret_cast<float*>(smem + A_OFF_X);   // [buffer][half][row]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + A_OFF_BAR);
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t q_full = bar0, kv_full0 = bar0 + 8, kv_empty0 = bar0 + 32, s_full0 = bar0 + 56, s_empty0 = bar0 + 72,
-                   p_full0 = bar0 + 88, p_empty0 = bar0 + 104, o_full = bar0 + 120, o_empty = bar0 + 128;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    const uint32_t q_full0 = bar0, q_empty0 = bar0 + 16, kv_full0 = bar0 + 32, kv_empty0 = bar0 + 56, s_full0 = bar0 + 80,
+                   s_empty0 = bar0 + 96, p_full0 = bar0 + 112, p_empty0 = bar0 + 128, o_full = bar0 + 144, o_empty = bar0 + 152;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qb = gridDim.x - 1 - blockIdx.x;     // long (late) query tiles first
-    const int h = blockIdx.y, b = blockIdx.z;
     const int d = a.H * ADK;
-    const int q0 = qb * AQ, nkb = qb + 1;
-    const int row_base = b * a.S;
+    const int nq = a.S / AQ;
+    const int total = nq * a.H * a.B;
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1); }
         for (int s = 0; s < A_KV_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
         for (int s = 0; s < 2; ++s) {
             mbar_init(s_full0 + 8 * s, 1); mbar_init(s_empty0 + 8 * s, 8);
@@ -98,173 +120,200 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(AK >> 3) << 17) | (uint32_t(AQ >> 4) << 24);
     constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (uint32_t(ADK >> 3) << 17) | (uint32_t(AQ >> 4) << 24);
 
+    // Every role walks the same list of tiles; the ring / buffer positions and barrier phases run on across
+    // tiles (kv: key-block counter; gj: the same counter as seen by the score / P / O' buffers; tn: tile counter).
     if (warp == 0) {
         if (lane == 0 && !*abort_flag) {
-            mbar_expect_tx(q_full, A_TILE);
-            tma_load_2d(smem_u32(sQ), &tmQKV, q_full, h * ADK, row_base + q0);
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int s = kb % A_KV_STAGES;
-                const uint32_t ph = (kb / A_KV_STAGES) & 1;
-                if (!mbar_wait(kv_empty0 + 8 * s, ph ^ 1, abort_flag, 1, &g_attn_error)) break;
-                mbar_expect_tx(kv_full0 + 8 * s, 2 * A_TILE);
-                const uint32_t kdst = smem_u32(sKV + s * 2 * A_TILE);
-                tma_load_2d(kdst, &tmQKV, kv_full0 + 8 * s, d + h * ADK, row_base + kb * AK);
-                tma_load_2d(kdst + A_TILE, &tmQKV, kv_full0 + 8 * s, 2 * d + h * ADK, row_base + kb * AK);
+            int kv = 0, tn = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+                const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
+                const int nkb = t.qb + 1, row_base = t.b * a.S, qs = tn & 1;
+                if (!mbar_wait(q_empty0 + 8 * qs, ((tn >> 1) & 1) ^ 1, abort_flag, 11, &g_attn_error)) break;
+                mbar_expect_tx(q_full0 + 8 * qs, A_TILE);
+                tma_load_2d(smem_u32(sQ + qs * A_TILE), &tmQKV, q_full0 + 8 * qs, t.h * ADK, row_base + t.qb * AQ);
+                for (int kb = 0; kb < nkb; ++kb, ++kv) {
+                    const int s = kv % A_KV_STAGES;
+                    const uint32_t ph = (kv / A_KV_STAGES) & 1;
+                    if (!mbar_wait(kv_empty0 + 8 * s, ph ^ 1, abort_flag, 1, &g_attn_error)) { ok = false; break; }
+                    mbar_expect_tx(kv_full0 + 8 * s, 2 * A_TILE);
+                    const uint32_t kdst = smem_u32(sKV + s * 2 * A_TILE);
+                    tma_load_2d(kdst, &tmQKV, kv_full0 + 8 * s, d + t.h * ADK, row_base + kb * AK);
+                    tma_load_2d(kdst + A_TILE, &tmQKV, kv_full0 + 8 * s, 2 * d + t.h * ADK, row_base + kb * AK);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && !*abort_flag) {
-            bool ok = mbar_wait(q_full, 0, abort_flag, 2, &g_attn_error);
-            const uint32_t q_addr = smem_u32(sQ);
-            auto issue_s = [&](int kb) -> bool {
-                const int st = kb % A_KV_STAGES, sb = kb & 1, u = kb >> 1;
-                if (!mbar_wait(kv_full0 + 8 * st, (kb / A_KV_STAGES) & 1, abort_flag, 5, &g_attn_error)) return false;
-                if (u >= 1 && !mbar_wait(s_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 6, &g_attn_error)) return false;
-                tc_fence_after();
-                const uint32_t k_addr = smem_u32(sKV + st * 2 * A_TILE);
+            int kv0 = 0, tn = 0;                                // kv0: key-block counter at the start of the tile
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+                const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
+                const int nkb = t.qb + 1, qs = tn & 1;
+                ok = mbar_wait(q_full0 + 8 * qs, (tn >> 1) & 1, abort_flag, 2, &g_attn_error);
+                const uint32_t q_addr = smem_u32(sQ + qs * A_TILE);
+                auto issue_s = [&](int gj) -> bool {
+                    const int st = gj % A_KV_STAGES, sb = gj & 1, u = gj >> 1;
+                    if (!mbar_wait(kv_full0 + 8 * st, (gj / A_KV_STAGES) & 1, abort_flag, 5, &g_attn_error)) return false;
+                    if (u >= 1 && !mbar_wait(s_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 6, &g_attn_error)) return false;
+                    tc_fence_after();
+                    const uint32_t k_addr = smem_u32(sKV + st * 2 * A_TILE);
 #pragma unroll
-                for (int k = 0; k < ADK / 16; ++k)
-                    umma_bf16(tmem_base + sb * 128, smem_desc(q_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 32, 16, 1024),
-                              IDESC_S, k > 0 ? 1u : 0u);
-                umma_commit(s_full0 + 8 * sb);
-                return true;
-            };
-            auto issue_pv = [&](int j) -> bool {
-                const int st = j % A_KV_STAGES, pb = j & 1;
-                if (!mbar_wait(p_full0 + 8 * pb, (j >> 1) & 1, abort_flag, 3, &g_attn_error)) return false;
-                if (j >= 1 && !mbar_wait(o_empty, (j - 1) & 1, abort_flag, 4, &g_attn_error)) return false;
-                tc_fence_after();
-                const uint32_t p_addr = smem_u32(sP + pb * 2 * A_TILE);
-                const uint32_t v_addr = smem_u32(sKV + st * 2 * A_TILE + A_TILE);
+                    for (int k = 0; k < ADK / 16; ++k)
+                        umma_bf16(tmem_base + sb * 128, smem_desc(q_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 32, 16, 1024),
+                                  IDESC_S, k > 0 ? 1u : 0u);
+                    umma_commit(s_full0 + 8 * sb);
+                    return true;
+                };
+                auto issue_pv = [&](int gj) -> bool {
+                    const int st = gj % A_KV_STAGES, pb = gj & 1;
+                    if (!mbar_wait(p_full0 + 8 * pb, (gj >> 1) & 1, abort_flag, 3, &g_attn_error)) return false;
+                    if (gj >= 1 && !mbar_wait(o_empty, (gj - 1) & 1, abort_flag, 4, &g_attn_error)) return false;
+                    tc_fence_after();
+                    const uint32_t p_addr = smem_u32(sP + pb * 2 * A_TILE);
+                    const uint32_t v_addr = smem_u32(sKV + st * 2 * A_TILE + A_TILE);
 #pragma unroll
-                for (int k = 0; k < AK / 16; ++k) {
-                    const uint64_t da = smem_desc(p_addr + (k >> 2) * A_TILE + (k & 3) * 32, 16, 1024);
-                    const uint64_t db = smem_desc(v_addr + k * 2048, A_TILE, 1024);
-                    umma_bf16(tmem_O, da, db, IDESC_PV, k > 0 ? 1u : 0u);
+                    for (int k = 0; k < AK / 16; ++k) {
+                        const uint64_t da = smem_desc(p_addr + (k >> 2) * A_TILE + (k & 3) * 32, 16, 1024);
+                        const uint64_t db = smem_desc(v_addr + k * 2048, A_TILE, 1024);
+                        umma_bf16(tmem_O, da, db, IDESC_PV, k > 0 ? 1u : 0u);
+                    }
+                    umma_commit(o_full);
+                    umma_commit(p_empty0 + 8 * pb);
+                    umma_commit(kv_empty0 + 8 * st);
+                    return true;
+                };
+                if (ok) ok = issue_s(kv0);
+                for (int kb = 0; ok && kb < nkb; ++kb) {
+                    if (kb + 1 < nkb) ok = issue_s(kv0 + kb + 1);
+                    if (ok) ok = issue_pv(kv0 + kb);
                 }
-                umma_commit(o_full);
-                umma_commit(p_empty0 + 8 * pb);
-                umma_commit(kv_empty0 + 8 * st);
-                return true;
-            };
-            if (ok) ok = issue_s(0);
-            for (int kb = 0; ok && kb < nkb; ++kb) {
-                if (kb + 1 < nkb) ok = issue_s(kb + 1);
-                if (ok) ok = issue_pv(kb);
+                if (ok) umma_commit(q_empty0 + 8 * qs);         // the query tile is free once this tile's MMAs are done
+                kv0 += nkb;
             }
         }
     } else {
         const int q = warp & 3, hf = (warp - 2) >> 2;          // TMEM lane quadrant, column half
         const int row = q * 32 + lane;
-        const int i = q0 + row;                                // query position inside the sequence
         const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
         const float scale2 = a.scale * kLog2eF;
-        const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kLog2eF : 0.f;
-        const int my_doc = DOC ? a.doc[row_base + i] : 0;
-        float m_run = -INFINITY, l_run = 0.f;
-        float o_acc[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) o_acc[c] = 0.f;
         const int sw = row & 7;
-        bool ok = !*abort_flag;
+        bool ok = true, bad = *abort_flag != 0;                 // bad: a wait of this thread gave up (reported at the next barrier)
+        int kv0 = 0, xc = 0;                                    // key-block counter; exchange counter (alternates the sX buffer)
 
-        auto fold_o = [&](int j) -> bool {                      // o_acc += O'(j), this thread's 32 columns
-            if (!mbar_wait(o_full, j & 1, abort_flag, 7, &g_attn_error)) return false;
-            tc_fence_after();
-            uint32_t r[32];
-            tmem_ld32(tmem_O + lane_addr + hf * 32, r);
-            tmem_ld_wait();
+        for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+            const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
+            const int h = t.h, b = t.b, q0 = t.qb * AQ, nkb = t.qb + 1, row_base = b * a.S;
+            const int i = q0 + row;                            // query position inside the sequence
+            const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kLog2eF : 0.f;
+            const int my_doc = DOC ? a.doc[row_base + i] : 0;
+            float m_run = -INFINITY, l_run = 0.f;
+            float o_acc[32];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) o_acc[c] += __uint_as_float(r[c]);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_empty);
-            return true;
-        };
+            for (int c = 0; c < 32; ++c) o_acc[c] = 0.f;
 
-        // One 128-key block.  DIAG: the block on the diagonal (causal mask inside it).  The score of
-        // column cj is r*scale2 + (slope2*cj + abase); with the loops unrolled cj is a literal.
-        auto block = [&](auto diag_tag, int kb) -> bool {
-            constexpr bool DIAG = decltype(diag_tag)::value;
-            const int sb = kb & 1, u = kb >> 1;
-            if (!mbar_wait(s_full0 + 8 * sb, u & 1, abort_flag, 8, &g_attn_error)) return false;
-            tc_fence_after();
-            const int k0 = kb * AK;
-            const int* dk_ptr = DOC ? a.doc + row_base + k0 + hf * 64 : nullptr;
-            const float abase = ALIBI ? -slope2 * static_cast<float>(i - k0 - hf * 64) : 0.f;
-            float s[64];
-            {
-                uint32_t r0[32], r1[32];
-                tmem_ld32(tmem_base + sb * 128 + lane_addr + hf * 64, r0);
-                tmem_ld32(tmem_base + sb * 128 + lane_addr + hf * 64 + 32, r1);
+            auto fold_o = [&](int gj) -> bool {                 // o_acc += O'(gj), this thread's 32 columns
+                if (!mbar_wait(o_full, gj & 1, abort_flag, 7, &g_attn_error)) return false;
+                tc_fence_after();
+                uint32_t r[32];
+                tmem_ld32(tmem_O + lane_addr + hf * 32, r);
                 tmem_ld_wait();
 #pragma unroll
-                for (int jj = 0; jj < 32; ++jj) { s[jj] = __uint_as_float(r0[jj]); s[32 + jj] = __uint_as_float(r1[jj]); }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty0 + 8 * sb);      // scores are in registers: the buffer may be overwritten
-            float mx = -INFINITY;
+                for (int c = 0; c < 32; ++c) o_acc[c] += __uint_as_float(r[c]);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(o_empty);
+                return true;
+            };
+
+            // One 128-key block.  DIAG: the block on the diagonal (causal mask inside it).  The score of
+            // column cj is r*scale2 + (slope2*cj + abase); with the loops unrolled cj is a literal.
+            auto block = [&](auto diag_tag, int kb) -> bool {
+                constexpr bool DIAG = decltype(diag_tag)::value;
+                const int gj = kv0 + kb, sb = gj & 1, u = gj >> 1;
+                bad |= !mbar_wait(s_full0 + 8 * sb, u & 1, abort_flag, 8, &g_attn_error);
+                tc_fence_after();
+                const int k0 = kb * AK;
+                const int* dk_ptr = DOC ? a.doc + row_base + k0 + hf * 64 : nullptr;
+                const float abase = ALIBI ? -slope2 * static_cast<float>(i - k0 - hf * 64) : 0.f;
+                float s[64];
+                {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(tmem_base + sb * 128 + lane_addr + hf * 64, r0);
+                    tmem_ld32(tmem_base + sb * 128 + lane_addr + hf * 64 + 32, r1);
+                    tmem_ld_wait();
 #pragma unroll
-            for (int cj = 0; cj < 64; ++cj) {
-                float sc = ALIBI ? fmaf(s[cj], scale2, fmaf(slope2, static_cast<float>(cj), abase)) : s[cj] * scale2;
-                if (DIAG && hf * 64 + cj > row) sc = -INFINITY;
-                if (DOC && dk_ptr[cj] != my_doc) sc = -INFINITY;
-                s[cj] = sc;
-                mx = fmaxf(mx, sc);
-            }
-            float* xs = sX + sb * 256;
-            xs[hf * 128 + row] = mx;
-            softmax_bar();
-            const float m_new = fmaxf(m_run, fmaxf(mx, xs[(hf ^ 1) * 128 + row]));
-            const float ms = (m_new == -INFINITY) ? 0.f : m_new;
-            const float corr = ex2_approx(m_run - ms);
-            if (kb >= 1) { if (!fold_o(kb - 1)) return false; }
-            if (__any_sync(0xffffffffu, corr != 1.0f)) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) o_acc[c] *= corr;
-            }
-            if (u >= 1 && !mbar_wait(p_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 10, &g_attn_error)) return false;
-            uint8_t* prow = sP + sb * 2 * A_TILE + hf * A_TILE + row * 128;
-            float rs = 0.f;
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                uint32_t pk[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = ex2_approx(s[g * 8 + e * 2] - ms), p1 = ex2_approx(s[g * 8 + e * 2 + 1] - ms);
-                    rs += p0 + p1;
-                    __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-                    pk[e] = *reinterpret_cast<uint32_t*>(&t);
+                    for (int jj = 0; jj < 32; ++jj) { s[jj] = __uint_as_float(r0[jj]); s[32 + jj] = __uint_as_float(r1[jj]); }
                 }
-                *reinterpret_cast<uint4*>(prow + ((g ^ sw) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
-            l_run = l_run * corr + rs;
-            m_run = m_new;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the tensor core
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_full0 + 8 * sb);
-            return true;
-        };
-        for (int kb = 0; ok && kb < nkb - 1; ++kb) ok = block(std::false_type{}, kb);
-        if (ok) ok = block(std::true_type{}, nkb - 1);
-        if (ok) ok = fold_o(nkb - 1);
-        // the row sum is split over the two halves: exchange once more
-        float* xs = sX + (nkb & 1) * 256;
-        xs[hf * 128 + row] = l_run;
-        softmax_bar();
-        if (ok) {
-            const float l_tot = l_run + xs[(hf ^ 1) * 128 + row];
-            const float inv = 1.0f / l_tot;
-            bf16* op = a.out + (static_cast<size_t>(row_base) + i) * d + h * ADK + hf * 32;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_empty0 + 8 * sb);  // scores are in registers: the buffer may be overwritten
+                float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-                Vec16<bf16> o;
+                for (int cj = 0; cj < 64; ++cj) {
+                    float sc = ALIBI ? fmaf(s[cj], scale2, fmaf(slope2, static_cast<float>(cj), abase)) : s[cj] * scale2;
+                    if (DIAG && hf * 64 + cj > row) sc = -INFINITY;
+                    if (DOC && dk_ptr[cj] != my_doc) sc = -INFINITY;
+                    s[cj] = sc;
+                    mx = fmaxf(mx, sc);
+                }
+                float* xs = sX + (xc & 1) * 256;
+                ++xc;
+                xs[hf * 128 + row] = mx;
+                if (softmax_any(bad)) return false;             // the same answer in all eight warps
+                const float m_new = fmaxf(m_run, fmaxf(mx, xs[(hf ^ 1) * 128 + row]));
+                const float ms = (m_new == -INFINITY) ? 0.f : m_new;
+                const float corr = ex2_approx(m_run - ms);
+                if (kb >= 1) bad |= !fold_o(gj - 1);
+                if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(o_acc[c + k] * inv);
-                st16(op + c, o);
+                    for (int c = 0; c < 32; ++c) o_acc[c] *= corr;
+                }
+                if (u >= 1) bad |= !mbar_wait(p_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 10, &g_attn_error);
+                uint8_t* prow = sP + sb * 2 * A_TILE + hf * A_TILE + row * 128;
+                float rs = 0.f;
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    uint32_t pk[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float p0 = ex2_approx(s[g * 8 + e * 2] - ms), p1 = ex2_approx(s[g * 8 + e * 2 + 1] - ms);
+                        rs += p0 + p1;
+                        __nv_bfloat162 tt = __floats2bfloat162_rn(p0, p1);
+                        pk[e] = *reinterpret_cast<uint32_t*>(&tt);
+                    }
+                    *reinterpret_cast<uint4*>(prow + ((g ^ sw) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                }
+                l_run = l_run * corr + rs;
+                m_run = m_new;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full0 + 8 * sb);
+                return true;
+            };
+            for (int kb = 0; ok && kb < nkb - 1; ++kb) ok = block(std::false_type{}, kb);
+            if (ok) ok = block(std::true_type{}, nkb - 1);
+            if (!ok) break;                                     // decided at a barrier: uniform over the softmax warps
+            bad |= !fold_o(kv0 + nkb - 1);
+            // the row sum is split over the two halves: exchange once more
+            float* xs = sX + (xc & 1) * 256;
+            ++xc;
+            xs[hf * 128 + row] = l_run;
+            if (softmax_any(bad)) break;
+            {
+                const float l_tot = l_run + xs[(hf ^ 1) * 128 + row];
+                const float inv = 1.0f / l_tot;
+                bf16* op = a.out + (static_cast<size_t>(row_base) + i) * d + h * ADK + hf * 32;
+#pragma unroll
+                for (int c = 0; c < 32; c += 8) {
+                    Vec16<bf16> o;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(o_acc[c + k] * inv);
+                    st16(op + c, o);
+                }
+                if (hf == 0) a.lse[(static_cast<size_t>(b) * a.H + h) * a.S + i] = (m_run + log2f(l_tot)) * kLn2F;
             }
-            if (hf == 0) a.lse[(static_cast<size_t>(b) * a.H + h) * a.S + i] = (m_run + log2f(l_tot)) * kLn2F;
+            kv0 += nkb;
         }
     }
 
@@ -301,7 +350,9 @@ int attention_fwd_tc(const bf16* qkv, bf16* out, float* lse, const int* doc, int
     const int d = H * dk;
     NNB_TRY(tensor_map_2d(qkv, 3LL * d, static_cast<long long>(B) * S, 3LL * d, ADK, 128, &tm, 2));
     AttnTcArgs a{out, lse, doc, B, S, H, alibi, 1.0f / sqrtf(static_cast<float>(dk))};
-    dim3 grid(S / AQ, H, B);
+    const long long tiles = static_cast<long long>(S / AQ) * H * B;
+    NNB_ARG_CHECK(tiles < (1ll << 31), "too many attention tiles");
+    dim3 grid(static_cast<unsigned>(tiles < kSmCount ? tiles : kSmCount));     // persistent: one CTA per SM walks the tile list
     if (doc && alibi) return launch_fwd_tc<true, true>(tm, a, grid, s);
     if (doc) return launch_fwd_tc<true, false>(tm, a, grid, s);
     if (alibi) return launch_fwd_tc<false, true>(tm, a, grid, s);
