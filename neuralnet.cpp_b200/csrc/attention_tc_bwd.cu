@@ -1,9 +1,9 @@
 // Attention backward on the 5th-generation tensor cores: two kernels, no atomics.
 //
-//   dQ kernel   CTA = 128 queries, loop over 64-key blocks up to the diagonal:
+//   dQ kernel   tile = 128 queries, loop over 64-key blocks up to the diagonal:
 //                 S = Q K^T, dP = dO V^T (TMEM, double-buffered) -> workers: P = exp2(S*scale+bias-lse),
 //                 dS = P o (dP - D) as bf16 into a K-major shared tile -> dQ += dS K (TMEM accumulator)
-//   dK/dV kernel CTA = 128 keys, loop over 64-query blocks from the diagonal to the end:
+//   dK/dV kernel tile = 128 keys, loop over 64-query blocks from the diagonal to the end:
 //                 S^T = K Q^T, dP^T = V dO^T -> workers: P^T, dS^T as bf16 tiles ->
 //                 dV += P^T dO, dK += dS^T Q (TMEM accumulators)
 // Ten warps per CTA: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 workers; worker (row, half)
@@ -47,11 +47,26 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 constexpr uint32_t IDESC_KK = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(64 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
 constexpr uint32_t IDESC_KM = IDESC_KK | (1u << 16);
 
+// Both kernels are persistent: one CTA per SM walks a list of (tile, head, batch) work items, heaviest
+// tiles first.  The resident tile (Q, dO resp. K, V) and the gradient accumulators in TMEM are double-
+// buffered, the rings, score buffers and barrier phases run on across tiles, so the loads and first MMAs of
+// the next tile overlap the tail and the write-out of the current one.
+struct BwdTile { int t, h, b; };
+__device__ __forceinline__ BwdTile bwd_tile(int w, int H, int HB)
+{
+    BwdTile r;
+    const int hb = w % HB;
+    r.t = w / HB;
+    r.h = hb % H;
+    r.b = hb / H;
+    return r;
+}
+
 // ======================================================================================
 // dQ
 // ======================================================================================
-// shared memory: Q | dO | ring of (K, V) 64-key tiles | dS (2 buffers) | barriers
-constexpr int DQ_OFF_RING = 2 * BT, DQ_OFF_DS = DQ_OFF_RING + B_STAGES * 2 * HT, DQ_OFF_BAR = DQ_OFF_DS + 2 * BT,
+// shared memory: Q (2) | dO (2) | ring of (K, V) 64-key tiles | dS (2 buffers) | barriers
+constexpr int DQ_OFF_DO = 2 * BT, DQ_OFF_RING = 4 * BT, DQ_OFF_DS = DQ_OFF_RING + B_STAGES * 2 * HT, DQ_OFF_BAR = DQ_OFF_DS + 2 * BT,
               DQ_SMEM = DQ_OFF_BAR + 256;
 
 template <bool DOC, bool ALIBI>
@@ -60,31 +75,29 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
                       const __grid_constant__ CUtensorMap tmDO128, const AttnBwdArgs a)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sQ = smem;
-    uint8_t* sDO = smem + BT;
+    uint8_t* sQ = smem;                            // tile buffer q at +q*BT
+    uint8_t* sDO = smem + DQ_OFF_DO;
     uint8_t* sRing = smem + DQ_OFF_RING;           // stage s: K at +s*2*HT, V right after
     uint8_t* sDS = smem + DQ_OFF_DS;               // buffer b at +b*BT
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DQ_OFF_BAR);
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t q_full = bar0, kv_full0 = bar0 + 8, kv_empty0 = bar0 + 32, sp_full0 = bar0 + 56, sp_empty0 = bar0 + 72,
-                   ds_full0 = bar0 + 88, ds_empty0 = bar0 + 104, done_bar = bar0 + 120;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    const uint32_t q_full0 = bar0, q_empty0 = bar0 + 16, kv_full0 = bar0 + 32, kv_empty0 = bar0 + 56, sp_full0 = bar0 + 80,
+                   sp_empty0 = bar0 + 96, ds_full0 = bar0 + 112, ds_empty0 = bar0 + 128, done0 = bar0 + 144, acc_empty0 = bar0 + 160;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int d = a.H * 64;
-    const int q0 = qb * 128, nkb = 2 * (qb + 1);   // 64-key blocks up to and including the diagonal
-    const int row_base = b * a.S;
+    const int nt = a.S / 128, HB = a.H * a.B, total = nt * HB;
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1); }
         for (int s = 0; s < B_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
         for (int s = 0; s < 2; ++s) {
             mbar_init(sp_full0 + 8 * s, 1); mbar_init(sp_empty0 + 8 * s, 8);
             mbar_init(ds_full0 + 8 * s, 8); mbar_init(ds_empty0 + 8 * s, 1);
+            mbar_init(done0 + 8 * s, 1); mbar_init(acc_empty0 + 8 * s, 8);
         }
-        mbar_init(done_bar, 1);
         *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;
         if (*abort_flag) atomicCAS(&g_attn_bwd_error, 0, (9 << 16));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -98,131 +111,158 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // TMEM columns: S buffers at 0 / 64, dP buffers at 128 / 192, dQ accumulator at 256
-    const uint32_t tmem_dQ = tmem_base + 256;
+    // TMEM columns: S buffers at 0 / 64, dP buffers at 128 / 192, dQ accumulators at 256 / 320
 
     if (warp == 0) {
         if (lane == 0 && !*abort_flag) {
-            mbar_expect_tx(q_full, 2 * BT);
-            tma_load_2d(smem_u32(sQ), &tmQ128, q_full, h * 64, row_base + q0);
-            tma_load_2d(smem_u32(sDO), &tmDO128, q_full, h * 64, row_base + q0);
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int st = kb % B_STAGES;
-                if (!mbar_wait(kv_empty0 + 8 * st, ((kb / B_STAGES) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) break;
-                mbar_expect_tx(kv_full0 + 8 * st, 2 * HT);
-                const uint32_t dst = smem_u32(sRing + st * 2 * HT);
-                tma_load_2d(dst, &tmKV64, kv_full0 + 8 * st, d + h * 64, row_base + kb * 64);
-                tma_load_2d(dst + HT, &tmKV64, kv_full0 + 8 * st, 2 * d + h * 64, row_base + kb * 64);
+            int kv = 0, tn = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+                const BwdTile t = bwd_tile(w, a.H, HB);
+                const int qb = nt - 1 - t.t, q0 = qb * 128, nkb = 2 * (qb + 1), row_base = t.b * a.S, qs = tn & 1;
+                if (!mbar_wait(q_empty0 + 8 * qs, ((tn >> 1) & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error)) break;
+                mbar_expect_tx(q_full0 + 8 * qs, 2 * BT);
+                tma_load_2d(smem_u32(sQ + qs * BT), &tmQ128, q_full0 + 8 * qs, t.h * 64, row_base + q0);
+                tma_load_2d(smem_u32(sDO + qs * BT), &tmDO128, q_full0 + 8 * qs, t.h * 64, row_base + q0);
+                for (int kb = 0; kb < nkb; ++kb, ++kv) {
+                    const int st = kv % B_STAGES;
+                    if (!mbar_wait(kv_empty0 + 8 * st, ((kv / B_STAGES) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) { ok = false; break; }
+                    mbar_expect_tx(kv_full0 + 8 * st, 2 * HT);
+                    const uint32_t dst = smem_u32(sRing + st * 2 * HT);
+                    tma_load_2d(dst, &tmKV64, kv_full0 + 8 * st, d + t.h * 64, row_base + kb * 64);
+                    tma_load_2d(dst + HT, &tmKV64, kv_full0 + 8 * st, 2 * d + t.h * 64, row_base + kb * 64);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && !*abort_flag) {
-            bool ok = mbar_wait(q_full, 0, abort_flag, 2, &g_attn_bwd_error);
-            const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
-            auto issue_sdp = [&](int kb) -> bool {
-                const int st = kb % B_STAGES, sb = kb & 1, u = kb >> 1;
-                if (!mbar_wait(kv_full0 + 8 * st, (kb / B_STAGES) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
-                if (u >= 1 && !mbar_wait(sp_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 4, &g_attn_bwd_error)) return false;
-                tc_fence_after();
-                const uint32_t k_addr = smem_u32(sRing + st * 2 * HT), v_addr = k_addr + HT;
+            int kv0 = 0, tn = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+                const BwdTile t = bwd_tile(w, a.H, HB);
+                const int nkb = 2 * (nt - t.t), qs = tn & 1, use = tn >> 1;
+                ok = mbar_wait(q_full0 + 8 * qs, use & 1, abort_flag, 2, &g_attn_bwd_error);
+                // the accumulator this tile writes was read out two tiles ago
+                if (ok && use >= 1) ok = mbar_wait(acc_empty0 + 8 * qs, (use - 1) & 1, abort_flag, 12, &g_attn_bwd_error);
+                const uint32_t q_addr = smem_u32(sQ + qs * BT), do_addr = smem_u32(sDO + qs * BT);
+                const uint32_t tmem_dQ = tmem_base + 256 + qs * 64;
+                auto issue_sdp = [&](int gj) -> bool {
+                    const int st = gj % B_STAGES, sb = gj & 1, u = gj >> 1;
+                    if (!mbar_wait(kv_full0 + 8 * st, (gj / B_STAGES) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
+                    if (u >= 1 && !mbar_wait(sp_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 4, &g_attn_bwd_error)) return false;
+                    tc_fence_after();
+                    const uint32_t k_addr = smem_u32(sRing + st * 2 * HT), v_addr = k_addr + HT;
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem_base + sb * 64, smem_desc(q_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + sb * 64, smem_desc(q_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem_base + 128 + sb * 64, smem_desc(do_addr + k * 32, 16, 1024), smem_desc(v_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
-                umma_commit(sp_full0 + 8 * sb);
-                return true;
-            };
-            auto issue_dq = [&](int kb) -> bool {
-                const int st = kb % B_STAGES, sb = kb & 1;
-                if (!mbar_wait(ds_full0 + 8 * sb, (kb >> 1) & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
-                tc_fence_after();
-                const uint32_t ds_addr = smem_u32(sDS + sb * BT), k_addr = smem_u32(sRing + st * 2 * HT);
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + 128 + sb * 64, smem_desc(do_addr + k * 32, 16, 1024), smem_desc(v_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
+                    umma_commit(sp_full0 + 8 * sb);
+                    return true;
+                };
+                auto issue_dq = [&](int gj, bool first) -> bool {
+                    const int st = gj % B_STAGES, sb = gj & 1;
+                    if (!mbar_wait(ds_full0 + 8 * sb, (gj >> 1) & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
+                    tc_fence_after();
+                    const uint32_t ds_addr = smem_u32(sDS + sb * BT), k_addr = smem_u32(sRing + st * 2 * HT);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem_dQ, smem_desc(ds_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 2048, HT, 1024), IDESC_KM, (kb > 0 || k > 0));
-                umma_commit(ds_empty0 + 8 * sb);
-                umma_commit(kv_empty0 + 8 * st);
-                return true;
-            };
-            if (ok) ok = issue_sdp(0);
-            for (int kb = 0; ok && kb < nkb; ++kb) {
-                if (kb + 1 < nkb) ok = issue_sdp(kb + 1);
-                if (ok) ok = issue_dq(kb);
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_dQ, smem_desc(ds_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 2048, HT, 1024), IDESC_KM, (!first || k > 0));
+                    umma_commit(ds_empty0 + 8 * sb);
+                    umma_commit(kv_empty0 + 8 * st);
+                    return true;
+                };
+                if (ok) ok = issue_sdp(kv0);
+                for (int kb = 0; ok && kb < nkb; ++kb) {
+                    if (kb + 1 < nkb) ok = issue_sdp(kv0 + kb + 1);
+                    if (ok) ok = issue_dq(kv0 + kb, kb == 0);
+                }
+                if (ok) { umma_commit(done0 + 8 * qs); umma_commit(q_empty0 + 8 * qs); }
+                kv0 += nkb;
             }
-            if (ok) umma_commit(done_bar);
         }
     } else {
         const int q = warp & 3, hf = (warp - 2) >> 2;
         const int row = q * 32 + lane;
-        const int i = q0 + row;
         const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
         const float scale2 = a.scale * kL2e;
-        const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kL2e : 0.f;
-        const int my_doc = DOC ? a.doc[row_base + i] : 0;
-        const size_t stat = (static_cast<size_t>(b) * a.H + h) * a.S + i;
-        const float lse2 = a.lse[stat] * kL2e, Dv = a.dvec[stat];
         const int sw = row & 7;
         bool ok = !*abort_flag;
+        int kv0 = 0, tn = 0;
 
-        auto block = [&](auto diag_tag, int kb) -> bool {
-            constexpr bool DIAG = decltype(diag_tag)::value;
-            const int sb = kb & 1, u = kb >> 1;
-            if (!mbar_wait(sp_full0 + 8 * sb, u & 1, abort_flag, 6, &g_attn_bwd_error)) return false;
-            tc_fence_after();
-            const int k0 = kb * 64 + hf * 32;                     // first key of this thread's 32 columns
-            uint32_t rs[32], rp[32];
-            tmem_ld32(tmem_base + sb * 64 + lane_addr + hf * 32, rs);
-            tmem_ld32(tmem_base + 128 + sb * 64 + lane_addr + hf * 32, rp);
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(sp_empty0 + 8 * sb);
-            const int* dk_ptr = DOC ? a.doc + row_base + k0 : nullptr;
-            const float base = (ALIBI ? -slope2 * static_cast<float>(i - k0) : 0.f) - lse2;
-            uint32_t pk[16];
+        for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+            const BwdTile t = bwd_tile(w, a.H, HB);
+            const int h = t.h, b = t.b, qb = nt - 1 - t.t, q0 = qb * 128, nkb = 2 * (qb + 1), row_base = b * a.S;
+            const int i = q0 + row;
+            const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kL2e : 0.f;
+            const int my_doc = DOC ? a.doc[row_base + i] : 0;
+            const size_t stat = (static_cast<size_t>(b) * a.H + h) * a.S + i;
+            const float lse2 = a.lse[stat] * kL2e, Dv = a.dvec[stat];
+
+            auto block = [&](auto diag_tag, int kb) -> bool {
+                constexpr bool DIAG = decltype(diag_tag)::value;
+                const int gj = kv0 + kb, sb = gj & 1, u = gj >> 1;
+                if (!mbar_wait(sp_full0 + 8 * sb, u & 1, abort_flag, 6, &g_attn_bwd_error)) return false;
+                tc_fence_after();
+                const int k0 = kb * 64 + hf * 32;                     // first key of this thread's 32 columns
+                uint32_t rs[32], rp[32];
+                tmem_ld32(tmem_base + sb * 64 + lane_addr + hf * 32, rs);
+                tmem_ld32(tmem_base + 128 + sb * 64 + lane_addr + hf * 32, rp);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sp_empty0 + 8 * sb);
+                const int* dk_ptr = DOC ? a.doc + row_base + k0 : nullptr;
+                const float base = (ALIBI ? -slope2 * static_cast<float>(i - k0) : 0.f) - lse2;
+                uint32_t pk[16];
 #pragma unroll
-            for (int cj = 0; cj < 32; cj += 2) {
-                float dsv[2];
+                for (int cj = 0; cj < 32; cj += 2) {
+                    float dsv[2];
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int c = cj + e;
-                    const float t = ALIBI ? fmaf(slope2, static_cast<float>(c), base) : base;
-                    float p = ex2a(fmaf(__uint_as_float(rs[c]), scale2, t));
-                    if (DIAG && k0 + c > i) p = 0.f;
-                    if (DOC && dk_ptr[c] != my_doc) p = 0.f;
-                    dsv[e] = p * (__uint_as_float(rp[c]) - Dv);
+                    for (int e = 0; e < 2; ++e) {
+                        const int c = cj + e;
+                        const float tt = ALIBI ? fmaf(slope2, static_cast<float>(c), base) : base;
+                        float p = ex2a(fmaf(__uint_as_float(rs[c]), scale2, tt));
+                        if (DIAG && k0 + c > i) p = 0.f;
+                        if (DOC && dk_ptr[c] != my_doc) p = 0.f;
+                        dsv[e] = p * (__uint_as_float(rp[c]) - Dv);
+                    }
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(dsv[0], dsv[1]);
+                    pk[cj >> 1] = *reinterpret_cast<uint32_t*>(&t2);
                 }
-                __nv_bfloat162 t2 = __floats2bfloat162_rn(dsv[0], dsv[1]);
-                pk[cj >> 1] = *reinterpret_cast<uint32_t*>(&t2);
+                if (u >= 1 && !mbar_wait(ds_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 7, &g_attn_bwd_error)) return false;
+                uint8_t* drow = sDS + sb * BT + row * 128;
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    *reinterpret_cast<uint4*>(drow + (((hf * 4 + g) ^ sw) << 4)) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ds_full0 + 8 * sb);
+                return true;
+            };
+            for (int kb = 0; ok && kb < nkb - 2; ++kb) ok = block(std::false_type{}, kb);
+            for (int kb = nkb - 2; ok && kb < nkb; ++kb) ok = block(std::true_type{}, kb);
+            const int acc = tn & 1;
+            if (ok) ok = mbar_wait(done0 + 8 * acc, (tn >> 1) & 1, abort_flag, 8, &g_attn_bwd_error);
+            if (ok) {
+                tc_fence_after();
+                uint32_t r[32];
+                tmem_ld32(tmem_base + 256 + acc * 64 + lane_addr + hf * 32, r);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);       // the accumulator may be overwritten
+                bf16* op = a.dqkv + (static_cast<size_t>(row_base) + i) * (3 * d) + h * 64 + hf * 32;
+#pragma unroll
+                for (int c = 0; c < 32; c += 8) {
+                    Vec16<bf16> o;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(__uint_as_float(r[c + k]) * a.scale);
+                    st16(op + c, o);
+                }
             }
-            if (u >= 1 && !mbar_wait(ds_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 7, &g_attn_bwd_error)) return false;
-            uint8_t* drow = sDS + sb * BT + row * 128;
-#pragma unroll
-            for (int g = 0; g < 4; ++g)
-                *reinterpret_cast<uint4*>(drow + (((hf * 4 + g) ^ sw) << 4)) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(ds_full0 + 8 * sb);
-            return true;
-        };
-        for (int kb = 0; ok && kb < nkb - 2; ++kb) ok = block(std::false_type{}, kb);
-        for (int kb = nkb - 2; ok && kb < nkb; ++kb) ok = block(std::true_type{}, kb);
-        if (ok) ok = mbar_wait(done_bar, 0, abort_flag, 8, &g_attn_bwd_error);
-        if (ok) {
-            tc_fence_after();
-            uint32_t r[32];
-            tmem_ld32(tmem_dQ + lane_addr + hf * 32, r);
-            tmem_ld_wait();
-            bf16* op = a.dqkv + (static_cast<size_t>(row_base) + i) * (3 * d) + h * 64 + hf * 32;
-#pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-                Vec16<bf16> o;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(__uint_as_float(r[c + k]) * a.scale);
-                st16(op + c, o);
-            }
+            kv0 += nkb;
         }
     }
     tc_fence_before();
@@ -236,8 +276,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
 // ======================================================================================
 // dK, dV
 // ======================================================================================
-// shared memory: K | V | ring of (Q, dO) 64-query tiles | P^T (2) | dS^T (2) | lse, D per stage | barriers
-constexpr int KV_OFF_RING = 2 * BT, KV_OFF_PT = KV_OFF_RING + B_STAGES * 2 * HT, KV_OFF_DST = KV_OFF_PT + 2 * BT,
+// shared memory: K (2) | V (2) | ring of (Q, dO) 64-query tiles | P^T (2) | dS^T (2) | lse, D per stage | barriers
+constexpr int KV_OFF_V = 2 * BT, KV_OFF_RING = 4 * BT, KV_OFF_PT = KV_OFF_RING + B_STAGES * 2 * HT, KV_OFF_DST = KV_OFF_PT + 2 * BT,
               KV_OFF_STAT = KV_OFF_DST + 2 * BT, KV_OFF_BAR = KV_OFF_STAT + B_STAGES * 512, KV_SMEM = KV_OFF_BAR + 256;
 
 template <bool DOC, bool ALIBI>
@@ -246,35 +286,31 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                        const __grid_constant__ CUtensorMap tmDO64, const AttnBwdArgs a)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sK = smem;
-    uint8_t* sV = smem + BT;
+    uint8_t* sK = smem;                            // tile buffer k at +k*BT
+    uint8_t* sV = smem + KV_OFF_V;
     uint8_t* sRing = smem + KV_OFF_RING;           // stage s: Q at +s*2*HT, dO right after
     uint8_t* sPT = smem + KV_OFF_PT;
     uint8_t* sDST = smem + KV_OFF_DST;
     float* sStat = reinterpret_cast<float*>(smem + KV_OFF_STAT);   // [stage][lse(64) | D(64)]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + KV_OFF_BAR);
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t kv_full = bar0, q_full0 = bar0 + 8, q_empty0 = bar0 + 32, sp_full0 = bar0 + 56, sp_empty0 = bar0 + 72,
-                   pd_full0 = bar0 + 88, pd_empty0 = bar0 + 104, done_bar = bar0 + 120;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    const uint32_t kv_full0 = bar0, kv_empty0 = bar0 + 16, q_full0 = bar0 + 32, q_empty0 = bar0 + 56, sp_full0 = bar0 + 80,
+                   sp_empty0 = bar0 + 96, pd_full0 = bar0 + 112, pd_empty0 = bar0 + 128, done0 = bar0 + 144, acc_empty0 = bar0 + 160;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;   // key tile 0 has the most query blocks: heavy first
     const int d = a.H * 64;
-    const int k0 = kt * 128;
-    const int qi0 = kt * 2, nit = a.S / 64 - qi0;                  // 64-query blocks from the diagonal to the end
-    const int row_base = b * a.S;
-    const size_t stat_base = (static_cast<size_t>(b) * a.H + h) * a.S;
+    const int nt = a.S / 128, HB = a.H * a.B, total = nt * HB;   // key tile 0 has the most query blocks: heavy first
 
     if (threadIdx.x == 0) {
-        mbar_init(kv_full, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
         for (int s = 0; s < B_STAGES; ++s) { mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1); }
         for (int s = 0; s < 2; ++s) {
             mbar_init(sp_full0 + 8 * s, 1); mbar_init(sp_empty0 + 8 * s, 8);
             mbar_init(pd_full0 + 8 * s, 8); mbar_init(pd_empty0 + 8 * s, 1);
+            mbar_init(done0 + 8 * s, 1); mbar_init(acc_empty0 + 8 * s, 8);
         }
-        mbar_init(done_bar, 1);
         *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;
         if (*abort_flag) atomicCAS(&g_attn_bwd_error, 0, (9 << 16));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -288,151 +324,178 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // TMEM columns: S^T buffers at 0 / 64, dP^T at 128 / 192, dV at 256, dK at 320
-    const uint32_t tmem_dV = tmem_base + 256, tmem_dK = tmem_base + 320;
+    // TMEM columns: S^T buffers at 0 / 64, dP^T at 128 / 192, accumulator pair a: dV at 256 + 128a, dK at 320 + 128a
 
     if (warp == 0) {
         if (lane == 0 && !*abort_flag) {
-            mbar_expect_tx(kv_full, 2 * BT);
-            tma_load_2d(smem_u32(sK), &tmKV128, kv_full, d + h * 64, row_base + k0);
-            tma_load_2d(smem_u32(sV), &tmKV128, kv_full, 2 * d + h * 64, row_base + k0);
-            for (int it = 0; it < nit; ++it) {
-                const int st = it % B_STAGES, qs = (qi0 + it) * 64;
-                if (!mbar_wait(q_empty0 + 8 * st, ((it / B_STAGES) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) break;
-                mbar_expect_tx(q_full0 + 8 * st, 2 * HT + 512);
-                const uint32_t dst = smem_u32(sRing + st * 2 * HT);
-                tma_load_2d(dst, &tmQ64, q_full0 + 8 * st, h * 64, row_base + qs);
-                tma_load_2d(dst + HT, &tmDO64, q_full0 + 8 * st, h * 64, row_base + qs);
-                bulk_load_1d(smem_u32(sStat + st * 128), a.lse + stat_base + qs, 256, q_full0 + 8 * st);
-                bulk_load_1d(smem_u32(sStat + st * 128 + 64), a.dvec + stat_base + qs, 256, q_full0 + 8 * st);
+            int qc = 0, tn = 0;                                    // query-block counter across tiles, tile counter
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+                const BwdTile t = bwd_tile(w, a.H, HB);
+                const int kt = t.t, k0 = kt * 128, qi0 = kt * 2, nit = a.S / 64 - qi0, row_base = t.b * a.S, ks = tn & 1;
+                const size_t stat_base = (static_cast<size_t>(t.b) * a.H + t.h) * a.S;
+                if (!mbar_wait(kv_empty0 + 8 * ks, ((tn >> 1) & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error)) break;
+                mbar_expect_tx(kv_full0 + 8 * ks, 2 * BT);
+                tma_load_2d(smem_u32(sK + ks * BT), &tmKV128, kv_full0 + 8 * ks, d + t.h * 64, row_base + k0);
+                tma_load_2d(smem_u32(sV + ks * BT), &tmKV128, kv_full0 + 8 * ks, 2 * d + t.h * 64, row_base + k0);
+                for (int it = 0; it < nit; ++it, ++qc) {
+                    const int st = qc % B_STAGES, qs = (qi0 + it) * 64;
+                    if (!mbar_wait(q_empty0 + 8 * st, ((qc / B_STAGES) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) { ok = false; break; }
+                    mbar_expect_tx(q_full0 + 8 * st, 2 * HT + 512);
+                    const uint32_t dst = smem_u32(sRing + st * 2 * HT);
+                    tma_load_2d(dst, &tmQ64, q_full0 + 8 * st, t.h * 64, row_base + qs);
+                    tma_load_2d(dst + HT, &tmDO64, q_full0 + 8 * st, t.h * 64, row_base + qs);
+                    bulk_load_1d(smem_u32(sStat + st * 128), a.lse + stat_base + qs, 256, q_full0 + 8 * st);
+                    bulk_load_1d(smem_u32(sStat + st * 128 + 64), a.dvec + stat_base + qs, 256, q_full0 + 8 * st);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && !*abort_flag) {
-            bool ok = mbar_wait(kv_full, 0, abort_flag, 2, &g_attn_bwd_error);
-            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            auto issue_st = [&](int it) -> bool {
-                const int st = it % B_STAGES, sb = it & 1, u = it >> 1;
-                if (!mbar_wait(q_full0 + 8 * st, (it / B_STAGES) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
-                if (u >= 1 && !mbar_wait(sp_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 4, &g_attn_bwd_error)) return false;
-                tc_fence_after();
-                const uint32_t q_addr = smem_u32(sRing + st * 2 * HT), do_addr = q_addr + HT;
+            int qc0 = 0, tn = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+                const BwdTile t = bwd_tile(w, a.H, HB);
+                const int nit = a.S / 64 - t.t * 2, ks = tn & 1, use = tn >> 1;
+                ok = mbar_wait(kv_full0 + 8 * ks, use & 1, abort_flag, 2, &g_attn_bwd_error);
+                if (ok && use >= 1) ok = mbar_wait(acc_empty0 + 8 * ks, (use - 1) & 1, abort_flag, 12, &g_attn_bwd_error);
+                const uint32_t k_addr = smem_u32(sK + ks * BT), v_addr = smem_u32(sV + ks * BT);
+                const uint32_t tmem_dV = tmem_base + 256 + ks * 128, tmem_dK = tmem_dV + 64;
+                auto issue_st = [&](int gi) -> bool {
+                    const int st = gi % B_STAGES, sb = gi & 1, u = gi >> 1;
+                    if (!mbar_wait(q_full0 + 8 * st, (gi / B_STAGES) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
+                    if (u >= 1 && !mbar_wait(sp_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 4, &g_attn_bwd_error)) return false;
+                    tc_fence_after();
+                    const uint32_t q_addr = smem_u32(sRing + st * 2 * HT), do_addr = q_addr + HT;
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem_base + sb * 64, smem_desc(k_addr + k * 32, 16, 1024), smem_desc(q_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + sb * 64, smem_desc(k_addr + k * 32, 16, 1024), smem_desc(q_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem_base + 128 + sb * 64, smem_desc(v_addr + k * 32, 16, 1024), smem_desc(do_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
-                umma_commit(sp_full0 + 8 * sb);
-                return true;
-            };
-            auto issue_dkv = [&](int it) -> bool {
-                const int st = it % B_STAGES, sb = it & 1;
-                if (!mbar_wait(pd_full0 + 8 * sb, (it >> 1) & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
-                tc_fence_after();
-                const uint32_t pt_addr = smem_u32(sPT + sb * BT), dst_addr = smem_u32(sDST + sb * BT);
-                const uint32_t q_addr = smem_u32(sRing + st * 2 * HT), do_addr = q_addr + HT;
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + 128 + sb * 64, smem_desc(v_addr + k * 32, 16, 1024), smem_desc(do_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
+                    umma_commit(sp_full0 + 8 * sb);
+                    return true;
+                };
+                auto issue_dkv = [&](int gi, bool first) -> bool {
+                    const int st = gi % B_STAGES, sb = gi & 1;
+                    if (!mbar_wait(pd_full0 + 8 * sb, (gi >> 1) & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
+                    tc_fence_after();
+                    const uint32_t pt_addr = smem_u32(sPT + sb * BT), dst_addr = smem_u32(sDST + sb * BT);
+                    const uint32_t q_addr = smem_u32(sRing + st * 2 * HT), do_addr = q_addr + HT;
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem_dV, smem_desc(pt_addr + k * 32, 16, 1024), smem_desc(do_addr + k * 2048, HT, 1024), IDESC_KM, (it > 0 || k > 0));
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_dV, smem_desc(pt_addr + k * 32, 16, 1024), smem_desc(do_addr + k * 2048, HT, 1024), IDESC_KM, (!first || k > 0));
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem_dK, smem_desc(dst_addr + k * 32, 16, 1024), smem_desc(q_addr + k * 2048, HT, 1024), IDESC_KM, (it > 0 || k > 0));
-                umma_commit(pd_empty0 + 8 * sb);
-                umma_commit(q_empty0 + 8 * st);
-                return true;
-            };
-            if (ok) ok = issue_st(0);
-            for (int it = 0; ok && it < nit; ++it) {
-                if (it + 1 < nit) ok = issue_st(it + 1);
-                if (ok) ok = issue_dkv(it);
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_dK, smem_desc(dst_addr + k * 32, 16, 1024), smem_desc(q_addr + k * 2048, HT, 1024), IDESC_KM, (!first || k > 0));
+                    umma_commit(pd_empty0 + 8 * sb);
+                    umma_commit(q_empty0 + 8 * st);
+                    return true;
+                };
+                if (ok) ok = issue_st(qc0);
+                for (int it = 0; ok && it < nit; ++it) {
+                    if (it + 1 < nit) ok = issue_st(qc0 + it + 1);
+                    if (ok) ok = issue_dkv(qc0 + it, it == 0);
+                }
+                if (ok) { umma_commit(done0 + 8 * ks); umma_commit(kv_empty0 + 8 * ks); }
+                qc0 += nit;
             }
-            if (ok) umma_commit(done_bar);
         }
     } else {
         const int q = warp & 3, hf = (warp - 2) >> 2;
         const int row = q * 32 + lane;
-        const int j = k0 + row;                                   // key position
         const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
         const float scale2 = a.scale * kL2e;
-        const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kL2e : 0.f;
-        const int my_doc = DOC ? a.doc[row_base + j] : 0;
         const int sw = row & 7;
         bool ok = !*abort_flag;
+        int qc0 = 0, tn = 0;
 
-        auto block = [&](auto diag_tag, int it) -> bool {
-            constexpr bool DIAG = decltype(diag_tag)::value;
-            const int st = it % B_STAGES, sb = it & 1, u = it >> 1;
-            if (!mbar_wait(sp_full0 + 8 * sb, u & 1, abort_flag, 6, &g_attn_bwd_error)) return false;
-            tc_fence_after();
-            const int qs = (qi0 + it) * 64 + hf * 32;              // first query of this thread's 32 columns
-            uint32_t rs[32], rp[32];
-            tmem_ld32(tmem_base + sb * 64 + lane_addr + hf * 32, rs);
-            tmem_ld32(tmem_base + 128 + sb * 64 + lane_addr + hf * 32, rp);
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(sp_empty0 + 8 * sb);
-            const float4* lse4 = reinterpret_cast<const float4*>(sStat + st * 128 + hf * 32);
-            const float4* dv4 = reinterpret_cast<const float4*>(sStat + st * 128 + 64 + hf * 32);
-            const int* dq_ptr = DOC ? a.doc + row_base + qs : nullptr;
-            const float base = ALIBI ? -slope2 * static_cast<float>(qs - j) : 0.f;
-            uint32_t pk[16], dk[16];
+        for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+            const BwdTile t = bwd_tile(w, a.H, HB);
+            const int h = t.h, b = t.b, kt = t.t, k0 = kt * 128, qi0 = kt * 2, nit = a.S / 64 - qi0, row_base = b * a.S;
+            const int j = k0 + row;                                   // key position
+            const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kL2e : 0.f;
+            const int my_doc = DOC ? a.doc[row_base + j] : 0;
+
+            auto block = [&](auto diag_tag, int it) -> bool {
+                constexpr bool DIAG = decltype(diag_tag)::value;
+                const int gi = qc0 + it, st = gi % B_STAGES, sb = gi & 1, u = gi >> 1;
+                if (!mbar_wait(sp_full0 + 8 * sb, u & 1, abort_flag, 6, &g_attn_bwd_error)) return false;
+                tc_fence_after();
+                const int qs = (qi0 + it) * 64 + hf * 32;              // first query of this thread's 32 columns
+                uint32_t rs[32], rp[32];
+                tmem_ld32(tmem_base + sb * 64 + lane_addr + hf * 32, rs);
+                tmem_ld32(tmem_base + 128 + sb * 64 + lane_addr + hf * 32, rp);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sp_empty0 + 8 * sb);
+                const float4* lse4 = reinterpret_cast<const float4*>(sStat + st * 128 + hf * 32);
+                const float4* dv4 = reinterpret_cast<const float4*>(sStat + st * 128 + 64 + hf * 32);
+                const int* dq_ptr = DOC ? a.doc + row_base + qs : nullptr;
+                const float base = ALIBI ? -slope2 * static_cast<float>(qs - j) : 0.f;
+                uint32_t pk[16], dk[16];
 #pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4) {
-                const float4 l4 = lse4[c4], d4 = dv4[c4];
-                const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
-                float pv[4], dsv[4];
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const float4 l4 = lse4[c4], d4 = dv4[c4];
+                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+                    float pv[4], dsv[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int c = c4 * 4 + e;
-                    const float t = (ALIBI ? fmaf(-slope2, static_cast<float>(c), base) : 0.f) - ls[e] * kL2e;
-                    float p = ex2a(fmaf(__uint_as_float(rs[c]), scale2, t));
-                    if (DIAG && j > qs + c) p = 0.f;
-                    if (DOC && dq_ptr[c] != my_doc) p = 0.f;
-                    pv[e] = p;
-                    dsv[e] = p * (__uint_as_float(rp[c]) - dd[e]);
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = c4 * 4 + e;
+                        const float tt = (ALIBI ? fmaf(-slope2, static_cast<float>(c), base) : 0.f) - ls[e] * kL2e;
+                        float p = ex2a(fmaf(__uint_as_float(rs[c]), scale2, tt));
+                        if (DIAG && j > qs + c) p = 0.f;
+                        if (DOC && dq_ptr[c] != my_doc) p = 0.f;
+                        pv[e] = p;
+                        dsv[e] = p * (__uint_as_float(rp[c]) - dd[e]);
+                    }
+                    __nv_bfloat162 t0 = __floats2bfloat162_rn(pv[0], pv[1]), t1 = __floats2bfloat162_rn(pv[2], pv[3]);
+                    __nv_bfloat162 u0 = __floats2bfloat162_rn(dsv[0], dsv[1]), u1 = __floats2bfloat162_rn(dsv[2], dsv[3]);
+                    pk[c4 * 2] = *reinterpret_cast<uint32_t*>(&t0); pk[c4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&t1);
+                    dk[c4 * 2] = *reinterpret_cast<uint32_t*>(&u0); dk[c4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&u1);
                 }
-                __nv_bfloat162 t0 = __floats2bfloat162_rn(pv[0], pv[1]), t1 = __floats2bfloat162_rn(pv[2], pv[3]);
-                __nv_bfloat162 u0 = __floats2bfloat162_rn(dsv[0], dsv[1]), u1 = __floats2bfloat162_rn(dsv[2], dsv[3]);
-                pk[c4 * 2] = *reinterpret_cast<uint32_t*>(&t0); pk[c4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&t1);
-                dk[c4 * 2] = *reinterpret_cast<uint32_t*>(&u0); dk[c4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&u1);
-            }
-            if (u >= 1 && !mbar_wait(pd_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 7, &g_attn_bwd_error)) return false;
-            uint8_t* prow = sPT + sb * BT + row * 128;
-            uint8_t* drow = sDST + sb * BT + row * 128;
+                if (u >= 1 && !mbar_wait(pd_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 7, &g_attn_bwd_error)) return false;
+                uint8_t* prow = sPT + sb * BT + row * 128;
+                uint8_t* drow = sDST + sb * BT + row * 128;
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const int off = ((hf * 4 + g) ^ sw) << 4;
-                *reinterpret_cast<uint4*>(prow + off) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-                *reinterpret_cast<uint4*>(drow + off) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(pd_full0 + 8 * sb);
-            return true;
-        };
-        for (int it = 0; ok && it < 2; ++it) ok = block(std::true_type{}, it);
-        for (int it = 2; ok && it < nit; ++it) ok = block(std::false_type{}, it);
-        if (ok) ok = mbar_wait(done_bar, 0, abort_flag, 8, &g_attn_bwd_error);
-        if (ok) {
-            tc_fence_after();
-            uint32_t rv[32], rk[32];
-            tmem_ld32(tmem_dV + lane_addr + hf * 32, rv);
-            tmem_ld32(tmem_dK + lane_addr + hf * 32, rk);
-            tmem_ld_wait();
-            bf16* kp = a.dqkv + (static_cast<size_t>(row_base) + j) * (3 * d) + d + h * 64 + hf * 32;
-#pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-                Vec16<bf16> ok8, ov8;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    ok8.v[k] = __float2bfloat16_rn(__uint_as_float(rk[c + k]) * a.scale);
-                    ov8.v[k] = __float2bfloat16_rn(__uint_as_float(rv[c + k]));
+                for (int g = 0; g < 4; ++g) {
+                    const int off = ((hf * 4 + g) ^ sw) << 4;
+                    *reinterpret_cast<uint4*>(prow + off) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                    *reinterpret_cast<uint4*>(drow + off) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
                 }
-                st16(kp + c, ok8);
-                st16(kp + d + c, ov8);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(pd_full0 + 8 * sb);
+                return true;
+            };
+            for (int it = 0; ok && it < 2; ++it) ok = block(std::true_type{}, it);
+            for (int it = 2; ok && it < nit; ++it) ok = block(std::false_type{}, it);
+            const int acc = tn & 1;
+            if (ok) ok = mbar_wait(done0 + 8 * acc, (tn >> 1) & 1, abort_flag, 8, &g_attn_bwd_error);
+            if (ok) {
+                tc_fence_after();
+                uint32_t rv[32], rk[32];
+                tmem_ld32(tmem_base + 256 + acc * 128 + lane_addr + hf * 32, rv);
+                tmem_ld32(tmem_base + 320 + acc * 128 + lane_addr + hf * 32, rk);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);       // the accumulators may be overwritten
+                bf16* kp = a.dqkv + (static_cast<size_t>(row_base) + j) * (3 * d) + d + h * 64 + hf * 32;
+#pragma unroll
+                for (int c = 0; c < 32; c += 8) {
+                    Vec16<bf16> ok8, ov8;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        ok8.v[k] = __float2bfloat16_rn(__uint_as_float(rk[c + k]) * a.scale);
+                        ov8.v[k] = __float2bfloat16_rn(__uint_as_float(rv[c + k]));
+                    }
+                    st16(kp + c, ok8);
+                    st16(kp + d + c, ov8);
+                }
             }
+            qc0 += nit;
         }
     }
     tc_fence_before();
@@ -478,7 +541,9 @@ int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const f
     NNB_TRY(tensor_map_2d(dout, d, rows, d, 64, 128, &do128, 2));
     NNB_TRY(tensor_map_2d(dout, d, rows, d, 64, 64, &do64, 2));
     AttnBwdArgs a{dqkv, lse, dvec, doc, B, S, H, 1.0f / sqrtf(static_cast<float>(dk))};
-    dim3 grid(S / 128, H, B);
+    const long long tiles = static_cast<long long>(S / 128) * H * B;
+    NNB_ARG_CHECK(tiles < (1ll << 31), "too many attention tiles");
+    dim3 grid(static_cast<unsigned>(tiles < kSmCount ? tiles : kSmCount));     // persistent: one CTA per SM walks the tile list
     if (doc && alibi) return launch_bwd_tc<true, true>(q128, q64, do128, do64, a, grid, s);
     if (doc) return launch_bwd_tc<true, false>(q128, q64, do128, do64, a, grid, s);
     if (alibi) return launch_bwd_tc<false, true>(q128, q64, do128, do64, a, grid, s);
