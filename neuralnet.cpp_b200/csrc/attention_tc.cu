@@ -126,7 +126,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
         if (lane == 0 && !*abort_flag) {
             int kv = 0, tn = 0;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+            for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
                 const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
                 const int nkb = t.qb + 1, row_base = t.b * a.S, qs = tn & 1;
                 if (!mbar_wait(q_empty0 + 8 * qs, ((tn >> 1) & 1) ^ 1, abort_flag, 11, &g_attn_error)) break;
@@ -147,7 +147,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
         if (lane == 0 && !*abort_flag) {
             int kv0 = 0, tn = 0;                                // kv0: key-block counter at the start of the tile
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+            for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
                 const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
                 const int nkb = t.qb + 1, qs = tn & 1;
                 ok = mbar_wait(q_full0 + 8 * qs, (tn >> 1) & 1, abort_flag, 2, &g_attn_error);
@@ -201,7 +201,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
         bool ok = true, bad = *abort_flag != 0;                 // bad: a wait of this thread gave up (reported at the next barrier)
         int kv0 = 0, xc = 0;                                    // key-block counter; exchange counter (alternates the sX buffer)
 
-        for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps) {
             const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
             const int h = t.h, b = t.b, q0 = t.qb * AQ, nkb = t.qb + 1, row_base = b * a.S;
             const int i = q0 + row;                            // query position inside the sequence

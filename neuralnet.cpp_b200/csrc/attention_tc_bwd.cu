@@ -117,7 +117,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
         if (lane == 0 && !*abort_flag) {
             int kv = 0, tn = 0;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+            for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
                 const BwdTile t = bwd_tile(w, a.H, HB);
                 const int qb = nt - 1 - t.t, q0 = qb * 128, nkb = 2 * (qb + 1), row_base = t.b * a.S, qs = tn & 1;
                 if (!mbar_wait(q_empty0 + 8 * qs, ((tn >> 1) & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error)) break;
@@ -138,7 +138,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
         if (lane == 0 && !*abort_flag) {
             int kv0 = 0, tn = 0;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+            for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
                 const BwdTile t = bwd_tile(w, a.H, HB);
                 const int nkb = 2 * (nt - t.t), qs = tn & 1, use = tn >> 1;
                 ok = mbar_wait(q_full0 + 8 * qs, use & 1, abort_flag, 2, &g_attn_bwd_error);
@@ -191,7 +191,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
         bool ok = !*abort_flag;
         int kv0 = 0, tn = 0;
 
-        for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
             const BwdTile t = bwd_tile(w, a.H, HB);
             const int h = t.h, b = t.b, qb = nt - 1 - t.t, q0 = qb * 128, nkb = 2 * (qb + 1), row_base = b * a.S;
             const int i = q0 + row;
@@ -330,7 +330,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
         if (lane == 0 && !*abort_flag) {
             int qc = 0, tn = 0;                                    // query-block counter across tiles, tile counter
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+            for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
                 const BwdTile t = bwd_tile(w, a.H, HB);
                 const int kt = t.t, k0 = kt * 128, qi0 = kt * 2, nit = a.S / 64 - qi0, row_base = t.b * a.S, ks = tn & 1;
                 const size_t stat_base = (static_cast<size_t>(t.b) * a.H + t.h) * a.S;
@@ -354,7 +354,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
         if (lane == 0 && !*abort_flag) {
             int qc0 = 0, tn = 0;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+            for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
                 const BwdTile t = bwd_tile(w, a.H, HB);
                 const int nit = a.S / 64 - t.t * 2, ks = tn & 1, use = tn >> 1;
                 ok = mbar_wait(kv_full0 + 8 * ks, use & 1, abort_flag, 2, &g_attn_bwd_error);
@@ -410,7 +410,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
         bool ok = !*abort_flag;
         int qc0 = 0, tn = 0;
 
-        for (int w = blockIdx.x; ok && w < total; w += gridDim.x, ++tn) {
+        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
             const BwdTile t = bwd_tile(w, a.H, HB);
             const int h = t.h, b = t.b, kt = t.t, k0 = kt * 128, qi0 = kt * 2, nit = a.S / 64 - qi0, row_base = b * a.S;
             const int j = k0 + row;                                   // key position

@@ -163,6 +163,14 @@ def test_attention_forward_backward(g, dtype, B, S, H, dk, alibi, docs):
         assert np.abs(got - want).max() < tol * scale(want) * 3, name
 
 
+@pytest.mark.parametrize("B,S,H,alibi,docs", [(13, 512, 4, 1, False), (7, 768, 8, 1, True), (5, 1024, 8, 0, False)])
+def test_attention_persistent_tile_loop(g, B, S, H, alibi, docs):
+    """More (tile, head, batch) work items than SMs: every persistent CTA of the tcgen05 kernels walks two or
+    three tiles, so the rings, the double-buffered resident tiles / TMEM accumulators and all barrier phases
+    carry over from one tile to the next (208, 336 and 320 tiles on 148 SMs)."""
+    test_attention_forward_backward(g, 1, B, S, H, 64, alibi, docs)
+
+
 def test_attention_matches_reference_primitives_golden(g):
     """The reference's five two-pass primitives (golden outputs of its CPU engine) against the fused
     kernels: m, l -> lse; O; gradQ/gradK/gradV with P = dO V^T."""
