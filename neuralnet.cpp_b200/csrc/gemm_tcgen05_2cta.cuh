@@ -172,17 +172,25 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const bool row_ok = m < p.M;
             const long long row_off = static_cast<long long>(m) * p.ldc;
             if (m0 < p.M) {
+            // In the bf16 case (two 32-column halves per block) the second half is fetched from TMEM while the first
+            // is converted.  Nothing is fetched across loop iterations: a register written by tcgen05.ld must not be
+            // touched, not even moved by the compiler at a loop edge, before the wait that follows it.
+            uint32_t ra[32], rb[32];
+            const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+            const bool piped = CB == 64 && !(p.debug & 8);
 #pragma unroll 1
             for (int cb = grp; cb * CB < BN; cb += 2) {
                 const int n0 = tile_n * BN + cb * CB;
                 if (n0 >= p.N) break;
                 if (elected) tma_wait_read0();                   // the group's previous store has read the staging tile
                 group_bar(bar_id);
-                uint32_t ra[32], rb[32];
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + cb * CB;
-                if (!(p.debug & 8)) {
-                    tmem_ld32(taddr, ra);
-                    if (CB == 64) tmem_ld32(taddr + 32, rb);
+                if (piped) {
+                    tmem_ld32(tbase + cb * CB, ra);
+                    tmem_ld_wait();
+                    tmem_ld32(tbase + cb * CB + 32, rb);         // in flight while the first half is converted
+                } else if (!(p.debug & 8)) {
+                    tmem_ld32(tbase + cb * CB, ra);
+                    if (CB == 64) tmem_ld32(tbase + cb * CB + 32, rb);
                     tmem_ld_wait();
                 } else {
 #pragma unroll
@@ -225,6 +233,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     }
                 };
                 emit(ra, 0);
+                if (piped) tmem_ld_wait();                       // second half
                 if (CB == 64) emit(rb, 1);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 group_bar(bar_id);
