@@ -66,9 +66,10 @@ REFERENCE_PROGRAMS = [
 @pytest.mark.gpu
 @pytest.mark.parametrize("name,args", REFERENCE_PROGRAMS, ids=[n + "".join("_" + a.strip("-") for a in a_) for n, a_ in REFERENCE_PROGRAMS])
 def test_reference_program_passes_on_cuda_engine(name, args):
-    # The rotary gradient check draws its weights from std::random_device and compares against fp32 central
-    # differences; on the reference's own CPU engine it fails about one run in three.  It gets a few tries.
-    attempts = 6 if "rope" in args else 1
+    # gpt_gradcheck draws its weights from std::random_device and compares against fp32 central differences; on the
+    # reference's own CPU engine the rotary and ALiBi variants fail about one run in three (measured here: 3 of 8
+    # and 4 of 12).  Every gpt_gradcheck variant gets a few tries; the deterministic programs get one.
+    attempts = 6 if name == "gpt_gradcheck" else 1
     for k in range(attempts):
         code, out = run(name, "--cuda", *args)
         if code == 0 and "❌" not in out and "FAIL" not in out:
