@@ -18,7 +18,7 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
-from . import _lib
+from . import _lib, checkpoint
 from ._lib import GptConfigC, call
 
 ACT_GELU, ACT_SWIGLU = 0, 1
@@ -169,6 +169,44 @@ class GptTrainer:
 
     def get_grads(self) -> List[np.ndarray]:
         return self._split(self.grads)
+
+    # -------------------------------------------------------------- checkpoints
+    def load_reference_checkpoint(self, path: str) -> bytes:
+        """Loads the parameters of a model file written by the reference (save_model, format v4,
+        model_serialization.hpp:389-428) — the analogue of load_model: the stored model description must match
+        this trainer's configuration and every matrix the shape the model expects.  Returns the embedded
+        tokenizer JSON (empty if none)."""
+        spec, buf, off = checkpoint.read_model_file(path)
+        checkpoint.check_spec_against_config(spec, self.cfg)
+        mats, tok = checkpoint.split_matrices(buf, off, [(r, c) for _, r, c in self.table])
+        self.load_params(mats)
+        return tok
+
+    def save_reference_checkpoint(self, path: str, tokenizer: bytes = b""):
+        """Writes the fp32 master weights as a reference model file that load_model / text_train --resume /
+        text_infer read."""
+        checkpoint.write_model_file(path, checkpoint.spec_of_config(self.cfg), self.get_params(), tokenizer)
+
+    def save_training_state(self, path: str):
+        """Everything a resumed run needs and the reference file lacks: parameters, Adam moments (the Muon
+        velocity of the hidden matrices lives in the first-moment arena) and the step counter."""
+        c = self.cfg
+        host = lambda t: t.detach().cpu().numpy()
+        checkpoint.save_training_state(path, {"params": host(self.params), "m": host(self.m), "v": host(self.v)}, self.t,
+                                       [c.vocab, c.d_model, c.heads, c.layers, c.d_ff, c.seq, c.act, c.norm, c.pos, int(self.muon)])
+
+    def load_training_state(self, path: str):
+        arenas, step, cfgv = checkpoint.load_training_state(path)
+        c = self.cfg
+        if cfgv != [c.vocab, c.d_model, c.heads, c.layers, c.d_ff, c.seq, c.act, c.norm, c.pos, int(self.muon)]:
+            raise ValueError("training state was written for a different model configuration or optimizer split")
+        for name, dst in (("params", self.params), ("m", self.m), ("v", self.v)):
+            if arenas[name].size != self.arena_elems:
+                raise ValueError(f"training state arena '{name}' has the wrong size")
+            dst.copy_(torch.from_numpy(arenas[name]))
+        self.t = step
+        self.grads.zero_()
+        self.refresh_shadow()
 
     # -------------------------------------------------------------- step pieces
     def _ints(self, a):
