@@ -238,6 +238,24 @@ class GptTrainer:
         call("nnb200_gpt_backward", C.byref(self._c), _ptr(self.params), _ptr(self.shadow), _ptr(self.grads),
              _ptr(self.workspace), _ptr(self._tokens), _ptr(self._docs), ev, _stream())
 
+    def evaluate(self, batches) -> float:
+        """Evaluation pass of the reference driver (src/text_train.cpp:1367-1466): forward and sparse cross-entropy
+        without backward, over an iterable of (tokens, labels[, loss_mask[, doc_ids]]); returns the per-batch losses
+        averaged with each batch's count of valid targets as weight, which is what the driver prints as test_loss.
+        Gradients are left untouched."""
+        weighted, valid = 0.0, 0.0
+        o = self._off["ce_stats"]
+        for b in batches:
+            tokens, labels = b[0], b[1]
+            mask = b[2] if len(b) > 2 else None
+            docs = b[3] if len(b) > 3 else None
+            self.forward(tokens, docs)
+            self.loss_and_grad(labels, mask, 1.0)          # overwrites the logits in the workspace; no gradient leaves it
+            n = float(self.workspace[o:o + 4].view(torch.float32).item())     # valid targets of this batch
+            weighted += float(self.loss_tensor().item()) * n
+            valid += n
+        return weighted / valid if valid > 0 else 0.0
+
     def loss_tensor(self) -> torch.Tensor:
         """Device view of the scalar loss of the last loss_and_grad call."""
         o = self._off["loss"]

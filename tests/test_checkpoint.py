@@ -142,6 +142,32 @@ def test_reference_driver_resumes_from_a_checkpoint_the_fused_trainer_wrote(tmp_
 
 
 @pytest.mark.gpu
+def test_evaluation_pass_weights_batches_by_valid_targets():
+    """GptTrainer.evaluate against the oracle on the fixture checkpoint: two batches with different numbers of masked
+    targets, averaged as the reference driver averages its test loss (text_train.cpp:1455-1463)."""
+    from oracle import gpt_oracle as go
+    from tests import gpu_util
+    nnb = gpu_util.nnb
+    tr = _trainer(nnb, nnb.FP32)
+    tr.load_reference_checkpoint(os.path.join(FIX, "start.bin"))
+    ocfg, _ = _fixture_shapes()
+    model = go.GptOracle(ocfg, tr.get_params())
+    r = np.random.default_rng(5)
+    batches, num, den = [], 0.0, 0.0
+    for keep in (0.9, 0.4):
+        x, y = _batch(int(keep * 10))
+        mask = (r.random(x.size) < keep).astype(np.float32)
+        batches.append((x, y, mask))
+        loss, _ = go.ce_forward_sparse(model.forward(x), y.astype(np.float32), mask, 414)
+        num += float(loss) * float(mask.sum())
+        den += float(mask.sum())
+    before = [g.copy() for g in tr.get_grads()]
+    got = tr.evaluate(batches)
+    assert abs(got - num / den) <= 1e-5 * abs(num / den), (got, num / den)
+    assert all(np.array_equal(a, b) for a, b in zip(before, tr.get_grads()))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("muon", [False, True])
 def test_training_state_resume_is_exact_in_check_mode(tmp_path, muon):
     """Save after three steps, run two more; a fresh trainer that loads the state runs the same two steps to the
