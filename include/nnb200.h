@@ -175,6 +175,16 @@ int nnb200_embedding_backward(float* token_grad, float* pos_grad, const int32_t*
                               int batch, int seq, int d, int vocab, int dtype, void* stream);
 size_t nnb200_embedding_scratch_bytes(int tokens_n);
 
+/* Rotary position encoding (RotaryEmbedding, compute_layer.hpp:876-988).  nnb200_rope_table fills a HOST buffer of
+ * seq*head_dim floats: cos (seq, head_dim/2) then sin (seq, head_dim/2), theta = pos / 10000^(2j/head_dim) computed with
+ * the reference's float calls; the caller copies it to the device.  nnb200_rope_apply rotates, in place, the Q and K
+ * thirds of a token-major buffer whose rows (length ld) start with heads*head_dim Q then K values, token i at sequence
+ * position i % seq: x[j] <- x[j] c - x[j+h/2] s, x[j+h/2] <- x[j+h/2] c + x[j] s; backward=1 applies the inverse
+ * rotation (to the gradients).  Replaces RotaryEmbedding::apply and the expression program it submits. */
+int nnb200_rope_table(int seq, int head_dim, float* host_out);
+int nnb200_rope_apply(void* qkv, const float* table, int tokens_n, int seq, int heads, int head_dim, long long ld, int backward,
+                      int dtype, void* stream);
+
 /* ===================================================================================== *
  * 4. Optimizers over flat fp32 ranges                                                    *
  * ===================================================================================== */
@@ -213,7 +223,7 @@ typedef struct nnb200_gpt_config {
     int32_t vocab, d_model, heads, layers, d_ff, seq, batch;
     int32_t act;        /* 0 QuickGeLU, 1 SwiGLU          (ActivationType, model_spec.hpp:33-37) */
     int32_t norm;       /* 0 LayerNorm, 1 RMSNorm         (NormType, model_spec.hpp:40-45)       */
-    int32_t pos;        /* 0 learned, 1 sinusoidal, 2 ALiBi (PosEncodingType, model_spec.hpp:24-30) */
+    int32_t pos;        /* 0 learned, 1 sinusoidal, 2 ALiBi, 3 rotary (PosEncodingType, model_spec.hpp:24-30) */
     int32_t precision;  /* 0 fp32 check mode, 1 bf16 tensor-core mode with fp32 master weights   */
     int32_t reserved[5];
 } nnb200_gpt_config;
@@ -232,7 +242,7 @@ long long nnb200_gpt_workspace_bytes(const nnb200_gpt_config* cfg);
 /* Byte offset of a named buffer inside the workspace, for inspection: 0 logits (tokens, vocab),
  * 1 loss scalar (1 float), 2 gradient w.r.t. the embedded input (tokens, d), 3 CE stats. */
 long long nnb200_gpt_workspace_offset(const nnb200_gpt_config* cfg, int which);
-/* Fills the constant tables of the workspace (sinusoidal positions).  Call once, and again after
+/* Fills the constant tables of the workspace (sinusoidal positions or rotary cos/sin).  Call once, and again after
  * the workspace moved. */
 int nnb200_gpt_init_workspace(const nnb200_gpt_config* cfg, void* workspace, void* stream);
 /* tokens, doc_ids (NULL = none): int32 (batch*seq), batch-major.  Logits are left in the workspace.

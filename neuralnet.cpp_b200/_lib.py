@@ -112,6 +112,8 @@ SIGNATURES = {
     "nnb200_rt_zero": [_p, _sz],
     "nnb200_rt_sync": [],
     "nnb200_gemm_pair_capacity": [],
+    "nnb200_rope_table": [_i, _i, _p],
+    "nnb200_rope_apply": [_p, _p, _i, _i, _i, _i, _ll, _i, _i, _p],
 }
 _RET = {
     "nnb200_launch_count": C.c_ulonglong,

@@ -203,6 +203,21 @@ int nnb200_embedding_backward(float* token_grad, float* pos_grad, const int32_t*
 }
 size_t nnb200_embedding_scratch_bytes(int tokens_n) { return embed_bwd_scratch_bytes(tokens_n); }
 
+int nnb200_rope_table(int seq, int head_dim, float* host_out)
+{
+    NNB_ARG_CHECK(seq > 0 && head_dim > 0 && head_dim % 2 == 0 && host_out, "rotary table needs seq > 0 and an even head size");
+    rope_table_host(seq, head_dim, host_out);
+    return 0;
+}
+int nnb200_rope_apply(void* qkv, const float* table, int tokens_n, int seq, int heads, int head_dim, long long ld, int backward,
+                      int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    NNB_ARG_CHECK(seq > 0 && tokens_n % seq == 0 && ld >= 2LL * heads * head_dim, "tokens must be whole sequences and rows must hold Q and K");
+    if (dtype == 1) return rope_apply<bf16>(static_cast<bf16*>(qkv), table, tokens_n, seq, heads, head_dim, ld, backward != 0, to_stream(stream));
+    return rope_apply<float>(static_cast<float*>(qkv), table, tokens_n, seq, heads, head_dim, ld, backward != 0, to_stream(stream));
+}
+
 int nnb200_adamw_step(float* p, const float* g, float* m, float* v, void* shadow_bf16, size_t n, float lr, float beta1,
                       float beta2, float eps, float weight_decay, int t_next, const float* grad_scale_dev, void* stream)
 {

@@ -8,6 +8,8 @@
 // adds rows in ascending i (cpu_engine.hpp:203-214); atomics cannot reproduce that order, so the
 // token positions are sorted by (id, i) and each destination row is accumulated by one block that
 // walks its segment in ascending i — the fp32 result is bit-identical to the sequential loop.
+#include <cmath>
+
 #include "kernels.h"
 
 namespace nnb {
@@ -238,6 +240,76 @@ __global__ void pos_bwd_kernel(float* __restrict__ pos_grad, const T* __restrict
         for (int b = 0; b < batch; ++b) acc += to_f32(g[static_cast<size_t>(b) * n + i]);
         pos_grad[i] = acc;
     }
+}
+
+// Rotary position encoding on the Q and K thirds of a token-major qkv buffer, in place (RotaryEmbedding::apply,
+// compute_layer.hpp:926-945): for j < dk/2 of every head, with c, s = table[t][j]
+//   forward   x[j] <- x[j] c - x[j+dk/2] s ,  x[j+dk/2] <- x[j+dk/2] c + x[j] s
+//   backward  the inverse rotation, applied to the gradients of Q and K
+// table: cos (seq, dk/2) then sin (seq, dk/2), fp32, built on the host with the reference's float calls.
+template <typename T, int VEC>
+__global__ void rope_kernel(T* __restrict__ qkv, const float* __restrict__ table, long long items, int seq, int heads, int dk,
+                            long long ld, int backward)
+{
+    const int half = dk / 2, vph = half / VEC;                 // vectors per half head
+    const float* cos_t = table;
+    const float* sin_t = table + static_cast<size_t>(seq) * half;
+    for (long long w = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; w < items;
+         w += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int jv = static_cast<int>(w % vph);
+        long long r = w / vph;
+        const int h = static_cast<int>(r % heads); r /= heads;
+        const int which = static_cast<int>(r % 2);              // 0: Q, 1: K
+        const long long tok = r / 2;
+        const int t = static_cast<int>(tok % seq), j0 = jv * VEC;
+        T* lo = qkv + tok * ld + static_cast<long long>(which) * heads * dk + h * dk + j0;
+        T* hi = lo + half;
+        float a[VEC], b[VEC];
+        if (VEC > 1) {
+            const Vec16<T> va = ld16(lo), vb = ld16(hi);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) { a[k] = to_f32(va.v[k]); b[k] = to_f32(vb.v[k]); }
+        } else { a[0] = to_f32(lo[0]); b[0] = to_f32(hi[0]); }
+        Vec16<T> oa, ob;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            const float c = cos_t[static_cast<size_t>(t) * half + j0 + k];
+            const float sn = backward ? -sin_t[static_cast<size_t>(t) * half + j0 + k] : sin_t[static_cast<size_t>(t) * half + j0 + k];
+            oa.v[k] = from_f32<T>(a[k] * c - b[k] * sn);
+            ob.v[k] = from_f32<T>(b[k] * c + a[k] * sn);
+        }
+        if (VEC > 1) { st16(lo, oa); st16(hi, ob); }
+        else { lo[0] = oa.v[0]; hi[0] = ob.v[0]; }
+    }
+}
+
+template <typename T>
+int rope_apply(T* qkv, const float* table, int ntok, int seq, int heads, int dk, long long ld, bool backward, cudaStream_t s)
+{
+    if (ntok == 0) return 0;
+    NNB_ARG_CHECK(dk > 0 && dk % 2 == 0, "rotary encoding needs an even head size");      // compute_layer.hpp:929-930
+    constexpr int VN = Vec16<T>::N;
+    const int half = dk / 2;
+    const bool vec = (half % VN) == 0 && (ld % VN) == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0;
+    const long long items = static_cast<long long>(ntok) * 2 * heads * (vec ? half / VN : half);
+    if (vec) rope_kernel<T, VN><<<grid_for(items, 256), 256, 0, s>>>(qkv, table, items, seq, heads, dk, ld, backward ? 1 : 0);
+    else rope_kernel<T, 1><<<grid_for(items, 256), 256, 0, s>>>(qkv, table, items, seq, heads, dk, ld, backward ? 1 : 0);
+    NNB_LAUNCH_CHECK();
+    return 0;
+}
+template int rope_apply<float>(float*, const float*, int, int, int, int, long long, bool, cudaStream_t);
+template int rope_apply<bf16>(bf16*, const float*, int, int, int, int, long long, bool, cudaStream_t);
+
+// host: the table the kernel reads, computed as RotaryEmbedding::fill_pos_column_ does (compute_layer.hpp:886-902)
+void rope_table_host(int seq, int dk, float* out)
+{
+    const int half = dk / 2;
+    for (int pos = 0; pos < seq; ++pos)
+        for (int j = 0; j < half; ++j) {
+            const float theta = static_cast<float>(pos) / std::pow(10000.0f, static_cast<float>(2 * j) / static_cast<float>(dk));
+            out[static_cast<size_t>(pos) * half + j] = std::cos(theta);
+            out[static_cast<size_t>(seq) * half + static_cast<size_t>(pos) * half + j] = std::sin(theta);
+        }
 }
 
 static int next_pow2(int n) { int p = 1; while (p < n) p <<= 1; return p; }

@@ -30,7 +30,8 @@ static bool config_ok(const nnb200_gpt_config* c)
 {
     return c && c->vocab > 0 && c->d_model > 0 && c->heads > 0 && c->layers > 0 && c->d_ff > 0 && c->seq > 0 &&
            c->batch > 0 && c->d_model % c->heads == 0 && c->act >= 0 && c->act <= 1 && c->norm >= 0 && c->norm <= 1 &&
-           c->pos >= 0 && c->pos <= 2 && c->precision >= 0 && c->precision <= 1;
+           c->pos >= 0 && c->pos <= 3 && (c->pos != 3 || (c->d_model / c->heads) % 2 == 0) && c->precision >= 0 &&
+           c->precision <= 1;
 }
 
 static ArenaLayout make_layout(const nnb200_gpt_config& c)
@@ -187,6 +188,8 @@ static int forward_t(const nnb200_gpt_config& c, const float* P, const bf16* H, 
         T* x_next = (l + 1 < c.layers) ? A(W.layers[l + 1].x_in) : A(W.x_final);
         NNB_TRY(norm_fwd<T>(A(a.x_in), P + lp.g1, PB(lp.be1), A(a.xn1), F(a.rinv1), F(a.mean1), N, d, ln, s));
         NNB_TRY(linear_fwd<T>(A(a.xn1), P + lp.wqkv, H ? H + lp.wqkv : nullptr, P + lp.bqkv, nullptr, A(a.qkv), N, d, 3 * d, s));
+        // rotary positions: Q and K are rotated in place, so the backward pass sees the rotated values (AttentionBase::forward, compute_layer.hpp:1178-1185)
+        if (c.pos == 3) NNB_TRY(rope_apply<T>(A(a.qkv), F(W.sin_table), N, c.seq, c.heads, d / c.heads, 3 * d, false, s));
         NNB_TRY(attention_fwd<T>(A(a.qkv), A(a.attn), F(a.lse), doc, c, s));
         NNB_TRY(linear_fwd<T>(A(a.attn), P + lp.wo, H ? H + lp.wo : nullptr, P + lp.bo, A(a.x_in), A(a.x_mid), N, d, d, s));
         NNB_TRY(norm_fwd<T>(A(a.x_mid), P + lp.g2, PB(lp.be2), A(a.xn2), F(a.rinv2), F(a.mean2), N, d, ln, s));
@@ -243,6 +246,8 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         NNB_TRY(linear_bwd_params<T>(g, A(a.attn), G + lp.wo, nullptr, cs, cn, N, d, d, s));
         NNB_TRY(linear_bwd_input<T>(g, P + lp.wo, Hh(lp.wo), A(W.d_attn), N, d, d, s));
         NNB_TRY(attention_bwd<T>(A(a.qkv), A(a.attn), A(W.d_attn), F(a.lse), F(W.dvec), A(W.d_qkv), doc, c, s));
+        // the gradients of the rotated Q and K go back through the inverse rotation (compute_layer.hpp:1365-1372)
+        if (c.pos == 3) NNB_TRY(rope_apply<T>(A(W.d_qkv), F(W.sin_table), N, c.seq, c.heads, d / c.heads, 3 * d, true, s));
         NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, cn, N, d, 3 * d, s));
         NNB_TRY(linear_bwd_input<T>(A(W.d_qkv), P + lp.wqkv, Hh(lp.wqkv), A(W.d_xn), N, d, 3 * d, s));
         NNB_TRY(norm_bwd<T>(A(W.d_xn), A(a.x_in), P + lp.g1, F(a.rinv1), F(a.mean1), g, g_other, G + lp.g1, GB(lp.be1), cs, N,
@@ -321,6 +326,16 @@ int nnb200_gpt_init_workspace(const nnb200_gpt_config* cfg, void* workspace, voi
     // the column-sum kernels expect their completion counters to start at zero (they reset them after use)
     NNB_CUDA_CHECK(cudaMemsetAsync(static_cast<uint8_t*>(workspace) + make_workspace(*cfg).counters, 0,
                                    kColsumCounters * sizeof(int), to_stream(stream)));
+    if (cfg->pos == 3) {
+        // rotary tables share the slot of the sinusoidal table (seq * d_k floats fit in seq * d_model)
+        const Workspace W = make_workspace(*cfg);
+        std::vector<float> tab(static_cast<size_t>(cfg->seq) * (cfg->d_model / cfg->heads));
+        rope_table_host(cfg->seq, cfg->d_model / cfg->heads, tab.data());
+        NNB_CUDA_CHECK(cudaMemcpyAsync(static_cast<uint8_t*>(workspace) + W.sin_table, tab.data(), tab.size() * 4,
+                                       cudaMemcpyHostToDevice, to_stream(stream)));
+        NNB_CUDA_CHECK(cudaStreamSynchronize(to_stream(stream)));   // `tab` is pageable host memory about to go away
+        return 0;
+    }
     if (cfg->pos != 1) return 0;
     // SinusoidalPositionEncoder (compute_layer.hpp:2604-2622): built on the host with the same
     // float pow/sin/cos calls as the reference, so the table is bit-identical to the CPU engine's

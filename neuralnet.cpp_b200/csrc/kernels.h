@@ -56,6 +56,9 @@ template <typename T> int embed_fwd(const float* tok_emb, const float* pos_table
 template <typename T> int embed_bwd(float* tok_grad, float* pos_grad, const int* tokens, const T* g, void* scratch,
                                     int batch, int seq, int d, int vocab, cudaStream_t s);
 size_t embed_bwd_scratch_bytes(int n_tok);
+template <typename T> int rope_apply(T* qkv, const float* table, int ntok, int seq, int heads, int dk, long long ld,
+                                    bool backward, cudaStream_t s);
+void rope_table_host(int seq, int dk, float* out);   // cos (seq, dk/2) then sin (seq, dk/2)
 
 // ---- attention_simt.cu / attention_mma.cu
 template <typename T> int attention_fwd_simt(const T* qkv, T* out, float* lse, const int* doc, int B, int S, int H, int dk,

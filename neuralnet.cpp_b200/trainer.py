@@ -23,7 +23,7 @@ from ._lib import GptConfigC, call
 
 ACT_GELU, ACT_SWIGLU = 0, 1
 NORM_LAYER, NORM_RMS = 0, 1
-POS_LEARNED, POS_SINUSOIDAL, POS_ALIBI = 0, 1, 2
+POS_LEARNED, POS_SINUSOIDAL, POS_ALIBI, POS_ROPE = 0, 1, 2, 3
 FP32, BF16 = 0, 1
 
 

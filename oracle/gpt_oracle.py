@@ -24,7 +24,7 @@ F32 = np.float32
 
 ACT_GELU, ACT_SWIGLU = 0, 1
 NORM_LAYER, NORM_RMS = 0, 1
-POS_LEARNED, POS_SINUSOIDAL, POS_ALIBI = 0, 1, 2
+POS_LEARNED, POS_SINUSOIDAL, POS_ALIBI, POS_ROPE = 0, 1, 2, 3
 OPT_ADAMW, OPT_MUON_SPLIT = 0, 1
 
 
@@ -116,6 +116,26 @@ def sinusoidal_table(seq: int, d: int) -> np.ndarray:
         angle = F32(pos) / denom
         pe[pos] = np.where(i % 2 == 0, np.sin(angle, dtype=F32), np.cos(angle, dtype=F32))
     return pe
+
+
+def rope_tables(seq: int, d_k: int):
+    """RotaryEmbedding::fill_pos_column_ (compute_layer.hpp:886-902): cos/sin tables (d_k, seq) with
+    theta = pos / 10000^(2j/d_k) in fp32, rows j and j + d_k/2 alike."""
+    half = d_k // 2
+    j = np.arange(half, dtype=F32)
+    inv = np.power(F32(10000), (F32(2) * j) / F32(d_k)).astype(F32)          # std::pow(float, float)
+    theta = (np.arange(seq, dtype=F32)[None, :] / inv[:, None]).astype(F32)
+    c, s_ = np.cos(theta).astype(F32), np.sin(theta).astype(F32)
+    return np.concatenate([c, c], axis=0), np.concatenate([s_, s_], axis=0)
+
+
+def rope_apply(x, cos, sin, backward=False):
+    """RotaryEmbedding::apply (compute_layer.hpp:926-945) on (BH, d_k, S): x*cos +/- rotate_half(x)*sin, where
+    rotate_half reads the other half of the head dimension and negates what it puts into the first half."""
+    half = x.shape[1] // 2
+    rot = np.concatenate([-x[:, half:], x[:, :half]], axis=1)
+    out = x * cos[None] - rot * sin[None] if backward else x * cos[None] + rot * sin[None]
+    return out.astype(F32)
 
 
 def alibi_slopes(heads: int) -> np.ndarray:
@@ -337,6 +357,7 @@ class GptOracle:
         self.grads = [np.zeros_like(p) for p in self.params]
         self.slopes = alibi_slopes(cfg.heads)
         self.sin_table = sinusoidal_table(cfg.seq, cfg.d_model) if cfg.pos == POS_SINUSOIDAL else None
+        self.rope = rope_tables(cfg.seq, cfg.d_k) if cfg.pos == POS_ROPE else None
 
     def p(self, name):
         return self.params[self.index[name]]
@@ -383,6 +404,8 @@ class GptOracle:
         q = rearrange_3d(self._linear(prefix + "wq", x), c.d_model, c.batch, S).reshape(BH, dk, S)
         k = rearrange_3d(self._linear(prefix + "wk", x), c.d_model, c.batch, S).reshape(BH, dk, S)
         v = rearrange_3d(self._linear(prefix + "wv", x), c.d_model, c.batch, S).reshape(BH, dk, S)
+        if self.rope is not None:                                  # compute_layer.hpp:1178-1185
+            q, k = rope_apply(q, *self.rope), rope_apply(k, *self.rope)
         scale = F32(1) / np.sqrt(F32(dk))
         s = scale * np.einsum("bki,bkj->bij", q, k).astype(F32) + mask
         s = s - s.max(axis=2, keepdims=True)
@@ -405,6 +428,8 @@ class GptOracle:
         gs = a * (ga - (a * ga).sum(axis=2, keepdims=True, dtype=F32))   # Softmax::backward (:851-861)
         gq = scale * np.einsum("bkj,bij->bki", k, gs).astype(F32)
         gk = scale * np.einsum("bki,bij->bkj", q, gs).astype(F32)
+        if self.rope is not None:                                  # compute_layer.hpp:1365-1372
+            gq, gk = rope_apply(gq, *self.rope, backward=True), rope_apply(gk, *self.rope, backward=True)
         back = lambda t: rearrange_3d(t.reshape(BH * dk, S), c.d_model, c.batch, S, inverse=True)
         x = cache["x"]
         gx = self._linear_backward(prefix + "wq", x, back(gq))

@@ -7,7 +7,7 @@ from oracle import gpt_oracle as go
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 GPT_CASES = ["ln_gelu_learned", "rms_swiglu_sin_clip", "rms_swiglu_alibi_accum", "docs_muon",
-             "tile_rms_swiglu_alibi", "tile_docs_learned"]
+             "tile_rms_swiglu_alibi", "tile_docs_learned", "rms_swiglu_rope", "tile_rope_docs"]
 INT_KW = {"steps", "accum", "optimizer", "warmup", "total_steps"}
 
 

@@ -401,3 +401,37 @@ def test_muon_step_matches_oracle(g, precision, rows, cols):
     upd = g.host(tp) - p0
     tol = 3e-2 if precision else 1e-4
     assert np.linalg.norm(upd - upd_ref) < tol * np.linalg.norm(upd_ref)
+
+
+# ----------------------------------------------------------------------------------------------
+# rotary position encoding
+# ----------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("B,S,H,dk", [(2, 16, 4, 8), (3, 24, 2, 64), (1, 40, 3, 6)])
+def test_rope_apply_matches_oracle_and_inverts(g, dtype, B, S, H, dk):
+    """Q and K thirds of a token-major qkv buffer against RotaryEmbedding as restated by the oracle; V untouched;
+    backward is the inverse rotation."""
+    import torch
+    from oracle import gpt_oracle as go
+    r = _rng(dk + S)
+    d, N = H * dk, B * S
+    rnd = g.bf16_round if dtype == 1 else (lambda a: np.asarray(a, np.float32))
+    qkv = rnd(r.standard_normal((N, 3 * d)))
+    table = np.zeros(S * dk, np.float32)
+    g.call("nnb200_rope_table", S, dk, table.ctypes.data_as(C.c_void_p))
+    cos, sin = go.rope_tables(S, dk)
+    assert np.array_equal(table[:S * dk // 2].reshape(S, dk // 2), cos[:dk // 2].T)       # same float calls as the reference
+    assert np.array_equal(table[S * dk // 2:].reshape(S, dk // 2), sin[:dk // 2].T)
+    tdt = torch.bfloat16 if dtype == 1 else torch.float32
+    t_qkv, t_tab = g.dev(qkv, tdt), g.dev(table)
+    g.call("nnb200_rope_apply", g.ptr(t_qkv), g.ptr(t_tab), N, S, H, dk, 3 * d, 0, dtype, g.stream())
+    got = g.host(t_qkv)
+    heads = lambda x: x.reshape(B, S, H, dk).transpose(0, 2, 3, 1).reshape(B * H, dk, S)          # (BH, dk, S) as the reference holds it
+    back = lambda x: x.reshape(B, H, dk, S).transpose(0, 3, 1, 2).reshape(N, d)
+    tol = 1e-2 if dtype == 1 else 1e-6
+    for third in (0, 1):
+        want = back(go.rope_apply(heads(qkv[:, third * d:(third + 1) * d]), cos, sin))
+        assert np.abs(got[:, third * d:(third + 1) * d] - want).max() <= tol * np.abs(want).max()
+    assert np.array_equal(got[:, 2 * d:], qkv[:, 2 * d:])
+    g.call("nnb200_rope_apply", g.ptr(t_qkv), g.ptr(t_tab), N, S, H, dk, 3 * d, 1, dtype, g.stream())
+    assert np.abs(g.host(t_qkv) - qkv).max() <= (2e-2 if dtype == 1 else 1e-5) * np.abs(qkv).max()
