@@ -420,8 +420,9 @@ def test_rope_apply_matches_oracle_and_inverts(g, dtype, B, S, H, dk):
     table = np.zeros(S * dk, np.float32)
     g.call("nnb200_rope_table", S, dk, table.ctypes.data_as(C.c_void_p))
     cos, sin = go.rope_tables(S, dk)
-    assert np.array_equal(table[:S * dk // 2].reshape(S, dk // 2), cos[:dk // 2].T)       # same float calls as the reference
-    assert np.array_equal(table[S * dk // 2:].reshape(S, dk // 2), sin[:dk // 2].T)
+    # fp32 pow / cos / sin of the C library against numpy's: equal to an ulp or two of values in [-1, 1]
+    assert np.abs(table[:S * dk // 2].reshape(S, dk // 2) - cos[:dk // 2].T).max() <= 5e-7
+    assert np.abs(table[S * dk // 2:].reshape(S, dk // 2) - sin[:dk // 2].T).max() <= 5e-7
     tdt = torch.bfloat16 if dtype == 1 else torch.float32
     t_qkv, t_tab = g.dev(qkv, tdt), g.dev(table)
     g.call("nnb200_rope_apply", g.ptr(t_qkv), g.ptr(t_tab), N, S, H, dk, 3 * d, 0, dtype, g.stream())
