@@ -22,7 +22,6 @@ __device__ int g_attn_bwd_error = 0;
 
 constexpr int BT = 128 * 128;          // bytes of a 128-row x 64-bf16 tile
 constexpr int HT = 64 * 128;           // bytes of a 64-row tile
-constexpr int B_STAGES = 3;
 constexpr float kL2e = 1.4426950408889634f;
 
 struct AttnBwdArgs {
@@ -47,10 +46,15 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 constexpr uint32_t IDESC_KK = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(64 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
 constexpr uint32_t IDESC_KM = IDESC_KK | (1u << 16);
 
-// Both kernels are persistent: one CTA per SM walks a list of (tile, head, batch) work items, heaviest
-// tiles first.  The resident tile (Q, dO resp. K, V) and the gradient accumulators in TMEM are double-
-// buffered, the rings, score buffers and barrier phases run on across tiles, so the loads and first MMAs of
-// the next tile overlap the tail and the write-out of the current one.
+// Both kernels are persistent: the CTAs resident on an SM walk a list of (tile, head, batch) work items, heaviest
+// tiles first, in snake order.  The rings, score buffers and barrier phases run on across tiles, so the loads and
+// first MMAs of the next tile overlap the tail and the write-out of the current one.  Two builds of each kernel:
+//   NB = 1 (default)  two CTAs per SM, every resource single-buffered (K/V ring of 2, 256 TMEM columns, 80 / 97 KB of
+//                     shared memory, 96 registers): while the workers of one CTA are in their dependency chain
+//                     (scores ready -> tcgen05.ld -> exp -> dS tile -> next MMA) the other CTA's MMAs run.
+//                     Measured 219 us against 255 us per layer at batch 16 x 12 heads x 1024.
+//   NB = 2            one CTA per SM with the resident tile, the score buffers and the TMEM gradient accumulators
+//                     double-buffered inside the CTA (environment NNB200_ATTN_BWD_CTAS=1, for comparison).
 struct BwdTile { int t, h, b; };
 __device__ __forceinline__ BwdTile bwd_tile(int w, int H, int HB)
 {
@@ -66,20 +70,28 @@ __device__ __forceinline__ BwdTile bwd_tile(int w, int H, int HB)
 // dQ
 // ======================================================================================
 // shared memory: Q (2) | dO (2) | ring of (K, V) 64-key tiles | dS (2 buffers) | barriers
-constexpr int DQ_OFF_DO = 2 * BT, DQ_OFF_RING = 4 * BT, DQ_OFF_DS = DQ_OFF_RING + B_STAGES * 2 * HT, DQ_OFF_BAR = DQ_OFF_DS + 2 * BT,
-              DQ_SMEM = DQ_OFF_BAR + 256;
+// NB = buffers per resource: 2 (one CTA per SM, everything double-buffered inside the CTA) or 1 (two CTAs per SM, each
+// single-buffered, so that one CTA's MMAs run while the other's workers are in their dependency chain)
+template <int NB> struct DqLayout {
+    static constexpr int ST = NB + 1;                               // (K, V) ring stages
+    static constexpr int OFF_DO = NB * BT, OFF_RING = 2 * NB * BT, OFF_DS = OFF_RING + ST * 2 * HT, OFF_BAR = OFF_DS + NB * BT,
+                         SMEM = OFF_BAR + 256;
+    static constexpr uint32_t TMEM_COLS = NB == 2 ? 512u : 256u;    // S | dP | dQ, 64 columns per buffer
+};
 
-template <bool DOC, bool ALIBI>
-__global__ void __launch_bounds__(320, 1)
+template <bool DOC, bool ALIBI, int NB>
+__global__ void __launch_bounds__(320, 3 - NB)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_constant__ CUtensorMap tmKV64,
                       const __grid_constant__ CUtensorMap tmDO128, const AttnBwdArgs a)
 {
+    using LY = DqLayout<NB>;
+    constexpr int ST = LY::ST;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;                            // tile buffer q at +q*BT
-    uint8_t* sDO = smem + DQ_OFF_DO;
-    uint8_t* sRing = smem + DQ_OFF_RING;           // stage s: K at +s*2*HT, V right after
-    uint8_t* sDS = smem + DQ_OFF_DS;               // buffer b at +b*BT
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DQ_OFF_BAR);
+    uint8_t* sDO = smem + LY::OFF_DO;
+    uint8_t* sRing = smem + LY::OFF_RING;           // stage s: K at +s*2*HT, V right after
+    uint8_t* sDS = smem + LY::OFF_DS;               // buffer b at +b*BT
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + LY::OFF_BAR);
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t q_full0 = bar0, q_empty0 = bar0 + 16, kv_full0 = bar0 + 32, kv_empty0 = bar0 + 56, sp_full0 = bar0 + 80,
                    sp_empty0 = bar0 + 96, ds_full0 = bar0 + 112, ds_empty0 = bar0 + 128, done0 = bar0 + 144, acc_empty0 = bar0 + 160;
@@ -92,7 +104,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) { mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1); }
-        for (int s = 0; s < B_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
+        for (int s = 0; s < ST; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
         for (int s = 0; s < 2; ++s) {
             mbar_init(sp_full0 + 8 * s, 1); mbar_init(sp_empty0 + 8 * s, 8);
             mbar_init(ds_full0 + 8 * s, 8); mbar_init(ds_empty0 + 8 * s, 1);
@@ -104,14 +116,14 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(DqLayout<NB>::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // TMEM columns: S buffers at 0 / 64, dP buffers at 128 / 192, dQ accumulators at 256 / 320
+    // TMEM columns, 64 per buffer: S buffers first, then the dP buffers, then the dQ accumulators
 
     if (warp == 0) {
         if (lane == 0 && !*abort_flag) {
@@ -119,14 +131,14 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
             bool ok = true;
             for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
                 const BwdTile t = bwd_tile(w, a.H, HB);
-                const int qb = nt - 1 - t.t, q0 = qb * 128, nkb = 2 * (qb + 1), row_base = t.b * a.S, qs = tn & 1;
-                if (!mbar_wait(q_empty0 + 8 * qs, ((tn >> 1) & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error)) break;
+                const int qb = nt - 1 - t.t, q0 = qb * 128, nkb = 2 * (qb + 1), row_base = t.b * a.S, qs = tn % NB;
+                if (!mbar_wait(q_empty0 + 8 * qs, ((tn / NB) & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error)) break;
                 mbar_expect_tx(q_full0 + 8 * qs, 2 * BT);
                 tma_load_2d(smem_u32(sQ + qs * BT), &tmQ128, q_full0 + 8 * qs, t.h * 64, row_base + q0);
                 tma_load_2d(smem_u32(sDO + qs * BT), &tmDO128, q_full0 + 8 * qs, t.h * 64, row_base + q0);
                 for (int kb = 0; kb < nkb; ++kb, ++kv) {
-                    const int st = kv % B_STAGES;
-                    if (!mbar_wait(kv_empty0 + 8 * st, ((kv / B_STAGES) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) { ok = false; break; }
+                    const int st = kv % ST;
+                    if (!mbar_wait(kv_empty0 + 8 * st, ((kv / ST) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) { ok = false; break; }
                     mbar_expect_tx(kv_full0 + 8 * st, 2 * HT);
                     const uint32_t dst = smem_u32(sRing + st * 2 * HT);
                     tma_load_2d(dst, &tmKV64, kv_full0 + 8 * st, d + t.h * 64, row_base + kb * 64);
@@ -140,15 +152,15 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
             bool ok = true;
             for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
                 const BwdTile t = bwd_tile(w, a.H, HB);
-                const int nkb = 2 * (nt - t.t), qs = tn & 1, use = tn >> 1;
+                const int nkb = 2 * (nt - t.t), qs = tn % NB, use = tn / NB;
                 ok = mbar_wait(q_full0 + 8 * qs, use & 1, abort_flag, 2, &g_attn_bwd_error);
                 // the accumulator this tile writes was read out two tiles ago
                 if (ok && use >= 1) ok = mbar_wait(acc_empty0 + 8 * qs, (use - 1) & 1, abort_flag, 12, &g_attn_bwd_error);
                 const uint32_t q_addr = smem_u32(sQ + qs * BT), do_addr = smem_u32(sDO + qs * BT);
-                const uint32_t tmem_dQ = tmem_base + 256 + qs * 64;
+                const uint32_t tmem_dQ = tmem_base + 2 * NB * 64 + qs * 64;
                 auto issue_sdp = [&](int gj) -> bool {
-                    const int st = gj % B_STAGES, sb = gj & 1, u = gj >> 1;
-                    if (!mbar_wait(kv_full0 + 8 * st, (gj / B_STAGES) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
+                    const int st = gj % ST, sb = gj % NB, u = gj / NB;
+                    if (!mbar_wait(kv_full0 + 8 * st, (gj / ST) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
                     if (u >= 1 && !mbar_wait(sp_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 4, &g_attn_bwd_error)) return false;
                     tc_fence_after();
                     const uint32_t k_addr = smem_u32(sRing + st * 2 * HT), v_addr = k_addr + HT;
@@ -157,13 +169,13 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
                         umma_bf16(tmem_base + sb * 64, smem_desc(q_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_base + 128 + sb * 64, smem_desc(do_addr + k * 32, 16, 1024), smem_desc(v_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
+                        umma_bf16(tmem_base + NB * 64 + sb * 64, smem_desc(do_addr + k * 32, 16, 1024), smem_desc(v_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
                     umma_commit(sp_full0 + 8 * sb);
                     return true;
                 };
                 auto issue_dq = [&](int gj, bool first) -> bool {
-                    const int st = gj % B_STAGES, sb = gj & 1;
-                    if (!mbar_wait(ds_full0 + 8 * sb, (gj >> 1) & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
+                    const int st = gj % ST, sb = gj % NB;
+                    if (!mbar_wait(ds_full0 + 8 * sb, (gj / NB) & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
                     tc_fence_after();
                     const uint32_t ds_addr = smem_u32(sDS + sb * BT), k_addr = smem_u32(sRing + st * 2 * HT);
 #pragma unroll
@@ -202,13 +214,13 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
 
             auto block = [&](auto diag_tag, int kb) -> bool {
                 constexpr bool DIAG = decltype(diag_tag)::value;
-                const int gj = kv0 + kb, sb = gj & 1, u = gj >> 1;
+                const int gj = kv0 + kb, sb = gj % NB, u = gj / NB;
                 if (!mbar_wait(sp_full0 + 8 * sb, u & 1, abort_flag, 6, &g_attn_bwd_error)) return false;
                 tc_fence_after();
                 const int k0 = kb * 64 + hf * 32;                     // first key of this thread's 32 columns
                 uint32_t rs[32], rp[32];
                 tmem_ld32(tmem_base + sb * 64 + lane_addr + hf * 32, rs);
-                tmem_ld32(tmem_base + 128 + sb * 64 + lane_addr + hf * 32, rp);
+                tmem_ld32(tmem_base + NB * 64 + sb * 64 + lane_addr + hf * 32, rp);
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -243,12 +255,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
             };
             for (int kb = 0; ok && kb < nkb - 2; ++kb) ok = block(std::false_type{}, kb);
             for (int kb = nkb - 2; ok && kb < nkb; ++kb) ok = block(std::true_type{}, kb);
-            const int acc = tn & 1;
-            if (ok) ok = mbar_wait(done0 + 8 * acc, (tn >> 1) & 1, abort_flag, 8, &g_attn_bwd_error);
+            const int acc = tn % NB;
+            if (ok) ok = mbar_wait(done0 + 8 * acc, (tn / NB) & 1, abort_flag, 8, &g_attn_bwd_error);
             if (ok) {
                 tc_fence_after();
                 uint32_t r[32];
-                tmem_ld32(tmem_base + 256 + acc * 64 + lane_addr + hf * 32, r);
+                tmem_ld32(tmem_base + 2 * NB * 64 + acc * 64 + lane_addr + hf * 32, r);
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -269,7 +281,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(DqLayout<NB>::TMEM_COLS) : "memory");
     }
 }
 
@@ -277,22 +289,28 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
 // dK, dV
 // ======================================================================================
 // shared memory: K (2) | V (2) | ring of (Q, dO) 64-query tiles | P^T (2) | dS^T (2) | lse, D per stage | barriers
-constexpr int KV_OFF_V = 2 * BT, KV_OFF_RING = 4 * BT, KV_OFF_PT = KV_OFF_RING + B_STAGES * 2 * HT, KV_OFF_DST = KV_OFF_PT + 2 * BT,
-              KV_OFF_STAT = KV_OFF_DST + 2 * BT, KV_OFF_BAR = KV_OFF_STAT + B_STAGES * 512, KV_SMEM = KV_OFF_BAR + 256;
+template <int NB> struct KvLayout {
+    static constexpr int ST = NB + 1;                               // (Q, dO) ring stages
+    static constexpr int OFF_V = NB * BT, OFF_RING = 2 * NB * BT, OFF_PT = OFF_RING + ST * 2 * HT, OFF_DST = OFF_PT + NB * BT,
+                         OFF_STAT = OFF_DST + NB * BT, OFF_BAR = OFF_STAT + ST * 512, SMEM = OFF_BAR + 256;
+    static constexpr uint32_t TMEM_COLS = NB == 2 ? 512u : 256u;    // S^T | dP^T | (dV, dK) per accumulator pair
+};
 
-template <bool DOC, bool ALIBI>
-__global__ void __launch_bounds__(320, 1)
+template <bool DOC, bool ALIBI, int NB>
+__global__ void __launch_bounds__(320, 3 - NB)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid_constant__ CUtensorMap tmQ64,
                        const __grid_constant__ CUtensorMap tmDO64, const AttnBwdArgs a)
 {
+    using LY = KvLayout<NB>;
+    constexpr int ST = LY::ST;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sK = smem;                            // tile buffer k at +k*BT
-    uint8_t* sV = smem + KV_OFF_V;
-    uint8_t* sRing = smem + KV_OFF_RING;           // stage s: Q at +s*2*HT, dO right after
-    uint8_t* sPT = smem + KV_OFF_PT;
-    uint8_t* sDST = smem + KV_OFF_DST;
-    float* sStat = reinterpret_cast<float*>(smem + KV_OFF_STAT);   // [stage][lse(64) | D(64)]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + KV_OFF_BAR);
+    uint8_t* sV = smem + LY::OFF_V;
+    uint8_t* sRing = smem + LY::OFF_RING;           // stage s: Q at +s*2*HT, dO right after
+    uint8_t* sPT = smem + LY::OFF_PT;
+    uint8_t* sDST = smem + LY::OFF_DST;
+    float* sStat = reinterpret_cast<float*>(smem + LY::OFF_STAT);   // [stage][lse(64) | D(64)]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + LY::OFF_BAR);
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t kv_full0 = bar0, kv_empty0 = bar0 + 16, q_full0 = bar0 + 32, q_empty0 = bar0 + 56, sp_full0 = bar0 + 80,
                    sp_empty0 = bar0 + 96, pd_full0 = bar0 + 112, pd_empty0 = bar0 + 128, done0 = bar0 + 144, acc_empty0 = bar0 + 160;
@@ -305,7 +323,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-        for (int s = 0; s < B_STAGES; ++s) { mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1); }
+        for (int s = 0; s < ST; ++s) { mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1); }
         for (int s = 0; s < 2; ++s) {
             mbar_init(sp_full0 + 8 * s, 1); mbar_init(sp_empty0 + 8 * s, 8);
             mbar_init(pd_full0 + 8 * s, 8); mbar_init(pd_empty0 + 8 * s, 1);
@@ -317,14 +335,14 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(KvLayout<NB>::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // TMEM columns: S^T buffers at 0 / 64, dP^T at 128 / 192, accumulator pair a: dV at 256 + 128a, dK at 320 + 128a
+    // TMEM columns, 64 per buffer: S^T buffers, dP^T buffers, then per accumulator pair dV and dK
 
     if (warp == 0) {
         if (lane == 0 && !*abort_flag) {
@@ -332,15 +350,15 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
             bool ok = true;
             for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
                 const BwdTile t = bwd_tile(w, a.H, HB);
-                const int kt = t.t, k0 = kt * 128, qi0 = kt * 2, nit = a.S / 64 - qi0, row_base = t.b * a.S, ks = tn & 1;
+                const int kt = t.t, k0 = kt * 128, qi0 = kt * 2, nit = a.S / 64 - qi0, row_base = t.b * a.S, ks = tn % NB;
                 const size_t stat_base = (static_cast<size_t>(t.b) * a.H + t.h) * a.S;
-                if (!mbar_wait(kv_empty0 + 8 * ks, ((tn >> 1) & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error)) break;
+                if (!mbar_wait(kv_empty0 + 8 * ks, ((tn / NB) & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error)) break;
                 mbar_expect_tx(kv_full0 + 8 * ks, 2 * BT);
                 tma_load_2d(smem_u32(sK + ks * BT), &tmKV128, kv_full0 + 8 * ks, d + t.h * 64, row_base + k0);
                 tma_load_2d(smem_u32(sV + ks * BT), &tmKV128, kv_full0 + 8 * ks, 2 * d + t.h * 64, row_base + k0);
                 for (int it = 0; it < nit; ++it, ++qc) {
-                    const int st = qc % B_STAGES, qs = (qi0 + it) * 64;
-                    if (!mbar_wait(q_empty0 + 8 * st, ((qc / B_STAGES) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) { ok = false; break; }
+                    const int st = qc % ST, qs = (qi0 + it) * 64;
+                    if (!mbar_wait(q_empty0 + 8 * st, ((qc / ST) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) { ok = false; break; }
                     mbar_expect_tx(q_full0 + 8 * st, 2 * HT + 512);
                     const uint32_t dst = smem_u32(sRing + st * 2 * HT);
                     tma_load_2d(dst, &tmQ64, q_full0 + 8 * st, t.h * 64, row_base + qs);
@@ -356,14 +374,14 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
             bool ok = true;
             for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
                 const BwdTile t = bwd_tile(w, a.H, HB);
-                const int nit = a.S / 64 - t.t * 2, ks = tn & 1, use = tn >> 1;
+                const int nit = a.S / 64 - t.t * 2, ks = tn % NB, use = tn / NB;
                 ok = mbar_wait(kv_full0 + 8 * ks, use & 1, abort_flag, 2, &g_attn_bwd_error);
                 if (ok && use >= 1) ok = mbar_wait(acc_empty0 + 8 * ks, (use - 1) & 1, abort_flag, 12, &g_attn_bwd_error);
                 const uint32_t k_addr = smem_u32(sK + ks * BT), v_addr = smem_u32(sV + ks * BT);
-                const uint32_t tmem_dV = tmem_base + 256 + ks * 128, tmem_dK = tmem_dV + 64;
+                const uint32_t tmem_dV = tmem_base + 2 * NB * 64 + ks * 128, tmem_dK = tmem_dV + 64;
                 auto issue_st = [&](int gi) -> bool {
-                    const int st = gi % B_STAGES, sb = gi & 1, u = gi >> 1;
-                    if (!mbar_wait(q_full0 + 8 * st, (gi / B_STAGES) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
+                    const int st = gi % ST, sb = gi % NB, u = gi / NB;
+                    if (!mbar_wait(q_full0 + 8 * st, (gi / ST) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
                     if (u >= 1 && !mbar_wait(sp_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 4, &g_attn_bwd_error)) return false;
                     tc_fence_after();
                     const uint32_t q_addr = smem_u32(sRing + st * 2 * HT), do_addr = q_addr + HT;
@@ -372,13 +390,13 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                         umma_bf16(tmem_base + sb * 64, smem_desc(k_addr + k * 32, 16, 1024), smem_desc(q_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_base + 128 + sb * 64, smem_desc(v_addr + k * 32, 16, 1024), smem_desc(do_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
+                        umma_bf16(tmem_base + NB * 64 + sb * 64, smem_desc(v_addr + k * 32, 16, 1024), smem_desc(do_addr + k * 32, 16, 1024), IDESC_KK, k > 0);
                     umma_commit(sp_full0 + 8 * sb);
                     return true;
                 };
                 auto issue_dkv = [&](int gi, bool first) -> bool {
-                    const int st = gi % B_STAGES, sb = gi & 1;
-                    if (!mbar_wait(pd_full0 + 8 * sb, (gi >> 1) & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
+                    const int st = gi % ST, sb = gi % NB;
+                    if (!mbar_wait(pd_full0 + 8 * sb, (gi / NB) & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
                     tc_fence_after();
                     const uint32_t pt_addr = smem_u32(sPT + sb * BT), dst_addr = smem_u32(sDST + sb * BT);
                     const uint32_t q_addr = smem_u32(sRing + st * 2 * HT), do_addr = q_addr + HT;
@@ -419,13 +437,13 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
 
             auto block = [&](auto diag_tag, int it) -> bool {
                 constexpr bool DIAG = decltype(diag_tag)::value;
-                const int gi = qc0 + it, st = gi % B_STAGES, sb = gi & 1, u = gi >> 1;
+                const int gi = qc0 + it, st = gi % ST, sb = gi % NB, u = gi / NB;
                 if (!mbar_wait(sp_full0 + 8 * sb, u & 1, abort_flag, 6, &g_attn_bwd_error)) return false;
                 tc_fence_after();
                 const int qs = (qi0 + it) * 64 + hf * 32;              // first query of this thread's 32 columns
                 uint32_t rs[32], rp[32];
                 tmem_ld32(tmem_base + sb * 64 + lane_addr + hf * 32, rs);
-                tmem_ld32(tmem_base + 128 + sb * 64 + lane_addr + hf * 32, rp);
+                tmem_ld32(tmem_base + NB * 64 + sb * 64 + lane_addr + hf * 32, rp);
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -471,13 +489,13 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
             };
             for (int it = 0; ok && it < 2; ++it) ok = block(std::true_type{}, it);
             for (int it = 2; ok && it < nit; ++it) ok = block(std::false_type{}, it);
-            const int acc = tn & 1;
-            if (ok) ok = mbar_wait(done0 + 8 * acc, (tn >> 1) & 1, abort_flag, 8, &g_attn_bwd_error);
+            const int acc = tn % NB;
+            if (ok) ok = mbar_wait(done0 + 8 * acc, (tn / NB) & 1, abort_flag, 8, &g_attn_bwd_error);
             if (ok) {
                 tc_fence_after();
                 uint32_t rv[32], rk[32];
-                tmem_ld32(tmem_base + 256 + acc * 128 + lane_addr + hf * 32, rv);
-                tmem_ld32(tmem_base + 320 + acc * 128 + lane_addr + hf * 32, rk);
+                tmem_ld32(tmem_base + 2 * NB * 64 + acc * 128 + lane_addr + hf * 32, rv);
+                tmem_ld32(tmem_base + 2 * NB * 64 + 64 + acc * 128 + lane_addr + hf * 32, rk);
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -502,28 +520,44 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(KvLayout<NB>::TMEM_COLS) : "memory");
     }
 }
 
 // ======================================================================================
 // host
 // ======================================================================================
-template <bool DOC, bool ALIBI>
-static int launch_bwd_tc(const CUtensorMap& q128, const CUtensorMap& q64, const CUtensorMap& do128, const CUtensorMap& do64,
-                         const AttnBwdArgs& a, dim3 grid, cudaStream_t s)
+// CTAs per SM of the backward kernels: 2 by default, 1 with NNB200_ATTN_BWD_CTAS=1 (read once; for A/B timing)
+static int bwd_ctas_per_sm()
+{
+    static const int n = [] { const char* e = getenv("NNB200_ATTN_BWD_CTAS"); return (e && e[0] == '1') ? 1 : 2; }();
+    return n;
+}
+
+template <bool DOC, bool ALIBI, int NB>
+static int launch_bwd_tc_nb(const CUtensorMap& q128, const CUtensorMap& q64, const CUtensorMap& do128, const CUtensorMap& do64,
+                            const AttnBwdArgs& a, long long tiles, cudaStream_t s)
 {
     static bool attr_set = false;
     if (!attr_set) {
-        NNB_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<DOC, ALIBI>, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM));
-        NNB_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<DOC, ALIBI>, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM));
+        NNB_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<DOC, ALIBI, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqLayout<NB>::SMEM));
+        NNB_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<DOC, ALIBI, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, KvLayout<NB>::SMEM));
         attr_set = true;
     }
-    attn_bwd_dq_tc_kernel<DOC, ALIBI><<<grid, 320, DQ_SMEM, s>>>(q128, q64, do128, a);
+    const long long cap = static_cast<long long>(kSmCount) * (3 - NB);          // persistent: NB = 1 runs two CTAs per SM
+    const dim3 grid(static_cast<unsigned>(tiles < cap ? tiles : cap));
+    attn_bwd_dq_tc_kernel<DOC, ALIBI, NB><<<grid, 320, DqLayout<NB>::SMEM, s>>>(q128, q64, do128, a);
     NNB_LAUNCH_CHECK();
-    attn_bwd_dkv_tc_kernel<DOC, ALIBI><<<grid, 320, KV_SMEM, s>>>(q128, q64, do64, a);
+    attn_bwd_dkv_tc_kernel<DOC, ALIBI, NB><<<grid, 320, KvLayout<NB>::SMEM, s>>>(q128, q64, do64, a);
     NNB_LAUNCH_CHECK();
     return 0;
+}
+template <bool DOC, bool ALIBI>
+static int launch_bwd_tc(const CUtensorMap& q128, const CUtensorMap& q64, const CUtensorMap& do128, const CUtensorMap& do64,
+                         const AttnBwdArgs& a, long long tiles, cudaStream_t s)
+{
+    if (bwd_ctas_per_sm() == 2) return launch_bwd_tc_nb<DOC, ALIBI, 1>(q128, q64, do128, do64, a, tiles, s);
+    return launch_bwd_tc_nb<DOC, ALIBI, 2>(q128, q64, do128, do64, a, tiles, s);
 }
 
 int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const float* lse, float* dvec, bf16* dqkv,
@@ -543,11 +577,10 @@ int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const f
     AttnBwdArgs a{dqkv, lse, dvec, doc, B, S, H, 1.0f / sqrtf(static_cast<float>(dk))};
     const long long tiles = static_cast<long long>(S / 128) * H * B;
     NNB_ARG_CHECK(tiles < (1ll << 31), "too many attention tiles");
-    dim3 grid(static_cast<unsigned>(tiles < kSmCount ? tiles : kSmCount));     // persistent: one CTA per SM walks the tile list
-    if (doc && alibi) return launch_bwd_tc<true, true>(q128, q64, do128, do64, a, grid, s);
-    if (doc) return launch_bwd_tc<true, false>(q128, q64, do128, do64, a, grid, s);
-    if (alibi) return launch_bwd_tc<false, true>(q128, q64, do128, do64, a, grid, s);
-    return launch_bwd_tc<false, false>(q128, q64, do128, do64, a, grid, s);
+    if (doc && alibi) return launch_bwd_tc<true, true>(q128, q64, do128, do64, a, tiles, s);
+    if (doc) return launch_bwd_tc<true, false>(q128, q64, do128, do64, a, tiles, s);
+    if (alibi) return launch_bwd_tc<false, true>(q128, q64, do128, do64, a, tiles, s);
+    return launch_bwd_tc<false, false>(q128, q64, do128, do64, a, tiles, s);
 }
 
 int attention_bwd_device_error(int* code)
