@@ -18,8 +18,13 @@ __device__ __forceinline__ float sigmoidf_ref(float x) { return 1.0f / (1.0f + e
 // bf16 mode rounds every activation to 8 mantissa bits anyway: use the fast exp / reciprocal there
 template <typename T> __device__ __forceinline__ float sigmoid_t(float x)
 {
-    if constexpr (sizeof(T) == 2) return __frcp_rn(1.0f + __expf(-x));
+    if constexpr (sizeof(T) == 2) return __fdividef(1.0f, 1.0f + __expf(-x));   // one reciprocal instruction; 0 for x < -87
     else return sigmoidf_ref(x);
+}
+template <typename T> __device__ __forceinline__ float exp_t(float x)
+{
+    if constexpr (sizeof(T) == 2) return __expf(x);
+    else return expf(x);
 }
 
 // ======================================================================================
@@ -236,7 +241,7 @@ norm_bwd_dx_reg_kernel(const T* __restrict__ g, const T* __restrict__ x, const f
 // registers.  Warps fold through shared memory, blocks write partials, and the block that finishes
 // last adds the partials up in fixed order: deterministic, no extra pass over the activations.
 constexpr int kNormFusedBlocks = 296;   // two per SM
-constexpr int kNormFoldGroup = 8;       // blocks per first-level fold group
+constexpr int kNormFoldGroup = 17;      // blocks per first-level fold group: about the square root of the block count, so both levels read as many rows
 constexpr int kNormFoldCounters = 64;   // ints at the end of the counter array: one per group, the last for the groups
 
 template <typename T, bool LAYER, int NV>
@@ -359,12 +364,16 @@ norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const fl
         float* dst = qn == 0 ? dgamma : (qn == 1 ? dbeta : osum);
         const float* src = gpartial + qn * gstride;
         for (int c4 = threadIdx.x; c4 < D / 4; c4 += 256) {
+            // all group rows are requested before the first is used: one round trip to L2 instead of one per row
+            constexpr int MAXG = (kNormFusedBlocks + kNormFoldGroup - 1) / kNormFoldGroup;
+            float4 v[MAXG];
+#pragma unroll
+            for (int k = 0; k < MAXG; ++k)
+                if (k < ngroups) v[k] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * D) + c4);
             float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-            for (int k = 0; k < ngroups; ++k) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * D) + c4);
-                t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
-            }
+#pragma unroll
+            for (int k = 0; k < MAXG; ++k)
+                if (k < ngroups) { t.x += v[k].x; t.y += v[k].y; t.z += v[k].z; t.w += v[k].w; }
             float4 o = reinterpret_cast<float4*>(dst)[c4];
             o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
             reinterpret_cast<float4*>(dst)[c4] = o;
@@ -654,9 +663,9 @@ ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const 
             const int i = threadIdx.x + j * blockDim.x;
             if (i < nvec) {
 #pragma unroll
-                for (int k = 0; k < VN; ++k) { ex[j][k] = expf(to_f32(cache[j].v[k]) - mx); den += ex[j][k]; } }
+                for (int k = 0; k < VN; ++k) { ex[j][k] = exp_t<T>(to_f32(cache[j].v[k]) - mx); den += ex[j][k]; } }
         }
-    } else for (int i = threadIdx.x; i < V; i += blockDim.x) den += expf(to_f32(row[i]) - mx);
+    } else for (int i = threadIdx.x; i < V; i += blockDim.x) den += exp_t<T>(to_f32(row[i]) - mx);
     den = block_sum(den, red);
     const float ll = to_f32(row[lbl]);
     __syncthreads();                                  // everyone has read row[lbl] before it is overwritten
@@ -676,7 +685,7 @@ ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const 
                 st16(row + i * VN, o); }
         }
     } else for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        float gv = inv * expf(to_f32(row[i]) - mx) / den;
+        float gv = inv * exp_t<T>(to_f32(row[i]) - mx) / den;
         if (i == lbl) gv -= inv;
         row[i] = from_f32<T>(gv);
     }
