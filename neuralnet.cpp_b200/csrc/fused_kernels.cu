@@ -26,6 +26,15 @@ template <typename T> __device__ __forceinline__ float exp_t(float x)
     if constexpr (sizeof(T) == 2) return __expf(x);
     else return expf(x);
 }
+// N consecutive floats (N a multiple of 4, p 16-byte aligned) with 16-byte loads: a per-lane slice of a parameter vector
+template <int N> __device__ __forceinline__ void ld_f32x(const float* __restrict__ p, float* out)
+{
+#pragma unroll
+    for (int k = 0; k < N; k += 4) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(p + k));
+        out[k] = t.x; out[k + 1] = t.y; out[k + 2] = t.z; out[k + 3] = t.w;
+    }
+}
 
 // ======================================================================================
 // normalisation: one warp per token row
@@ -131,29 +140,37 @@ norm_bwd_dx_kernel(const T* __restrict__ g, const T* __restrict__ x, const float
 // Register-resident variants for d == 32 * NV * (elements per 16 bytes): a lane keeps its NV vectors of
 // the row and of gamma/beta in registers, so every activation is read once and the parameters once per warp.
 template <typename T, bool LAYER, int NV>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 norm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
                     T* __restrict__ y, float* __restrict__ rinv_out, float* __restrict__ mean_out, int rows)
 {
     constexpr int VN = Vec16<T>::N, D = 32 * NV * VN;
     const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    // the first row is requested before the parameters, and every next row before the current one is reduced
+    const int stride = gridDim.x * wpb;
+    int r = blockIdx.x * wpb + (threadIdx.x >> 5);
+    Vec16<T> nx[NV];
+    if (r < rows) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) nx[v] = ld16(x + static_cast<size_t>(r) * D + (v * 32 + lane) * VN);
+    }
     float gm[NV][VN], bt[NV][VN];
 #pragma unroll
-    for (int v = 0; v < NV; ++v)
-#pragma unroll
-        for (int k = 0; k < VN; ++k) {
-            const int c = (v * 32 + lane) * VN + k;
-            gm[v][k] = gamma[c];
-            bt[v][k] = LAYER ? beta[c] : 0.f;
-        }
+    for (int v = 0; v < NV; ++v) {
+        ld_f32x<VN>(gamma + (v * 32 + lane) * VN, gm[v]);
+        if (LAYER) ld_f32x<VN>(beta + (v * 32 + lane) * VN, bt[v]);
+    }
     const float inv_d = 1.0f / static_cast<float>(D);
-    for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
-        const T* xr = x + static_cast<size_t>(r) * D;
+    for (; r < rows; r += stride) {
         float xv[NV][VN];
 #pragma unroll
-        for (int v = 0; v < NV; ++v) { const Vec16<T> t = ld16(xr + (v * 32 + lane) * VN);
+        for (int v = 0; v < NV; ++v)
 #pragma unroll
-            for (int k = 0; k < VN; ++k) xv[v][k] = to_f32(t.v[k]); }
+            for (int k = 0; k < VN; ++k) xv[v][k] = to_f32(nx[v].v[k]);
+        if (r + stride < rows) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) nx[v] = ld16(x + static_cast<size_t>(r + stride) * D + (v * 32 + lane) * VN);
+        }
         float mean = 0.f;
         if (LAYER) {
             float sm = 0.f;
@@ -195,9 +212,7 @@ norm_bwd_dx_reg_kernel(const T* __restrict__ g, const T* __restrict__ x, const f
     const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
     float gm[NV][VN];
 #pragma unroll
-    for (int v = 0; v < NV; ++v)
-#pragma unroll
-        for (int k = 0; k < VN; ++k) gm[v][k] = gamma[(v * 32 + lane) * VN + k];
+    for (int v = 0; v < NV; ++v) ld_f32x<VN>(gamma + (v * 32 + lane) * VN, gm[v]);
     const float inv_d = 1.0f / static_cast<float>(D);
     for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
         const size_t off = static_cast<size_t>(r) * D;
@@ -259,7 +274,9 @@ norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const fl
 #pragma unroll
     for (int v = 0; v < NV; ++v)
 #pragma unroll
-        for (int k = 0; k < VN; ++k) { gm[v][k] = gamma[(v * 32 + lane) * VN + k]; a_dg[v][k] = 0.f; a_db[v][k] = 0.f; a_os[v][k] = 0.f; }
+        for (int k = 0; k < VN; ++k) { a_dg[v][k] = 0.f; a_db[v][k] = 0.f; a_os[v][k] = 0.f; }
+#pragma unroll
+    for (int v = 0; v < NV; ++v) ld_f32x<VN>(gamma + (v * 32 + lane) * VN, gm[v]);
     const float inv_d = 1.0f / static_cast<float>(D);
     for (int r = blockIdx.x * wpb + warp; r < rows; r += gridDim.x * wpb) {
         const size_t off = static_cast<size_t>(r) * D;
@@ -820,12 +837,14 @@ int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rin
 {
     if (rows == 0) return 0;
     const int grid = grid_for(rows, 8);
+    const int grid_reg = grid_for(rows, 8, 3);          // the register-resident kernel: one wave of three blocks per SM, rows prefetched
     constexpr int VN = Vec16<T>::N;
-    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(gamma) |
+                           reinterpret_cast<uintptr_t>(beta)) & 15) == 0;
 #define NNB_NORM_FWD_REG(nv)                                                                                          \
     if (aligned && d == 32 * VN * nv) {                                                                               \
-        if (layer) norm_fwd_reg_kernel<T, true, nv><<<grid, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows);         \
-        else norm_fwd_reg_kernel<T, false, nv><<<grid, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows);              \
+        if (layer) norm_fwd_reg_kernel<T, true, nv><<<grid_reg, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows);     \
+        else norm_fwd_reg_kernel<T, false, nv><<<grid_reg, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows);          \
         LAUNCH_CHECK();                                                                                               \
         return 0;                                                                                                     \
     }
@@ -887,7 +906,7 @@ int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, cons
     const int grid = grid_for(rows, 8);
     constexpr int VN = Vec16<T>::N;
     const bool aligned = ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) |
-                           reinterpret_cast<uintptr_t>(add)) & 15) == 0;
+                           reinterpret_cast<uintptr_t>(add) | reinterpret_cast<uintptr_t>(gamma)) & 15) == 0;
     const bool out_ok = ((reinterpret_cast<uintptr_t>(dgamma) | reinterpret_cast<uintptr_t>(dbeta) |
                           reinterpret_cast<uintptr_t>(out_colsum)) & 15) == 0;
     // fused path: needs the caller's zero-initialised completion counter and norm_bwd_scratch_floats of scratch

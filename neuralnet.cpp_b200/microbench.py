@@ -3,6 +3,9 @@
 
   python neuralnet.cpp_b200/microbench.py                   the whole sweep, one JSON line per case
   python neuralnet.cpp_b200/microbench.py --only gemm        one family: gemm | attention | ce | rmsnorm | step_gemms
+  python neuralnet.cpp_b200/microbench.py --only train_step --shape 2,16 --iters 2 --no-time
+                                                             training steps of a shallow copy of the benchmark model (layers,
+                                                             micro-batch): every kernel of the step on ~2 GB, for profiler captures
   python neuralnet.cpp_b200/microbench.py --only gemm --shape 16384,4096,768 --iters 3 --no-time
                                                              a few launches of one shape (for an ncu capture)
 
@@ -172,6 +175,29 @@ def run_rmsnorm(rows, d, args):
              peak_source=src)
 
 
+def run_train_step(layers, batch, args):
+    """The benchmark model (d 768, 12 heads, SwiGLU 2048, RMSNorm, ALiBi, vocab 8192, seq 1024, bf16) with `layers` layers:
+    forward + loss + backward + AdamW per step, token ids from a seed."""
+    cfg = nnb.GptConfig(8192, 768, 12, layers, 2048, 1024, batch, nnb.ACT_SWIGLU, nnb.NORM_RMS, nnb.POS_ALIBI, nnb.BF16)
+    tr = nnb.GptTrainer(cfg, lr=3e-4, weight_decay=0.01)
+    tr.init_params_normal(seed=42, std=0.02)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    ids = torch.randint(0, 8192, (batch, 1025), device="cuda", generator=g, dtype=torch.int32)
+    tok, lab = ids[:, :-1].reshape(-1).contiguous(), ids[:, 1:].reshape(-1).contiguous()
+    mask = torch.ones(batch * 1024, device="cuda")
+
+    def step():
+        tr.micro_step(tok, lab, mask, None, grad_scale=1.0, last=True)
+        tr.optimizer_step(lr=3e-4)
+    if args.no_time:
+        for _ in range(args.iters):
+            step()
+        torch.cuda.synchronize()
+        return
+    ms = timed(step, args.iters, False)
+    emit(kernel="train_step", layers=layers, micro_batch=batch, seq=1024, ms=ms, tokens_per_s=batch * 1024 / ms * 1e3)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="all")
@@ -199,6 +225,8 @@ def main():
             run_attention(*s, args)
     if fam in ("all", "ce"):
         run_ce(*(shape or (16384, 32768)), args)
+    if fam == "train_step":
+        run_train_step(*(shape or (2, 16)), args)
     if fam in ("all", "rmsnorm"):
         run_rmsnorm(*(shape or (65536, 4096)), args)
     code = C.c_int(0)
