@@ -174,3 +174,57 @@ def test_document_mask_invariance_full_seq(nnb):
     assert np.abs(a[100:] - b[100:]).max() <= 1e-4
     a, b = logits(t1, None), logits(t2, None)
     assert np.abs(a[100:512] - b[100:512]).max() > 1e-2
+
+
+def _packed_doc_ids(rng, batch, seq, mean_len):
+    """Rows packed with documents whose lengths are geometric(mean_len): ids 1, 2, ... along each row."""
+    docs = np.zeros((batch, seq), np.int32)
+    for b in range(batch):
+        pos, k = 0, 1
+        while pos < seq:
+            n = int(rng.geometric(1.0 / mean_len))
+            docs[b, pos:pos + n] = k
+            pos, k = pos + n, k + 1
+    return docs
+
+
+def test_packed_document_shape_bf16_muon(nnb):
+    """The packed-document configuration at its full width (vocab 16384, d 1024, 16 heads, SwiGLU 2816, RMSNorm,
+    learned positions, seq 2048, geometric(300) documents), two layers deep, in bf16 mode on the tensor-core kernels:
+    (1) logits outside a document do not change at all when that document's tokens change (masked keys contribute an
+    exact zero, every other kernel works per token), while the document's own logits do; (2) Muon + AdamW steps with
+    clipping on one batch lower the loss and leave the device status word clear."""
+    import torch
+    cfg = nnb.GptConfig(16384, 1024, 16, 2, 2816, 2048, 2, nnb.ACT_SWIGLU, nnb.NORM_RMS, nnb.POS_LEARNED, nnb.BF16)
+    tr = nnb.GptTrainer(cfg, lr=1e-3, weight_decay=0.01, muon=True, muon_lr=0.02)
+    tr.init_params_normal(seed=11, std=0.02)
+    r = np.random.default_rng(4)
+    n = 2 * 2048
+    docs = _packed_doc_ids(r, 2, 2048, 300)
+    assert docs[0].max() >= 3                                   # several documents per row
+    t1 = r.integers(0, 16384, n).astype(np.int32)
+    victim = (docs[0] == 2)                                     # second document of row 0
+    t2 = t1.copy()
+    t2[:2048][victim] = (t2[:2048][victim] + 101) % 16384
+    flat_docs = docs.reshape(-1)
+
+    def logits(tok):
+        tr.forward(tok, flat_docs)
+        torch.cuda.synchronize()
+        return tr.logits().float().cpu().numpy().copy()
+    a, b = logits(t1), logits(t2)
+    outside = np.ones(n, bool)
+    outside[:2048] = ~victim
+    assert np.array_equal(a[outside], b[outside])
+    assert np.abs(a[~outside] - b[~outside]).max() > 1e-3
+    labels = np.roll(t1, -1).astype(np.int32)
+    losses = []
+    for _ in range(4):
+        tr.forward(t1, flat_docs)
+        tr.loss_and_grad(labels, None, 1.0)
+        tr.backward()
+        losses.append(float(tr.loss_tensor().item()))
+        tr.optimizer_step(clip=1.0)
+    torch.cuda.synchronize()
+    tr.check_device_status()
+    assert all(np.isfinite(losses)) and losses[-1] < losses[0] - 0.05, losses
