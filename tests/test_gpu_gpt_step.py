@@ -263,3 +263,38 @@ def test_config2_full_size_bf16_follows_check_mode(nnb):
     a, b = curves[nnb.FP32], curves[nnb.BF16]
     assert np.all(np.abs(a - b) <= 1e-2 * np.abs(a)), (a, b)
     assert a[-1] < a[0] - 0.1, a
+
+
+def test_config3_full_size_bf16_follows_check_mode(nnb):
+    """The benchmark configuration at full size (vocab 8192, d 768, 12 heads, 12 layers, SwiGLU 2048, RMSNorm, ALiBi,
+    seq 1024, micro-batch 16 x accumulation 2, AdamW with a falling learning rate): bf16 tensor-core path against
+    the fp32 check path on the same weights and batches, per-micro-batch losses within 1e-2 relative."""
+    import torch
+    r = np.random.default_rng(33)
+    ranks = np.arange(1, 8193, dtype=np.float64)
+    p = ranks ** -1.1
+    p /= p.sum()
+    steps, accum, n = 3, 2, 16 * 1024
+    ids = r.choice(8192, size=(steps * accum, 16, 1025), p=p).astype(np.int32)
+    curves = {}
+    for prec in (nnb.FP32, nnb.BF16):
+        cfg = nnb.GptConfig(8192, 768, 12, 12, 2048, 1024, 16, nnb.ACT_SWIGLU, nnb.NORM_RMS, nnb.POS_ALIBI, prec)
+        tr = nnb.GptTrainer(cfg, lr=3e-4, weight_decay=0.01)
+        tr.init_params_normal(seed=42, std=0.02)
+        losses = []
+        for s in range(steps):
+            for a in range(accum):
+                i = s * accum + a
+                tok = np.ascontiguousarray(ids[i, :, :-1]).reshape(n)
+                lab = np.ascontiguousarray(ids[i, :, 1:]).reshape(n)
+                tr.micro_step(tok, lab, None, None, grad_scale=1.0 / accum, last=(a == accum - 1))
+                losses.append(float(tr.loss_tensor().item()))
+            tr.optimizer_step(lr=3e-4 * (1.0 - 0.2 * s))
+        torch.cuda.synchronize()
+        tr.check_device_status()
+        curves[prec] = np.array(losses)
+        del tr
+        torch.cuda.empty_cache()
+    a, b = curves[nnb.FP32], curves[nnb.BF16]
+    assert np.all(np.abs(a - b) <= 1e-2 * np.abs(a)), (a, b)
+    assert a[-1] < a[0], a
