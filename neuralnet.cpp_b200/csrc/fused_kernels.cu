@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(256, 2)
 norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ gamma,
                       const float* __restrict__ rinv_in, const float* __restrict__ mean_in, const T* __restrict__ add,
                       T* __restrict__ dx, float* __restrict__ partial, int* __restrict__ counter,
-                      float* __restrict__ dgamma, float* __restrict__ dbeta, float* __restrict__ osum, int rows)
+                      float* __restrict__ dgamma, float* __restrict__ dbeta, float* __restrict__ osum, int rows, int defer)
 {
     constexpr int VN = Vec16<T>::N, D = 32 * NV * VN, NQ = 3;
     __shared__ float red[8][D];
@@ -335,6 +335,7 @@ norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const fl
             partial[qn * pstride + static_cast<size_t>(blockIdx.x) * D + c] = sacc;
         }
     }
+    if (defer) return;          // the partial rows are folded later, by norm_fold_deferred_kernel
     // Two-level fold in fixed order (deterministic, whatever order the blocks finish in): the last block of each
     // group of kNormFoldGroup consecutive blocks adds that group's rows into one group row; the last group to
     // finish adds the group rows into the gradients.  One block folding all 296 rows alone took longer than
@@ -397,6 +398,55 @@ norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const fl
         }
     }
     if (threadIdx.x == 0) counter[kNormFoldCounters - 1] = 0;
+}
+
+// The cross-block fold of norm_bwd_fused_kernel, deferred: a training step runs that kernel dozens of times per
+// micro-batch, and the two fold levels at its end (two fences, two atomics, two round trips to L2 on one block) are a
+// third of each launch although nothing needs the parameter gradients before the optimizer.  In deferred mode each
+// launch leaves its kNormFusedBlocks partial rows in a slot of its own and this kernel folds all slots at once: block
+// (column group, quantity, slot).
+__global__ void __launch_bounds__(256)
+norm_fold_deferred_kernel(const float* __restrict__ partials, size_t slot_stride, NormFoldSlots slots, float* __restrict__ G,
+                          int nblocks, int d)
+{
+    // 64 float4 columns x 4 row segments per block: segment q sums rows [q*seg, (q+1)*seg) in order, 16 loads in
+    // flight; the four segment sums are then added in segment order (fixed order: deterministic)
+    __shared__ float4 seg_sum[4][64];
+    const int slot = blockIdx.z, qn = blockIdx.y;
+    const long long dst_off = qn == 0 ? slots.dgamma[slot] : (qn == 1 ? slots.dbeta[slot] : slots.osum[slot]);
+    if (dst_off < 0) return;                                      // uniform over the block
+    const int lane = threadIdx.x & 63, q = threadIdx.x >> 6;
+    const int c4 = blockIdx.x * 64 + lane;
+    const bool live = c4 < d / 4;
+    const int seg = (nblocks + 3) / 4;
+    const int k0 = q * seg, k1 = min(nblocks, k0 + seg);
+    const float* src = partials + slot * slot_stride + static_cast<size_t>(qn) * nblocks * d;
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+        int k = k0;
+        for (; k + 16 <= k1; k += 16) {
+            float4 v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k + j) * d) + c4);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { t.x += v[j].x; t.y += v[j].y; t.z += v[j].z; t.w += v[j].w; }
+        }
+        for (; k < k1; ++k) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * d) + c4);
+            t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        }
+    }
+    seg_sum[q][lane] = t;
+    __syncthreads();
+    if (q == 0 && live) {
+        float4 r = seg_sum[0][lane];
+#pragma unroll
+        for (int j = 1; j < 4; ++j) { const float4 v = seg_sum[j][lane]; r.x += v.x; r.y += v.y; r.z += v.z; r.w += v.w; }
+        float4* dst = reinterpret_cast<float4*>(G + dst_off) + c4;
+        float4 o = *dst;
+        o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+        *dst = o;
+    }
 }
 
 // ======================================================================================
@@ -897,11 +947,26 @@ size_t norm_bwd_scratch_floats(int rows, int d)
     return a > b ? a : b;
 }
 
+// floats one deferred slot of norm_bwd holds: three quantities x kNormFusedBlocks partial rows
+size_t norm_bwd_defer_slot_floats(int d) { return static_cast<size_t>(3) * kNormFusedBlocks * d; }
+
+// folds `n` deferred slots (destinations are offsets into G, -1 = absent) and adds them into the gradients
+int norm_bwd_fold_deferred(const float* partials, const NormFoldSlots& slots, int n, float* G, int d, cudaStream_t s)
+{
+    if (n == 0) return 0;
+    NNB_ARG_CHECK(n <= kNormFoldMaxSlots && (d % 4) == 0, "too many deferred slots or unaligned width");
+    dim3 grid(static_cast<unsigned>(ceil_div(d / 4, 64)), 3, static_cast<unsigned>(n));
+    norm_fold_deferred_kernel<<<grid, 256, 0, s>>>(partials, norm_bwd_defer_slot_floats(d), slots, G, kNormFusedBlocks, d);
+    LAUNCH_CHECK();
+    return 0;
+}
+
 template <typename T>
 int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, const float* mean, const T* add, T* dx,
              float* dgamma, float* dbeta, float* scratch, int rows, int d, bool layer, cudaStream_t s, int* counters,
-             float* out_colsum)
+             float* out_colsum, float* defer_partial, bool* deferred)
 {
+    if (deferred) *deferred = false;
     if (rows == 0) return 0;
     const int grid = grid_for(rows, 8);
     constexpr int VN = Vec16<T>::N;
@@ -912,11 +977,14 @@ int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, cons
     // fused path: needs the caller's zero-initialised completion counter and norm_bwd_scratch_floats of scratch
 #define NNB_NORM_BWD_FUSED(nv)                                                                                        \
     if (counters && aligned && out_ok && d == 32 * VN * nv) {                                                         \
+        const bool defer = defer_partial != nullptr && deferred != nullptr;                                           \
+        float* part = defer ? defer_partial : scratch;                                                                \
         if (layer) norm_bwd_fused_kernel<T, true, nv><<<kNormFusedBlocks, 256, 0, s>>>(                                \
-            g, x, gamma, rinv, mean, add, dx, scratch, counters + kColsumCounters - kNormFoldCounters, dgamma, dbeta, out_colsum, rows); \
+            g, x, gamma, rinv, mean, add, dx, part, counters + kColsumCounters - kNormFoldCounters, dgamma, dbeta, out_colsum, rows, defer ? 1 : 0); \
         else norm_bwd_fused_kernel<T, false, nv><<<kNormFusedBlocks, 256, 0, s>>>(                                     \
-            g, x, gamma, rinv, mean, add, dx, scratch, counters + kColsumCounters - kNormFoldCounters, dgamma, dbeta, out_colsum, rows); \
+            g, x, gamma, rinv, mean, add, dx, part, counters + kColsumCounters - kNormFoldCounters, dgamma, dbeta, out_colsum, rows, defer ? 1 : 0); \
         LAUNCH_CHECK();                                                                                               \
+        if (defer) *deferred = true;                                                                                  \
         return 0;                                                                                                     \
     }
     NNB_NORM_BWD_FUSED(1) NNB_NORM_BWD_FUSED(2) NNB_NORM_BWD_FUSED(3) NNB_NORM_BWD_FUSED(4)
@@ -1062,7 +1130,7 @@ int bf16_to_f32(const bf16* in, float* out, size_t n, cudaStream_t s)
 #define INSTANTIATE(T)                                                                                                 \
     template int norm_fwd<T>(const T*, const float*, const float*, T*, float*, float*, int, int, bool, cudaStream_t);  \
     template int norm_bwd<T>(const T*, const T*, const float*, const float*, const float*, const T*, T*, float*,       \
-                             float*, float*, int, int, bool, cudaStream_t, int*, float*);                              \
+                             float*, float*, int, int, bool, cudaStream_t, int*, float*, float*, bool*);                \
     template int colsum_accumulate<T>(const T*, long long, const T*, const float*, const float*, const float*, int,    \
                                       float*, float*, int, int, cudaStream_t, int*);                                   \
     template int act_fwd<T>(const T*, T*, int, int, bool, cudaStream_t);                                               \

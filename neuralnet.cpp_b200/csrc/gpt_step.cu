@@ -69,7 +69,7 @@ struct Workspace {
     size_t sin_table, stats, loss, loss_vec;
     std::vector<LayerActs> layers;
     size_t x_final, xnf, rinvf, meanf, logits;
-    size_t g_a, g_b, d_xn, d_h2, d_h1, d_attn, d_qkv, dvec, colsum, counters, embed_scratch;
+    size_t g_a, g_b, d_xn, d_h2, d_h1, d_attn, d_qkv, dvec, colsum, counters, embed_scratch, norm_partials;
     size_t total;
 };
 
@@ -99,6 +99,9 @@ static Workspace make_workspace(const nnb200_gpt_config& c)
     W.colsum = take(std::max(colsum_scratch_floats(static_cast<int>(N), static_cast<int>(widest)),
                              norm_bwd_scratch_floats(static_cast<int>(N), static_cast<int>(d))) * 4);
     W.counters = take(kColsumCounters * sizeof(int));
+    // one slot per norm backward of a micro-batch (2 per layer + the final norm) for the deferred parameter-gradient fold
+    const size_t norm_slots = 2 * static_cast<size_t>(c.layers) + 1;
+    W.norm_partials = take(norm_slots <= kNormFoldMaxSlots ? norm_slots * norm_bwd_defer_slot_floats(static_cast<int>(d)) * 4 : 0);
     W.embed_scratch = take(embed_bwd_scratch_bytes(static_cast<int>(N)));
     W.total = off;
     return W;
@@ -217,6 +220,19 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
     auto Hh = [&](long long off) { return H ? H + off : nullptr; };
     float* cs = F(W.colsum);
     int* cn = reinterpret_cast<int*>(ws + W.counters);
+    // the norm backward kernels leave their per-block partial sums of the scale / shift / bias gradients in a slot each;
+    // one kernel after the last layer folds all slots into the gradient arena (nothing reads them before the optimizer)
+    const bool defer = 2 * c.layers + 1 <= kNormFoldMaxSlots;
+    const size_t slot_floats = norm_bwd_defer_slot_floats(d);
+    NormFoldSlots slots;
+    int nslots = 0;
+    auto slot_ptr = [&]() -> float* { return defer ? F(W.norm_partials) + nslots * slot_floats : nullptr; };
+    auto slot_done = [&](bool deferred, long long dgamma, long long dbeta, long long osum) {
+        if (!deferred) return;
+        slots.dgamma[nslots] = dgamma; slots.dbeta[nslots] = dbeta; slots.osum[nslots] = osum;
+        ++nslots;
+    };
+    bool was_deferred = false;
 
     // LM head and final norm (GPTModel::backward, compute_layer.hpp:2849-2856)
     T* dlogits = A(W.logits);
@@ -227,7 +243,8 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
     // each norm backward also sums the columns of the gradient it produces: that is the bias gradient
     // of the Linear layer whose output this gradient belongs to (fc2 of the layer below, or wo)
     NNB_TRY(norm_bwd<T>(A(W.d_xn), A(W.x_final), P + L.lnf_g, F(W.rinvf), F(W.meanf), nullptr, g, G + L.lnf_g, GB(L.lnf_b),
-                        cs, N, d, ln, s, cn, G + L.layers[c.layers - 1].b2));
+                        cs, N, d, ln, s, cn, G + L.layers[c.layers - 1].b2, slot_ptr(), &was_deferred));
+    slot_done(was_deferred, L.lnf_g, L.lnf_b, L.layers[c.layers - 1].b2);
 
     for (int l = c.layers - 1; l >= 0; --l) {
         const LayerParams& lp = L.layers[l];
@@ -240,7 +257,8 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         NNB_TRY(linear_bwd_input<T>(A(W.d_h1), P + lp.w1, Hh(lp.w1), A(W.d_xn), N, d, fc1, s));
         // grad_r1 = grad_output + norm2.backward (GPTBlock::backward, compute_layer.hpp:2388-2404)
         NNB_TRY(norm_bwd<T>(A(W.d_xn), A(a.x_mid), P + lp.g2, F(a.rinv2), F(a.mean2), g, g_other, G + lp.g2, GB(lp.be2), cs,
-                            N, d, ln, s, cn, G + lp.bo));
+                            N, d, ln, s, cn, G + lp.bo, slot_ptr(), &was_deferred));
+        slot_done(was_deferred, lp.g2, lp.be2, lp.bo);
         std::swap(g, g_other);
         // AttentionBase::backward (compute_layer.hpp:1271-1412)
         NNB_TRY(linear_bwd_params<T>(g, A(a.attn), G + lp.wo, nullptr, cs, cn, N, d, d, s));
@@ -251,10 +269,12 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, cn, N, d, 3 * d, s));
         NNB_TRY(linear_bwd_input<T>(A(W.d_qkv), P + lp.wqkv, Hh(lp.wqkv), A(W.d_xn), N, d, 3 * d, s));
         NNB_TRY(norm_bwd<T>(A(W.d_xn), A(a.x_in), P + lp.g1, F(a.rinv1), F(a.mean1), g, g_other, G + lp.g1, GB(lp.be1), cs, N,
-                            d, ln, s, cn, l >= 1 ? G + L.layers[l - 1].b2 : nullptr));
+                            d, ln, s, cn, l >= 1 ? G + L.layers[l - 1].b2 : nullptr, slot_ptr(), &was_deferred));
+        slot_done(was_deferred, lp.g1, lp.be1, l >= 1 ? L.layers[l - 1].b2 : -1);
         std::swap(g, g_other);
         if (events && events[l]) NNB_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(events[l]), s));
     }
+    NNB_TRY(norm_bwd_fold_deferred(F(W.norm_partials), slots, nslots, G, d, s));
     // embeddings (compute_layer.hpp:2882-2891): deterministic scatter-add
     NNB_TRY(embed_bwd<T>(G + L.tok_emb, c.pos == 0 ? G + L.pos_emb : nullptr, tokens, g, ws + W.embed_scratch, c.batch, c.seq,
                          d, c.vocab, s));

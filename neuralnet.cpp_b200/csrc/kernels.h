@@ -25,8 +25,17 @@ template <typename T> int norm_fwd(const T* x, const float* gamma, const float* 
                                    int rows, int d, bool layer, cudaStream_t s);
 template <typename T> int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, const float* mean,
                                    const T* add, T* dx, float* dgamma, float* dbeta, float* scratch, int rows, int d,
-                                   bool layer, cudaStream_t s, int* counters = nullptr, float* out_colsum = nullptr);
+                                   bool layer, cudaStream_t s, int* counters = nullptr, float* out_colsum = nullptr,
+                                   float* defer_partial = nullptr, bool* deferred = nullptr);
 size_t norm_bwd_scratch_floats(int rows, int d);
+// Deferred parameter-gradient fold of norm_bwd: with defer_partial (norm_bwd_defer_slot_floats(d) floats, one slot per
+// call) the fused kernel leaves its per-block partial sums there and sets *deferred; norm_bwd_fold_deferred later adds
+// every slot into its destinations (offsets into the gradient arena, -1 = absent) in one launch.  *deferred stays
+// false when the shape takes a path that folds at once; the caller then must not list that slot.
+constexpr int kNormFoldMaxSlots = 64;
+struct NormFoldSlots { long long dgamma[kNormFoldMaxSlots], dbeta[kNormFoldMaxSlots], osum[kNormFoldMaxSlots]; };
+size_t norm_bwd_defer_slot_floats(int d);
+int norm_bwd_fold_deferred(const float* partials, const NormFoldSlots& slots, int n, float* G, int d, cudaStream_t s);
 template <typename T> int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma, const float* rinv,
                                             const float* mean, int mode, float* out, float* scratch, int rows, int cols,
                                             cudaStream_t s, int* counters = nullptr);
