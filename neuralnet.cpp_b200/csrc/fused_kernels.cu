@@ -906,10 +906,65 @@ int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rin
     return 0;
 }
 
+// Fold of deferred column-sum slots: block (64 float4 columns, slot) with 4 row segments, like norm_fold_deferred_kernel.
+__global__ void __launch_bounds__(256)
+colsum_fold_deferred_kernel(const float* __restrict__ base, ColsumFoldSlots slots, float* __restrict__ G)
+{
+    __shared__ float4 seg_sum[4][64];
+    const int slot = blockIdx.y;
+    const int cols = slots.cols[slot], chunks = slots.chunks[slot];
+    if (blockIdx.x * 64 >= cols / 4) return;                      // uniform over the block
+    const int lane = threadIdx.x & 63, q = threadIdx.x >> 6;
+    const int c4 = blockIdx.x * 64 + lane;
+    const bool live = c4 < cols / 4;
+    const int seg = (chunks + 3) / 4;
+    const int k0 = q * seg, k1 = min(chunks, k0 + seg);
+    const float* src = base + slots.part[slot];
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+        int k = k0;
+        for (; k + 8 <= k1; k += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k + j) * cols) + c4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { t.x += v[j].x; t.y += v[j].y; t.z += v[j].z; t.w += v[j].w; }
+        }
+        for (; k < k1; ++k) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * cols) + c4);
+            t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        }
+    }
+    seg_sum[q][lane] = t;
+    __syncthreads();
+    if (q == 0 && live) {
+        float4 r = seg_sum[0][lane];
+#pragma unroll
+        for (int j = 1; j < 4; ++j) { const float4 v = seg_sum[j][lane]; r.x += v.x; r.y += v.y; r.z += v.z; r.w += v.w; }
+        float4* dst = reinterpret_cast<float4*>(G + slots.dst[slot]) + c4;
+        float4 o = *dst;
+        o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+        *dst = o;
+    }
+}
+
+int colsum_fold_deferred(const float* partial_base, const ColsumFoldSlots& slots, int n, float* G, cudaStream_t s)
+{
+    if (n == 0) return 0;
+    NNB_ARG_CHECK(n <= kColsumFoldMaxSlots, "too many deferred slots");
+    int widest = 0;
+    for (int i = 0; i < n; ++i) widest = slots.cols[i] > widest ? slots.cols[i] : widest;
+    dim3 grid(static_cast<unsigned>(ceil_div(widest / 4, 64)), static_cast<unsigned>(n));
+    colsum_fold_deferred_kernel<<<grid, 256, 0, s>>>(partial_base, slots, G);
+    LAUNCH_CHECK();
+    return 0;
+}
+
 template <typename T>
 int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma, const float* rinv, const float* mean,
-                      int mode, float* out, float* scratch, int rows, int cols, cudaStream_t s, int* counters)
+                      int mode, float* out, float* scratch, int rows, int cols, cudaStream_t s, int* counters, ColsumDefer* defer)
 {
+    if (defer) defer->deferred = false;
     if (rows == 0 || cols == 0) return 0;
     constexpr int VN = Vec16<T>::N;
     int chunks = static_cast<int>(ceil_div(rows, CS_CHUNK_ROWS));
@@ -924,9 +979,13 @@ int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma,
         chunks = static_cast<int>(ceil_div(rows, chunk_rows));
         dim3 grid(static_cast<unsigned>(col_blocks), chunks);
         if (counters && grid.x > static_cast<unsigned>(kColsumCounters - kNormFoldCounters)) counters = nullptr;   // the last 64 of the 1024 counters are the norm kernel's
-        if (mode == 0) colsum_vec_kernel<T, 0><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks, chunk_rows);
-        else colsum_vec_kernel<T, 1><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, scratch, counters, out, rows, cols, chunks, chunk_rows);
+        const bool deferring = defer && defer->partial && (cols % 4) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+        float* part = deferring ? defer->partial : scratch;
+        int* cnt = deferring ? nullptr : counters;                // without counters the kernel stops after its chunk partials
+        if (mode == 0) colsum_vec_kernel<T, 0><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, part, cnt, out, rows, cols, chunks, chunk_rows);
+        else colsum_vec_kernel<T, 1><<<grid, 256, 0, s>>>(g, ldg, x, gamma, rinv, mean, part, cnt, out, rows, cols, chunks, chunk_rows);
         LAUNCH_CHECK();
+        if (deferring) { defer->chunks = chunks; defer->deferred = true; return 0; }
         if (counters) return 0;
     } else {
         dim3 grid(static_cast<unsigned>(ceil_div(cols, CS_COLS)), chunks);
@@ -1023,8 +1082,9 @@ int act_fwd(const T* h1, T* h2, int rows, int ff, bool swiglu, cudaStream_t s)
 }
 template <typename T>
 int act_bwd(const T* g, const T* h1, T* dh1, int rows, int ff, bool swiglu, cudaStream_t s, float* dbias, float* scratch,
-            int* counters)
+            int* counters, ColsumDefer* defer)
 {
+    if (defer) defer->deferred = false;
     const size_t n = static_cast<size_t>(rows) * ff;
     if (n == 0) return 0;
     constexpr int VN = Vec16<T>::N;
@@ -1032,7 +1092,7 @@ int act_bwd(const T* g, const T* h1, T* dh1, int rows, int ff, bool swiglu, cuda
     if (swiglu) swiglu_bwd_kernel<T><<<grid_for(static_cast<long long>(n / VN + 1), 256), 256, 0, s>>>(g, h1, dh1, rows, ff);
     else gelu_bwd_kernel<T><<<grid_for(static_cast<long long>(n), 256), 256, 0, s>>>(g, h1, dh1, n);
     LAUNCH_CHECK();
-    if (dbias) NNB_TRY(colsum_accumulate<T>(dh1, width, nullptr, nullptr, nullptr, nullptr, 0, dbias, scratch, rows, width, s, counters));
+    if (dbias) NNB_TRY(colsum_accumulate<T>(dh1, width, nullptr, nullptr, nullptr, nullptr, 0, dbias, scratch, rows, width, s, counters, defer));
     return 0;
 }
 template <typename T>
@@ -1132,9 +1192,9 @@ int bf16_to_f32(const bf16* in, float* out, size_t n, cudaStream_t s)
     template int norm_bwd<T>(const T*, const T*, const float*, const float*, const float*, const T*, T*, float*,       \
                              float*, float*, int, int, bool, cudaStream_t, int*, float*, float*, bool*);                \
     template int colsum_accumulate<T>(const T*, long long, const T*, const float*, const float*, const float*, int,    \
-                                      float*, float*, int, int, cudaStream_t, int*);                                   \
+                                      float*, float*, int, int, cudaStream_t, int*, ColsumDefer*);                     \
     template int act_fwd<T>(const T*, T*, int, int, bool, cudaStream_t);                                               \
-    template int act_bwd<T>(const T*, const T*, T*, int, int, bool, cudaStream_t, float*, float*, int*);               \
+    template int act_bwd<T>(const T*, const T*, T*, int, int, bool, cudaStream_t, float*, float*, int*, ColsumDefer*); \
     template int cross_entropy<T>(T*, const int*, const float*, float, float*, float*, float*, int, int, int,          \
                                   cudaStream_t);                                                                       \
     template int muon_normalize<T>(const float*, const float*, float, T*, size_t, cudaStream_t);                       \

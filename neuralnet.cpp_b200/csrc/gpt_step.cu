@@ -69,7 +69,7 @@ struct Workspace {
     size_t sin_table, stats, loss, loss_vec;
     std::vector<LayerActs> layers;
     size_t x_final, xnf, rinvf, meanf, logits;
-    size_t g_a, g_b, d_xn, d_h2, d_h1, d_attn, d_qkv, dvec, colsum, counters, embed_scratch, norm_partials;
+    size_t g_a, g_b, d_xn, d_h2, d_h1, d_attn, d_qkv, dvec, colsum, counters, embed_scratch, norm_partials, colsum_partials;
     size_t total;
 };
 
@@ -102,6 +102,12 @@ static Workspace make_workspace(const nnb200_gpt_config& c)
     // one slot per norm backward of a micro-batch (2 per layer + the final norm) for the deferred parameter-gradient fold
     const size_t norm_slots = 2 * static_cast<size_t>(c.layers) + 1;
     W.norm_partials = take(norm_slots <= kNormFoldMaxSlots ? norm_slots * norm_bwd_defer_slot_floats(static_cast<int>(d)) * 4 : 0);
+    // and one per bias gradient that has a column-sum pass of its own: the LM head, and fc1 and qkv of every layer
+    W.colsum_partials = take(2 * static_cast<size_t>(c.layers) + 1 <= kColsumFoldMaxSlots
+                                 ? (colsum_scratch_floats(static_cast<int>(N), static_cast<int>(V)) +
+                                    c.layers * (colsum_scratch_floats(static_cast<int>(N), static_cast<int>(fc1)) +
+                                                colsum_scratch_floats(static_cast<int>(N), static_cast<int>(3 * d)))) * 4
+                                 : 0);
     W.embed_scratch = take(embed_bwd_scratch_bytes(static_cast<int>(N)));
     W.total = off;
     return W;
@@ -134,7 +140,7 @@ static int linear_bwd_input(const T* dY, const float* Wf, const bf16* Wh, T* dX,
 // dW[out, in] += dY^T X ; db[out] += column sums of dY
 template <typename T>
 static int linear_bwd_params(const T* dY, const T* X, float* dW, float* db, float* scratch, int* counters, int ntok, int in,
-                             int out, cudaStream_t s)
+                             int out, cudaStream_t s, ColsumDefer* defer = nullptr)
 {
     if (Mode<T>::bf)
         NNB_TRY(gemm_bf16(reinterpret_cast<const bf16*>(dY), reinterpret_cast<const bf16*>(X), dW, out, in, ntok, out, in, in,
@@ -142,8 +148,9 @@ static int linear_bwd_params(const T* dY, const T* X, float* dW, float* db, floa
     else
         NNB_TRY(sgemm_strided(reinterpret_cast<const float*>(dY), reinterpret_cast<const float*>(X), dW, out, in, ntok, 1,
                               out, 1, in, in, 1, 0, 0, 0, 1.0f, nullptr, nullptr, nullptr, 1, s));
+    if (defer) defer->deferred = false;
     if (!db) return 0;                       // the bias gradient was already summed by the kernel that produced dY
-    return colsum_accumulate<T>(dY, out, nullptr, nullptr, nullptr, nullptr, 0, db, scratch, ntok, out, s, counters);
+    return colsum_accumulate<T>(dY, out, nullptr, nullptr, nullptr, nullptr, 0, db, scratch, ntok, out, s, counters, defer);
 }
 
 template <typename T>
@@ -233,10 +240,27 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         ++nslots;
     };
     bool was_deferred = false;
+    ColsumFoldSlots csl;
+    int ncs = 0;
+    size_t cs_off = 0;                                            // floats used of W.colsum_partials
+    ColsumDefer cd{nullptr, 0, false};
+    auto cs_begin = [&]() -> ColsumDefer* {
+        if (!defer) return nullptr;
+        cd.partial = F(W.colsum_partials) + cs_off; cd.chunks = 0; cd.deferred = false;
+        return &cd;
+    };
+    auto cs_done = [&](long long dst, int cols) {
+        if (!cd.deferred) return;
+        csl.dst[ncs] = dst; csl.part[ncs] = static_cast<long long>(cs_off); csl.chunks[ncs] = cd.chunks; csl.cols[ncs] = cols;
+        ++ncs;
+        cs_off += colsum_scratch_floats(N, cols);
+        cd.deferred = false;
+    };
 
     // LM head and final norm (GPTModel::backward, compute_layer.hpp:2849-2856)
     T* dlogits = A(W.logits);
-    NNB_TRY(linear_bwd_params<T>(dlogits, A(W.xnf), G + L.lm_w, G + L.lm_b, cs, cn, N, d, c.vocab, s));
+    NNB_TRY(linear_bwd_params<T>(dlogits, A(W.xnf), G + L.lm_w, G + L.lm_b, cs, cn, N, d, c.vocab, s, cs_begin()));
+    cs_done(L.lm_b, c.vocab);
     NNB_TRY(linear_bwd_input<T>(dlogits, P + L.lm_w, Hh(L.lm_w), A(W.d_xn), N, d, c.vocab, s));
     T* g = A(W.g_a);
     T* g_other = A(W.g_b);
@@ -252,7 +276,8 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         // FeedForward::backward (compute_layer.hpp:1674-1688)
         NNB_TRY(linear_bwd_params<T>(g, A(a.h2), G + lp.w2, nullptr, cs, cn, N, ff, d, s));
         NNB_TRY(linear_bwd_input<T>(g, P + lp.w2, Hh(lp.w2), A(W.d_h2), N, ff, d, s));
-        NNB_TRY(act_bwd<T>(A(W.d_h2), A(a.h1), A(W.d_h1), N, ff, swiglu, s, G + lp.b1, cs, cn));   // also sums fc1's bias gradient
+        NNB_TRY(act_bwd<T>(A(W.d_h2), A(a.h1), A(W.d_h1), N, ff, swiglu, s, G + lp.b1, cs, cn, cs_begin()));   // also sums fc1's bias gradient
+        cs_done(lp.b1, fc1);
         NNB_TRY(linear_bwd_params<T>(A(W.d_h1), A(a.xn2), G + lp.w1, nullptr, cs, cn, N, d, fc1, s));
         NNB_TRY(linear_bwd_input<T>(A(W.d_h1), P + lp.w1, Hh(lp.w1), A(W.d_xn), N, d, fc1, s));
         // grad_r1 = grad_output + norm2.backward (GPTBlock::backward, compute_layer.hpp:2388-2404)
@@ -266,7 +291,8 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         NNB_TRY(attention_bwd<T>(A(a.qkv), A(a.attn), A(W.d_attn), F(a.lse), F(W.dvec), A(W.d_qkv), doc, c, s));
         // the gradients of the rotated Q and K go back through the inverse rotation (compute_layer.hpp:1365-1372)
         if (c.pos == 3) NNB_TRY(rope_apply<T>(A(W.d_qkv), F(W.sin_table), N, c.seq, c.heads, d / c.heads, 3 * d, true, s));
-        NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, cn, N, d, 3 * d, s));
+        NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, cn, N, d, 3 * d, s, cs_begin()));
+        cs_done(lp.bqkv, 3 * d);
         NNB_TRY(linear_bwd_input<T>(A(W.d_qkv), P + lp.wqkv, Hh(lp.wqkv), A(W.d_xn), N, d, 3 * d, s));
         NNB_TRY(norm_bwd<T>(A(W.d_xn), A(a.x_in), P + lp.g1, F(a.rinv1), F(a.mean1), g, g_other, G + lp.g1, GB(lp.be1), cs, N,
                             d, ln, s, cn, l >= 1 ? G + L.layers[l - 1].b2 : nullptr, slot_ptr(), &was_deferred));
@@ -275,6 +301,7 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         if (events && events[l]) NNB_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(events[l]), s));
     }
     NNB_TRY(norm_bwd_fold_deferred(F(W.norm_partials), slots, nslots, G, d, s));
+    NNB_TRY(colsum_fold_deferred(F(W.colsum_partials), csl, ncs, G, s));
     // embeddings (compute_layer.hpp:2882-2891): deterministic scatter-add
     NNB_TRY(embed_bwd<T>(G + L.tok_emb, c.pos == 0 ? G + L.pos_emb : nullptr, tokens, g, ws + W.embed_scratch, c.batch, c.seq,
                          d, c.vocab, s));

@@ -36,14 +36,22 @@ constexpr int kNormFoldMaxSlots = 64;
 struct NormFoldSlots { long long dgamma[kNormFoldMaxSlots], dbeta[kNormFoldMaxSlots], osum[kNormFoldMaxSlots]; };
 size_t norm_bwd_defer_slot_floats(int d);
 int norm_bwd_fold_deferred(const float* partials, const NormFoldSlots& slots, int n, float* G, int d, cudaStream_t s);
+// Deferred fold of the column sums, as for norm_bwd: with `defer` (partial = a buffer of colsum_scratch_floats(rows, cols)
+// floats of the caller's) the chunk partials are left there, `chunks` and `deferred` are filled in, and
+// colsum_fold_deferred adds every listed slot into its destination later.
+struct ColsumDefer { float* partial; int chunks; bool deferred; };
+constexpr int kColsumFoldMaxSlots = 64;
+struct ColsumFoldSlots { long long dst[kColsumFoldMaxSlots], part[kColsumFoldMaxSlots]; int chunks[kColsumFoldMaxSlots], cols[kColsumFoldMaxSlots]; };
+int colsum_fold_deferred(const float* partial_base, const ColsumFoldSlots& slots, int n, float* G, cudaStream_t s);
 template <typename T> int colsum_accumulate(const T* g, long long ldg, const T* x, const float* gamma, const float* rinv,
                                             const float* mean, int mode, float* out, float* scratch, int rows, int cols,
-                                            cudaStream_t s, int* counters = nullptr);
+                                            cudaStream_t s, int* counters = nullptr, ColsumDefer* defer = nullptr);
 constexpr int kColsumCounters = 1024;   // ints a caller-provided, zero-initialised counter array must hold
 size_t colsum_scratch_floats(int rows, int cols);
 template <typename T> int act_fwd(const T* h1, T* h2, int rows, int ff, bool swiglu, cudaStream_t s);
 template <typename T> int act_bwd(const T* g, const T* h1, T* dh1, int rows, int ff, bool swiglu, cudaStream_t s,
-                                  float* dbias = nullptr, float* scratch = nullptr, int* counters = nullptr);
+                                  float* dbias = nullptr, float* scratch = nullptr, int* counters = nullptr,
+                                  ColsumDefer* defer = nullptr);
 template <typename T> int cross_entropy(T* logits, const int* labels, const float* mask, float grad_scale,
                                         float* loss_vec, float* stats, float* loss_out, int rows, int V, int vocab,
                                         cudaStream_t s);
