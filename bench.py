@@ -196,7 +196,7 @@ def main():
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
         pg = dist.group.WORLD
     w = WORKLOAD
-    K, W = max(1, args.steps), max(int(os.environ.get("NNB200_BENCH_MIN_WARMUP", "3")), args.warmup)   # the override is for profiling captures only
+    K, W = max(1, args.steps), max(0, args.warmup)
     cfg = nnb.GptConfig(w["vocab"], w["d_model"], w["heads"], w["layers"], w["d_ff"], w["seq"], w["batch"],
                         nnb.ACT_SWIGLU, nnb.NORM_RMS, nnb.POS_ALIBI, nnb.BF16)
     tr = nnb.GptTrainer(cfg, lr=BASE_LR, weight_decay=WEIGHT_DECAY, process_group=pg)

@@ -114,15 +114,23 @@ int nnb200_gemm_status(int* host_code);
 
 /* Causal, optionally document-masked and ALiBi-biased attention over qkv (tokens, 3*d) = q|k|v,
  * tokens = batch*seq in batch-major order; out (tokens, d); lse (batch*heads*seq).  doc_ids may be
- * NULL.  One fused kernel replaces batched_matmul_reduce/_softmax_denom/_softmax_apply and the
- * materialised-score path (compute_layer.hpp:1193-1252; compute_engine.hpp:217-243). */
-int nnb200_attention_forward(const void* qkv, void* out, float* lse, const int32_t* doc_ids, int batch, int seq,
-                             int heads, int head_dim, int alibi, int dtype, void* stream);
+ * NULL.  In bf16, head sizes 64 and 128 with seq a multiple of 128 run on tcgen05 tensor cores.
+ * doc_ranges (NULL, or the table nnb200_attention_doc_ranges made of the same doc_ids) lets those
+ * kernels skip the key blocks a document mask leaves nothing of; the result is bit-identical either
+ * way.  One fused kernel replaces batched_matmul_reduce/_softmax_denom/_softmax_apply, the
+ * materialised-score path (compute_layer.hpp:1193-1252; compute_engine.hpp:217-243) and the
+ * (batch*heads*seq, seq) mask build_attention_mask fills on the host (compute_layer.hpp:2081-2128). */
+int nnb200_attention_forward(const void* qkv, void* out, float* lse, const int32_t* doc_ids, const int32_t* doc_ranges,
+                             int batch, int seq, int heads, int head_dim, int alibi, int dtype, void* stream);
 /* dqkv (tokens, 3*d) from dout (tokens, d); dvec is scratch (batch*heads*seq floats).  Replaces
  * batched_matmul_softmax_backward_q/_kv and the materialised backward (compute_layer.hpp:1296-1360). */
 int nnb200_attention_backward(const void* qkv, const void* out, const void* dout, const float* lse, float* dvec,
-                              void* dqkv, const int32_t* doc_ids, int batch, int seq, int heads, int head_dim, int alibi,
-                              int dtype, void* stream);
+                              void* dqkv, const int32_t* doc_ids, const int32_t* doc_ranges, int batch, int seq, int heads,
+                              int head_dim, int alibi, int dtype, void* stream);
+/* ranges[2*(b*seq/64 + k)], [.. + 1] = smallest and largest document id among rows [64k, 64k+64) of
+ * sequence b; seq must be a multiple of 64; ranges holds 2*batch*seq/64 ints.  The device-side
+ * counterpart of the per-step mask rebuild of CausalSelfAttention (compute_layer.hpp:2226-2246). */
+int nnb200_attention_doc_ranges(const int32_t* doc_ids, int batch, int seq, int32_t* ranges, void* stream);
 
 /* y = norm(x) * gamma (+ beta); layer=1 LayerNorm, 0 RMSNorm; eps 1e-5; rinv (rows), mean (rows,
  * LayerNorm only) are saved for backward.  Replaces LayerNorm/RMSNorm::forward

@@ -58,8 +58,9 @@ SIGNATURES = {
     "nnb200_gemm_profile": [_i],
     "nnb200_gemm_profile_read": [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)],
     "nnb200_launch_count": [_i],
-    "nnb200_attention_forward": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
-    "nnb200_attention_backward": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "nnb200_attention_forward": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "nnb200_attention_backward": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "nnb200_attention_doc_ranges": [_p, _i, _i, _p, _p],
     "nnb200_norm_forward": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
     "nnb200_norm_backward": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
     "nnb200_colsum_scratch_floats": [_i, _i],

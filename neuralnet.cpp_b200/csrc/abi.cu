@@ -106,14 +106,19 @@ int nnb200_gemm_status(int* host_code)
     return 0;
 }
 
-int nnb200_attention_forward(const void* qkv, void* out, float* lse, const int32_t* doc_ids, int batch, int seq,
-                             int heads, int head_dim, int alibi, int dtype, void* stream)
+int nnb200_attention_doc_ranges(const int32_t* doc_ids, int batch, int seq, int32_t* ranges, void* stream)
+{
+    return attention_doc_ranges(doc_ids, batch, seq, ranges, to_stream(stream));
+}
+
+int nnb200_attention_forward(const void* qkv, void* out, float* lse, const int32_t* doc_ids, const int32_t* doc_ranges,
+                             int batch, int seq, int heads, int head_dim, int alibi, int dtype, void* stream)
 {
     DT_CHECK(dtype);
     cudaStream_t s = to_stream(stream);
     if (dtype == 1) {
         if (attention_tc_supported(head_dim, seq, heads * head_dim))
-            return attention_fwd_tc(static_cast<const bf16*>(qkv), static_cast<bf16*>(out), lse, doc_ids, batch, seq, heads, head_dim, alibi, s);
+            return attention_fwd_tc(static_cast<const bf16*>(qkv), static_cast<bf16*>(out), lse, doc_ids, doc_ranges, batch, seq, heads, head_dim, alibi, s);
         if (attention_mma_supported(head_dim, heads * head_dim))
             return attention_fwd_mma(static_cast<const bf16*>(qkv), static_cast<bf16*>(out), lse, doc_ids, batch, seq, heads, head_dim, alibi, s);
         return attention_fwd_simt<bf16>(static_cast<const bf16*>(qkv), static_cast<bf16*>(out), lse, doc_ids, batch, seq, heads, head_dim, alibi, s);
@@ -122,14 +127,14 @@ int nnb200_attention_forward(const void* qkv, void* out, float* lse, const int32
 }
 
 int nnb200_attention_backward(const void* qkv, const void* out, const void* dout, const float* lse, float* dvec,
-                              void* dqkv, const int32_t* doc_ids, int batch, int seq, int heads, int head_dim, int alibi,
-                              int dtype, void* stream)
+                              void* dqkv, const int32_t* doc_ids, const int32_t* doc_ranges, int batch, int seq, int heads,
+                              int head_dim, int alibi, int dtype, void* stream)
 {
     DT_CHECK(dtype);
     cudaStream_t s = to_stream(stream);
     if (dtype == 1) {
         if (attention_tc_supported(head_dim, seq, heads * head_dim))
-            return attention_bwd_tc(static_cast<const bf16*>(qkv), static_cast<const bf16*>(out), static_cast<const bf16*>(dout), lse, dvec, static_cast<bf16*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);
+            return attention_bwd_tc(static_cast<const bf16*>(qkv), static_cast<const bf16*>(out), static_cast<const bf16*>(dout), lse, dvec, static_cast<bf16*>(dqkv), doc_ids, doc_ranges, batch, seq, heads, head_dim, alibi, s);
         if (attention_mma_supported(head_dim, heads * head_dim))
             return attention_bwd_mma(static_cast<const bf16*>(qkv), static_cast<const bf16*>(out), static_cast<const bf16*>(dout), lse, dvec, static_cast<bf16*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);
         return attention_bwd_simt<bf16>(static_cast<const bf16*>(qkv), static_cast<const bf16*>(out), static_cast<const bf16*>(dout), lse, dvec, static_cast<bf16*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);
@@ -160,6 +165,9 @@ size_t nnb200_colsum_scratch_floats(int rows, int cols) { return colsum_scratch_
 int nnb200_bias_grad(const void* g, long long ldg, float* out, float* scratch, int rows, int cols, int dtype, void* stream)
 {
     DT_CHECK(dtype);
+    NNB_ARG_CHECK(rows >= 0 && cols >= 0, "negative shape");
+    NNB_ARG_CHECK(rows == 0 || cols == 0 || (g && out && scratch), "null gradient, output or scratch pointer");
+    NNB_ARG_CHECK(ldg >= cols, "the row stride is shorter than a row (rows would overlap)");
     if (dtype == 1) return colsum_accumulate<bf16>(static_cast<const bf16*>(g), ldg, nullptr, nullptr, nullptr, nullptr, 0, out, scratch, rows, cols, to_stream(stream));
     return colsum_accumulate<float>(static_cast<const float*>(g), ldg, nullptr, nullptr, nullptr, nullptr, 0, out, scratch, rows, cols, to_stream(stream));
 }

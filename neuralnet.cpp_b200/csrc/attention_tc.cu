@@ -1,29 +1,34 @@
-// Fused causal / document-masked / ALiBi attention forward on the 5th-generation tensor cores.
+// Fused causal / document-masked / ALiBi attention forward on the 5th-generation tensor cores, head sizes 64 and 128.
 //
-// Persistent: one CTA per SM walks the list of (128-query tile, head, batch) work items, longest tiles first,
-// in snake order (snake_tile in tc_ptx.cuh).  Ten warps:
-//   warp 0      TMA producer: the tile's Q (two tile buffers, so the next tile's Q is fetched early), then K/V
-//               tiles of 128 keys through a 3-stage ring that runs on across tiles
-//   warp 1      MMA issuer:   S = Q K^T   (128x128x64)  into one of two TMEM score buffers
-//                             O' = P V    (128x64x128)  into TMEM columns [256,320)
-//   warps 2..9  softmax: thread (row, half) owns 64 of the 128 score columns of one query row
-//               (two warps share each 32-lane TMEM quadrant; four per quadrant with 32 columns each
-//               measured slower: 104 against 98 us at batch 16 x 12 heads x 1024).  It reads its scores
-//               once with tcgen05.ld, applies scale, causal / document mask and ALiBi bias, exchanges the
-//               row maximum with its partner through shared memory, writes P as bf16 into a K-major
-//               128B-swizzled shared tile (the A operand of the second MMA) and folds its 32 columns
-//               of O' into registers; at the end of a tile it normalises and stores its output row.
-// The score buffer and the P tile are double-buffered, so Q K^T of block k+1 and P V of block k run
-// on the tensor core while the softmax warps work on block k / k+1; all buffer positions and barrier
-// phases are counted across tiles, so the first MMAs of the next tile overlap the write-out of this one.
-// V is consumed as an MN-major B operand straight from its (key, head_dim) tile.  Nothing of size (S, S)
-// ever reaches memory.
-// Replaces batched_matmul_reduce / _softmax_denom / _softmax_apply and the materialised score path
-// of the reference (compute_layer.hpp:1193-1252; cpu_engine.hpp:426-699).
-// Every wait is bounded; a wait that gives up raises a status word, the softmax warps learn of it together
-// at their next exchange barrier, and the CTA drains.
+// Persistent: the CTAs resident on an SM (two for head size 64: 98 KB of shared memory and 256 TMEM columns each; one
+// for head size 128) walk the list of (128-query tile, head, batch) work items, longest tiles first, in snake order
+// (snake_tile in tc_ptx.cuh).  Ten warps:
+//   warp 0      TMA producer: the tile's Q, then per 128-key block one K tile and one V tile (ring of two)
+//   warp 1      MMA issuer:   S = Q K^T   (128 x 128 x head)  into TMEM columns [0, 128)
+//                             O' = P V    (128 x head x 128)  into TMEM columns [128, 128 + head)
+//   warps 2..9  softmax: thread (row, half) owns 64 of the 128 score columns of one query row (two warps share each
+//               32-lane TMEM quadrant).  It reads its scores from TMEM twice, 32 columns at a time (row maximum, then
+//               P), so that it never holds more than 32 of them; applies scale, causal / document mask and ALiBi bias;
+//               exchanges the row maximum with its partner through shared memory; writes P as bf16 into a K-major
+//               128B-swizzled shared tile (the A operand of the second MMA) and folds its half of the columns of O'
+//               into registers; at the end of a tile it normalises and stores its output row.
+// Q, K, S and P are single-buffered (the key tile is released as soon as Q K^T has read it): with two CTAs per SM the
+// softmax chain of one CTA is covered by the other CTA's MMAs.  All ring positions and barrier phases are counted
+// across tiles, so the first loads and MMAs of the next tile overlap the write-out of this one.
+// K-major operands wider than 64 values are kept as sub-tiles of 64 columns (one 128-byte swizzle atom per row);
+// V is consumed as an MN-major B operand straight from its (key, head) tile.  Nothing of size (S, S) reaches memory.
+//
+// Document masks: with a table of per-64-row (min, max) document ids (attention_doc_ranges) every role skips the key
+// blocks whose id range cannot meet the query tile's range.  A skipped block would have contributed P = 0 everywhere,
+// so the result is bit-identical with and without the table.
+//
+// Replaces batched_matmul_reduce / _softmax_denom / _softmax_apply and the materialised score path of the reference
+// (compute_layer.hpp:1193-1252; cpu_engine.hpp:426-699) and the per-step host mask build (:2081-2128, 2226-2246).
+// Every wait is bounded; a wait that gives up raises a status word, the softmax warps learn of it together at their
+// next exchange barrier, and the CTA drains.
 #include <type_traits>
 
+#include "attention_tc.cuh"
 #include "kernels.h"
 #include "tc_ptx.cuh"
 
@@ -31,17 +36,21 @@ namespace nnb {
 
 __device__ int g_attn_error = 0;
 
-constexpr int AQ = 128, AK = 128, ADK = 64;
-constexpr int A_TILE = 128 * 128;                  // bytes of a 128-row x 64-bf16 tile
-constexpr int A_KV_STAGES = 3;
-// Q (2 tiles) | K,V ring | P (2 buffers x two 64-key halves) | row-max exchange | barriers
-constexpr int A_OFF_KV = 2 * A_TILE, A_OFF_P = A_OFF_KV + A_KV_STAGES * 2 * A_TILE, A_OFF_X = A_OFF_P + 4 * A_TILE,
-              A_OFF_BAR = A_OFF_X + 2 * 2 * 128 * 4, A_SMEM = A_OFF_BAR + 256;
-constexpr uint32_t A_TMEM_COLS = 512;
+constexpr int AQ = 128, AK = 128;
+constexpr int A_TILE = 128 * 128;                  // bytes of a 128-row x 64-bf16 sub-tile
 constexpr float kLog2eF = 1.4426950408889634f, kLn2F = 0.6931471805599453f;
 
+// shared memory: Q | K | V ring of two | P (two 64-key halves) | row-max exchange | barriers
+template <int DK> struct FwdLayout {
+    static constexpr int NS = DK / 64;                                  // 64-column sub-tiles per operand tile
+    static constexpr int OFF_K = NS * A_TILE, OFF_V = 2 * NS * A_TILE, OFF_P = 4 * NS * A_TILE, OFF_X = OFF_P + 2 * A_TILE,
+                         OFF_BAR = OFF_X + 2 * 2 * 128 * 4, SMEM = OFF_BAR + 256;
+    static constexpr uint32_t TMEM_COLS = 256;                          // scores [0, 128), O' [128, 128 + DK)
+    static constexpr int CTAS_PER_SM = DK == 64 ? 2 : 1;
+};
+
 struct AttnTcArgs {
-    bf16* out; float* lse; const int* doc;
+    bf16* out; float* lse; const int* doc; const int2* ranges;
     int B, S, H, alibi;
     float scale;
 };
@@ -78,277 +87,19 @@ __device__ __forceinline__ AttnTile attn_tile(int w, int nq, int H, int HB)
     return t;
 }
 
-template <bool DOC, bool ALIBI>
-__global__ void __launch_bounds__(320, 1)
+template <int DK, bool DOC, bool ALIBI>
+__global__ void __launch_bounds__(320, FwdLayout<DK>::CTAS_PER_SM)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a)
 {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sQ = smem;                            // two query tiles: the next one is fetched while this one is in use
-    uint8_t* sKV = smem + A_OFF_KV;                // stage s: K at sKV + s*2*A_TILE, V right after it
-    uint8_t* sP = smem + A_OFF_P;                  // buffer b at sP + b*2*A_TILE (two 64-key halves)
-    float* sX = reinterpret_cast<float*>(smem + A_OFF_X);   // [buffer][half][row]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + A_OFF_BAR);
-    const uint32_t bar0 = smem_u32(bars);
-    const uint32_t q_full0 = bar0, q_empty0 = bar0 + 16, kv_full0 = bar0 + 32, kv_empty0 = bar0 + 56, s_full0 = bar0 + 80,
-                   s_empty0 = bar0 + 96, p_full0 = bar0 + 112, p_empty0 = bar0 + 128, o_full = bar0 + 144, o_empty = bar0 + 152;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int d = a.H * ADK;
-    const int nq = a.S / AQ;
-    const int total = nq * a.H * a.B;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < 2; ++s) { mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1); }
-        for (int s = 0; s < A_KV_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(s_full0 + 8 * s, 1); mbar_init(s_empty0 + 8 * s, 8);
-            mbar_init(p_full0 + 8 * s, 8); mbar_init(p_empty0 + 8 * s, 1);
-        }
-        mbar_init(o_full, 1); mbar_init(o_empty, 8);
-        *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;        // the swizzled tiles need a 1024-byte aligned base
-        if (*abort_flag) atomicCAS(&g_attn_error, 0, (9 << 16));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(A_TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_O = tmem_base + 256;
-
-    // instruction descriptors: fp32 accumulate, bf16 operands; S: N=128, both K-major; PV: N=64, B MN-major
-    constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(AK >> 3) << 17) | (uint32_t(AQ >> 4) << 24);
-    constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (uint32_t(ADK >> 3) << 17) | (uint32_t(AQ >> 4) << 24);
-
-    // Every role walks the same list of tiles; the ring / buffer positions and barrier phases run on across
-    // tiles (kv: key-block counter; gj: the same counter as seen by the score / P / O' buffers; tn: tile counter).
-    if (warp == 0) {
-        if (lane == 0 && !*abort_flag) {
-            int kv = 0, tn = 0;
-            bool ok = true;
-            for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
-                const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
-                const int nkb = t.qb + 1, row_base = t.b * a.S, qs = tn & 1;
-                if (!mbar_wait(q_empty0 + 8 * qs, ((tn >> 1) & 1) ^ 1, abort_flag, 11, &g_attn_error)) break;
-                mbar_expect_tx(q_full0 + 8 * qs, A_TILE);
-                tma_load_2d(smem_u32(sQ + qs * A_TILE), &tmQKV, q_full0 + 8 * qs, t.h * ADK, row_base + t.qb * AQ);
-                for (int kb = 0; kb < nkb; ++kb, ++kv) {
-                    const int s = kv % A_KV_STAGES;
-                    const uint32_t ph = (kv / A_KV_STAGES) & 1;
-                    if (!mbar_wait(kv_empty0 + 8 * s, ph ^ 1, abort_flag, 1, &g_attn_error)) { ok = false; break; }
-                    mbar_expect_tx(kv_full0 + 8 * s, 2 * A_TILE);
-                    const uint32_t kdst = smem_u32(sKV + s * 2 * A_TILE);
-                    tma_load_2d(kdst, &tmQKV, kv_full0 + 8 * s, d + t.h * ADK, row_base + kb * AK);
-                    tma_load_2d(kdst + A_TILE, &tmQKV, kv_full0 + 8 * s, 2 * d + t.h * ADK, row_base + kb * AK);
-                }
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0 && !*abort_flag) {
-            int kv0 = 0, tn = 0;                                // kv0: key-block counter at the start of the tile
-            bool ok = true;
-            for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
-                const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
-                const int nkb = t.qb + 1, qs = tn & 1;
-                ok = mbar_wait(q_full0 + 8 * qs, (tn >> 1) & 1, abort_flag, 2, &g_attn_error);
-                const uint32_t q_addr = smem_u32(sQ + qs * A_TILE);
-                auto issue_s = [&](int gj) -> bool {
-                    const int st = gj % A_KV_STAGES, sb = gj & 1, u = gj >> 1;
-                    if (!mbar_wait(kv_full0 + 8 * st, (gj / A_KV_STAGES) & 1, abort_flag, 5, &g_attn_error)) return false;
-                    if (u >= 1 && !mbar_wait(s_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 6, &g_attn_error)) return false;
-                    tc_fence_after();
-                    const uint32_t k_addr = smem_u32(sKV + st * 2 * A_TILE);
-#pragma unroll
-                    for (int k = 0; k < ADK / 16; ++k)
-                        umma_bf16(tmem_base + sb * 128, smem_desc(q_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 32, 16, 1024),
-                                  IDESC_S, k > 0 ? 1u : 0u);
-                    umma_commit(s_full0 + 8 * sb);
-                    return true;
-                };
-                auto issue_pv = [&](int gj) -> bool {
-                    const int st = gj % A_KV_STAGES, pb = gj & 1;
-                    if (!mbar_wait(p_full0 + 8 * pb, (gj >> 1) & 1, abort_flag, 3, &g_attn_error)) return false;
-                    if (gj >= 1 && !mbar_wait(o_empty, (gj - 1) & 1, abort_flag, 4, &g_attn_error)) return false;
-                    tc_fence_after();
-                    const uint32_t p_addr = smem_u32(sP + pb * 2 * A_TILE);
-                    const uint32_t v_addr = smem_u32(sKV + st * 2 * A_TILE + A_TILE);
-#pragma unroll
-                    for (int k = 0; k < AK / 16; ++k) {
-                        const uint64_t da = smem_desc(p_addr + (k >> 2) * A_TILE + (k & 3) * 32, 16, 1024);
-                        const uint64_t db = smem_desc(v_addr + k * 2048, A_TILE, 1024);
-                        umma_bf16(tmem_O, da, db, IDESC_PV, k > 0 ? 1u : 0u);
-                    }
-                    umma_commit(o_full);
-                    umma_commit(p_empty0 + 8 * pb);
-                    umma_commit(kv_empty0 + 8 * st);
-                    return true;
-                };
-                if (ok) ok = issue_s(kv0);
-                for (int kb = 0; ok && kb < nkb; ++kb) {
-                    if (kb + 1 < nkb) ok = issue_s(kv0 + kb + 1);
-                    if (ok) ok = issue_pv(kv0 + kb);
-                }
-                if (ok) umma_commit(q_empty0 + 8 * qs);         // the query tile is free once this tile's MMAs are done
-                kv0 += nkb;
-            }
-        }
-    } else {
-        const int q = warp & 3, hf = (warp - 2) >> 2;          // TMEM lane quadrant, column half
-        const int row = q * 32 + lane;
-        const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-        const float scale2 = a.scale * kLog2eF;
-        const int sw = row & 7;
-        bool ok = true, bad = *abort_flag != 0;                 // bad: a wait of this thread gave up (reported at the next barrier)
-        int kv0 = 0, xc = 0;                                    // key-block counter; exchange counter (alternates the sX buffer)
-
-        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps) {
-            const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
-            const int h = t.h, b = t.b, q0 = t.qb * AQ, nkb = t.qb + 1, row_base = b * a.S;
-            const int i = q0 + row;                            // query position inside the sequence
-            const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kLog2eF : 0.f;
-            const int my_doc = DOC ? a.doc[row_base + i] : 0;
-            float m_run = -INFINITY, l_run = 0.f;
-            float o_acc[32];
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o_acc[c] = 0.f;
-
-            auto fold_o = [&](int gj) -> bool {                 // o_acc += O'(gj), this thread's 32 columns
-                if (!mbar_wait(o_full, gj & 1, abort_flag, 7, &g_attn_error)) return false;
-                tc_fence_after();
-                uint32_t r[32];
-                tmem_ld32(tmem_O + lane_addr + hf * 32, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 32; ++c) o_acc[c] += __uint_as_float(r[c]);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(o_empty);
-                return true;
-            };
-
-            // One 128-key block.  DIAG: the block on the diagonal (causal mask inside it).  The score of
-            // column cj is r*scale2 + (slope2*cj + abase); with the loops unrolled cj is a literal.
-            auto block = [&](auto diag_tag, int kb) -> bool {
-                constexpr bool DIAG = decltype(diag_tag)::value;
-                const int gj = kv0 + kb, sb = gj & 1, u = gj >> 1;
-                bad |= !mbar_wait(s_full0 + 8 * sb, u & 1, abort_flag, 8, &g_attn_error);
-                tc_fence_after();
-                const int k0 = kb * AK;
-                const int* dk_ptr = DOC ? a.doc + row_base + k0 + hf * 64 : nullptr;
-                const float abase = ALIBI ? -slope2 * static_cast<float>(i - k0 - hf * 64) : 0.f;
-                float s[64];
-                {
-                    uint32_t r0[32], r1[32];
-                    tmem_ld32(tmem_base + sb * 128 + lane_addr + hf * 64, r0);
-                    tmem_ld32(tmem_base + sb * 128 + lane_addr + hf * 64 + 32, r1);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) { s[jj] = __uint_as_float(r0[jj]); s[32 + jj] = __uint_as_float(r1[jj]); }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(s_empty0 + 8 * sb);  // scores are in registers: the buffer may be overwritten
-                float mx = -INFINITY;
-#pragma unroll
-                for (int cj = 0; cj < 64; ++cj) {
-                    float sc = ALIBI ? fmaf(s[cj], scale2, fmaf(slope2, static_cast<float>(cj), abase)) : s[cj] * scale2;
-                    if (DIAG && hf * 64 + cj > row) sc = -INFINITY;
-                    if (DOC && dk_ptr[cj] != my_doc) sc = -INFINITY;
-                    s[cj] = sc;
-                    mx = fmaxf(mx, sc);
-                }
-                float* xs = sX + (xc & 1) * 256;
-                ++xc;
-                xs[hf * 128 + row] = mx;
-                if (softmax_any(bad)) return false;             // the same answer in all eight warps
-                const float m_new = fmaxf(m_run, fmaxf(mx, xs[(hf ^ 1) * 128 + row]));
-                const float ms = (m_new == -INFINITY) ? 0.f : m_new;
-                const float corr = ex2_approx(m_run - ms);
-                if (kb >= 1) bad |= !fold_o(gj - 1);
-                if (__any_sync(0xffffffffu, corr != 1.0f)) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) o_acc[c] *= corr;
-                }
-                if (u >= 1) bad |= !mbar_wait(p_empty0 + 8 * sb, (u - 1) & 1, abort_flag, 10, &g_attn_error);
-                uint8_t* prow = sP + sb * 2 * A_TILE + hf * A_TILE + row * 128;
-                float rs = 0.f;
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    uint32_t pk[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float p0 = ex2_approx(s[g * 8 + e * 2] - ms), p1 = ex2_approx(s[g * 8 + e * 2 + 1] - ms);
-                        rs += p0 + p1;
-                        __nv_bfloat162 tt = __floats2bfloat162_rn(p0, p1);
-                        pk[e] = *reinterpret_cast<uint32_t*>(&tt);
-                    }
-                    *reinterpret_cast<uint4*>(prow + ((g ^ sw) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                }
-                l_run = l_run * corr + rs;
-                m_run = m_new;
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the tensor core
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_full0 + 8 * sb);
-                return true;
-            };
-            for (int kb = 0; ok && kb < nkb - 1; ++kb) ok = block(std::false_type{}, kb);
-            if (ok) ok = block(std::true_type{}, nkb - 1);
-            if (!ok) break;                                     // decided at a barrier: uniform over the softmax warps
-            bad |= !fold_o(kv0 + nkb - 1);
-            // the row sum is split over the two halves: exchange once more
-            float* xs = sX + (xc & 1) * 256;
-            ++xc;
-            xs[hf * 128 + row] = l_run;
-            if (softmax_any(bad)) break;
-            {
-                const float l_tot = l_run + xs[(hf ^ 1) * 128 + row];
-                const float inv = 1.0f / l_tot;
-                bf16* op = a.out + (static_cast<size_t>(row_base) + i) * d + h * ADK + hf * 32;
-#pragma unroll
-                for (int c = 0; c < 32; c += 8) {
-                    Vec16<bf16> o;
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(o_acc[c + k] * inv);
-                    st16(op + c, o);
-                }
-                if (hf == 0) a.lse[(static_cast<size_t>(b) * a.H + h) * a.S + i] = (m_run + log2f(l_tot)) * kLn2F;
-            }
-            kv0 += nkb;
-        }
-    }
-
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(A_TMEM_COLS) : "memory");
-    }
-}
-
-// The same kernel with every resource single-buffered, so that two CTAs fit on an SM (98 KB of shared memory, 256 TMEM
-// columns each): while the softmax warps of one CTA are in their dependency chain the other CTA's MMAs run.  The key
-// tile is freed as soon as Q K^T of its block has run, the value tiles go through a ring of two.
-constexpr int A2_OFF_K = A_TILE, A2_OFF_V = 2 * A_TILE, A2_OFF_P = 4 * A_TILE, A2_OFF_X = 6 * A_TILE, A2_OFF_BAR = A2_OFF_X + 2 * 2 * 128 * 4,
-              A2_SMEM = A2_OFF_BAR + 256;
-constexpr uint32_t A2_TMEM_COLS = 256;
-
-template <bool DOC, bool ALIBI>
-__global__ void __launch_bounds__(320, 2)
-attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a)
-{
+    using LY = FwdLayout<DK>;
+    constexpr int NS = LY::NS, TILE = NS * A_TILE;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;                            // one query tile
-    uint8_t* sK = smem + A2_OFF_K;                 // one key tile: free again as soon as Q K^T of its block has run
-    uint8_t* sV = smem + A2_OFF_V;                 // two value tiles
-    uint8_t* sP = smem + A2_OFF_P;                 // one P tile (two 64-key halves)
-    float* sX = reinterpret_cast<float*>(smem + A2_OFF_X);   // [buffer][half][row]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + A2_OFF_BAR);
+    uint8_t* sK = smem + LY::OFF_K;                // one key tile: free again as soon as Q K^T of its block has run
+    uint8_t* sV = smem + LY::OFF_V;                // two value tiles
+    uint8_t* sP = smem + LY::OFF_P;                // one P tile (two 64-key halves)
+    float* sX = reinterpret_cast<float*>(smem + LY::OFF_X);   // [buffer][half][row]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + LY::OFF_BAR);
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t q_full = bar0, q_empty = bar0 + 8, k_full = bar0 + 16, k_empty = bar0 + 24, v_full0 = bar0 + 32, v_empty0 = bar0 + 48,
                    s_full = bar0 + 64, s_empty = bar0 + 72, p_full = bar0 + 80, p_empty = bar0 + 88, o_full = bar0 + 96, o_empty = bar0 + 104;
@@ -356,7 +107,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int d = a.H * ADK;
+    const int d = a.H * DK;
     const int nq = a.S / AQ;
     const int total = nq * a.H * a.B;
 
@@ -371,49 +122,68 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(A2_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(LY::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_O = tmem_base + 128;           // scores in columns [0,128), O' in [128,192)
+    const uint32_t tmem_O = tmem_base + 128;
 
-    // instruction descriptors: fp32 accumulate, bf16 operands; S: N=128, both K-major; PV: N=64, B MN-major
+    // instruction descriptors: fp32 accumulate, bf16 operands; S: N=128, both K-major; PV: N=DK, B MN-major
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(AK >> 3) << 17) | (uint32_t(AQ >> 4) << 24);
-    constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (uint32_t(ADK >> 3) << 17) | (uint32_t(AQ >> 4) << 24);
+    constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (uint32_t(DK >> 3) << 17) | (uint32_t(AQ >> 4) << 24);
 
-    // Every role walks the same list of tiles; the ring / buffer positions and barrier phases run on across
-    // tiles (kv: key-block counter; gj: the same counter as seen by the score / P / O' buffers; tn: tile counter).
+    // Every role walks the same list of tiles and, inside a tile, the same list of active key blocks; the ring / buffer
+    // positions and barrier phases run on across tiles (kv: count of key blocks processed; tn: tile counter).
+    // A whole warp evaluates the block mask (one ballot per 32 blocks); lane 0 of warps 0 and 1 then does the work.
+    auto tile_mask = [&](const AttnTile& t, int nkb) -> BlockMask {
+        if (!DOC || a.ranges == nullptr) return block_mask_all();
+        const int2* rng = a.ranges + static_cast<size_t>(t.b) * (a.S / 64);
+        return doc_block_mask(rng, 0, nkb, 2, rng[2 * t.qb], rng[2 * t.qb + 1], nkb - 1, nkb, lane);
+    };
+
     if (warp == 0) {
-        if (lane == 0 && !*abort_flag) {
-            int kv = 0, tn = 0;
-            bool ok = true;
-            for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
-                const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
-                const int nkb = t.qb + 1, row_base = t.b * a.S;
-                if (!mbar_wait(q_empty, (tn & 1) ^ 1, abort_flag, 11, &g_attn_error)) break;
-                mbar_expect_tx(q_full, A_TILE);
-                tma_load_2d(smem_u32(sQ), &tmQKV, q_full, t.h * ADK, row_base + t.qb * AQ);
-                for (int kb = 0; kb < nkb; ++kb, ++kv) {
+        int kv = 0, tn = 0;
+        bool ok = !*abort_flag;
+        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
+            const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
+            const int nkb = t.qb + 1, row_base = t.b * a.S;
+            const BlockMask bm = tile_mask(t, nkb);
+            if (lane == 0) {
+                ok = mbar_wait(q_empty, (tn & 1) ^ 1, abort_flag, 11, &g_attn_error);
+                if (ok) {
+                    mbar_expect_tx(q_full, TILE);
+#pragma unroll
+                    for (int j = 0; j < NS; ++j) tma_load_2d(smem_u32(sQ + j * A_TILE), &tmQKV, q_full, t.h * DK + j * 64, row_base + t.qb * AQ);
+                }
+                for (int kb = 0; ok && kb < nkb; ++kb) {
+                    if (!block_active(bm, kb)) continue;
                     if (!mbar_wait(k_empty, (kv & 1) ^ 1, abort_flag, 1, &g_attn_error)) { ok = false; break; }
-                    mbar_expect_tx(k_full, A_TILE);
-                    tma_load_2d(smem_u32(sK), &tmQKV, k_full, d + t.h * ADK, row_base + kb * AK);
+                    mbar_expect_tx(k_full, TILE);
+#pragma unroll
+                    for (int j = 0; j < NS; ++j) tma_load_2d(smem_u32(sK + j * A_TILE), &tmQKV, k_full, d + t.h * DK + j * 64, row_base + kb * AK);
                     const int vs = kv & 1;
                     if (!mbar_wait(v_empty0 + 8 * vs, ((kv >> 1) & 1) ^ 1, abort_flag, 12, &g_attn_error)) { ok = false; break; }
-                    mbar_expect_tx(v_full0 + 8 * vs, A_TILE);
-                    tma_load_2d(smem_u32(sV + vs * A_TILE), &tmQKV, v_full0 + 8 * vs, 2 * d + t.h * ADK, row_base + kb * AK);
+                    mbar_expect_tx(v_full0 + 8 * vs, TILE);
+#pragma unroll
+                    for (int j = 0; j < NS; ++j)
+                        tma_load_2d(smem_u32(sV + vs * TILE + j * A_TILE), &tmQKV, v_full0 + 8 * vs, 2 * d + t.h * DK + j * 64, row_base + kb * AK);
+                    ++kv;
                 }
             }
+            kv = __shfl_sync(0xffffffffu, kv, 0);
+            ok = __shfl_sync(0xffffffffu, static_cast<int>(ok), 0) != 0;
         }
     } else if (warp == 1) {
-        if (lane == 0 && !*abort_flag) {
-            int kv0 = 0, tn = 0;                                // kv0: key-block counter at the start of the tile
-            bool ok = true;
-            for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
-                const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
-                const int nkb = t.qb + 1;
+        int kv = 0, tn = 0;
+        bool ok = !*abort_flag;
+        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
+            const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
+            const int nkb = t.qb + 1;
+            const BlockMask bm = tile_mask(t, nkb);
+            if (lane == 0) {
                 ok = mbar_wait(q_full, tn & 1, abort_flag, 2, &g_attn_error);
                 const uint32_t q_addr = smem_u32(sQ);
                 auto issue_s = [&](int gj) -> bool {
@@ -422,9 +192,10 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
                     tc_fence_after();
                     const uint32_t k_addr = smem_u32(sK);
 #pragma unroll
-                    for (int k = 0; k < ADK / 16; ++k)
-                        umma_bf16(tmem_base, smem_desc(q_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 32, 16, 1024),
-                                  IDESC_S, k > 0 ? 1u : 0u);
+                    for (int k = 0; k < DK / 16; ++k) {
+                        const uint32_t o = (k >> 2) * A_TILE + (k & 3) * 32;
+                        umma_bf16(tmem_base, smem_desc(q_addr + o, 16, 1024), smem_desc(k_addr + o, 16, 1024), IDESC_S, k > 0 ? 1u : 0u);
+                    }
                     umma_commit(s_full);
                     umma_commit(k_empty);                           // the key tile is free once these MMAs have read it
                     return true;
@@ -436,11 +207,11 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
                     if (!mbar_wait(v_full0 + 8 * vs, (gj >> 1) & 1, abort_flag, 13, &g_attn_error)) return false;
                     tc_fence_after();
                     const uint32_t p_addr = smem_u32(sP);
-                    const uint32_t v_addr = smem_u32(sV + vs * A_TILE);
+                    const uint32_t v_addr = smem_u32(sV + vs * TILE);
 #pragma unroll
                     for (int k = 0; k < AK / 16; ++k) {
                         const uint64_t da = smem_desc(p_addr + (k >> 2) * A_TILE + (k & 3) * 32, 16, 1024);
-                        const uint64_t db = smem_desc(v_addr + k * 2048, A_TILE, 1024);
+                        const uint64_t db = smem_desc(v_addr + k * 2048, A_TILE, 1024);   // the next 64 head columns: one sub-tile on
                         umma_bf16(tmem_O, da, db, IDESC_PV, k > 0 ? 1u : 0u);
                     }
                     umma_commit(o_full);
@@ -448,14 +219,18 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
                     umma_commit(v_empty0 + 8 * vs);
                     return true;
                 };
-                if (ok) ok = issue_s(kv0);
-                for (int kb = 0; ok && kb < nkb; ++kb) {
-                    if (kb + 1 < nkb) ok = issue_s(kv0 + kb + 1);
-                    if (ok) ok = issue_pv(kv0 + kb);
+                // the scores of the next active block are issued before P V of the current one
+                const int nact = block_count(bm, nkb);
+                if (ok) ok = issue_s(kv);
+                for (int j = 0; ok && j < nact; ++j) {
+                    if (j + 1 < nact) ok = issue_s(kv + j + 1);
+                    if (ok) ok = issue_pv(kv + j);
                 }
                 if (ok) umma_commit(q_empty);                   // the query tile is free once this tile's MMAs are done
-                kv0 += nkb;
+                kv += nact;
             }
+            kv = __shfl_sync(0xffffffffu, kv, 0);
+            ok = __shfl_sync(0xffffffffu, static_cast<int>(ok), 0) != 0;
         }
     } else {
         const int q = warp & 3, hf = (warp - 2) >> 2;          // TMEM lane quadrant, column half
@@ -463,47 +238,49 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
         const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
         const float scale2 = a.scale * kLog2eF;
         const int sw = row & 7;
+        constexpr int OC = DK / 2;                              // output columns this thread keeps
         bool ok = true, bad = *abort_flag != 0;                 // bad: a wait of this thread gave up (reported at the next barrier)
         int kv0 = 0, xc = 0;                                    // key-block counter; exchange counter (alternates the sX buffer)
 
         for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps) {
             const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
             const int h = t.h, b = t.b, q0 = t.qb * AQ, nkb = t.qb + 1, row_base = b * a.S;
+            const BlockMask bm = tile_mask(t, nkb);
             const int i = q0 + row;                            // query position inside the sequence
             const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kLog2eF : 0.f;
             const int my_doc = DOC ? a.doc[row_base + i] : 0;
             float m_run = -INFINITY, l_run = 0.f;
-            float o_acc[32];
+            float o_acc[OC];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) o_acc[c] = 0.f;
+            for (int c = 0; c < OC; ++c) o_acc[c] = 0.f;
 
-            auto fold_o = [&](int gj) -> bool {                 // o_acc += O'(gj), this thread's 32 columns
+            auto fold_o = [&](int gj) -> bool {                 // o_acc += O'(gj), this thread's columns
                 if (!mbar_wait(o_full, gj & 1, abort_flag, 7, &g_attn_error)) return false;
                 tc_fence_after();
-                uint32_t r[32];
-                tmem_ld32(tmem_O + lane_addr + hf * 32, r);
-                tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 32; ++c) o_acc[c] += __uint_as_float(r[c]);
+                for (int c0 = 0; c0 < OC; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_O + lane_addr + hf * OC + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o_acc[c0 + c] += __uint_as_float(r[c]);
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(o_empty);
                 return true;
             };
 
-            // One 128-key block.  DIAG: the block on the diagonal (causal mask inside it).  The score of
-            // column cj is r*scale2 + (slope2*cj + abase); with the loops unrolled cj is a literal.
-            auto block = [&](auto diag_tag, int kb) -> bool {
+            // One 128-key block, the cnt-th active one of the tile.  DIAG: the block on the diagonal (causal mask
+            // inside it).  The score of column cj is r*scale2 + (slope2*cj + abase); with the loops unrolled cj is a literal.
+            auto block = [&](auto diag_tag, int kb, int cnt) -> bool {
                 constexpr bool DIAG = decltype(diag_tag)::value;
-                const int gj = kv0 + kb;
+                const int gj = kv0 + cnt;
                 bad |= !mbar_wait(s_full, gj & 1, abort_flag, 8, &g_attn_error);
                 tc_fence_after();
                 const int k0 = kb * AK;
                 const int* dk_ptr = DOC ? a.doc + row_base + k0 + hf * 64 : nullptr;
                 const float abase = ALIBI ? -slope2 * static_cast<float>(i - k0 - hf * 64) : 0.f;
-                // Two passes over the scores in TMEM, 32 columns at a time, so that the thread never holds more than
-                // 32 of them: the first finds the row maximum, the second makes P.  The score buffer is released
-                // after the second pass.
                 auto score = [&](float raw, int cj) -> float {
                     // cj is a literal once unrolled: nothing here is loop-invariant, so nothing is kept live across the passes
                     float sc = ALIBI ? fmaf(slope2, static_cast<float>(cj), fmaf(raw, scale2, abase)) : raw * scale2;
@@ -527,10 +304,10 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
                 const float m_new = fmaxf(m_run, fmaxf(mx, xs[(hf ^ 1) * 128 + row]));
                 const float ms = (m_new == -INFINITY) ? 0.f : m_new;
                 const float corr = ex2_approx(m_run - ms);
-                if (kb >= 1) bad |= !fold_o(gj - 1);
+                if (cnt >= 1) bad |= !fold_o(gj - 1);
                 if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) o_acc[c] *= corr;
+                    for (int c = 0; c < OC; ++c) o_acc[c] *= corr;
                 }
                 if (gj >= 1) bad |= !mbar_wait(p_empty, (gj - 1) & 1, abort_flag, 10, &g_attn_error);
                 uint8_t* prow = sP + hf * A_TILE + row * 128;
@@ -565,10 +342,15 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
                 if (lane == 0) mbar_arrive(p_full);
                 return true;
             };
-            for (int kb = 0; ok && kb < nkb - 1; ++kb) ok = block(std::false_type{}, kb);
-            if (ok) ok = block(std::true_type{}, nkb - 1);
+            int cnt = 0;
+            for (int kb = 0; ok && kb < nkb - 1; ++kb) {
+                if (!block_active(bm, kb)) continue;
+                ok = block(std::false_type{}, kb, cnt);
+                ++cnt;
+            }
+            if (ok) { ok = block(std::true_type{}, nkb - 1, cnt); ++cnt; }
             if (!ok) break;                                     // decided at a barrier: uniform over the softmax warps
-            bad |= !fold_o(kv0 + nkb - 1);
+            bad |= !fold_o(kv0 + cnt - 1);
             // the row sum is split over the two halves: exchange once more
             float* xs = sX + (xc & 1) * 256;
             ++xc;
@@ -577,9 +359,9 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
             {
                 const float l_tot = l_run + xs[(hf ^ 1) * 128 + row];
                 const float inv = 1.0f / l_tot;
-                bf16* op = a.out + (static_cast<size_t>(row_base) + i) * d + h * ADK + hf * 32;
+                bf16* op = a.out + (static_cast<size_t>(row_base) + i) * d + h * DK + hf * OC;
 #pragma unroll
-                for (int c = 0; c < 32; c += 8) {
+                for (int c = 0; c < OC; c += 8) {
                     Vec16<bf16> o;
 #pragma unroll
                     for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(o_acc[c + k] * inv);
@@ -587,7 +369,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
                 }
                 if (hf == 0) a.lse[(static_cast<size_t>(b) * a.H + h) * a.S + i] = (m_run + log2f(l_tot)) * kLn2F;
             }
-            kv0 += nkb;
+            kv0 += cnt;
         }
     }
 
@@ -595,70 +377,74 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs 
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(A2_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(LY::TMEM_COLS) : "memory");
     }
 }
 
-template <bool DOC, bool ALIBI>
-static int launch_fwd_tc(const CUtensorMap& tm, const AttnTcArgs& a, dim3 grid, cudaStream_t s)
+// ---------------------------------------------------------------- document ranges
+// ranges[b * S/64 + blk] = (min, max) of the document ids of rows [64 blk, 64 blk + 64) of sequence b: one warp per block
+__global__ void doc_ranges_kernel(const int* __restrict__ doc, int2* __restrict__ ranges, int nblocks)
 {
-    static bool attr_set = false;
-    if (!attr_set) {
-        NNB_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_tc_kernel<DOC, ALIBI>, cudaFuncAttributeMaxDynamicSharedMemorySize, A_SMEM));
-        attr_set = true;
+    const int blk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (blk >= nblocks) return;
+    const int a0 = doc[static_cast<size_t>(blk) * 64 + lane], a1 = doc[static_cast<size_t>(blk) * 64 + 32 + lane];
+    int lo = min(a0, a1), hi = max(a0, a1);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+        hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
     }
-    attn_fwd_tc_kernel<DOC, ALIBI><<<grid, 320, A_SMEM, s>>>(tm, a);
+    if (lane == 0) ranges[blk] = make_int2(lo, hi);
+}
+
+int attention_doc_ranges(const int* doc, int B, int S, int* ranges, cudaStream_t s)
+{
+    NNB_ARG_CHECK(doc && ranges, "document ids and the range table are required");
+    NNB_ARG_CHECK(S % 64 == 0, "the sequence length must be a multiple of 64");
+    const int nblocks = B * (S / 64);
+    if (nblocks == 0) return 0;
+    doc_ranges_kernel<<<static_cast<unsigned>(ceil_div(nblocks, 8)), 256, 0, s>>>(doc, reinterpret_cast<int2*>(ranges), nblocks);
     NNB_LAUNCH_CHECK();
     return 0;
 }
 
-template <bool DOC, bool ALIBI>
-static int launch_fwd_tc2(const CUtensorMap& tm, const AttnTcArgs& a, dim3 grid, cudaStream_t s)
+// ---------------------------------------------------------------- host
+template <int DK, bool DOC, bool ALIBI>
+static int launch_fwd_tc(const CUtensorMap& tm, const AttnTcArgs& a, long long tiles, cudaStream_t s)
 {
-    static bool attr_set = false;
-    if (!attr_set) {
-        NNB_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<DOC, ALIBI>, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM));
-        attr_set = true;
-    }
-    attn_fwd_tc2_kernel<DOC, ALIBI><<<grid, 320, A2_SMEM, s>>>(tm, a);
+    using LY = FwdLayout<DK>;
+    static PerDeviceOnce once;
+    NNB_TRY(once.run([] { return cudaFuncSetAttribute(attn_fwd_tc_kernel<DK, DOC, ALIBI>, cudaFuncAttributeMaxDynamicSharedMemorySize, LY::SMEM); }));
+    const long long slots = static_cast<long long>(device_sm_count()) * LY::CTAS_PER_SM;
+    const dim3 grid(static_cast<unsigned>(tiles < slots ? tiles : slots));     // persistent: each CTA walks the tile list
+    attn_fwd_tc_kernel<DK, DOC, ALIBI><<<grid, 320, LY::SMEM, s>>>(tm, a);
     NNB_LAUNCH_CHECK();
     return 0;
 }
 
-// CTAs per SM of the forward kernel: 2 (single-buffered) unless NNB200_ATTN_FWD_CTAS=1 asks for the double-buffered one.
-static int fwd_ctas_per_sm()
-{
-    static const int v = [] { const char* e = getenv("NNB200_ATTN_FWD_CTAS"); return (e && e[0] == '1') ? 1 : 2; }();
-    return v;
-}
+bool attention_tc_supported(int dk, int S, int d) { return (dk == 64 || dk == 128) && (S % AQ) == 0 && (d % 8) == 0; }
 
-bool attention_tc_supported(int dk, int S, int d) { return dk == ADK && (S % AQ) == 0 && (d % 8) == 0; }
-
-int attention_fwd_tc(const bf16* qkv, bf16* out, float* lse, const int* doc, int B, int S, int H, int dk, int alibi,
-                     cudaStream_t s)
+int attention_fwd_tc(const bf16* qkv, bf16* out, float* lse, const int* doc, const int* doc_ranges, int B, int S, int H, int dk,
+                     int alibi, cudaStream_t s)
 {
     if (static_cast<long long>(B) * S * H == 0) return 0;
     NNB_ARG_CHECK(attention_tc_supported(dk, S, H * dk), "shape not supported by the tcgen05 attention kernel");
-    NNB_ARG_CHECK(B <= 65535 && H <= 65535, "batch / heads exceed the grid limits");
     CUtensorMap tm;
     const int d = H * dk;
-    NNB_TRY(tensor_map_2d(qkv, 3LL * d, static_cast<long long>(B) * S, 3LL * d, ADK, 128, &tm, 2));
-    AttnTcArgs a{out, lse, doc, B, S, H, alibi, 1.0f / sqrtf(static_cast<float>(dk))};
+    NNB_TRY(tensor_map_2d(qkv, 3LL * d, static_cast<long long>(B) * S, 3LL * d, 64, 128, &tm, 2));
+    AttnTcArgs a{out, lse, doc, doc ? reinterpret_cast<const int2*>(doc_ranges) : nullptr, B, S, H, alibi, 1.0f / sqrtf(static_cast<float>(dk))};
     const long long tiles = static_cast<long long>(S / AQ) * H * B;
     NNB_ARG_CHECK(tiles < (1ll << 31), "too many attention tiles");
-    const int per_sm = fwd_ctas_per_sm();
-    const long long slots = static_cast<long long>(kSmCount) * per_sm;
-    dim3 grid(static_cast<unsigned>(tiles < slots ? tiles : slots));           // persistent: each CTA walks the tile list
-    if (per_sm == 2) {
-        if (doc && alibi) return launch_fwd_tc2<true, true>(tm, a, grid, s);
-        if (doc) return launch_fwd_tc2<true, false>(tm, a, grid, s);
-        if (alibi) return launch_fwd_tc2<false, true>(tm, a, grid, s);
-        return launch_fwd_tc2<false, false>(tm, a, grid, s);
-    }
-    if (doc && alibi) return launch_fwd_tc<true, true>(tm, a, grid, s);
-    if (doc) return launch_fwd_tc<true, false>(tm, a, grid, s);
-    if (alibi) return launch_fwd_tc<false, true>(tm, a, grid, s);
-    return launch_fwd_tc<false, false>(tm, a, grid, s);
+#define NNB_FWD(DKV)                                                                          \
+    do {                                                                                      \
+        if (doc && alibi) return launch_fwd_tc<DKV, true, true>(tm, a, tiles, s);             \
+        if (doc) return launch_fwd_tc<DKV, true, false>(tm, a, tiles, s);                     \
+        if (alibi) return launch_fwd_tc<DKV, false, true>(tm, a, tiles, s);                   \
+        return launch_fwd_tc<DKV, false, false>(tm, a, tiles, s);                             \
+    } while (0)
+    if (dk == 64) NNB_FWD(64);
+    NNB_FWD(128);
+#undef NNB_FWD
 }
 
 int attention_device_error(int* code)

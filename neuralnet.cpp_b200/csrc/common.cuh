@@ -3,6 +3,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
+#include <climits>
 #include <cstdint>
 #include <cstdio>
 
@@ -51,6 +53,44 @@ static inline cudaStream_t to_stream(void* s) { return static_cast<cudaStream_t>
 constexpr int kSmCount = 148;   // B200: 2 dies x 74 SMs; grids are sized in multiples of this
 
 __host__ __device__ constexpr inline long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
+
+// Per-device caches.  A process may drive several GPUs (one after the other or from several threads), and function
+// attributes, SM counts and occupancy figures belong to the device that is current when they are set or read.
+inline int current_device_slot()
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return dev & 63;
+}
+// SMs of the current device
+inline int device_sm_count()
+{
+    static std::atomic<int> cache[64];
+    const int dev = current_device_slot();
+    int v = cache[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        v = kSmCount;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { cudaGetLastError(); v = kSmCount; }
+        cache[dev].store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+// Runs `f` (returning cudaError_t) once per device: the opt-in to more than 48 KB of dynamic shared memory and the like.
+struct PerDeviceOnce {
+    std::atomic<unsigned long long> done{0};
+    template <typename F> int run(F f)
+    {
+        const unsigned long long bit = 1ull << current_device_slot();
+        if (done.load(std::memory_order_acquire) & bit) return 0;
+        const cudaError_t e = f();
+        if (e != cudaSuccess) {
+            fprintf(stderr, "nnb200: CUDA error setting up a kernel: %s\n", cudaGetErrorString(e));
+            return static_cast<int>(e);
+        }
+        done.fetch_or(bit, std::memory_order_release);
+        return 0;
+    }
+};
 
 // number of blocks for a grid-stride kernel: enough to fill the machine, never more than the work
 static inline int grid_for(long long work_items, int per_block, int blocks_per_sm = 8)

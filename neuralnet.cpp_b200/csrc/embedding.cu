@@ -361,11 +361,8 @@ int embed_bwd(float* tok_grad, float* pos_grad, const int* tokens, const T* g, v
     segment_heads_kernel<<<blocks, 256, 0, s>>>(keys, n_pad, flags, long_list, long_count);
     NNB_LAUNCH_CHECK();
     constexpr int sc_smem = SC_TILE_BYTES;
-    static bool sc_attr = false;
-    if (!sc_attr) {
-        NNB_CUDA_CHECK(cudaFuncSetAttribute(scatter_segments_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, sc_smem));
-        sc_attr = true;
-    }
+    static PerDeviceOnce sc_attr;
+    NNB_TRY(sc_attr.run([] { return cudaFuncSetAttribute(scatter_segments_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SC_TILE_BYTES); }));
     const int rows_aligned = ((reinterpret_cast<uintptr_t>(g) & 15) == 0 && (static_cast<size_t>(d) * sizeof(T)) % 16 == 0) ? 1 : 0;
     scatter_short_kernel<T><<<static_cast<unsigned>(ceil_div(static_cast<long long>(n_pad) * 32, 256)), 256, 0, s>>>(tok_grad, keys, flags, g, n_pad, d, rows_aligned);
     NNB_LAUNCH_CHECK();

@@ -30,8 +30,13 @@ int nnb200_rt_init(int device, char* name_out, size_t name_len, size_t* total_me
         if (count <= 0) { fprintf(stderr, "nnb200_rt_init: no CUDA device\n"); return -2; }
         if (device < 0) {                                    // one process per GPU: the launcher's local rank picks it
             const char* lr = std::getenv("LOCAL_RANK");
-            device = lr ? std::atoi(lr) % count : 0;
+            device = lr ? std::atoi(lr) : 0;
+            if (device >= count) {                           // never wrap: two replicas on one GPU would fight over its SMs and TMEM
+                fprintf(stderr, "nnb200_rt_init: LOCAL_RANK %d but only %d CUDA device(s): start one process per GPU\n", device, count);
+                return -1;
+            }
         }
+        if (device < 0) { fprintf(stderr, "nnb200_rt_init: negative LOCAL_RANK\n"); return -1; }
         if (device >= count) { fprintf(stderr, "nnb200_rt_init: device %d of %d\n", device, count); return -1; }
         NNB_CUDA_CHECK(cudaSetDevice(device));
         NNB_CUDA_CHECK(cudaStreamCreateWithFlags(&g_rt.stream, cudaStreamNonBlocking));

@@ -41,7 +41,6 @@ struct GemmParams {
     const float* bias_n;
     const void* residual;
     float alpha;
-    int debug;          // timing experiments only (NNB200_GEMM_DEBUG): bit 0 = skip the TMA loads, bit 1 = skip the MMAs, bit 2 = skip the stores, bit 3 = skip the TMEM loads; results are garbage
 };
 
 // ---------------------------------------------------------------- kernel
@@ -378,11 +377,7 @@ int tensor_map_2d(const void* ptr, long long inner, long long outer, long long l
     return 0;
 }
 
-static int sm_count()
-{
-    static int n = [] { int dev = 0, v = kSmCount; cudaGetDevice(&dev); cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev); return v; }();
-    return n;
-}
+static int sm_count() { return device_sm_count(); }
 
 // Optional per-launch timing: CUDA events recorded on the launching stream around each GEMM kernel,
 // so a benchmark can report achieved FLOP/s of this kernel from inside a real training step.
@@ -412,11 +407,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     constexpr int STAGES = (BN == 256) ? 4 : 6;
     constexpr int SMEM = STAGES * (A_STAGE_BYTES + BN * BK * 2) + 2 * C_STAGE_BYTES + BN * 4 + 1024 + 256;
     static_assert(SMEM <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
-    static bool attr_set = false;
-    if (!attr_set) {
-        NNB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN, A_MN, B_MN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-        attr_set = true;
-    }
+    static PerDeviceOnce once;
+    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_kernel<BN, A_MN, B_MN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); }));
     const int units = p.tiles_m * p.tiles_n * p.splits;
     const int grid = units < sm_count() ? units : sm_count();
     if (g_prof.on) prof_event(s);
@@ -448,32 +440,28 @@ constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + 2 * C_STAGE_BYTES + 256 * 4 + 1024 + 256;
 static_assert(PAIR_SMEM <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 
-// number of CTA pairs the machine runs at once; 0 = the pair kernel cannot be used (or is switched off by
-// NNB200_GEMM_PAIR=0, which exists for A/B timing)
+// number of CTA pairs the current device runs at once; 0 = the pair kernel cannot be used there
 static int pair_capacity()
 {
-    static int n = [] {
-        const char* e = getenv("NNB200_GEMM_PAIR");
-        if (e && e[0] == '0') return 0;
-        if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<false, false, PAIR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM) != cudaSuccess) { cudaGetLastError(); return 0; }
-        return max_pairs(gemm_bf16_pair_kernel<false, false, PAIR_STAGES>, PAIR_SMEM);
-    }();
-    return n;
+    static std::atomic<int> cache[64];                      // per device: 0 = not asked yet, -1 = unavailable
+    const int dev = current_device_slot();
+    int n = cache[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<false, false, PAIR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM) != cudaSuccess) { cudaGetLastError(); n = -1; }
+        else n = max_pairs(gemm_bf16_pair_kernel<false, false, PAIR_STAGES>, PAIR_SMEM);
+        if (n <= 0) n = -1;
+        cache[dev].store(n, std::memory_order_relaxed);
+    }
+    return n > 0 ? n : 0;
 }
 
 template <bool A_MN, bool B_MN>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tcm, const GemmParams& p, cudaStream_t s)
 {
-    static bool attr_set = false;
-    if (!attr_set) {
-        NNB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, PAIR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM));
-        attr_set = true;
-    }
+    static PerDeviceOnce once;
+    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, PAIR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
     const int units = p.tiles_m * p.tiles_n * p.splits;
     const int pairs = units < pair_capacity() ? units : pair_capacity();
-    static const int debug = [] { const char* e = getenv("NNB200_GEMM_DEBUG"); return e ? atoi(e) : 0; }();
-    GemmParams pd = p;
-    pd.debug = debug;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(PAIR_THREADS);
@@ -484,7 +472,7 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
     if (g_prof.on) prof_event(s);
-    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, PAIR_STAGES>, ta, tb, tcm, pd));
+    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, PAIR_STAGES>, ta, tb, tcm, p));
     if (g_prof.on) { prof_event(s); g_prof.flops += 2.0 * p.M * p.N * p.K; }
     NNB_LAUNCH_CHECK();
     return 0;

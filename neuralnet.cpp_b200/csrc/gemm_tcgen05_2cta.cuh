@@ -87,7 +87,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, 1, &g_gemm_error)) break;
-                    if (p.debug & 1) { if (rank == 0) mbar_arrive(full0 + 8 * s); continue; }
                     if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);
                     const uint32_t fb = leader_full0 + 8 * s;
                     const uint32_t a_dst = smem_u32(sA + s * A_STAGE_BYTES), b_dst = smem_u32(sB + s * B_STAGE_BYTES);
@@ -124,7 +123,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                                                  : smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
                         const uint64_t db = B_MN ? smem_desc(b_addr + k * (UMMA_K * 128), BK * 128, 1024)
                                                  : smem_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
-                        if (!(p.debug & 2)) umma_bf16_pair(d_tmem, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+                        umma_bf16_pair(d_tmem, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit_pair(empty0 + 8 * s, 3);         // frees the stage in both CTAs
                 }
@@ -177,7 +176,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             // touched, not even moved by the compiler at a loop edge, before the wait that follows it.
             uint32_t ra[32], rb[32];
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-            const bool piped = CB == 64 && !(p.debug & 8);
+            const bool piped = CB == 64;
 #pragma unroll 1
             for (int cb = grp; cb * CB < BN; cb += 2) {
                 const int n0 = tile_n * BN + cb * CB;
@@ -188,13 +187,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     tmem_ld32(tbase + cb * CB, ra);
                     tmem_ld_wait();
                     tmem_ld32(tbase + cb * CB + 32, rb);         // in flight while the first half is converted
-                } else if (!(p.debug & 8)) {
-                    tmem_ld32(tbase + cb * CB, ra);
-                    if (CB == 64) tmem_ld32(tbase + cb * CB + 32, rb);
-                    tmem_ld_wait();
                 } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) { ra[j] = 0u; rb[j] = 0u; }
+                    tmem_ld32(tbase + cb * CB, ra);
+                    tmem_ld_wait();
                 }
                 auto emit = [&](const uint32_t (&r)[32], int half) {
                     float v[32];
@@ -237,7 +232,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 if (CB == 64) emit(rb, 1);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 group_bar(bar_id);
-                if (elected && !(p.debug & 4)) {
+                if (elected) {
                     if (p.accumulate) tma_reduce_add_2d(&tmC, smem_u32(stage), n0, m0);
                     else tma_store_2d(&tmC, smem_u32(stage), n0, m0);
                     tma_commit();

@@ -69,7 +69,7 @@ struct Workspace {
     size_t sin_table, stats, loss, loss_vec;
     std::vector<LayerActs> layers;
     size_t x_final, xnf, rinvf, meanf, logits;
-    size_t g_a, g_b, d_xn, d_h2, d_h1, d_attn, d_qkv, dvec, colsum, counters, embed_scratch, norm_partials, colsum_partials;
+    size_t g_a, g_b, d_xn, d_h2, d_h1, d_attn, d_qkv, dvec, colsum, counters, embed_scratch, norm_partials, colsum_partials, doc_ranges;
     size_t total;
 };
 
@@ -109,6 +109,7 @@ static Workspace make_workspace(const nnb200_gpt_config& c)
                                                 colsum_scratch_floats(static_cast<int>(N), static_cast<int>(3 * d)))) * 4
                                  : 0);
     W.embed_scratch = take(embed_bwd_scratch_bytes(static_cast<int>(N)));
+    W.doc_ranges = take((N / 64 + 1) * 2 * sizeof(int));      // (min, max) document id per 64 token rows
     W.total = off;
     return W;
 }
@@ -154,23 +155,23 @@ static int linear_bwd_params(const T* dY, const T* X, float* dW, float* db, floa
 }
 
 template <typename T>
-static int attention_fwd(const T* qkv, T* out, float* lse, const int* doc, const nnb200_gpt_config& c, cudaStream_t s)
+static int attention_fwd(const T* qkv, T* out, float* lse, const int* doc, const int* ranges, const nnb200_gpt_config& c, cudaStream_t s)
 {
     const int dk = c.d_model / c.heads, alibi = c.pos == 2;
     if constexpr (Mode<T>::bf) {
-        if (attention_tc_supported(dk, c.seq, c.d_model)) return attention_fwd_tc(qkv, out, lse, doc, c.batch, c.seq, c.heads, dk, alibi, s);
+        if (attention_tc_supported(dk, c.seq, c.d_model)) return attention_fwd_tc(qkv, out, lse, doc, ranges, c.batch, c.seq, c.heads, dk, alibi, s);
         if (attention_mma_supported(dk, c.d_model)) return attention_fwd_mma(qkv, out, lse, doc, c.batch, c.seq, c.heads, dk, alibi, s);
     }
     return attention_fwd_simt<T>(qkv, out, lse, doc, c.batch, c.seq, c.heads, dk, alibi, s);
 }
 template <typename T>
 static int attention_bwd(const T* qkv, const T* out, const T* dout, const float* lse, float* dvec, T* dqkv, const int* doc,
-                         const nnb200_gpt_config& c, cudaStream_t s)
+                         const int* ranges, const nnb200_gpt_config& c, cudaStream_t s)
 {
     const int dk = c.d_model / c.heads, alibi = c.pos == 2;
     if constexpr (Mode<T>::bf) {
         if (attention_tc_supported(dk, c.seq, c.d_model))
-            return attention_bwd_tc(qkv, out, dout, lse, dvec, dqkv, doc, c.batch, c.seq, c.heads, dk, alibi, s);
+            return attention_bwd_tc(qkv, out, dout, lse, dvec, dqkv, doc, ranges, c.batch, c.seq, c.heads, dk, alibi, s);
         if (attention_mma_supported(dk, c.d_model))
             return attention_bwd_mma(qkv, out, dout, lse, dvec, dqkv, doc, c.batch, c.seq, c.heads, dk, alibi, s);
     }
@@ -190,6 +191,13 @@ static int forward_t(const nnb200_gpt_config& c, const float* P, const bf16* H, 
     auto PB = [&](long long off) { return off >= 0 ? P + off : nullptr; };
 
     const float* pos_table = c.pos == 0 ? P + L.pos_emb : (c.pos == 1 ? F(W.sin_table) : nullptr);
+    // document-id range of every 64 token rows, once per micro-batch: the attention kernels of every layer, forward
+    // and backward, skip the blocks it shows to be fully masked (what build_attention_mask leaves as -inf everywhere)
+    const int* ranges = nullptr;
+    if (Mode<T>::bf && doc && attention_tc_supported(d / c.heads, c.seq, d)) {
+        NNB_TRY(attention_doc_ranges(doc, c.batch, c.seq, reinterpret_cast<int*>(ws + W.doc_ranges), s));
+        ranges = reinterpret_cast<const int*>(ws + W.doc_ranges);
+    }
     T* x = A(W.layers[0].x_in);
     NNB_TRY(embed_fwd<T>(P + L.tok_emb, pos_table, tokens, x, N, c.seq, d, c.vocab, s));
     for (int l = 0; l < c.layers; ++l) {
@@ -200,7 +208,7 @@ static int forward_t(const nnb200_gpt_config& c, const float* P, const bf16* H, 
         NNB_TRY(linear_fwd<T>(A(a.xn1), P + lp.wqkv, H ? H + lp.wqkv : nullptr, P + lp.bqkv, nullptr, A(a.qkv), N, d, 3 * d, s));
         // rotary positions: Q and K are rotated in place, so the backward pass sees the rotated values (AttentionBase::forward, compute_layer.hpp:1178-1185)
         if (c.pos == 3) NNB_TRY(rope_apply<T>(A(a.qkv), F(W.sin_table), N, c.seq, c.heads, d / c.heads, 3 * d, false, s));
-        NNB_TRY(attention_fwd<T>(A(a.qkv), A(a.attn), F(a.lse), doc, c, s));
+        NNB_TRY(attention_fwd<T>(A(a.qkv), A(a.attn), F(a.lse), doc, ranges, c, s));
         NNB_TRY(linear_fwd<T>(A(a.attn), P + lp.wo, H ? H + lp.wo : nullptr, P + lp.bo, A(a.x_in), A(a.x_mid), N, d, d, s));
         NNB_TRY(norm_fwd<T>(A(a.x_mid), P + lp.g2, PB(lp.be2), A(a.xn2), F(a.rinv2), F(a.mean2), N, d, ln, s));
         NNB_TRY(linear_fwd<T>(A(a.xn2), P + lp.w1, H ? H + lp.w1 : nullptr, P + lp.b1, nullptr, A(a.h1), N, d, fc1, s));
@@ -227,6 +235,8 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
     auto Hh = [&](long long off) { return H ? H + off : nullptr; };
     float* cs = F(W.colsum);
     int* cn = reinterpret_cast<int*>(ws + W.counters);
+    // the table the forward pass of this micro-batch left in the workspace (same tokens, same document ids)
+    const int* ranges = (Mode<T>::bf && doc && attention_tc_supported(d / c.heads, c.seq, d)) ? reinterpret_cast<const int*>(ws + W.doc_ranges) : nullptr;
     // the norm backward kernels leave their per-block partial sums of the scale / shift / bias gradients in a slot each;
     // one kernel after the last layer folds all slots into the gradient arena (nothing reads them before the optimizer)
     const bool defer = 2 * c.layers + 1 <= kNormFoldMaxSlots;
@@ -288,7 +298,7 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         // AttentionBase::backward (compute_layer.hpp:1271-1412)
         NNB_TRY(linear_bwd_params<T>(g, A(a.attn), G + lp.wo, nullptr, cs, cn, N, d, d, s));
         NNB_TRY(linear_bwd_input<T>(g, P + lp.wo, Hh(lp.wo), A(W.d_attn), N, d, d, s));
-        NNB_TRY(attention_bwd<T>(A(a.qkv), A(a.attn), A(W.d_attn), F(a.lse), F(W.dvec), A(W.d_qkv), doc, c, s));
+        NNB_TRY(attention_bwd<T>(A(a.qkv), A(a.attn), A(W.d_attn), F(a.lse), F(W.dvec), A(W.d_qkv), doc, ranges, c, s));
         // the gradients of the rotated Q and K go back through the inverse rotation (compute_layer.hpp:1365-1372)
         if (c.pos == 3) NNB_TRY(rope_apply<T>(A(W.d_qkv), F(W.sin_table), N, c.seq, c.heads, d / c.heads, 3 * d, true, s));
         NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, cn, N, d, 3 * d, s, cs_begin()));

@@ -85,14 +85,16 @@ template <typename T> int attention_bwd_simt(const T* qkv, const T* out, const T
                                              cudaStream_t s);
 int attention_dvec_bf16(const bf16* out, const bf16* dout, float* dvec, int B, int S, int H, int dk, cudaStream_t s);
 bool attention_mma_supported(int dk, int d);
-// attention_tc.cu : tcgen05 forward (head size 64, seq a multiple of 128)
+// attention_tc.cu : tcgen05 forward (head size 64 or 128, seq a multiple of 128).  doc_ranges (may be null): the table
+// attention_doc_ranges fills, 2 ints (min, max document id) per 64 rows, with which fully masked blocks are skipped
 bool attention_tc_supported(int dk, int S, int d);
-int attention_fwd_tc(const bf16* qkv, bf16* out, float* lse, const int* doc, int B, int S, int H, int dk, int alibi,
-                     cudaStream_t s);
+int attention_doc_ranges(const int* doc, int B, int S, int* ranges, cudaStream_t s);
+int attention_fwd_tc(const bf16* qkv, bf16* out, float* lse, const int* doc, const int* doc_ranges, int B, int S, int H, int dk,
+                     int alibi, cudaStream_t s);
 int attention_device_error(int* code);
 // attention_tc_bwd.cu : tcgen05 backward (same shape limits)
 int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const float* lse, float* dvec, bf16* dqkv,
-                     const int* doc, int B, int S, int H, int dk, int alibi, cudaStream_t s);
+                     const int* doc, const int* doc_ranges, int B, int S, int H, int dk, int alibi, cudaStream_t s);
 int attention_bwd_device_error(int* code);
 int attention_fwd_mma(const bf16* qkv, bf16* out, float* lse, const int* doc, int B, int S, int H, int dk, int alibi,
                       cudaStream_t s);

@@ -15,7 +15,7 @@ namespace nnb {
 static __device__ __align__(256) float g_bias_grad_scratch[NNB200_BIAS_GRAD_STATIC_MAX_FLOATS];
 
 constexpr int kMaxDevices = 64;
-static float* g_scratch_addr[kMaxDevices] = {};
+static std::atomic<float*> g_scratch_addr[kMaxDevices];     // zero-initialised; two threads that race here store the same address
 
 // In host code the array's name is only a handle for the runtime, not an address a kernel can use:
 // the device address is looked up once per device, with that device current, and cached.
@@ -24,12 +24,14 @@ static int static_scratch(float** out)
     int dev = 0;
     NNB_CUDA_CHECK(cudaGetDevice(&dev));
     NNB_ARG_CHECK(dev >= 0 && dev < kMaxDevices, "device ordinal out of range");
-    if (!g_scratch_addr[dev]) {
+    float* addr = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!addr) {
         void* p = nullptr;
         NNB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_bias_grad_scratch));
-        g_scratch_addr[dev] = static_cast<float*>(p);
+        addr = static_cast<float*>(p);
+        g_scratch_addr[dev].store(addr, std::memory_order_release);
     }
-    *out = g_scratch_addr[dev];
+    *out = addr;
     return 0;
 }
 
@@ -42,6 +44,8 @@ extern "C" int nnb200_bias_grad_static(const void* g, long long ldg, float* out,
 {
     NNB_ARG_CHECK(dtype == 0 || dtype == 1, "dtype must be 0 (fp32) or 1 (bf16)");
     NNB_ARG_CHECK(rows >= 0 && cols >= 0, "negative shape");
+    NNB_ARG_CHECK(rows == 0 || cols == 0 || (g && out), "null gradient or output pointer");
+    NNB_ARG_CHECK(ldg >= cols, "the row stride is shorter than a row (rows would overlap)");
     if (colsum_scratch_floats(rows, cols) > static_cast<size_t>(NNB200_BIAS_GRAD_STATIC_MAX_FLOATS)) {
         fprintf(stderr,
                 "nnb200_bias_grad_static: %d x %d needs %zu scratch floats, the built-in buffer holds %d; "

@@ -110,8 +110,8 @@ def run_attention(B, S_, H, dk, args):
     dqkv = torch.zeros_like(qkv)
     lse = torch.zeros(B * H * S_, device="cuda")
     dvec = torch.zeros_like(lse)
-    fwd = lambda: call("nnb200_attention_forward", P(qkv), P(out), P(lse), None, B, S_, H, dk, 0, 1, S())
-    bwd = lambda: call("nnb200_attention_backward", P(qkv), P(out), P(dout), P(lse), P(dvec), P(dqkv), None, B, S_, H, dk, 0, 1, S())
+    fwd = lambda: call("nnb200_attention_forward", P(qkv), P(out), P(lse), None, None, B, S_, H, dk, 0, 1, S())
+    bwd = lambda: call("nnb200_attention_backward", P(qkv), P(out), P(dout), P(lse), P(dvec), P(dqkv), None, None, B, S_, H, dk, 0, 1, S())
     if args.no_time:
         for _ in range(args.iters):
             fwd()

@@ -41,6 +41,31 @@ CASES = {
     "tile_rope_docs": (go.GptConfig(256, 128, 2, 1, 256, 128, 2, go.ACT_SWIGLU, go.NORM_RMS, go.POS_ROPE),
                        dict(steps=2, accum=2, lr=1e-3, wd=0.01), "zipf", True),
 }
+# Full-width cases (BASELINE configurations 2, 3 and 4 at the model shapes the benchmark runs): too large to
+# store whole, so each keeps per-micro-batch losses, a fixed sample of the first logits, and per tensor the
+# L2 norm plus a fixed sample (sample_indices) of the first-step gradient and of the final parameters.
+FULL_CASES = {
+    # configuration 2 at full size, two optimizer steps
+    "full_c2": (go.GptConfig(4096, 384, 6, 6, 1024, 256, 32, go.ACT_SWIGLU, go.NORM_RMS, go.POS_SINUSOIDAL),
+                dict(steps=2, lr=6e-4, wd=0.01, clip=1.0), "zipf", False),
+    # configuration 3 at full model shape, micro-batch 2 x accumulation 2, cosine schedule
+    "full_c3": (go.GptConfig(8192, 768, 12, 12, 2048, 1024, 2, go.ACT_SWIGLU, go.NORM_RMS, go.POS_ALIBI),
+                dict(steps=2, accum=2, lr=6e-4, wd=0.01, cosine=True, warmup=1, total_steps=4, min_lr=6e-5),
+                "zipf", False),
+    # configuration 4 at full width, two layers, one packed row of geometric(300) documents, Muon split
+    "full_c4": (go.GptConfig(16384, 1024, 16, 2, 2816, 2048, 1, go.ACT_SWIGLU, go.NORM_RMS, go.POS_LEARNED),
+                dict(steps=2, lr=1e-3, wd=0.01, optimizer=go.OPT_MUON_SPLIT, muon_lr=0.02), "zipf", True),
+}
+SAMPLE = 4096
+
+
+def sample_indices(size, k=SAMPLE):
+    """Fixed, well-spread flat indices into a tensor of `size` elements (all of them when size <= k)."""
+    if size <= k:
+        return np.arange(size, dtype=np.int64)
+    return (np.arange(k, dtype=np.int64) * 7919003) % size
+
+
 # BASELINE configuration 1 (tiny GPT, 20 steps): only losses and per-tensor norms are stored
 C1 = go.GptConfig(512, 128, 4, 2, 512, 128, 8, go.ACT_GELU, go.NORM_LAYER, go.POS_LEARNED)
 
@@ -70,6 +95,31 @@ def gpt_cases(only=None):
             arrays[f"g_{i}"], arrays[f"p1_{i}"] = g, p1
         np.savez_compressed(os.path.join(OUT, f"gpt_{name}.npz"), **arrays)
         print(name, "losses", ref["losses"])
+
+
+def full_cases(only=None):
+    for name, (cfg, kw, dist, docs) in FULL_CASES.items():
+        if only and name not in only:
+            continue
+        params = go.init_params(cfg, 42)
+        mbs = go.make_batches(cfg, kw["steps"] * kw.get("accum", 1), seed=1, dist=dist, docs=docs)
+        ref = rr.run_reference(cfg, params, mbs, dump_grads=True, dump_logits=True, timeout=6 * 3600, **kw)
+        lg = ref["logits"].T.reshape(-1)                       # token-major (tokens, vocab)
+        arrays = {"cfg": np.array(list(vars(cfg).values()), np.int64),
+                  "kw_keys": np.array(list(kw.keys())), "kw_vals": np.array([float(v) for v in kw.values()]),
+                  "losses": ref["losses"], "logits_sample": lg[sample_indices(lg.size, 4 * SAMPLE)],
+                  "logits_absmax": np.array([np.abs(lg).max()]),
+                  "seconds": ref["seconds"]}
+        arrays.update(pack_batches(mbs))
+        arrays["p0_checksum"] = np.array([float(sum(np.abs(p.astype(np.float64)).sum() for p in params))])
+        arrays["g_norms"] = np.array([np.linalg.norm(g.astype(np.float64)) for g in ref["grads"]])
+        arrays["p1_norms"] = np.array([np.linalg.norm(p.astype(np.float64)) for p in ref["params"]])
+        arrays["g_absmax"] = np.array([np.abs(g).max() for g in ref["grads"]])
+        for i, (g, p1) in enumerate(zip(ref["grads"], ref["params"])):
+            idx = sample_indices(g.size)
+            arrays[f"g_{i}"], arrays[f"p1_{i}"] = g.reshape(-1)[idx], p1.reshape(-1)[idx]
+        np.savez_compressed(os.path.join(OUT, f"gpt_{name}.npz"), **arrays)
+        print(name, "losses", ref["losses"], "s/step", ref["seconds"], flush=True)
 
 
 def c1_case():
@@ -130,5 +180,8 @@ if __name__ == "__main__":
     named = [w for w in which if w in CASES]          # e.g. `make_golden.py rms_swiglu_rope` regenerates one case
     if named:
         gpt_cases(named)
+    named = [w for w in which if w in FULL_CASES]     # hours of CPU time in total: only when named, or with `full`
+    if named or "full" in which:
+        full_cases(named or None)
     if "c1" in which:
         c1_case()

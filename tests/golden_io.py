@@ -29,6 +29,43 @@ def load_gpt_case(name):
                 grads=[z[f"g_{i}"] for i in range(k)], final=[z[f"p1_{i}"] for i in range(k)])
 
 
+FULL_CASES = ["full_c2", "full_c3", "full_c4"]
+
+
+def sample_indices(size, k=4096):
+    """The fixed flat indices tests/golden/make_golden.py sampled every tensor of a full-width case at."""
+    if size <= k:
+        return np.arange(size, dtype=np.int64)
+    return (np.arange(k, dtype=np.int64) * 7919003) % size
+
+
+def load_full_case(name):
+    """A full-width case (BASELINE configurations 2, 3, 4 at the model shapes the benchmark runs): outputs of the
+    reference CPU engine stored as per-micro-batch losses, a sample of the first logits, and per tensor the L2 norm and
+    a 4096-element sample of the first-step gradient and of the final parameters."""
+    z = np.load(os.path.join(GOLDEN, f"gpt_{name}.npz"))
+    cfg = go.GptConfig(*[int(v) for v in z["cfg"]])
+    kw = {}
+    for k, v in zip(z["kw_keys"], z["kw_vals"]):
+        k = str(k)
+        kw[k] = int(v) if k in INT_KW else (bool(v) if k == "cosine" else float(v))
+    n = kw["steps"] * kw.get("accum", 1)
+    mbs = [{"tokens": z["tokens"][i], "labels": z["labels"][i], "mask": z["mask"][i],
+            "doc_ids": z["doc_ids"][i] if "doc_ids" in z.files else None} for i in range(n)]
+    params = go.init_params(cfg, 42)
+    chk = float(sum(np.abs(p.astype(np.float64)).sum() for p in params))
+    assert abs(chk - float(z["p0_checksum"][0])) <= 1e-9 * chk, "numpy RNG stream changed: regenerate goldens"
+    k = len(go.param_shapes(cfg))
+    return dict(cfg=cfg, kw=kw, batches=mbs, params=params, losses=z["losses"], logits_sample=z["logits_sample"],
+                logits_absmax=float(z["logits_absmax"][0]), g_norms=z["g_norms"], p1_norms=z["p1_norms"],
+                g_absmax=z["g_absmax"], grads=[z[f"g_{i}"] for i in range(k)], final=[z[f"p1_{i}"] for i in range(k)])
+
+
+def sample_tensors(tensors):
+    """Each tensor reduced to the sample the full-width goldens keep."""
+    return [np.asarray(t).reshape(-1)[sample_indices(np.asarray(t).size)] for t in tensors]
+
+
 def rel_err(a, b):
     """max |a-b| / max |b| — the relative norm the parity bar is stated in."""
     a = np.asarray(a, np.float64)

@@ -133,8 +133,8 @@ def _attention_reference(q, k, v, dout, B, S, H, dk, alibi, doc):
 @pytest.mark.parametrize("B,S,H,dk,alibi,docs", [
     (2, 64, 2, 32, 0, False), (2, 128, 2, 64, 1, False), (3, 96, 4, 64, 0, True), (2, 200, 2, 64, 1, True),
     (2, 24, 4, 8, 0, True), (1, 256, 1, 128, 1, False), (2, 512, 3, 64, 1, True), (1, 1024, 2, 64, 0, False),
-    (2, 384, 2, 64, 0, True)])
-def test_attention_forward_backward(g, dtype, B, S, H, dk, alibi, docs):
+    (2, 384, 2, 64, 0, True), (2, 512, 2, 128, 0, True), (2, 1024, 3, 128, 1, True), (3, 384, 2, 128, 0, False)])
+def test_attention_forward_backward(g, dtype, B, S, H, dk, alibi, docs, mean_len=None):
     import torch
     from oracle import gpt_oracle as go
     r = _rng(S + dk)
@@ -143,7 +143,7 @@ def test_attention_forward_backward(g, dtype, B, S, H, dk, alibi, docs):
     rnd = g.bf16_round if dtype == 1 else (lambda a: np.asarray(a, np.float32))
     qkv = rnd(r.standard_normal((N, 3 * d)))
     dout = rnd(r.standard_normal((N, d)))
-    doc = go.packed_doc_ids(r, B, S, mean_len=S / 3) if docs else None
+    doc = go.packed_doc_ids(r, B, S, mean_len=mean_len or S / 3) if docs else None
     o_ref, dq, dk_, dv = _attention_reference(qkv[:, :d], qkv[:, d:2 * d], qkv[:, 2 * d:], dout, B, S, H, dk, alibi, doc)
     tdt = torch.bfloat16 if dtype == 1 else torch.float32
     t_qkv, t_dout = g.dev(qkv, tdt), g.dev(dout, tdt)
@@ -152,10 +152,23 @@ def test_attention_forward_backward(g, dtype, B, S, H, dk, alibi, docs):
     lse = torch.zeros(B * H * S, dtype=torch.float32, device="cuda")
     dvec = torch.zeros(B * H * S, dtype=torch.float32, device="cuda")
     t_doc = g.dev(doc.astype(np.int32)) if docs else None
-    g.call("nnb200_attention_forward", g.ptr(t_qkv), g.ptr(t_out), g.ptr(lse), g.ptr(t_doc), B, S, H, dk, alibi, dtype, g.stream())
+    g.call("nnb200_attention_forward", g.ptr(t_qkv), g.ptr(t_out), g.ptr(lse), g.ptr(t_doc), None, B, S, H, dk, alibi, dtype, g.stream())
     g.call("nnb200_attention_backward", g.ptr(t_qkv), g.ptr(t_out), g.ptr(t_dout), g.ptr(lse), g.ptr(dvec), g.ptr(t_dqkv),
-           g.ptr(t_doc), B, S, H, dk, alibi, dtype, g.stream())
+           g.ptr(t_doc), None, B, S, H, dk, alibi, dtype, g.stream())
     out, dqkv = g.host(t_out), g.host(t_dqkv)
+    if docs and S % 64 == 0:
+        # the same with the document-range table: fully masked blocks are skipped, and no result bit may change
+        ranges = torch.zeros(2 * B * (S // 64), dtype=torch.int32, device="cuda")
+        g.call("nnb200_attention_doc_ranges", g.ptr(t_doc), B, S, g.ptr(ranges), g.stream())
+        want = np.stack([doc.reshape(B, S // 64, 64).min(axis=2), doc.reshape(B, S // 64, 64).max(axis=2)], axis=2)
+        assert np.array_equal(g.host(ranges).reshape(B, S // 64, 2), want)
+        t_out2, t_dqkv2, lse2 = torch.zeros_like(t_out), torch.zeros_like(t_dqkv), torch.zeros_like(lse)
+        g.call("nnb200_attention_forward", g.ptr(t_qkv), g.ptr(t_out2), g.ptr(lse2), g.ptr(t_doc), g.ptr(ranges), B, S, H, dk,
+               alibi, dtype, g.stream())
+        g.call("nnb200_attention_backward", g.ptr(t_qkv), g.ptr(t_out2), g.ptr(t_dout), g.ptr(lse2), g.ptr(dvec), g.ptr(t_dqkv2),
+               g.ptr(t_doc), g.ptr(ranges), B, S, H, dk, alibi, dtype, g.stream())
+        torch.cuda.synchronize()
+        assert torch.equal(t_out2, t_out) and torch.equal(lse2, lse) and torch.equal(t_dqkv2, t_dqkv)
     tol = 1e-2 if dtype == 1 else 1e-5        # the stated bars: bf16 tensor-core path / fp32 check mode
     scale = lambda x: np.abs(x).max()
     assert np.abs(out - o_ref).max() < tol * scale(o_ref) * 3
@@ -169,6 +182,14 @@ def test_attention_persistent_tile_loop(g, B, S, H, alibi, docs):
     three tiles, so the rings, the double-buffered resident tiles / TMEM accumulators and all barrier phases
     carry over from one tile to the next (208, 336 and 320 tiles on 148 SMs)."""
     test_attention_forward_backward(g, 1, B, S, H, 64, alibi, docs)
+
+
+@pytest.mark.parametrize("dk,H", [(64, 16), (128, 8)])
+def test_attention_packed_documents_seq_2048(g, dk, H):
+    """The packed-document configuration's attention shape (seq 2048, geometric(300) documents, d 1024) on the tcgen05
+    kernels: most 128 x 128 blocks of a row are fully masked and skipped through the range table."""
+    test_attention_forward_backward(g, 1, 1, 2048, H, dk, 0, True, mean_len=300.0)
+    assert g.gemm_status() == 0
 
 
 def test_attention_matches_reference_primitives_golden(g):
@@ -196,7 +217,7 @@ def test_attention_matches_reference_primitives_golden(g):
     t_qkv = g.dev(qkv)
     t_out = torch.zeros(batch * M, dk, device="cuda")
     lse = torch.zeros(batch * M, device="cuda")
-    g.call("nnb200_attention_forward", g.ptr(t_qkv), g.ptr(t_out), g.ptr(lse), None, batch, M, 1, dk, 0, 0, g.stream())
+    g.call("nnb200_attention_forward", g.ptr(t_qkv), g.ptr(t_out), g.ptr(lse), None, None, batch, M, 1, dk, 0, 0, g.stream())
     want_lse = (z["out_m"] + np.log(z["out_l"])).reshape(-1)
     assert np.allclose(g.host(lse), want_lse, atol=1e-5)
     assert np.allclose(g.host(t_out)[:, :D], z["out_O"].reshape(batch * M, D), atol=1e-5)
