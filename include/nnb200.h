@@ -183,6 +183,18 @@ int nnb200_embedding_backward(float* token_grad, float* pos_grad, const int32_t*
                               int batch, int seq, int d, int vocab, int dtype, void* stream);
 size_t nnb200_embedding_scratch_bytes(int tokens_n);
 
+/* Token ids as the reference hands them to GPTModel::forward — a (seq, batch) row-major matrix of floats
+ * (compute_layer.hpp:2783-2790) — to the int32 batch-major ids the fused step takes: out[b*seq + t] =
+ * (int) ids[t*batch + b]; negative or non-finite values become -1 (out of range: zero embedding row). */
+int nnb200_ids_from_float(const float* ids_seq_major, int32_t* out_batch_major, int seq, int batch, void* stream);
+/* Logits of the fused step, (tokens, vocab) in the step's precision, to the reference's (vocab, tokens) fp32
+ * matrix (the Tensor GPTModel::forward returns, compute_layer.hpp:2836-2838). */
+int nnb200_logits_to_reference(const void* logits_token_major, float* out_vocab_major, int tokens, int vocab, int dtype,
+                               void* stream);
+/* p[0..n) = 0 in one launch; p 16-byte aligned.  Replaces the per-tensor engine.zero calls of
+ * Layer::zero_grad / Optimizer::zero_grad (compute_layer.hpp:57-65, compute_optimizer.hpp:141-150). */
+int nnb200_zero_f32(float* p, size_t n, void* stream);
+
 /* Rotary position encoding (RotaryEmbedding, compute_layer.hpp:876-988).  nnb200_rope_table fills a HOST buffer of
  * seq*head_dim floats: cos (seq, head_dim/2) then sin (seq, head_dim/2), theta = pos / 10000^(2j/head_dim) computed with
  * the reference's float calls; the caller copies it to the device.  nnb200_rope_apply rotates, in place, the Q and K
@@ -262,8 +274,9 @@ int nnb200_gpt_forward(const nnb200_gpt_config* cfg, const float* params, const 
 int nnb200_gpt_loss(const nnb200_gpt_config* cfg, void* workspace, const int32_t* labels, const float* loss_mask,
                     float grad_scale, void* stream);
 /* Adds this micro-batch's parameter gradients into `grads` (arena layout).  layer_events (NULL or
- * layers+1 cudaEvent_t): event[l] is recorded when layer l's matrix gradients are final, event
- * [layers] when every gradient is.  Replaces GPTModel::backward (compute_layer.hpp:2841-2896). */
+ * layers+2 entries, each a cudaEvent_t or NULL): event[l] is recorded when layer l's matrix gradients
+ * are final, event[layers] when every gradient is, event[layers+1] when the LM head's weight gradient
+ * is (right after the first GEMM).  Replaces GPTModel::backward (compute_layer.hpp:2841-2896). */
 int nnb200_gpt_backward(const nnb200_gpt_config* cfg, const float* params, const void* params_bf16, float* grads,
                         void* workspace, const int32_t* tokens, const int32_t* doc_ids, void* const* layer_events,
                         void* stream);
@@ -349,6 +362,10 @@ int nnb200_rt_download(void* host_dst, const void* src, size_t bytes);
 int nnb200_rt_copy(void* dst, const void* src, size_t bytes);
 int nnb200_rt_zero(void* dst, size_t bytes);
 int nnb200_rt_sync(void);
+/* A pair of CUDA events on the runtime's stream: _stop waits for the queue up to it and returns (host) the device
+ * time since _start in milliseconds.  The reference times its loop on the host clock (text_train.cpp:1107). */
+int nnb200_rt_timer_start(void);
+int nnb200_rt_timer_stop(float* host_ms);
 
 #ifdef __cplusplus
 }

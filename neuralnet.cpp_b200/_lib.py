@@ -61,6 +61,11 @@ SIGNATURES = {
     "nnb200_attention_forward": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "nnb200_attention_backward": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "nnb200_attention_doc_ranges": [_p, _i, _i, _p, _p],
+    "nnb200_ids_from_float": [_p, _p, _i, _i, _p],
+    "nnb200_logits_to_reference": [_p, _p, _i, _i, _i, _p],
+    "nnb200_zero_f32": [_p, _sz, _p],
+    "nnb200_rt_timer_start": [],
+    "nnb200_rt_timer_stop": [C.POINTER(C.c_float)],
     "nnb200_norm_forward": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
     "nnb200_norm_backward": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
     "nnb200_colsum_scratch_floats": [_i, _i],

@@ -142,6 +142,22 @@ int nnb200_attention_backward(const void* qkv, const void* out, const void* dout
     return attention_bwd_simt<float>(static_cast<const float*>(qkv), static_cast<const float*>(out), static_cast<const float*>(dout), lse, dvec, static_cast<float*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);
 }
 
+int nnb200_ids_from_float(const float* ids_seq_major, int32_t* out_batch_major, int seq, int batch, void* stream)
+{
+    NNB_ARG_CHECK(seq >= 0 && batch >= 0 && (static_cast<long long>(seq) * batch == 0 || (ids_seq_major && out_batch_major)), "bad arguments");
+    return ids_from_float(ids_seq_major, out_batch_major, seq, batch, to_stream(stream));
+}
+
+int nnb200_logits_to_reference(const void* logits_token_major, float* out_vocab_major, int tokens, int vocab, int dtype, void* stream)
+{
+    DT_CHECK(dtype);
+    NNB_ARG_CHECK(tokens >= 0 && vocab >= 0 && (static_cast<long long>(tokens) * vocab == 0 || (logits_token_major && out_vocab_major)), "bad arguments");
+    if (dtype == 1) return logits_to_reference<bf16>(static_cast<const bf16*>(logits_token_major), out_vocab_major, tokens, vocab, to_stream(stream));
+    return logits_to_reference<float>(static_cast<const float*>(logits_token_major), out_vocab_major, tokens, vocab, to_stream(stream));
+}
+
+int nnb200_zero_f32(float* p, size_t n, void* stream) { return zero_f32(p, n, to_stream(stream)); }
+
 int nnb200_norm_forward(const void* x, const float* gamma, const float* beta, void* y, float* rinv, float* mean,
                         int rows, int d, int layer, int dtype, void* stream)
 {

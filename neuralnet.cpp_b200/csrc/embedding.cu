@@ -380,4 +380,71 @@ template int embed_fwd<bf16>(const float*, const float*, const int*, bf16*, int,
 template int embed_bwd<float>(float*, float*, const int*, const float*, void*, int, int, int, int, cudaStream_t);
 template int embed_bwd<bf16>(float*, float*, const int*, const bf16*, void*, int, int, int, int, cudaStream_t);
 
+// ---------------------------------------------------------------- host-interface helpers
+// The reference hands GPTModel::forward its token ids as a (seq, batch) matrix of floats (compute_layer.hpp:2783-2790);
+// the fused step wants int32 ids in batch-major order.  out[b*seq + t] = (int) ids[t*batch + b]; a value that is not a
+// finite non-negative number becomes -1, which the embedding lookup treats as out of range (zero row).
+__global__ void ids_from_float_kernel(const float* __restrict__ ids, int* __restrict__ out, int seq, int batch)
+{
+    const int n = seq * batch;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int b = i / seq, t = i - b * seq;
+        const float v = ids[static_cast<size_t>(t) * batch + b];
+        out[i] = (v >= 0.f && v < 2147483520.f) ? static_cast<int>(v) : -1;
+    }
+}
+int ids_from_float(const float* ids, int* out, int seq, int batch, cudaStream_t s)
+{
+    if (seq <= 0 || batch <= 0) return 0;
+    ids_from_float_kernel<<<grid_for(static_cast<long long>(seq) * batch, 256), 256, 0, s>>>(ids, out, seq, batch);
+    NNB_LAUNCH_CHECK();
+    return 0;
+}
+
+// Token-major logits (tokens, vocab) of the fused step -> the reference's (vocab, tokens) fp32 matrix: 32 x 32 tiles
+// through shared memory, coalesced on both sides.
+template <typename T>
+__global__ void logits_to_reference_kernel(const T* __restrict__ in, float* __restrict__ out, int tokens, int vocab)
+{
+    __shared__ float tile[32][33];
+    const int v0 = blockIdx.x * 32, t0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int t = t0 + j, v = v0 + threadIdx.x;
+        tile[j][threadIdx.x] = (t < tokens && v < vocab) ? to_f32(in[static_cast<size_t>(t) * vocab + v]) : 0.f;
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int v = v0 + j, t = t0 + threadIdx.x;
+        if (v < vocab && t < tokens) out[static_cast<size_t>(v) * tokens + t] = tile[threadIdx.x][j];
+    }
+}
+template <typename T> int logits_to_reference(const T* in, float* out, int tokens, int vocab, cudaStream_t s)
+{
+    if (tokens <= 0 || vocab <= 0) return 0;
+    const dim3 grid(static_cast<unsigned>(ceil_div(vocab, 32)), static_cast<unsigned>(ceil_div(tokens, 32)));
+    NNB_ARG_CHECK(grid.y <= 65535u, "too many token rows for one launch");
+    logits_to_reference_kernel<T><<<grid, dim3(32, 8), 0, s>>>(in, out, tokens, vocab);
+    NNB_LAUNCH_CHECK();
+    return 0;
+}
+template int logits_to_reference<float>(const float*, float*, int, int, cudaStream_t);
+template int logits_to_reference<bf16>(const bf16*, float*, int, int, cudaStream_t);
+
+__global__ void zero_f32_kernel(float4* __restrict__ p4, size_t n4, float* __restrict__ tail, int ntail)
+{
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += static_cast<size_t>(gridDim.x) * blockDim.x) p4[i] = z;
+    if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < ntail) tail[threadIdx.x] = 0.f;
+}
+// zero_grad over a flat fp32 range (Layer::zero_grad / Optimizer::zero_grad, compute_layer.hpp:57-65): one launch
+int zero_f32(float* p, size_t n, cudaStream_t s)
+{
+    if (n == 0) return 0;
+    NNB_ARG_CHECK((reinterpret_cast<uintptr_t>(p) & 15) == 0, "the range must start on a 16-byte boundary");
+    const size_t n4 = n / 4;
+    zero_f32_kernel<<<grid_for(static_cast<long long>(n4 ? n4 : 1), 256), 256, 0, s>>>(reinterpret_cast<float4*>(p), n4, p + 4 * n4, static_cast<int>(n - 4 * n4));
+    NNB_LAUNCH_CHECK();
+    return 0;
+}
+
 }  // namespace nnb

@@ -16,6 +16,7 @@ struct Runtime {
     bool ready = false;
     int device = 0;
     cudaStream_t stream = nullptr;
+    cudaEvent_t t0 = nullptr, t1 = nullptr;          // nnb200_rt_timer_start / _stop
 };
 Runtime g_rt;
 }  // namespace
@@ -107,6 +108,24 @@ int nnb200_rt_zero(void* dst, size_t bytes)
     if (!g_rt.ready) return -1;
     if (bytes == 0) return 0;
     NNB_CUDA_CHECK(cudaMemsetAsync(dst, 0, bytes, g_rt.stream));
+    return 0;
+}
+
+// One pair of CUDA events on the runtime's stream: _start records the first, _stop records the second, waits for it
+// and returns the device time between the two in milliseconds (what a driver program times a run of steps with).
+int nnb200_rt_timer_start(void)
+{
+    if (!g_rt.ready) return -1;
+    if (!g_rt.t0) { NNB_CUDA_CHECK(cudaEventCreate(&g_rt.t0)); NNB_CUDA_CHECK(cudaEventCreate(&g_rt.t1)); }
+    NNB_CUDA_CHECK(cudaEventRecord(g_rt.t0, g_rt.stream));
+    return 0;
+}
+int nnb200_rt_timer_stop(float* host_ms)
+{
+    if (!g_rt.ready || !g_rt.t0 || !host_ms) return -1;
+    NNB_CUDA_CHECK(cudaEventRecord(g_rt.t1, g_rt.stream));
+    NNB_CUDA_CHECK(cudaEventSynchronize(g_rt.t1));
+    NNB_CUDA_CHECK(cudaEventElapsedTime(host_ms, g_rt.t0, g_rt.t1));
     return 0;
 }
 

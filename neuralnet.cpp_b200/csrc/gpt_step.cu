@@ -271,6 +271,8 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
     T* dlogits = A(W.logits);
     NNB_TRY(linear_bwd_params<T>(dlogits, A(W.xnf), G + L.lm_w, G + L.lm_b, cs, cn, N, d, c.vocab, s, cs_begin()));
     cs_done(L.lm_b, c.vocab);
+    // lm_head.W's gradient is final here (its bias gradient only after the deferred fold at the end)
+    if (events && events[c.layers + 1]) NNB_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(events[c.layers + 1]), s));
     NNB_TRY(linear_bwd_input<T>(dlogits, P + L.lm_w, Hh(L.lm_w), A(W.d_xn), N, d, c.vocab, s));
     T* g = A(W.g_a);
     T* g_other = A(W.g_b);

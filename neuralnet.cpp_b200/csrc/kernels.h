@@ -76,6 +76,9 @@ size_t embed_bwd_scratch_bytes(int n_tok);
 template <typename T> int rope_apply(T* qkv, const float* table, int ntok, int seq, int heads, int dk, long long ld,
                                     bool backward, cudaStream_t s);
 void rope_table_host(int seq, int dk, float* out);   // cos (seq, dk/2) then sin (seq, dk/2)
+int ids_from_float(const float* ids_seq_major, int* out_batch_major, int seq, int batch, cudaStream_t s);
+template <typename T> int logits_to_reference(const T* logits_token_major, float* out_vocab_major, int tokens, int vocab, cudaStream_t s);
+int zero_f32(float* p, size_t n, cudaStream_t s);
 
 // ---- attention_simt.cu / attention_mma.cu
 template <typename T> int attention_fwd_simt(const T* qkv, T* out, float* lse, const int* doc, int B, int S, int H, int dk,

@@ -46,19 +46,21 @@ class CudaBuffer
 private:
     void* ptr_ = nullptr;
     std::size_t size_ = 0;
+    bool owned_ = true;             // false: a view into memory another buffer owns (see borrowed())
 
     void release() noexcept
     {
-        if (ptr_) (void)nnb200_rt_free(ptr_);
+        if (ptr_ && owned_) (void)nnb200_rt_free(ptr_);
         ptr_ = nullptr;
         size_ = 0;
+        owned_ = true;
     }
 
 public:
     CudaBuffer() = default;
     CudaBuffer(void* ptr, std::size_t size) : ptr_(ptr), size_(size) {}
     ~CudaBuffer() { release(); }
-    CudaBuffer(CudaBuffer&& o) noexcept : ptr_(o.ptr_), size_(o.size_) { o.ptr_ = nullptr; o.size_ = 0; }
+    CudaBuffer(CudaBuffer&& o) noexcept : ptr_(o.ptr_), size_(o.size_), owned_(o.owned_) { o.ptr_ = nullptr; o.size_ = 0; }
     CudaBuffer& operator=(CudaBuffer&& o) noexcept
     {
         if (this != &o)
@@ -66,6 +68,7 @@ public:
             release();
             ptr_ = o.ptr_;
             size_ = o.size_;
+            owned_ = o.owned_;
             o.ptr_ = nullptr;
             o.size_ = 0;
         }
@@ -83,6 +86,15 @@ public:
             return std::unexpected(Error{"device allocation failed (code " + std::to_string(rc) + ", " +
                                          std::to_string(bytes) + " bytes)"});
         return CudaBuffer(p, elem_count);
+    }
+
+    // A non-owning buffer over `elem_count` floats at `ptr`: parameter and gradient tensors that are slices of one
+    // arena (the fused GPT model) are built on these; the arena's own buffer frees the memory.
+    [[nodiscard]] static CudaBuffer borrowed(void* ptr, std::size_t elem_count) noexcept
+    {
+        CudaBuffer b(ptr, elem_count);
+        b.owned_ = false;
+        return b;
     }
 
     [[nodiscard]] void* ptr() const noexcept { return ptr_; }

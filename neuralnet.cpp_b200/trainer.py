@@ -56,14 +56,26 @@ def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def gradient_buckets(layer_begin: Sequence[int], matrix_begin: int):
-    """All-reduce buckets of the gradient arena as (start, end) element ranges, in issue order: the hidden
-    matrices of the last layer first (the backward pass finishes them first), down to layer 0, then the
-    vectors-and-embeddings region, which is final only when the embedding scatter-add has run.  `layer_begin`
-    has layers+1 entries (nnb200_gpt_layer_matrix_begin); the buckets tile [0, layer_begin[-1]) exactly."""
+def gradient_buckets(layer_begin: Sequence[int], matrix_begin: int, lm_head: Optional[Sequence[int]] = None):
+    """All-reduce buckets of the gradient arena as (event index, start, end) with element ranges, in issue order.
+    The LM head's weight gradient comes first: it is final after the first GEMM of the backward pass (event
+    layers+1).  Then the hidden matrices of the last layer (event layers-1: the backward pass finishes them first)
+    down to layer 0, then what is final only when the embedding scatter-add and the deferred bias / scale folds have
+    run (event layers): the vectors-and-embeddings region around the LM head's weight.  `layer_begin` has layers+1
+    entries (nnb200_gpt_layer_matrix_begin); `lm_head` = (start, end) of lm_head.W inside [0, matrix_begin), or None
+    to leave it in the last bucket.  The buckets tile [0, layer_begin[-1]) exactly."""
     n = len(layer_begin) - 1
-    out = [(layer_begin[l], layer_begin[l + 1]) for l in range(n - 1, -1, -1)]
-    out.append((0, matrix_begin))
+    out = []
+    if lm_head is not None and lm_head[1] > lm_head[0]:
+        out.append((n + 1, lm_head[0], lm_head[1]))
+    out += [(l, layer_begin[l], layer_begin[l + 1]) for l in range(n - 1, -1, -1)]
+    if lm_head is not None and lm_head[1] > lm_head[0]:
+        if lm_head[0] > 0:
+            out.append((n, 0, lm_head[0]))
+        if lm_head[1] < matrix_begin:
+            out.append((n, lm_head[1], matrix_begin))
+    else:
+        out.append((n, 0, matrix_begin))
     return out
 
 
@@ -72,7 +84,7 @@ class GptTrainer:
 
     def __init__(self, cfg: GptConfig, device: Optional[torch.device] = None, *, lr=1e-3, weight_decay=0.01,
                  beta1=0.9, beta2=0.999, eps=1e-8, muon: bool = False, muon_lr=0.02, muon_momentum=0.95,
-                 ns_steps=5, ns_eps=1e-7, process_group=None):
+                 ns_steps=5, ns_eps=1e-7, process_group=None, grad_reduce_dtype: str = "fp32"):
         if not torch.cuda.is_available():
             raise RuntimeError("GptTrainer needs a CUDA device: there is no CPU path")
         self.cfg = cfg
@@ -112,8 +124,20 @@ class GptTrainer:
         self.pg = process_group
         self.world = torch.distributed.get_world_size(process_group) if process_group is not None else 1
         self.side = torch.cuda.Stream(device=self.device) if self.world > 1 else None
-        self.events = [torch.cuda.Event() for _ in range(cfg.layers + 1)]
-        self._event_handles = (C.c_void_p * (cfg.layers + 1))()
+        self.events = [torch.cuda.Event() for _ in range(cfg.layers + 2)]
+        self._event_handles = (C.c_void_p * (cfg.layers + 2))()
+        lm_off, lm_r, lm_c = self.table[-2]                                 # lm_head.W
+        self.buckets = gradient_buckets(self.layer_begin, self.matrix_begin, (lm_off, lm_off + lm_r * lm_c))
+        # gradient buckets cross NVLink as fp32 (bit-for-bit the sum NCCL forms) or, halving the bytes and the time
+        # NCCL's kernels hold SMs, as bf16 (converted on the side stream; only with the bf16 compute path)
+        if grad_reduce_dtype not in ("fp32", "bf16"):
+            raise ValueError("grad_reduce_dtype is 'fp32' or 'bf16'")
+        self.grad_reduce_dtype = grad_reduce_dtype
+        self._bf16_stage = (torch.empty(max(hi - lo for _, lo, hi in self.buckets), dtype=torch.bfloat16, device=self.device)
+                            if (self.world > 1 and grad_reduce_dtype == "bf16") else None)
+        self.skip_all_reduce = False          # benchmark switch: measures the step without its exchange
+        self.time_optimizer = False           # CUDA events around the Muon part of the next optimizer_step
+        self._muon_events = None
         self.launches = 0
 
     # -------------------------------------------------------------- parameters
@@ -279,17 +303,38 @@ class GptTrainer:
 
     # -------------------------------------------------------------- data parallel
     def _all_reduce_buckets(self):
-        """Sum-all-reduce of the gradient arena, one bucket per layer's matrices (in the order the
-        backward pass completes them) and a final bucket for embeddings, head and vectors; issued
-        on the side stream behind the events the backward pass recorded."""
+        """Sum-all-reduce of the gradient arena in the buckets of gradient_buckets (LM head weight, one bucket per
+        layer's matrices in the order the backward pass completes them, then embeddings and vectors), issued on the
+        side stream behind the events the backward pass recorded."""
         import torch.distributed as dist
-        L = self.cfg.layers
-        order = list(range(L - 1, -1, -1)) + [L]            # event index behind which each bucket is final
+        if self.skip_all_reduce:
+            return
         with torch.cuda.stream(self.side):
-            for ev, (lo, hi) in zip(order, gradient_buckets(self.layer_begin, self.matrix_begin)):
+            for ev, lo, hi in self.buckets:
                 self.side.wait_event(self.events[ev])
-                dist.all_reduce(self.grads[lo:hi], group=self.pg)
+                if self._bf16_stage is None:
+                    dist.all_reduce(self.grads[lo:hi], group=self.pg)
+                else:
+                    st = self._bf16_stage[:hi - lo]
+                    s = C.c_void_p(self.side.cuda_stream)
+                    call("nnb200_f32_to_bf16", C.c_void_p(self.grads.data_ptr() + 4 * lo), _ptr(st), hi - lo, s)
+                    dist.all_reduce(st, group=self.pg)
+                    call("nnb200_bf16_to_f32", _ptr(st), C.c_void_p(self.grads.data_ptr() + 4 * lo), hi - lo, s)
         torch.cuda.current_stream().wait_stream(self.side)
+
+    def all_reduce_bytes_per_elem(self) -> int:
+        return 2 if self.grad_reduce_dtype == "bf16" else 4
+
+    def grad_bucket_dtype(self) -> str:
+        return self.grad_reduce_dtype
+
+    def muon_ms(self) -> Optional[float]:
+        """Device time of the Muon part of the last optimizer_step that ran with time_optimizer set (synchronises)."""
+        if self._muon_events is None:
+            return None
+        e0, e1 = self._muon_events
+        e1.synchronize()
+        return float(e0.elapsed_time(e1))
 
     # -------------------------------------------------------------- optimizer
     def optimizer_step(self, clip: Optional[float] = None, lr: Optional[float] = None,
@@ -311,6 +356,9 @@ class GptTrainer:
              n_adam, C.c_float(lr), C.c_float(self.b1), C.c_float(self.b2), C.c_float(self.eps), C.c_float(self.wd),
              self.t, gscale, s)
         if self.muon:
+            if self.time_optimizer:
+                self._muon_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                self._muon_events[0].record()
             mlr = self.muon_lr if muon_lr is None else muon_lr
             base = self.params.data_ptr()
             for off, r, c in self.table:
@@ -320,7 +368,10 @@ class GptTrainer:
                 call("nnb200_muon_step", C.c_void_p(base + 4 * off), C.c_void_p(self.grads.data_ptr() + 4 * off),
                      C.c_void_p(self.m.data_ptr() + 4 * off), sh, r, c, C.c_float(mlr), C.c_float(self.muon_mu),
                      self.ns_steps, C.c_float(self.ns_eps), self.cfg.precision, _ptr(self.muon_scratch), gscale, s)
-        self.grads.zero_()
+            if self.time_optimizer:
+                self._muon_events[1].record()
+                self.time_optimizer = False
+        call("nnb200_zero_f32", _ptr(self.grads), self.arena_elems, s)       # zero_grad
 
     def grad_norm(self) -> float:
         """Norm computed by the last optimizer_step that clipped (host read; synchronises)."""

@@ -22,6 +22,16 @@ def _layout(cfg_args):
     return layer_begin, int(nnb.call("nnb200_gpt_matrix_region_begin", C.byref(cfg))), int(nnb.call("nnb200_gpt_arena_elems", C.byref(cfg)))
 
 
+def _lm_head(cfg_args):
+    """(start, end) of lm_head.W in the arena: the last but one tensor of the reference's parameter order."""
+    nnb = entry.load_package()
+    cfg = nnb.GptConfig(*cfg_args).c_struct()
+    n = nnb.call("nnb200_gpt_param_table", C.byref(cfg), None, None, None)
+    offs, rows, cols = (C.c_longlong * n)(), (C.c_int32 * n)(), (C.c_int32 * n)()
+    nnb.call("nnb200_gpt_param_table", C.byref(cfg), offs, rows, cols)
+    return int(offs[n - 2]), int(offs[n - 2]) + int(rows[n - 2]) * int(cols[n - 2])
+
+
 CFG = (96, 48, 6, 3, 80, 12, 4, 1, 1, 2, 0)
 
 
@@ -30,15 +40,23 @@ def test_buckets_tile_the_arena():
     from neuralnet_cpp_b200.trainer import gradient_buckets
     layer_begin, matrix_begin, total = _layout(CFG)
     assert layer_begin[0] == matrix_begin and layer_begin[-1] == total
-    spans = sorted(gradient_buckets(layer_begin, matrix_begin))
-    assert spans[0][0] == 0 and spans[-1][1] == total
-    assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
-    # issue order: last layer first, vectors/embeddings last
-    order = gradient_buckets(layer_begin, matrix_begin)
-    assert order[0] == (layer_begin[-2], layer_begin[-1]) and order[-1] == (0, matrix_begin)
+    L = len(layer_begin) - 1
+    for lm in (None, _lm_head(CFG)):
+        order = gradient_buckets(layer_begin, matrix_begin, lm)
+        spans = sorted((lo, hi) for _, lo, hi in order)
+        assert spans[0][0] == 0 and spans[-1][1] == total
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        # issue order: (LM head weight first, behind its own event;) last layer first; vectors / embeddings last
+        first_layer = order[1] if lm else order[0]
+        assert first_layer == (L - 1, layer_begin[-2], layer_begin[-1])
+        assert order[-1][0] == L and order[-1][2] == matrix_begin
+        if lm:
+            assert order[0] == (L + 1, lm[0], lm[1]) and 0 < lm[0] < lm[1] < matrix_begin
+        else:
+            assert order[-1] == (L, 0, matrix_begin)
 
 
-def _worker(rank, world, port, layer_begin, matrix_begin, total, q):
+def _worker(rank, world, port, layer_begin, matrix_begin, total, lm, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     entry.load_package()
@@ -47,7 +65,7 @@ def _worker(rank, world, port, layer_begin, matrix_begin, total, q):
     grads = torch.from_numpy(rng.standard_normal(total).astype(np.float32))
     whole = grads.clone()
     dist.all_reduce(whole)
-    for lo, hi in gradient_buckets(layer_begin, matrix_begin):
+    for _, lo, hi in gradient_buckets(layer_begin, matrix_begin, lm):
         dist.all_reduce(grads[lo:hi])
     same = torch.equal(grads, whole)
     # identical data on every rank: sum * (1/world) is exact for world = 2
@@ -66,7 +84,7 @@ def test_bucketed_all_reduce_world2_gloo():
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, layer_begin, matrix_begin, total, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, layer_begin, matrix_begin, total, _lm_head(CFG), q)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in procs]
