@@ -232,6 +232,15 @@ int nnb200_muon_step(float* p, const float* g, float* velocity, void* shadow_bf1
                      float momentum, int ns_steps, float ns_eps, int precision, void* scratch,
                      const float* grad_scale_dev, void* stream);
 size_t nnb200_muon_scratch_bytes(int rows, int cols, int precision);
+/* nnb200_muon_step on `count` matrices (host arrays of device pointers and shapes), spread round-robin over `lanes`
+ * (1..16) auxiliary streams of the library that start behind `stream` and that `stream` waits for at the end: the
+ * Newton-Schulz GEMMs of a hidden matrix fill a fraction of the machine, so several matrices run side by side.
+ * scratch holds lanes * scratch_bytes_per_lane bytes, scratch_bytes_per_lane >= nnb200_muon_scratch_bytes of every
+ * matrix; shadow_bf16 may be NULL.  The updates are independent, so the result equals `count` single calls.
+ * Replaces the loop over parameters of Muon::step (compute_optimizer.hpp:546-587). */
+int nnb200_muon_step_many(int count, float* const* p, const float* const* g, float* const* velocity, void* const* shadow_bf16,
+                          const int* rows, const int* cols, float lr, float momentum, int ns_steps, float ns_eps, int precision,
+                          void* scratch, size_t scratch_bytes_per_lane, int lanes, const float* grad_scale_dev, void* stream);
 int nnb200_f32_to_bf16(const float* in, void* out, size_t n, void* stream);
 int nnb200_bf16_to_f32(const void* in, float* out, size_t n, void* stream);
 

@@ -284,6 +284,54 @@ int nnb200_muon_step(float* p, const float* g, float* velocity, void* shadow_bf1
     return muon_apply<float>(p, u, static_cast<bf16*>(shadow_bf16), lr, n, s);     // non-2-D: p -= lr*u
 }
 
+// Auxiliary streams ("lanes") of the current device, created on first use, and one event per lane plus one for the fork.
+namespace {
+constexpr int kMaxLanes = 16;
+struct Lanes { cudaStream_t stream[kMaxLanes] = {}; cudaEvent_t done[kMaxLanes] = {}; cudaEvent_t fork = nullptr; int made = 0; };
+Lanes g_lanes[64];
+int lanes_for_device(int want, Lanes** out)
+{
+    Lanes& L = g_lanes[nnb::current_device_slot()];
+    if (!L.fork) NNB_CUDA_CHECK(cudaEventCreateWithFlags(&L.fork, cudaEventDisableTiming));
+    for (; L.made < want; ++L.made) {
+        NNB_CUDA_CHECK(cudaStreamCreateWithFlags(&L.stream[L.made], cudaStreamNonBlocking));
+        NNB_CUDA_CHECK(cudaEventCreateWithFlags(&L.done[L.made], cudaEventDisableTiming));
+    }
+    *out = &L;
+    return 0;
+}
+}  // namespace
+
+int nnb200_muon_step_many(int count, float* const* p, const float* const* g, float* const* velocity, void* const* shadow_bf16,
+                          const int* rows, const int* cols, float lr, float momentum, int ns_steps, float ns_eps, int precision,
+                          void* scratch, size_t scratch_bytes_per_lane, int lanes, const float* grad_scale_dev, void* stream)
+{
+    NNB_ARG_CHECK(count >= 0 && lanes >= 1 && lanes <= kMaxLanes, "bad count or lane count (1..16)");
+    if (count == 0) return 0;
+    NNB_ARG_CHECK(p && g && velocity && rows && cols && scratch, "null argument");
+    for (int i = 0; i < count; ++i)
+        NNB_ARG_CHECK(nnb200_muon_scratch_bytes(rows[i], cols[i], precision) <= scratch_bytes_per_lane, "a lane's scratch is too small for one of the matrices");
+    if (lanes > count) lanes = count;
+    cudaStream_t s = to_stream(stream);
+    Lanes* L = nullptr;
+    NNB_TRY(lanes_for_device(lanes, &L));
+    // fork: every lane starts behind what is queued on `stream`; join: `stream` continues behind every lane
+    NNB_CUDA_CHECK(cudaEventRecord(L->fork, s));
+    for (int l = 0; l < lanes; ++l) NNB_CUDA_CHECK(cudaStreamWaitEvent(L->stream[l], L->fork, 0));
+    int rc = 0;
+    for (int i = 0; i < count && rc == 0; ++i) {
+        const int l = i % lanes;
+        rc = nnb200_muon_step(p[i], g[i], velocity[i], shadow_bf16 ? shadow_bf16[i] : nullptr, rows[i], cols[i], lr, momentum, ns_steps,
+                              ns_eps, precision, static_cast<uint8_t*>(scratch) + static_cast<size_t>(l) * scratch_bytes_per_lane,
+                              grad_scale_dev, L->stream[l]);
+    }
+    for (int l = 0; l < lanes; ++l) {
+        NNB_CUDA_CHECK(cudaEventRecord(L->done[l], L->stream[l]));
+        NNB_CUDA_CHECK(cudaStreamWaitEvent(s, L->done[l], 0));
+    }
+    return rc;
+}
+
 unsigned long long nnb200_launch_count(int reset)
 {
     const unsigned long long v = g_launches;

@@ -458,6 +458,13 @@ class FusedMuon final : public Optimizer
     Result<void> init_ = {};
     Scalar lr_, momentum_, ns_eps_;
     int ns_steps_;
+    // the hidden matrices as arrays of device pointers / shapes, and the streams ("lanes") they are spread over: the
+    // Newton-Schulz GEMMs of one matrix fill only a fraction of the machine
+    std::vector<float*> p_, g_, v_;
+    std::vector<void*> sh_;
+    std::vector<int> rows_, cols_;
+    std::size_t lane_bytes_ = 0;
+    int lanes_ = 1;
 
 public:
     FusedMuon(ComputeEngine& engine, B200GPTModel& model, Scalar lr, Scalar momentum = 0.95f, std::size_t ns_steps = 5,
@@ -469,11 +476,23 @@ public:
         const auto total = static_cast<std::size_t>(model.arena_elems());
         std::size_t worst = 0;
         const auto& views = model.parameter_views();
+        if (auto r = velocity_.allocate(total - begin); !r) { init_ = r; return; }
+        char* shadow = static_cast<char*>(model.shadow_bf16());
         for (std::size_t i = 0; i < views.size(); ++i)
-            if (static_cast<std::size_t>(model.offsets()[i]) >= begin)
-                worst = std::max(worst, nnb200_muon_scratch_bytes(static_cast<int>(views[i].rows()), static_cast<int>(views[i].cols()), model.config().precision));
-        if (auto r = velocity_.allocate(total - begin); !r) init_ = r;
-        else if (auto r2 = scratch_.allocate((worst + 3) / 4); !r2) init_ = r2;
+        {
+            const auto off = static_cast<std::size_t>(model.offsets()[i]);
+            if (off < begin) continue;
+            worst = std::max(worst, nnb200_muon_scratch_bytes(static_cast<int>(views[i].rows()), static_cast<int>(views[i].cols()), model.config().precision));
+            p_.push_back(model.params_f32() + off);
+            g_.push_back(model.grads_f32() + off);
+            v_.push_back(velocity_.f32() + (off - begin));
+            sh_.push_back(shadow ? shadow + 2 * off : nullptr);
+            rows_.push_back(static_cast<int>(views[i].rows()));
+            cols_.push_back(static_cast<int>(views[i].cols()));
+        }
+        lane_bytes_ = (worst + 255) / 256 * 256;
+        lanes_ = static_cast<int>(std::max<std::size_t>(1, std::min<std::size_t>(8, p_.size())));
+        if (auto r2 = scratch_.allocate(lane_bytes_ * static_cast<std::size_t>(lanes_) / 4); !r2) init_ = r2;
         model_.set_shadow_managed(true);
     }
     void set_lr(Scalar lr) override { lr_ = lr; }
@@ -481,19 +500,11 @@ public:
     [[nodiscard]] Result<void> step() override
     {
         if (!init_) return init_;
-        const auto begin = static_cast<std::size_t>(model_.matrix_region_begin());
-        const auto& views = model_.parameter_views();
-        char* shadow = static_cast<char*>(model_.shadow_bf16());
-        for (std::size_t i = 0; i < views.size(); ++i)
-        {
-            const auto off = static_cast<std::size_t>(model_.offsets()[i]);
-            if (off < begin) continue;
-            if (auto r = b200_detail::ok(nnb200_muon_step(model_.params_f32() + off, model_.grads_f32() + off, velocity_.f32() + (off - begin),
-                                                          shadow ? shadow + 2 * off : nullptr, static_cast<int>(views[i].rows()),
-                                                          static_cast<int>(views[i].cols()), static_cast<float>(lr_), static_cast<float>(momentum_),
-                                                          ns_steps_, static_cast<float>(ns_eps_), model_.config().precision, scratch_.ptr(),
-                                                          model_.grad_scale_dev(), nnb200_rt_stream()), "nnb200_muon_step"); !r) return r;
-        }
+        if (auto r = b200_detail::ok(nnb200_muon_step_many(static_cast<int>(p_.size()), p_.data(), g_.data(), v_.data(),
+                                                           model_.shadow_bf16() ? sh_.data() : nullptr, rows_.data(), cols_.data(),
+                                                           static_cast<float>(lr_), static_cast<float>(momentum_), ns_steps_,
+                                                           static_cast<float>(ns_eps_), model_.config().precision, scratch_.ptr(), lane_bytes_,
+                                                           lanes_, model_.grad_scale_dev(), nnb200_rt_stream()), "nnb200_muon_step_many"); !r) return r;
         model_.shadow_is_current();      // the AdamW half, stepped before or after, keeps its own range current
         return {};
     }

@@ -220,8 +220,6 @@ def main():
             run_gemm(n, k, T, args, a_mn=1, b_mn=1, c_bf16=0, acc=1, tag=tag + ".dw")
     if fam in ("all", "attention"):
         for s in ([shape] if shape else [(4, sq, 16, dk) for dk in (64, 128) for sq in (512, 1024, 2048, 4096, 8192)]):
-            if s[3] == 128 and s[1] > 2048:
-                continue        # head size 128 runs the SIMT fallback: too slow to be worth timing at long sequences
             run_attention(*s, args)
     if fam in ("all", "ce"):
         run_ce(*(shape or (16384, 32768)), args)

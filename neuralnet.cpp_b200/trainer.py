@@ -117,9 +117,19 @@ class GptTrainer:
         self.muon = muon
         self.muon_lr, self.muon_mu, self.ns_steps, self.ns_eps = muon_lr, muon_momentum, ns_steps, ns_eps
         if muon:
-            worst = max(int(call("nnb200_muon_scratch_bytes", r, c, cfg.precision))
-                        for o, r, c in self.table if o >= self.matrix_begin)
-            self.muon_scratch = torch.empty(worst, dtype=torch.uint8, device=self.device)
+            # the hidden matrices as host arrays of device pointers for nnb200_muon_step_many; the Newton-Schulz GEMMs of
+            # one matrix fill a fraction of the machine, so the matrices go round-robin over several streams ("lanes")
+            mats = [(o, r, c) for o, r, c in self.table if o >= self.matrix_begin]
+            worst = max(int(call("nnb200_muon_scratch_bytes", r, c, cfg.precision)) for _, r, c in mats)
+            self.muon_lane_bytes = (worst + 255) // 256 * 256
+            self.muon_lanes = max(1, min(8, len(mats)))
+            self.muon_scratch = torch.empty(self.muon_lane_bytes * self.muon_lanes, dtype=torch.uint8, device=self.device)
+            n = len(mats)
+            PA, IA = C.c_void_p * n, C.c_int * n
+            base = lambda t, esz: [t.data_ptr() + esz * o for o, _, _ in mats]
+            self._muon_args = (n, PA(*base(self.params, 4)), PA(*base(self.grads, 4)), PA(*base(self.m, 4)),
+                               PA(*base(self.shadow, 2)) if self.shadow is not None else None,
+                               IA(*[r for _, r, _ in mats]), IA(*[c for _, _, c in mats]))
         # data parallel state
         self.pg = process_group
         self.world = torch.distributed.get_world_size(process_group) if process_group is not None else 1
@@ -360,14 +370,10 @@ class GptTrainer:
                 self._muon_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                 self._muon_events[0].record()
             mlr = self.muon_lr if muon_lr is None else muon_lr
-            base = self.params.data_ptr()
-            for off, r, c in self.table:
-                if off < self.matrix_begin:
-                    continue
-                sh = C.c_void_p(self.shadow.data_ptr() + 2 * off) if self.shadow is not None else None
-                call("nnb200_muon_step", C.c_void_p(base + 4 * off), C.c_void_p(self.grads.data_ptr() + 4 * off),
-                     C.c_void_p(self.m.data_ptr() + 4 * off), sh, r, c, C.c_float(mlr), C.c_float(self.muon_mu),
-                     self.ns_steps, C.c_float(self.ns_eps), self.cfg.precision, _ptr(self.muon_scratch), gscale, s)
+            n, pp, gg, vv, sh, rr_, cc_ = self._muon_args
+            call("nnb200_muon_step_many", n, pp, gg, vv, sh, rr_, cc_, C.c_float(mlr), C.c_float(self.muon_mu), self.ns_steps,
+                 C.c_float(self.ns_eps), self.cfg.precision, _ptr(self.muon_scratch), self.muon_lane_bytes, self.muon_lanes,
+                 gscale, s)
             if self.time_optimizer:
                 self._muon_events[1].record()
                 self.time_optimizer = False

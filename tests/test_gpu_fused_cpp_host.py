@@ -57,6 +57,7 @@ def test_cpp_host_save_model_is_the_reference_file():
     this repository's Python writer (pinned against reference-written files) makes of the same parameters, and the
     reference CPU engine, started from those parameters, continues with the losses the fused run would have."""
     _need_binary()
+    nnb = entry.load_package()
     from neuralnet_cpp_b200 import checkpoint
     case = load_gpt_case("rms_swiglu_alibi_accum")
     cfg = case["cfg"]
@@ -68,7 +69,6 @@ def test_cpp_host_save_model_is_the_reference_file():
         assert tok == b""
         for got, want in zip(mats, out["params"]):
             assert np.array_equal(got, want)
-        nnb = entry.load_package()
         tcfg = nnb.GptConfig(cfg.vocab, cfg.d_model, cfg.heads, cfg.layers, cfg.d_ff, cfg.seq, cfg.batch, cfg.act, cfg.norm, cfg.pos, 0)
         ref_path = os.path.join(td, "py.bin")
         checkpoint.write_model_file(ref_path, checkpoint.spec_of_config(tcfg), out["params"], b"")
