@@ -318,28 +318,33 @@ def main():
     host_doc = torch.from_numpy(docs_np).pin_memory() if w["docs"] else None
     dev_tok, dev_lab, dev_mask = host_tok.cuda(), host_lab.cuda(), host_mask.cuda()
     dev_doc = host_doc.cuda() if w["docs"] else None
-    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
 
-    def run_step(step, resident):
-        last = None
+    # end to end: the user hands host arrays to the input pipeline (pinned staging, the copy of the next micro-batch
+    # overlaps the current one, losses come back without stalling the device) — every micro-batch still crosses the
+    # bus inside the timed region, and every loss is read before the region ends
+    pipe = nnb.AsyncInputPipeline(tr)
+    host_np = dict(tok=host_tok.numpy(), lab=host_lab.numpy(), msk=host_mask.numpy(), doc=host_doc.numpy() if w["docs"] else None)
+
+    def submit(j):
+        i = j % n_micro
+        pipe.submit(host_np["tok"][i], host_np["lab"][i], host_np["msk"][i], host_np["doc"][i] if w["docs"] else None)
+
+    def run_step(step, resident, end_step=None):
         for a in range(accum):
-            i = (step * accum + a) % n_micro
+            j = step * accum + a
             if resident:
-                t, l, m = dev_tok[i], dev_lab[i], dev_mask[i]
-                dd = dev_doc[i] if w["docs"] else None
-            else:   # the user's call: host buffers in, loss out
-                t = host_tok[i].cuda(non_blocking=True)
-                l = host_lab[i].cuda(non_blocking=True)
-                m = host_mask[i].cuda(non_blocking=True)
-                dd = host_doc[i].cuda(non_blocking=True) if w["docs"] else None
-            tr.micro_step(t, l, m, dd, grad_scale=1.0 / accum, last=(a == accum - 1))
-            if not resident:
-                loss_host.copy_(tr.loss_tensor(), non_blocking=True)
-                torch.cuda.current_stream().synchronize()
-                last = float(loss_host[0])
+                i = j % n_micro
+                tr.micro_step(dev_tok[i], dev_lab[i], dev_mask[i], dev_doc[i] if w["docs"] else None, grad_scale=1.0 / accum,
+                              last=(a == accum - 1))
+            else:
+                if pipe.n_sub == pipe.n_run:
+                    submit(j)                                  # the first micro-batch of a run: nothing staged yet
+                if end_step is None or j + 1 < end_step * accum:
+                    submit(j + 1)                              # the next one travels while this one computes
+                pipe.run(grad_scale=1.0 / accum, last=(a == accum - 1))
         lr = step_lr(step, w)
         tr.optimizer_step(clip=w["clip"], lr=lr, muon_lr=lr * MUON_LR / BASE_LR)
-        return last
+        return None
 
     def timed(resident, first_step):
         if world > 1:
@@ -349,7 +354,10 @@ def main():
         e0.record()
         last = None
         for s in range(K):
-            last = run_step(first_step + s, resident)
+            last = run_step(first_step + s, resident, first_step + K)
+        if not resident:
+            losses = pipe.drain()                              # every loss of the region has reached the host
+            last = losses[-1] if losses else None
         e1.record()
         torch.cuda.synchronize()
         if world > 1:
@@ -369,7 +377,8 @@ def main():
     ms_resident, _ = timed(True, W)
     launches = int(nnb.call("nnb200_launch_count", 1))
     clocks = sampler.stop() if sampler else None
-    run_step(W + K, False)                 # warm the host-buffer path
+    run_step(W + K, False, W + K + 1)      # warm the host-buffer path
+    pipe.drain()
     ms_e2e, last_loss = timed(False, W + K + 1)
 
     # roofline of the dominant kernel (tcgen05 GEMM): event pairs around every launch of one more step

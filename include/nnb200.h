@@ -290,6 +290,19 @@ int nnb200_gpt_backward(const nnb200_gpt_config* cfg, const float* params, const
                         void* workspace, const int32_t* tokens, const int32_t* doc_ids, void* const* layer_events,
                         void* stream);
 
+/* Incremental inference with a key/value cache (GPTModel::forward_step, compute_layer.hpp:2906-2950; the per-block
+ * step :1426-1511; ALiBi bias of a step :2267-2290).  The decode workspace holds the cache of every layer
+ * (layers x {K, V} x seq x d_model, fp32), the position tables and one token's activations; cfg->batch is not used
+ * (one sequence).  _init fills the sinusoidal / rotary tables: call once, and again after the workspace moved.
+ * _forward_step runs token `token_id` at cache row `cur_len` (0 <= cur_len < seq; rows [0, cur_len) must hold the
+ * earlier tokens of the context) with position encoding index `pos`, appends its key and value to the cache and
+ * writes the (vocab) fp32 logits to logits_out (device; NULL = left in the workspace).  Weights are read as bf16
+ * (params_bf16, bf16 mode) or fp32 (check mode); activations and the cache are fp32 in both. */
+long long nnb200_gpt_decode_workspace_bytes(const nnb200_gpt_config* cfg);
+int nnb200_gpt_decode_init(const nnb200_gpt_config* cfg, void* workspace, void* stream);
+int nnb200_gpt_forward_step(const nnb200_gpt_config* cfg, const float* params, const void* params_bf16, void* workspace, int token_id,
+                            int pos, int cur_len, float* logits_out, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Engine primitives in the reference's own layouts (fp32; matrices row-major, batch blocks stacked
  * along rows).  These are the ComputeEngine virtuals the reference's CudaEngine answers "not

@@ -62,6 +62,9 @@ SIGNATURES = {
     "nnb200_attention_backward": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "nnb200_attention_doc_ranges": [_p, _i, _i, _p, _p],
     "nnb200_muon_step_many": [_i, _p, _p, _p, _p, _p, _p, _f, _f, _i, _f, _i, _p, _sz, _i, _p, _p],
+    "nnb200_gpt_decode_workspace_bytes": [_cfgp],
+    "nnb200_gpt_decode_init": [_cfgp, _p, _p],
+    "nnb200_gpt_forward_step": [_cfgp, _p, _p, _p, _i, _i, _i, _p, _p],
     "nnb200_ids_from_float": [_p, _p, _i, _i, _p],
     "nnb200_logits_to_reference": [_p, _p, _i, _i, _i, _p],
     "nnb200_zero_f32": [_p, _sz, _p],
@@ -127,6 +130,7 @@ _RET = {
     "nnb200_colsum_scratch_floats": _sz, "nnb200_embedding_scratch_bytes": _sz, "nnb200_sumsq_scratch_floats": _sz,
     "nnb200_muon_scratch_bytes": _sz, "nnb200_gpt_arena_elems": _ll, "nnb200_gpt_matrix_region_begin": _ll,
     "nnb200_gpt_layer_matrix_begin": _ll, "nnb200_gpt_workspace_bytes": _ll, "nnb200_gpt_workspace_offset": _ll,
+    "nnb200_gpt_decode_workspace_bytes": _ll,
     "nnb200_eval_expr_scratch_floats": _sz, "nnb200_rt_stream": C.c_void_p,
 }
 # functions whose int return value is a count, not a status

@@ -18,6 +18,12 @@
 // K-major operands wider than 64 values are kept as sub-tiles of 64 columns (one 128-byte swizzle atom per row);
 // V is consumed as an MN-major B operand straight from its (key, head) tile.  Nothing of size (S, S) reaches memory.
 //
+// ALiBi: the bias -slope_h (i - j) is linear in the key position, so the tensor core adds it: one more MMA step per
+// block multiplies a (128 x 16) tile that holds slope_h / scale, split into three bf16 terms (24 bits), in every query
+// row by a constant tile that holds the key's position inside the block (exact in bf16) three times.  What is left
+// per block is one constant per row (slope_h * first key of the block; the -slope_h * i term cannot change a row's
+// softmax and is put back into the log-sum-exp at the end), so a score costs one packed multiply-add and one ex2.
+//
 // Document masks: with a table of per-64-row (min, max) document ids (attention_doc_ranges) every role skips the key
 // blocks whose id range cannot meet the query tile's range.  A skipped block would have contributed P = 0 everywhere,
 // so the result is bit-identical with and without the table.
@@ -40,11 +46,13 @@ constexpr int AQ = 128, AK = 128;
 constexpr int A_TILE = 128 * 128;                  // bytes of a 128-row x 64-bf16 sub-tile
 constexpr float kLog2eF = 1.4426950408889634f, kLn2F = 0.6931471805599453f;
 
-// shared memory: Q | K | V ring of two | P (two 64-key halves) | row-max exchange | barriers
+// shared memory: Q | K | V ring of two | P (two 64-key halves) | row-max exchange | ALiBi operand tiles | barriers
+constexpr int A_BIAS_TILE = 128 * 32;              // bytes of a 128-row x 16-bf16 tile without swizzle
 template <int DK> struct FwdLayout {
     static constexpr int NS = DK / 64;                                  // 64-column sub-tiles per operand tile
     static constexpr int OFF_K = NS * A_TILE, OFF_V = 2 * NS * A_TILE, OFF_P = 4 * NS * A_TILE, OFF_X = OFF_P + 2 * A_TILE,
-                         OFF_BAR = OFF_X + 2 * 2 * 128 * 4, SMEM = OFF_BAR + 256;
+                         OFF_U = OFF_X + 2 * 2 * 128 * 4, OFF_W = OFF_U + A_BIAS_TILE, OFF_BAR = OFF_W + A_BIAS_TILE,
+                         SMEM = OFF_BAR + 256;
     static constexpr uint32_t TMEM_COLS = 256;                          // scores [0, 128), O' [128, 128 + DK)
     static constexpr int CTAS_PER_SM = DK == 64 ? 2 : 1;
 };
@@ -130,6 +138,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_O = tmem_base + 128;
+    uint8_t* sU = smem + LY::OFF_U;                // slope_h / scale in every query row (rewritten per tile by warp 0)
+    uint8_t* sW = smem + LY::OFF_W;                // key position inside the block, constant
+    if (ALIBI) {
+        // unswizzled K-major tiles, 16 values deep: row r, values [8c, 8c + 8) at (r / 8) * 256 + c * 128 + (r % 8) * 16
+        for (int r = threadIdx.x; r < 128; r += blockDim.x) {
+            const uint32_t off = (r >> 3) * 256 + (r & 7) * 16;
+            const __nv_bfloat162 jj = __floats2bfloat162_rn(static_cast<float>(r), static_cast<float>(r));
+            const uint32_t j2 = *reinterpret_cast<const uint32_t*>(&jj);
+            *reinterpret_cast<uint4*>(sW + off) = make_uint4(j2, j2 & 0xffffu, 0u, 0u);      // [r, r, r, 0, 0, 0, 0, 0]
+            *reinterpret_cast<uint4*>(sW + off + 128) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(sU + off) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(sU + off + 128) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+    }
 
     // instruction descriptors: fp32 accumulate, bf16 operands; S: N=128, both K-major; PV: N=DK, B MN-major
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(AK >> 3) << 17) | (uint32_t(AQ >> 4) << 24);
@@ -151,8 +175,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
             const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
             const int nkb = t.qb + 1, row_base = t.b * a.S;
             const BlockMask bm = tile_mask(t, nkb);
+            if (lane == 0) ok = mbar_wait(q_empty, (tn & 1) ^ 1, abort_flag, 11, &g_attn_error);   // the previous tile's MMAs are done
+            ok = __shfl_sync(0xffffffffu, static_cast<int>(ok), 0) != 0;
+            if (ALIBI && ok) {
+                // this head's slope / scale as three bf16 terms, in every query row of the U tile
+                const float sv = exp2f(-8.0f * static_cast<float>(t.h) / static_cast<float>(a.H)) / a.scale;
+                const bf16 s0 = __float2bfloat16_rn(sv);
+                const float r1 = sv - __bfloat162float(s0);
+                const bf16 s1 = __float2bfloat16_rn(r1);
+                const bf16 s2 = __float2bfloat16_rn(r1 - __bfloat162float(s1));
+                const uint32_t w0 = static_cast<uint32_t>(__bfloat16_as_ushort(s0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(s1)) << 16);
+                const uint32_t w1 = static_cast<uint32_t>(__bfloat16_as_ushort(s2));
+                for (int r = lane; r < 128; r += 32)
+                    *reinterpret_cast<uint4*>(sU + (r >> 3) * 256 + (r & 7) * 16) = make_uint4(w0, w1, 0u, 0u);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+            }
             if (lane == 0) {
-                ok = mbar_wait(q_empty, (tn & 1) ^ 1, abort_flag, 11, &g_attn_error);
                 if (ok) {
                     mbar_expect_tx(q_full, TILE);
 #pragma unroll
@@ -196,6 +235,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
                         const uint32_t o = (k >> 2) * A_TILE + (k & 3) * 32;
                         umma_bf16(tmem_base, smem_desc(q_addr + o, 16, 1024), smem_desc(k_addr + o, 16, 1024), IDESC_S, k > 0 ? 1u : 0u);
                     }
+                    if (ALIBI)       // + (slope / scale) * (key position inside the block)
+                        umma_bf16(tmem_base, smem_desc_noswizzle(smem_u32(sU), 128, 256), smem_desc_noswizzle(smem_u32(sW), 128, 256), IDESC_S, 1u);
                     umma_commit(s_full);
                     umma_commit(k_empty);                           // the key tile is free once these MMAs have read it
                     return true;
@@ -249,10 +290,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
             const int i = q0 + row;                            // query position inside the sequence
             const float slope2 = ALIBI ? exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(a.H)) * kLog2eF : 0.f;
             const int my_doc = DOC ? a.doc[row_base + i] : 0;
+            // Running maximum and sum in the base-2 domain.  With ALiBi the -slope2 * i term of the bias is left out
+            // here (it is the same for every key of the row) and goes back into the log-sum-exp at the end.
             float m_run = -INFINITY, l_run = 0.f;
-            float o_acc[OC];
+            uint64_t o_acc[OC / 2];                            // packed pairs of output columns
 #pragma unroll
-            for (int c = 0; c < OC; ++c) o_acc[c] = 0.f;
+            for (int c = 0; c < OC / 2; ++c) o_acc[c] = 0ull;
+            const uint64_t scale2x2 = pack2(scale2, scale2);
 
             auto fold_o = [&](int gj) -> bool {                 // o_acc += O'(gj), this thread's columns
                 if (!mbar_wait(o_full, gj & 1, abort_flag, 7, &g_attn_error)) return false;
@@ -263,7 +307,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
                     tmem_ld32(tmem_O + lane_addr + hf * OC + c0, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) o_acc[c0 + c] += __uint_as_float(r[c]);
+                    for (int c = 0; c < 16; ++c)
+                        o_acc[c0 / 2 + c] = add2(o_acc[c0 / 2 + c], pack2(__uint_as_float(r[2 * c]), __uint_as_float(r[2 * c + 1])));
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -272,7 +317,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
             };
 
             // One 128-key block, the cnt-th active one of the tile.  DIAG: the block on the diagonal (causal mask
-            // inside it).  The score of column cj is r*scale2 + (slope2*cj + abase); with the loops unrolled cj is a literal.
+            // inside it).  The tensor core left raw = q.k (+ slope / scale * position inside the block) in TMEM, so
+            // the base-2 score of column cj is raw * scale2 + okb with okb = slope2 * (first key of the block).
             auto block = [&](auto diag_tag, int kb, int cnt) -> bool {
                 constexpr bool DIAG = decltype(diag_tag)::value;
                 const int gj = kv0 + cnt;
@@ -280,23 +326,30 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
                 tc_fence_after();
                 const int k0 = kb * AK;
                 const int* dk_ptr = DOC ? a.doc + row_base + k0 + hf * 64 : nullptr;
-                const float abase = ALIBI ? -slope2 * static_cast<float>(i - k0 - hf * 64) : 0.f;
-                auto score = [&](float raw, int cj) -> float {
-                    // cj is a literal once unrolled: nothing here is loop-invariant, so nothing is kept live across the passes
-                    float sc = ALIBI ? fmaf(slope2, static_cast<float>(cj), fmaf(raw, scale2, abase)) : raw * scale2;
-                    if (DIAG && hf * 64 + cj > row) sc = -INFINITY;
-                    if (DOC && dk_ptr[cj] != my_doc) sc = -INFINITY;
-                    return sc;
+                const float okb = ALIBI ? slope2 * static_cast<float>(k0) : 0.f;
+                auto masked = [&](int cj) -> bool {             // cj is a literal once unrolled
+                    bool m = false;
+                    if (DIAG) m = hf * 64 + cj > row;
+                    if (DOC) m = m || dk_ptr[cj] != my_doc;
+                    return m;
                 };
-                float mx = -INFINITY;
+                // Two passes over the scores in TMEM, 32 columns at a time, so that the thread never holds more than
+                // 32 of them: the first finds the row maximum (of the raw values: the scale is positive), the second
+                // makes P.  The score buffer is released after the second pass.
+                float mxr = -INFINITY;
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     uint32_t r[32];
                     tmem_ld32(tmem_base + lane_addr + hf * 64 + c * 32, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) mx = fmaxf(mx, score(__uint_as_float(r[jj]), c * 32 + jj));
+                    for (int jj = 0; jj < 32; ++jj) {
+                        float v = __uint_as_float(r[jj]);
+                        if ((DIAG || DOC) && masked(c * 32 + jj)) v = -INFINITY;
+                        mxr = fmaxf(mxr, v);
+                    }
                 }
+                const float mx = fmaf(mxr, scale2, okb);         // -inf stays -inf
                 float* xs = sX + (xc & 1) * 256;
                 ++xc;
                 xs[hf * 128 + row] = mx;
@@ -306,12 +359,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
                 const float corr = ex2_approx(m_run - ms);
                 if (cnt >= 1) bad |= !fold_o(gj - 1);
                 if (__any_sync(0xffffffffu, corr != 1.0f)) {
+                    const uint64_t corr2 = pack2(corr, corr);
 #pragma unroll
-                    for (int c = 0; c < OC; ++c) o_acc[c] *= corr;
+                    for (int c = 0; c < OC / 2; ++c) o_acc[c] = mul2(o_acc[c], corr2);
                 }
                 if (gj >= 1) bad |= !mbar_wait(p_empty, (gj - 1) & 1, abort_flag, 10, &g_attn_error);
                 uint8_t* prow = sP + hf * A_TILE + row * 128;
-                float rs = 0.f;
+                const uint64_t shift2 = pack2(okb - ms, okb - ms);
+                uint64_t rs2 = 0ull;
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     uint32_t r[32];
@@ -323,9 +378,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int jj = g * 8 + e * 2;
-                            const float p0 = ex2_approx(score(__uint_as_float(r[jj]), c * 32 + jj) - ms);
-                            const float p1 = ex2_approx(score(__uint_as_float(r[jj + 1]), c * 32 + jj + 1) - ms);
-                            rs += p0 + p1;
+                            float x0, x1;
+                            unpack2(fma2(pack2(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1])), scale2x2, shift2), x0, x1);
+                            float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                            if ((DIAG || DOC) && masked(c * 32 + jj)) p0 = 0.f;
+                            if ((DIAG || DOC) && masked(c * 32 + jj + 1)) p1 = 0.f;
+                            rs2 = add2(rs2, pack2(p0, p1));
                             __nv_bfloat162 tt = __floats2bfloat162_rn(p0, p1);
                             pk[e] = *reinterpret_cast<uint32_t*>(&tt);
                         }
@@ -335,7 +393,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_empty);            // both passes have read the scores
-                l_run = l_run * corr + rs;
+                float rs_lo, rs_hi;
+                unpack2(rs2, rs_lo, rs_hi);
+                l_run = l_run * corr + (rs_lo + rs_hi);
                 m_run = m_new;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the tensor core
                 __syncwarp();
@@ -360,14 +420,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
                 const float l_tot = l_run + xs[(hf ^ 1) * 128 + row];
                 const float inv = 1.0f / l_tot;
                 bf16* op = a.out + (static_cast<size_t>(row_base) + i) * d + h * DK + hf * OC;
+                const uint64_t inv2 = pack2(inv, inv);
 #pragma unroll
                 for (int c = 0; c < OC; c += 8) {
-                    Vec16<bf16> o;
+                    uint32_t pk[4];
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(o_acc[c + k] * inv);
-                    st16(op + c, o);
+                    for (int k = 0; k < 4; ++k) {
+                        float v0, v1;
+                        unpack2(mul2(o_acc[c / 2 + k], inv2), v0, v1);
+                        __nv_bfloat162 tt = __floats2bfloat162_rn(v0, v1);
+                        pk[k] = *reinterpret_cast<uint32_t*>(&tt);
+                    }
+                    *reinterpret_cast<uint4*>(op + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
-                if (hf == 0) a.lse[(static_cast<size_t>(b) * a.H + h) * a.S + i] = (m_run + log2f(l_tot)) * kLn2F;
+                // log-sum-exp in natural units; the ALiBi term left out of the running maximum comes back here
+                if (hf == 0)
+                    a.lse[(static_cast<size_t>(b) * a.H + h) * a.S + i] = (m_run + log2f(l_tot) - slope2 * static_cast<float>(i)) * kLn2F;
             }
             kv0 += cnt;
         }

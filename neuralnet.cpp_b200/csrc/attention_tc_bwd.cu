@@ -12,6 +12,9 @@
 // MN-major (second MMAs) from the same shared-memory tile.  Recomputing S in both kernels keeps the
 // gradients deterministic (the reference's backward_q / backward_kv split, cpu_engine.hpp:702-915).
 // K-major operands wider than 64 values are kept as sub-tiles of 64 columns (one 128-byte swizzle atom per row).
+// ALiBi: the bias -slope_h (i - j) is linear in both positions, so the tensor core adds its in-block part: one more
+// MMA step per score block multiplies a 16-deep tile holding slope_h / scale (three bf16 terms) in every row by a
+// constant tile holding the position inside the block of the other side; the workers add one constant per row.
 // With a table of per-64-row document-id ranges (attention_doc_ranges) every role skips the blocks a document mask
 // leaves nothing of; a skipped block would have contributed exact zeros, so no result bit changes.
 #include <type_traits>
@@ -26,6 +29,7 @@ __device__ int g_attn_bwd_error = 0;
 
 constexpr int BT = 128 * 128;          // bytes of a 128-row x 64-bf16 tile
 constexpr int HT = 64 * 128;           // bytes of a 64-row tile
+constexpr int XT = 128 * 32;           // bytes of a 128-row x 16-bf16 tile without swizzle (the ALiBi operand tiles)
 constexpr float kL2e = 1.4426950408889634f;
 
 struct AttnBwdArgs {
@@ -51,6 +55,36 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 constexpr uint32_t IDESC_KK = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(64 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
 template <int DK> __host__ __device__ constexpr uint32_t idesc_km() { return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (uint32_t(DK >> 3) << 17) | (uint32_t(128 >> 4) << 24); }
 
+// Unswizzled K-major tiles, 16 values deep: row r, values [8c, 8c + 8) at (r / 8) * 256 + c * 128 + (r % 8) * 16.
+// slope_h / scale as three bf16 terms (24 bits) in values 0..2 of every one of the 128 rows; called by a whole warp.
+__device__ __forceinline__ void write_slope_tile(uint8_t* tile, int h, int H, float scale, int lane)
+{
+    const float sv = exp2f(-8.0f * static_cast<float>(h) / static_cast<float>(H)) / scale;
+    const bf16 s0 = __float2bfloat16_rn(sv);
+    const float r1 = sv - __bfloat162float(s0);
+    const bf16 s1 = __float2bfloat16_rn(r1);
+    const bf16 s2 = __float2bfloat16_rn(r1 - __bfloat162float(s1));
+    const uint32_t w0 = static_cast<uint32_t>(__bfloat16_as_ushort(s0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(s1)) << 16);
+    const uint32_t w1 = static_cast<uint32_t>(__bfloat16_as_ushort(s2));
+    for (int r = lane; r < 128; r += 32) *reinterpret_cast<uint4*>(tile + (r >> 3) * 256 + (r & 7) * 16) = make_uint4(w0, w1, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+}
+// value `sign * r` three times in row r (r < rows), zeros elsewhere; called by the whole block before its first barrier
+__device__ __forceinline__ void init_position_tiles(uint8_t* pos_tile, uint8_t* slope_tile, int rows, float sign)
+{
+    for (int r = threadIdx.x; r < 128; r += blockDim.x) {
+        const uint32_t off = (r >> 3) * 256 + (r & 7) * 16;
+        const __nv_bfloat162 jj = __floats2bfloat162_rn(sign * static_cast<float>(r), sign * static_cast<float>(r));
+        const uint32_t j2 = r < rows ? *reinterpret_cast<const uint32_t*>(&jj) : 0u;
+        *reinterpret_cast<uint4*>(pos_tile + off) = make_uint4(j2, j2 & 0xffffu, 0u, 0u);
+        *reinterpret_cast<uint4*>(pos_tile + off + 128) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(slope_tile + off) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(slope_tile + off + 128) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // Both kernels are persistent: the CTAs resident on an SM walk a list of (tile, head, batch) work items, heaviest
 // tiles first, in snake order.  The rings, score buffers and barrier phases run on across tiles, so the loads and
 // first MMAs of the next tile overlap the tail and the write-out of the current one.  Every resource is
@@ -75,8 +109,8 @@ __device__ __forceinline__ BwdTile bwd_tile(int w, int H, int HB)
 template <int DK> struct DqLayout {
     static constexpr int NS = DK / 64;                              // 64-column sub-tiles per operand tile
     static constexpr int ST = 2;                                    // (K, V) ring stages
-    static constexpr int OFF_DO = NS * BT, OFF_RING = 2 * NS * BT, OFF_DS = OFF_RING + ST * 2 * NS * HT, OFF_BAR = OFF_DS + BT,
-                         SMEM = OFF_BAR + 256;
+    static constexpr int OFF_DO = NS * BT, OFF_RING = 2 * NS * BT, OFF_DS = OFF_RING + ST * 2 * NS * HT, OFF_U = OFF_DS + BT,
+                         OFF_W = OFF_U + XT, OFF_BAR = OFF_W + XT, SMEM = OFF_BAR + 256;
     static constexpr uint32_t TMEM_COLS = 256u;                     // S [0, 64) | dP [64, 128) | dQ [128, 128 + DK)
     static constexpr int CTAS_PER_SM = DK == 64 ? 2 : 1;
 };
@@ -124,6 +158,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 64, tmem_dQ = tmem_base + 128;
+    uint8_t* sU = smem + LY::OFF_U;                 // slope_h / scale in every query row (rewritten per tile by warp 0)
+    uint8_t* sW = smem + LY::OFF_W;                 // key position inside the 64-key block, constant
+    if (ALIBI) {
+        init_position_tiles(sW, sU, 64, 1.0f);
+        __syncthreads();
+    }
 
     // key blocks (64 keys each) of a query tile that the document mask leaves anything of; whole-warp call
     auto tile_mask = [&](int b, int qb, int nkb) -> BlockMask {
@@ -139,8 +179,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
             const BwdTile t = bwd_tile(w, a.H, HB);
             const int qb = nt - 1 - t.t, q0 = qb * 128, nkb = 2 * (qb + 1), row_base = t.b * a.S;
             const BlockMask bm = tile_mask(t.b, qb, nkb);
+            if (lane == 0) ok = mbar_wait(q_empty, (tn & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error);   // the previous tile's MMAs are done
+            ok = __shfl_sync(0xffffffffu, static_cast<int>(ok), 0) != 0;
+            if (ALIBI && ok) write_slope_tile(sU, t.h, a.H, a.scale, lane);
             if (lane == 0) {
-                ok = mbar_wait(q_empty, (tn & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error);
                 if (ok) {
                     mbar_expect_tx(q_full, 2 * NS * BT);
 #pragma unroll
@@ -189,6 +231,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
                     for (int k = 0; k < DK / 16; ++k)
                         umma_bf16(tmem_S, smem_desc(q_addr + (k >> 2) * BT + (k & 3) * 32, 16, 1024),
                                   smem_desc(k_addr + (k >> 2) * HT + (k & 3) * 32, 16, 1024), IDESC_KK, k > 0);
+                    if (ALIBI)       // + (slope / scale) * (key position inside the block)
+                        umma_bf16(tmem_S, smem_desc_noswizzle(smem_u32(sU), 128, 256), smem_desc_noswizzle(smem_u32(sW), 128, 256), IDESC_KK, 1u);
 #pragma unroll
                     for (int k = 0; k < DK / 16; ++k)
                         umma_bf16(tmem_dP, smem_desc(do_addr + (k >> 2) * BT + (k & 3) * 32, 16, 1024),
@@ -253,21 +297,22 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sp_empty);
                 const int* dk_ptr = DOC ? a.doc + row_base + k0 : nullptr;
-                const float base = (ALIBI ? -slope2 * static_cast<float>(i - k0) : 0.f) - lse2;
+                // base-2 exponent of P: raw * scale2 + cc, the in-block part of the ALiBi bias being in raw already
+                const float cc = (ALIBI ? -slope2 * static_cast<float>(i - kb * 64) : 0.f) - lse2;
+                const uint64_t cc2 = pack2(cc, cc), scale2x2 = pack2(scale2, scale2), negD2 = pack2(-Dv, -Dv);
                 uint32_t pk[16];
 #pragma unroll
                 for (int cj = 0; cj < 32; cj += 2) {
-                    float dsv[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int c = cj + e;
-                        const float tt = ALIBI ? fmaf(slope2, static_cast<float>(c), base) : base;
-                        float p = ex2a(fmaf(__uint_as_float(rs[c]), scale2, tt));
-                        if (DIAG && k0 + c > i) p = 0.f;
-                        if (DOC && dk_ptr[c] != my_doc) p = 0.f;
-                        dsv[e] = p * (__uint_as_float(rp[c]) - Dv);
-                    }
-                    __nv_bfloat162 t2 = __floats2bfloat162_rn(dsv[0], dsv[1]);
+                    float x0, x1;
+                    unpack2(fma2(pack2(__uint_as_float(rs[cj]), __uint_as_float(rs[cj + 1])), scale2x2, cc2), x0, x1);
+                    float p0 = ex2a(x0), p1 = ex2a(x1);
+                    if (DIAG && k0 + cj > i) p0 = 0.f;
+                    if (DIAG && k0 + cj + 1 > i) p1 = 0.f;
+                    if (DOC && dk_ptr[cj] != my_doc) p0 = 0.f;
+                    if (DOC && dk_ptr[cj + 1] != my_doc) p1 = 0.f;
+                    float d0, d1;
+                    unpack2(mul2(pack2(p0, p1), add2(pack2(__uint_as_float(rp[cj]), __uint_as_float(rp[cj + 1])), negD2)), d0, d1);
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(d0, d1);
                     pk[cj >> 1] = *reinterpret_cast<uint32_t*>(&t2);
                 }
                 if (gj >= 1 && !mbar_wait(ds_empty, (gj - 1) & 1, abort_flag, 7, &g_attn_bwd_error)) return false;
@@ -327,7 +372,8 @@ template <int DK> struct KvLayout {
     static constexpr int NS = DK / 64;
     static constexpr int ST = 2;                                    // (Q, dO) ring stages
     static constexpr int OFF_V = NS * BT, OFF_RING = 2 * NS * BT, OFF_PT = OFF_RING + ST * 2 * NS * HT, OFF_DST = OFF_PT + BT,
-                         OFF_STAT = OFF_DST + BT, OFF_BAR = OFF_STAT + ST * 512, SMEM = OFF_BAR + 256;
+                         OFF_STAT = OFF_DST + BT, OFF_U = OFF_STAT + ST * 512, OFF_W = OFF_U + XT, OFF_BAR = OFF_W + XT,
+                         SMEM = OFF_BAR + 256;
     static constexpr uint32_t TMEM_COLS = DK == 64 ? 256u : 512u;   // S^T [0, 64) | dP^T [64, 128) | dV [128, 128 + DK) | dK after it
     static constexpr int CTAS_PER_SM = DK == 64 ? 2 : 1;
 };
@@ -377,6 +423,12 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_ST = tmem_base, tmem_dPT = tmem_base + 64, tmem_dV = tmem_base + 128, tmem_dK = tmem_base + 128 + DK;
+    uint8_t* sU = smem + LY::OFF_U;                 // slope_h / scale in every key row (rewritten per tile by warp 0)
+    uint8_t* sW = smem + LY::OFF_W;                 // minus the query position inside the 64-query block, constant
+    if (ALIBI) {
+        init_position_tiles(sW, sU, 64, -1.0f);
+        __syncthreads();
+    }
 
     // query blocks (64 queries each, from the diagonal on) of a key tile that the document mask leaves anything of
     auto tile_mask = [&](int b, int kt, int nit) -> BlockMask {
@@ -392,9 +444,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
             const BwdTile t = bwd_tile(w, a.H, HB);
             const int kt = t.t, k0 = kt * 128, qi0 = kt * 2, nit = a.S / 64 - qi0, row_base = t.b * a.S;
             const BlockMask bm = tile_mask(t.b, kt, nit);
+            if (lane == 0) ok = mbar_wait(kv_empty, (tn & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error);   // the previous tile's MMAs are done
+            ok = __shfl_sync(0xffffffffu, static_cast<int>(ok), 0) != 0;
+            if (ALIBI && ok) write_slope_tile(sU, t.h, a.H, a.scale, lane);
             if (lane == 0) {
                 const size_t stat_base = (static_cast<size_t>(t.b) * a.H + t.h) * a.S;
-                ok = mbar_wait(kv_empty, (tn & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error);
                 if (ok) {
                     mbar_expect_tx(kv_full, 2 * NS * BT);
 #pragma unroll
@@ -444,6 +498,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                     for (int k = 0; k < DK / 16; ++k)
                         umma_bf16(tmem_ST, smem_desc(k_addr + (k >> 2) * BT + (k & 3) * 32, 16, 1024),
                                   smem_desc(q_addr + (k >> 2) * HT + (k & 3) * 32, 16, 1024), IDESC_KK, k > 0);
+                    if (ALIBI)       // - (slope / scale) * (query position inside the block)
+                        umma_bf16(tmem_ST, smem_desc_noswizzle(smem_u32(sU), 128, 256), smem_desc_noswizzle(smem_u32(sW), 128, 256), IDESC_KK, 1u);
 #pragma unroll
                     for (int k = 0; k < DK / 16; ++k)
                         umma_bf16(tmem_dPT, smem_desc(v_addr + (k >> 2) * BT + (k & 3) * 32, 16, 1024),
@@ -512,27 +568,32 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                 const float4* lse4 = reinterpret_cast<const float4*>(sStat + st * 128 + hf * 32);
                 const float4* dv4 = reinterpret_cast<const float4*>(sStat + st * 128 + 64 + hf * 32);
                 const int* dq_ptr = DOC ? a.doc + row_base + qs : nullptr;
-                const float base = ALIBI ? -slope2 * static_cast<float>(qs - j) : 0.f;
+                // base-2 exponent of P^T: raw * scale2 + base - lse2 of the column's query; the -slope2 * (query position
+                // inside the block) part of the ALiBi bias is in raw already
+                const float base = ALIBI ? -slope2 * static_cast<float>((qi0 + it) * 64 - j) : 0.f;
+                const uint64_t base2 = pack2(base, base), scale2x2 = pack2(scale2, scale2), negl2e = pack2(-kL2e, -kL2e),
+                               neg1 = pack2(-1.f, -1.f);
                 uint32_t pk[16], dk[16];
 #pragma unroll
                 for (int c4 = 0; c4 < 8; ++c4) {
                     const float4 l4 = lse4[c4], d4 = dv4[c4];
-                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
-                    float pv[4], dsv[4];
+                    const uint64_t lsp[2] = {pack2(l4.x, l4.y), pack2(l4.z, l4.w)}, ddp[2] = {pack2(d4.x, d4.y), pack2(d4.z, d4.w)};
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int c = c4 * 4 + e;
-                        const float tt = (ALIBI ? fmaf(-slope2, static_cast<float>(c), base) : 0.f) - ls[e] * kL2e;
-                        float p = ex2a(fmaf(__uint_as_float(rs[c]), scale2, tt));
-                        if (DIAG && j > qs + c) p = 0.f;
-                        if (DOC && dq_ptr[c] != my_doc) p = 0.f;
-                        pv[e] = p;
-                        dsv[e] = p * (__uint_as_float(rp[c]) - dd[e]);
+                    for (int e2 = 0; e2 < 2; ++e2) {
+                        const int c = c4 * 4 + e2 * 2;
+                        float x0, x1;
+                        unpack2(fma2(lsp[e2], negl2e, fma2(pack2(__uint_as_float(rs[c]), __uint_as_float(rs[c + 1])), scale2x2, base2)), x0, x1);
+                        float p0 = ex2a(x0), p1 = ex2a(x1);
+                        if (DIAG && j > qs + c) p0 = 0.f;
+                        if (DIAG && j > qs + c + 1) p1 = 0.f;
+                        if (DOC && dq_ptr[c] != my_doc) p0 = 0.f;
+                        if (DOC && dq_ptr[c + 1] != my_doc) p1 = 0.f;
+                        float d0, d1;
+                        unpack2(mul2(pack2(p0, p1), fma2(ddp[e2], neg1, pack2(__uint_as_float(rp[c]), __uint_as_float(rp[c + 1])))), d0, d1);
+                        __nv_bfloat162 tp = __floats2bfloat162_rn(p0, p1), td = __floats2bfloat162_rn(d0, d1);
+                        pk[c4 * 2 + e2] = *reinterpret_cast<uint32_t*>(&tp);
+                        dk[c4 * 2 + e2] = *reinterpret_cast<uint32_t*>(&td);
                     }
-                    __nv_bfloat162 t0 = __floats2bfloat162_rn(pv[0], pv[1]), t1 = __floats2bfloat162_rn(pv[2], pv[3]);
-                    __nv_bfloat162 u0 = __floats2bfloat162_rn(dsv[0], dsv[1]), u1 = __floats2bfloat162_rn(dsv[2], dsv[3]);
-                    pk[c4 * 2] = *reinterpret_cast<uint32_t*>(&t0); pk[c4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&t1);
-                    dk[c4 * 2] = *reinterpret_cast<uint32_t*>(&u0); dk[c4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&u1);
                 }
                 if (gi >= 1 && !mbar_wait(pd_empty, (gi - 1) & 1, abort_flag, 7, &g_attn_bwd_error)) return false;
                 uint8_t* prow = sPT + row * 128;

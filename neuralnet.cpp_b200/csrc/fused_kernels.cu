@@ -689,13 +689,18 @@ __global__ void ce_count_kernel(const int* __restrict__ labels, const float* __r
     if (threadIdx.x == 0) { stats[0] = c; stats[1] = c > 0.f ? 1.0f / c : 0.f; }
 }
 
-template <typename T, int NV>   // NV 16-byte vectors cached per thread (0 = re-read from memory)
-__global__ void __launch_bounds__(512)
+// NV 16-byte vectors of the row cached per thread (0 = re-read from memory).  Up to 4 vectors the exponentials are
+// kept in registers too (computed once, used for the sum and the gradient); beyond that they are recomputed in the
+// last pass, so that a block stays at 64 registers per thread and two blocks share an SM: with one block per SM the
+// load, reduce and store phases of a 64 KB row do not overlap with anything.
+template <typename T, int NV>
+__global__ void __launch_bounds__(512, NV > 4 ? 2 : 0)
 ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const float* __restrict__ mask,
                   const float* __restrict__ stats, float grad_scale, float* __restrict__ loss_vec, int rows, int V,
                   int vocab)
 {
     constexpr int VN = Vec16<T>::N;
+    constexpr bool KEEP_EX = NV > 0 && NV <= 4;
     __shared__ float red[32];
     const int r = blockIdx.x;
     T* row = logits + static_cast<size_t>(r) * V;
@@ -723,14 +728,18 @@ ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const 
     } else for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, to_f32(row[i]));
     mx = block_max(mx, red);
     float den = 0.f;
-    float ex[NV > 0 ? NV : 1][VN];                    // exp(x - max) of the cached row: computed once, used for the sum and the gradient
+    float ex[KEEP_EX ? NV : 1][VN];
     if (NV > 0) {
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
             if (i < nvec) {
 #pragma unroll
-                for (int k = 0; k < VN; ++k) { ex[j][k] = exp_t<T>(to_f32(cache[j].v[k]) - mx); den += ex[j][k]; } }
+                for (int k = 0; k < VN; ++k) {
+                    const float e = exp_t<T>(to_f32(cache[j].v[k]) - mx);
+                    if (KEEP_EX) ex[j][k] = e;
+                    den += e;
+                } }
         }
     } else for (int i = threadIdx.x; i < V; i += blockDim.x) den += exp_t<T>(to_f32(row[i]) - mx);
     den = block_sum(den, red);
@@ -745,7 +754,7 @@ ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const 
             if (i < nvec) { Vec16<T> o;
 #pragma unroll
                 for (int k = 0; k < VN; ++k) {
-                    float gv = ex[j][k] * inv_den;
+                    float gv = (KEEP_EX ? ex[j][k] : exp_t<T>(to_f32(cache[j].v[k]) - mx)) * inv_den;
                     if (i * VN + k == lbl) gv -= inv;
                     o.v[k] = from_f32<T>(gv);
                 }

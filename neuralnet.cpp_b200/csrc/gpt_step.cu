@@ -63,6 +63,14 @@ static ArenaLayout make_layout(const nnb200_gpt_config& c)
     return L;
 }
 
+DecodeLayout decode_layout(const nnb200_gpt_config& c)
+{
+    const ArenaLayout L = make_layout(c);
+    DecodeLayout D{L.tok_emb, L.pos_emb, L.lnf_g, L.lnf_b, L.lm_w, L.lm_b, {}};
+    for (const auto& lp : L.layers) D.layers.push_back(DecodeLayer{lp.wqkv, lp.bqkv, lp.wo, lp.bo, lp.g1, lp.be1, lp.w1, lp.b1, lp.w2, lp.b2, lp.g2, lp.be2});
+    return D;
+}
+
 // ---------------------------------------------------------------- workspace
 struct LayerActs { size_t x_in, xn1, qkv, attn, x_mid, xn2, h1, h2; size_t rinv1, mean1, rinv2, mean2, lse; };
 struct Workspace {

@@ -1,8 +1,17 @@
 // Internal C++ interface between the translation units of the library (not part of the C ABI).
 #pragma once
+#include <vector>
+
 #include "common.cuh"
 
+struct nnb200_gpt_config;      // include/nnb200.h
+
 namespace nnb {
+
+// ---- gpt_step.cu : where a layer's tensors lie in the parameter arena (elements; -1 = absent), for decode.cu
+struct DecodeLayer { long long wqkv, bqkv, wo, bo, g1, be1, w1, b1, w2, b2, g2, be2; };
+struct DecodeLayout { long long tok_emb, pos_emb, lnf_g, lnf_b, lm_w, lm_b; std::vector<DecodeLayer> layers; };
+DecodeLayout decode_layout(const ::nnb200_gpt_config& c);
 
 // ---- gemm_simt.cu : fp32, arbitrary strides, optional batch
 int sgemm_strided(const float* A, const float* B, float* C, int M, int N, int K, long long sam, long long sak,

@@ -191,7 +191,42 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
     return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
            (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
+// The same for a tile without swizzle (the "interleaved" canonical layout), K-major: 8-row x 16-byte core matrices
+// stored as 128 contiguous bytes; element (r, k) of a bf16 tile lies at (r / 8) * sbo + (k / 8) * lbo + (r % 8) * 16 +
+// (k % 8) * 2.  Used for operands that are only 16 values deep (one MMA K step), where a 128-byte swizzled row would
+// waste seven eighths of the tile.
+__device__ __forceinline__ uint64_t smem_desc_noswizzle(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+           (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46);
+}
 
+// ---- packed fp32 pairs: one instruction works on two floats held in a 64-bit register
+__device__ __forceinline__ uint64_t pack2(float a, float b)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
 
 // host: cached 2-D tensor map with 128-byte swizzle (esz 2 = bf16, 4 = fp32); defined in gemm_tcgen05.cu
 int tensor_map_2d(const void* ptr, long long inner, long long outer, long long ld, int box_inner, int box_outer,

@@ -14,7 +14,10 @@
 //       (0 AdamW; 1 Muon on the hidden matrices + AdamW on the rest), 14 clip on, 15 cosine schedule, 16 warm-up steps,
 //       17 total steps, 18 dump the gradients of step 0, 19 dump the logits of micro-batch 0, 20 skip the final parameters.
 //       F: 0 lr, 1 weight decay, 2 clip norm, 3 minimum lr, 4 Muon lr.
-//       Output: f32 loss per micro-batch; [gradients]; [logits (vocab, tokens)]; [final parameters]; f64 seconds per step.
+//       21 > 0: after training, GPTModel-style forward_step over the first I[21] tokens of a list that follows the
+//       batches (i32 count, i32 ids[count]); 22 > 0: generate I[22] tokens from that list as the prompt, temperature 0.
+//       Output: f32 loss per micro-batch; [gradients]; [logits (vocab, tokens)]; [final parameters]; f64 seconds per step;
+//       [f32 logits of every decode step (vocab each)]; [i32 count, i32 generated ids].
 //   fused_train bench [--steps K] [--warmup W] [--layers L] [--batch B]
 //       BASELINE configuration 3 (vocab 8192, d 768, 12 heads, 12 layers, SwiGLU 2048, RMSNorm, ALiBi, seq 1024,
 //       micro-batch 16 x accumulation 2, AdamW + cosine schedule, bf16) on synthetic Zipf(1.1) tokens: prints one JSON
@@ -183,6 +186,29 @@ int run_file(int argc, char** argv)
     if (!skip_params)
         for (auto& p : params) { auto m = engine.to_matrix(p.get()); TRY(m); wr_matrix(out, *m); }
     out.write(reinterpret_cast<const char*>(secs.data()), static_cast<std::streamsize>(secs.size() * sizeof(double)));
+    if (I[21] > 0 || I[22] > 0)
+    {   // incremental inference: a token list follows the batches; I[21] forward_step logits and / or I[22] generated ids (temperature 0)
+        std::int32_t count = 0;
+        if (!rd(in, &count, 1) || count <= 0) { std::cerr << "fused_train: decode token list missing\n"; return 1; }
+        std::vector<std::int32_t> ids(static_cast<std::size_t>(count));
+        if (!rd(in, ids.data(), ids.size())) { std::cerr << "fused_train: short decode token list\n"; return 1; }
+        for (int t = 0; t < I[21] && t < count; ++t)
+        {
+            auto lg = gpt.forward_step(engine, static_cast<std::size_t>(ids[t]), static_cast<std::size_t>(t), static_cast<std::size_t>(t));
+            TRY(lg);
+            auto m = engine.to_matrix(*lg); TRY(m);
+            wr_matrix(out, *m);
+        }
+        if (I[22] > 0)
+        {
+            std::vector<std::size_t> prompt(ids.begin(), ids.end());
+            auto gen = gpt.generate(engine, prompt, static_cast<std::size_t>(I[22]), Scalar{0});
+            TRY(gen);
+            const std::int32_t n = static_cast<std::int32_t>(gen->size());
+            out.write(reinterpret_cast<const char*>(&n), sizeof(n));
+            for (auto id : *gen) { const std::int32_t v = static_cast<std::int32_t>(id); out.write(reinterpret_cast<const char*>(&v), sizeof(v)); }
+        }
+    }
     if (!save_path.empty())
         TRY(save_model(save_path, model, make_gpt_spec(V, D, S, H, FF, L, pos, act, norm)));
     std::cerr << "fused_train: precision=" << precision << " steps=" << steps << " last_loss=" << (losses.empty() ? 0.f : losses.back()) << "\n";

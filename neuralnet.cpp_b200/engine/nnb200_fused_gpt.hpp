@@ -79,7 +79,7 @@ class B200GPTModel final : public Layer
     nnb200_gpt_config cfg_{};
     std::size_t tokens_ = 0;
     Result<void> init_ = {};
-    b200_detail::Arena params_, grads_, shadow_, workspace_, ids_, scal_, sumsq_;
+    b200_detail::Arena params_, grads_, shadow_, workspace_, ids_, scal_, sumsq_, decode_ws_;
     std::vector<Tensor> param_views_, grad_views_;
     std::vector<long long> offsets_;
     long long arena_elems_ = 0, matrix_begin_ = 0;
@@ -352,6 +352,102 @@ public:
         float v = 0.f;
         if (auto r = b200_detail::ok(nnb200_rt_download(&v, scal_.f32() + 1, 4), "download norm"); !r) return std::unexpected(r.error());
         return static_cast<Scalar>(v);
+    }
+
+    // ── inference with a key/value cache ────────────────────────────────────────────────────────
+    // GPTModel::forward_step (compute_layer.hpp:2906-2950) without its cache arguments: the cache of every layer lives
+    // in the model's own decode workspace (allocated at the first call).  Returns the (vocab, 1) logits.
+    [[nodiscard]] Result<Tensor> forward_step(ComputeEngine& engine, std::size_t token_id, std::size_t pos, std::size_t cur_len)
+    {
+        if (!init_) return std::unexpected(init_.error());
+        if (!decode_ws_.ptr())
+        {
+            const long long n = nnb200_gpt_decode_workspace_bytes(&cfg_);
+            if (n <= 0) return b200_detail::fail("B200GPTModel::forward_step: workspace size query failed");
+            if (auto r = decode_ws_.allocate((static_cast<std::size_t>(n) + 3) / 4); !r) return std::unexpected(r.error());
+            if (auto r = b200_detail::ok(nnb200_gpt_decode_init(&cfg_, decode_ws_.ptr(), stream()), "nnb200_gpt_decode_init"); !r)
+                return std::unexpected(r.error());
+        }
+        if (cfg_.precision == 1 && (shadow_stale_ || !shadow_managed_))
+        {
+            if (auto r = b200_detail::ok(nnb200_f32_to_bf16(params_.f32(), shadow_.ptr(), static_cast<std::size_t>(arena_elems_), stream()),
+                                         "nnb200_f32_to_bf16"); !r) return std::unexpected(r.error());
+            shadow_stale_ = false;
+        }
+        Tensor out = engine.create_tensor(static_cast<std::size_t>(cfg_.vocab), 1);
+        if (!out.valid()) return b200_detail::fail("B200GPTModel::forward_step: allocation failed");
+        if (auto r = b200_detail::ok(nnb200_gpt_forward_step(&cfg_, params_.f32(), shadow_.ptr(), decode_ws_.ptr(), static_cast<int>(token_id),
+                                                             static_cast<int>(pos), static_cast<int>(cur_len), out.cuda_tensor().data(), stream()),
+                                     "nnb200_gpt_forward_step"); !r) return std::unexpected(r.error());
+        return out;
+    }
+
+    // GPTModel::generate (compute_layer.hpp:2952-3096), same arguments: prompt into the cache (its last seq tokens), then
+    // per new token softmax-sampling of the last logits on the host at `temperature` (0 = arg max), stop at eos_token_id
+    // once min_new_tokens were produced, and a rebuild of the cache from the last seq-1 tokens when it is full.
+    [[nodiscard]] Result<std::vector<std::size_t>> generate(ComputeEngine& engine, const std::vector<std::size_t>& prompt,
+                                                            std::size_t max_new_tokens, Scalar temperature = 1.0,
+                                                            std::size_t eos_token_id = static_cast<std::size_t>(-1),
+                                                            std::size_t min_new_tokens = 0)
+    {
+        const auto seq = static_cast<std::size_t>(cfg_.seq), vocab = static_cast<std::size_t>(cfg_.vocab);
+        std::vector<std::size_t> context(prompt), generated;
+        std::mt19937_64 rng{std::random_device{}()};
+        std::uniform_real_distribution<Scalar> dist(0.0, 1.0);
+        std::size_t cur_len = 0;
+        Tensor last;
+        auto fill = [&](std::size_t start) -> Result<void> {
+            for (std::size_t i = start; i < context.size(); ++i)
+            {
+                auto r = forward_step(engine, context[i], cur_len, cur_len);
+                if (!r) return std::unexpected(r.error());
+                last = std::move(*r);
+                ++cur_len;
+            }
+            return {};
+        };
+        if (auto r = fill(context.size() > seq ? context.size() - seq : 0); !r) return std::unexpected(r.error());
+        for (std::size_t step = 0; step < max_new_tokens; ++step)
+        {
+            if (cur_len >= seq)
+            {
+                cur_len = 0;
+                const std::size_t keep = seq - 1;
+                if (auto r = fill(context.size() > keep ? context.size() - keep : 0); !r) return std::unexpected(r.error());
+            }
+            if (!last.valid()) return b200_detail::fail("B200GPTModel::generate: empty prompt");
+            auto lm = engine.to_matrix(last);
+            if (!lm) return std::unexpected(lm.error());
+            std::vector<Scalar> p(vocab);
+            for (std::size_t v = 0; v < vocab; ++v) p[v] = lm->at_unchecked(v, 0);
+            if (temperature > 0.0 && temperature != 1.0) for (auto& v : p) v /= temperature;
+            Scalar mx = p[0];
+            for (std::size_t v = 1; v < vocab; ++v) mx = std::max(mx, p[v]);
+            Scalar sum = 0;
+            for (auto& v : p) { v = std::exp(v - mx); sum += v; }
+            for (auto& v : p) v /= sum;
+            std::size_t next = 0;
+            if (temperature > 0.0)
+            {
+                const Scalar r = dist(rng);
+                Scalar cum = 0;
+                next = vocab - 1;
+                for (std::size_t v = 0; v < vocab; ++v) { cum += p[v]; if (r <= cum) { next = v; break; } }
+            }
+            else
+            {
+                Scalar best = p[0];
+                for (std::size_t v = 1; v < vocab; ++v) if (p[v] > best) { best = p[v]; next = v; }
+            }
+            context.push_back(next);
+            if (step >= min_new_tokens && next == eos_token_id) break;
+            generated.push_back(next);
+            auto r = forward_step(engine, next, cur_len, cur_len);
+            if (!r) return std::unexpected(r.error());
+            last = std::move(*r);
+            ++cur_len;
+        }
+        return generated;
     }
 
     // Status word of the device-side bounded waits (tcgen05 GEMM and attention kernels): an error if one ever gave up.

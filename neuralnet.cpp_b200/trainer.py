@@ -290,6 +290,68 @@ class GptTrainer:
             valid += n
         return weighted / valid if valid > 0 else 0.0
 
+    # -------------------------------------------------------------- inference with a key/value cache
+    def _decode_state(self):
+        if getattr(self, "_decode_ws", None) is None:
+            n = int(call("nnb200_gpt_decode_workspace_bytes", C.byref(self._c)))
+            self._decode_ws = torch.empty(n, dtype=torch.uint8, device=self.device)
+            call("nnb200_gpt_decode_init", C.byref(self._c), _ptr(self._decode_ws), _stream())
+            self._decode_logits = torch.empty(self.cfg.vocab, dtype=torch.float32, device=self.device)
+        return self._decode_ws, self._decode_logits
+
+    def forward_step(self, token_id: int, pos: int, cur_len: int) -> torch.Tensor:
+        """One token through the model with the key/value cache (GPTModel::forward_step, compute_layer.hpp:2906-2950):
+        writes the token's keys and values at cache row cur_len, attends over rows [0, cur_len] and returns the
+        (vocab,) fp32 logits (a device tensor that the next call overwrites)."""
+        ws, logits = self._decode_state()
+        call("nnb200_gpt_forward_step", C.byref(self._c), _ptr(self.params), _ptr(self.shadow), _ptr(ws), int(token_id), int(pos),
+             int(cur_len), _ptr(logits), _stream())
+        return logits
+
+    def generate(self, prompt: Sequence[int], max_new_tokens: int, temperature: float = 1.0, eos_token_id: int = -1,
+                 min_new_tokens: int = 0, rng: Optional[np.random.Generator] = None) -> List[int]:
+        """GPTModel::generate (compute_layer.hpp:2952-3096): fills the cache with the prompt (its last seq tokens), then per
+        new token softmax-samples the last logits at `temperature` (0 = arg max, first maximum wins), stops at
+        eos_token_id once min_new_tokens were produced, and when the cache is full rebuilds it from the last seq-1
+        tokens of the context.  Sampling is on the host, as in the reference; `rng` makes it repeatable."""
+        rng = rng or np.random.default_rng()
+        seq = self.cfg.seq
+        context, generated = list(int(t) for t in prompt), []
+        cur_len, last = 0, None
+
+        def fill(start):
+            nonlocal cur_len, last
+            for t in context[start:]:
+                last = self.forward_step(t, cur_len, cur_len)
+                cur_len += 1
+        fill(max(0, len(context) - seq))
+        for step in range(max_new_tokens):
+            if cur_len >= seq:                       # sliding window: keep the last seq-1 tokens
+                cur_len = 0
+                fill(max(0, len(context) - (seq - 1)))
+            if last is None:
+                raise ValueError("generate needs a non-empty prompt")
+            logits = last.detach().cpu().numpy().astype(np.float32)
+            if temperature > 0.0 and temperature != 1.0:
+                logits = logits / np.float32(temperature)
+            p = np.exp(logits - logits.max())
+            p /= p.sum(dtype=np.float32)
+            if temperature > 0.0:
+                r, nxt = np.float32(rng.random()), self.cfg.vocab - 1
+                c = np.cumsum(p, dtype=np.float32)
+                hit = np.nonzero(r <= c)[0]
+                if hit.size:
+                    nxt = int(hit[0])
+            else:
+                nxt = int(np.argmax(p))
+            context.append(nxt)
+            if step >= min_new_tokens and nxt == eos_token_id:
+                break
+            generated.append(nxt)
+            last = self.forward_step(nxt, cur_len, cur_len)
+            cur_len += 1
+        return generated
+
     def loss_tensor(self) -> torch.Tensor:
         """Device view of the scalar loss of the last loss_and_grad call."""
         o = self._off["loss"]
@@ -389,3 +451,106 @@ class GptTrainer:
         call("nnb200_gemm_status", C.byref(code))
         if code.value:
             raise _lib.NnbError(f"tcgen05 GEMM reported a timed-out wait (code {code.value >> 16}, block {code.value & 0xffff})")
+
+
+class AsyncInputPipeline:
+    """Keeps the host side of the training loop off the critical path.
+
+    The reference loop uploads the ids, labels and loss mask of a micro-batch right before it needs them and downloads
+    the scalar loss right after (CrossEntropyLoss::forward_sparse, compute_loss.hpp:259-307; src/text_train.cpp:1137-1181),
+    stalling the device twice per micro-batch.  Here every micro-batch is staged in pinned host memory, copied to the
+    device on a copy stream while the previous micro-batch computes, and its loss is copied back without blocking: the
+    value is read `depth - 1` submissions later, when its copy has long finished.
+
+        pipe = AsyncInputPipeline(trainer)
+        for tokens, labels in data:
+            pipe.submit(tokens, labels)                  # host arrays; returns at once
+            ...
+            pipe.run(grad_scale=1/accum, last=...)       # forward + loss + backward of the oldest staged micro-batch
+        losses = pipe.drain()                            # every loss, in submission order
+    """
+
+    def __init__(self, trainer: GptTrainer, depth: int = 3):
+        if depth < 2:
+            raise ValueError("depth must be at least 2 (one micro-batch computing, one being staged)")
+        self.tr = trainer
+        n = trainer.cfg.batch * trainer.cfg.seq
+        dev = trainer.device
+        self.depth = depth
+        pin = lambda dt: torch.empty(n, dtype=dt).pin_memory()
+        self.h_tok = [pin(torch.int32) for _ in range(depth)]
+        self.h_lab = [pin(torch.int32) for _ in range(depth)]
+        self.h_msk = [pin(torch.float32) for _ in range(depth)]
+        self.h_doc = [pin(torch.int32) for _ in range(depth)]
+        mk = lambda dt: torch.empty(n, dtype=dt, device=dev)
+        self.d_tok = [mk(torch.int32) for _ in range(depth)]
+        self.d_lab = [mk(torch.int32) for _ in range(depth)]
+        self.d_msk = [mk(torch.float32) for _ in range(depth)]
+        self.d_doc = [mk(torch.int32) for _ in range(depth)]
+        self.flags = [(False, False)] * depth                   # (has mask, has document ids) per slot
+        self.copy_stream = torch.cuda.Stream(device=dev)
+        self.staged = [torch.cuda.Event() for _ in range(depth)]     # H2D of the slot finished
+        self.consumed = [torch.cuda.Event() for _ in range(depth)]   # the step that read the slot finished
+        self.loss_host = torch.zeros(depth, dtype=torch.float32).pin_memory()
+        self.loss_ready = [torch.cuda.Event() for _ in range(depth)]
+        self.n_sub = self.n_run = self.n_read = 0
+        self._losses: List[float] = []
+        self.h2d_bytes = 0
+
+    def submit(self, tokens, labels, mask=None, doc_ids=None):
+        """Stages one micro-batch (host arrays or tensors) and starts its copy to the device."""
+        if self.n_sub - self.n_run >= self.depth - 1:
+            raise RuntimeError("pipeline full: call run() before submitting more")
+        s = self.n_sub % self.depth
+        if self.n_sub >= self.depth:
+            self.consumed[s].synchronize()                     # the step that used this slot has read its buffers
+        as_t = lambda a, dt: a.to(dt) if isinstance(a, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(a, {torch.int32: np.int32, torch.float32: np.float32}[dt]))
+        self.h_tok[s].copy_(as_t(tokens, torch.int32).reshape(-1))
+        self.h_lab[s].copy_(as_t(labels, torch.int32).reshape(-1))
+        if mask is not None:
+            self.h_msk[s].copy_(as_t(mask, torch.float32).reshape(-1))
+        if doc_ids is not None:
+            self.h_doc[s].copy_(as_t(doc_ids, torch.int32).reshape(-1))
+        self.flags[s] = (mask is not None, doc_ids is not None)
+        with torch.cuda.stream(self.copy_stream):
+            self.d_tok[s].copy_(self.h_tok[s], non_blocking=True)
+            self.d_lab[s].copy_(self.h_lab[s], non_blocking=True)
+            nbytes = 8 * self.h_tok[s].numel()
+            if mask is not None:
+                self.d_msk[s].copy_(self.h_msk[s], non_blocking=True)
+                nbytes += 4 * self.h_tok[s].numel()
+            if doc_ids is not None:
+                self.d_doc[s].copy_(self.h_doc[s], non_blocking=True)
+                nbytes += 4 * self.h_tok[s].numel()
+            self.staged[s].record(self.copy_stream)
+        self.h2d_bytes += nbytes
+        self.n_sub += 1
+
+    def run(self, grad_scale: float = 1.0, last: bool = True):
+        """forward + loss + backward of the oldest staged micro-batch; its loss starts its way back to the host."""
+        if self.n_run >= self.n_sub:
+            raise RuntimeError("nothing staged")
+        s = self.n_run % self.depth
+        cur = torch.cuda.current_stream()
+        cur.wait_event(self.staged[s])
+        has_mask, has_doc = self.flags[s]
+        self._collect(self.n_run - (self.depth - 1))           # the slot's previous loss, copied long ago
+        self.tr.micro_step(self.d_tok[s], self.d_lab[s], self.d_msk[s] if has_mask else None,
+                           self.d_doc[s] if has_doc else None, grad_scale=grad_scale, last=last)
+        self.loss_host[s:s + 1].copy_(self.tr.loss_tensor(), non_blocking=True)
+        self.loss_ready[s].record(cur)
+        self.consumed[s].record(cur)
+        self.n_run += 1
+
+    def _collect(self, upto: int):
+        while self.n_read <= upto and self.n_read < self.n_run:
+            s = self.n_read % self.depth
+            self.loss_ready[s].synchronize()
+            self._losses.append(float(self.loss_host[s]))
+            self.n_read += 1
+
+    def drain(self) -> List[float]:
+        """Waits for every micro-batch run so far and returns all losses not handed out yet, in order."""
+        self._collect(self.n_run - 1)
+        out, self._losses = self._losses, []
+        return out

@@ -20,9 +20,13 @@
 //      11 optimizer steps 12 accum 13 optimizer(0 AdamW, 1 Muon on hidden 2-D + AdamW rest)
 //      14 clip enabled 15 cosine schedule 16 warmup 17 total_steps 18 dump grads of step 0
 //      19 dump logits of micro-step 0 20 skip final params
+//      21 decode: after training, run GPTModel::forward_step over the first I[21] tokens of a token list that follows
+//         the batches in the input (i32 count, i32 ids[count]) and dump the (vocab) logits of every step
+//      22 generate: GPTModel::generate(those tokens as the prompt, I[22] new tokens, temperature 0) and dump the ids
 //   F: 0 lr 1 weight decay 2 clip max norm 3 min_lr 4 muon lr
 // Output file: f32 loss[steps*accum]; [grads, reference order]; [logits (V, B*S)];
-//   [final params, reference order]; f64 seconds[steps] (wall time per optimizer step).
+//   [final params, reference order]; f64 seconds[steps] (wall time per optimizer step);
+//   [decode: f32 logits[I[21]][vocab]]; [generate: i32 count, i32 ids[count]].
 #include <chrono>
 #include <cstdint>
 #include <cstdio>
@@ -196,6 +200,35 @@ int main(int argc, char** argv)
     if (!skip_params)
         for (auto& p : params) { auto m = engine.to_matrix(p.get()); CHECK(m); wr_matrix(out, *m); }
     out.write(reinterpret_cast<const char*>(secs.data()), static_cast<std::streamsize>(secs.size() * sizeof(double)));
+    if (I[21] > 0 || I[22] > 0)
+    {
+        std::int32_t count = 0;
+        if (!rd(in, &count, 1) || count <= 0) { std::cerr << "ref_gpt: decode token list missing\n"; return 1; }
+        std::vector<std::int32_t> ids(static_cast<std::size_t>(count));
+        if (!rd(in, ids.data(), ids.size())) { std::cerr << "ref_gpt: short decode token list\n"; return 1; }
+        auto& gpt = static_cast<GPTModel&>(model.layer_at(0));
+        if (I[21] > 0)
+        {
+            std::vector<Tensor> kc, vc;
+            for (std::size_t l = 0; l < L; ++l) { kc.push_back(engine.create_tensor(S, D)); vc.push_back(engine.create_tensor(S, D)); }
+            for (int t = 0; t < I[21] && t < count; ++t)
+            {
+                auto lg = gpt.forward_step(engine, static_cast<std::size_t>(ids[t]), static_cast<std::size_t>(t), kc, vc, static_cast<std::size_t>(t));
+                CHECK(lg);
+                auto m = engine.to_matrix(*lg); CHECK(m);
+                wr_matrix(out, *m);
+            }
+        }
+        if (I[22] > 0)
+        {
+            std::vector<std::size_t> prompt(ids.begin(), ids.end());
+            auto gen = gpt.generate(engine, prompt, static_cast<std::size_t>(I[22]), Scalar{0});
+            CHECK(gen);
+            const std::int32_t n = static_cast<std::int32_t>(gen->size());
+            out.write(reinterpret_cast<const char*>(&n), sizeof(n));
+            for (auto id : *gen) { const std::int32_t v = static_cast<std::int32_t>(id); out.write(reinterpret_cast<const char*>(&v), sizeof(v)); }
+        }
+    }
     std::cerr << "ref_gpt: threads=" << std::thread::hardware_concurrency() << " steps=" << steps
               << " last_loss=" << (losses.empty() ? 0.f : losses.back()) << "\n";
     return out ? 0 : 1;

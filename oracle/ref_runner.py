@@ -26,14 +26,15 @@ def available() -> bool:
 
 def write_input(path, cfg: go.GptConfig, params, micro_batches, *, steps, accum=1, lr=1e-3, wd=0.01,
                 optimizer=go.OPT_ADAMW, muon_lr=0.02, clip=None, cosine=False, warmup=0, total_steps=1, min_lr=0.0,
-                dump_grads=False, dump_logits=False, skip_params=False):
+                dump_grads=False, dump_logits=False, skip_params=False, decode_tokens=None, decode_steps=0, generate=0):
     """Writes the binary run description oracle/ref_harness.cpp documents."""
     shapes = go.param_shapes(cfg)
     use_doc = micro_batches[0].get("doc_ids") is not None
     I = np.zeros(32, np.int32)
-    I[:21] = [cfg.vocab, cfg.d_model, cfg.heads, cfg.layers, cfg.d_ff, cfg.seq, cfg.batch, cfg.act,
+    I[:23] = [cfg.vocab, cfg.d_model, cfg.heads, cfg.layers, cfg.d_ff, cfg.seq, cfg.batch, cfg.act,
               cfg.norm, cfg.pos, int(use_doc), steps, accum, optimizer, int(clip is not None),
-              int(cosine), warmup, total_steps, int(dump_grads), int(dump_logits), int(skip_params)]
+              int(cosine), warmup, total_steps, int(dump_grads), int(dump_logits), int(skip_params),
+              int(decode_steps), int(generate)]
     F = np.zeros(16, np.float32)
     F[:5] = [lr, wd, clip if clip is not None else 0.0, min_lr, muon_lr]
     with open(path, "wb") as f:
@@ -51,10 +52,15 @@ def write_input(path, cfg: go.GptConfig, params, micro_batches, *, steps, accum=
             f.write(np.asarray(mb["mask"], np.float32).tobytes())
             if use_doc:
                 f.write(np.asarray(mb["doc_ids"], np.int32).tobytes())
+        if decode_tokens is not None:
+            ids = np.asarray(decode_tokens, np.int32)
+            f.write(struct.pack("<i", ids.size))
+            f.write(ids.tobytes())
 
 
-def parse_output(raw: bytes, cfg: go.GptConfig, *, steps, accum=1, dump_grads=False, dump_logits=False, skip_params=False):
-    """dict(losses, grads|None, logits|None, params|None, seconds) from the output file of a run."""
+def parse_output(raw: bytes, cfg: go.GptConfig, *, steps, accum=1, dump_grads=False, dump_logits=False, skip_params=False,
+                 decode_steps=0, generate=0):
+    """dict(losses, grads|None, logits|None, params|None, seconds[, decode_logits, generated]) from the output file of a run."""
     shapes = go.param_shapes(cfg)
     off = 0
 
@@ -72,6 +78,11 @@ def parse_output(raw: bytes, cfg: go.GptConfig, *, steps, accum=1, dump_grads=Fa
     if not skip_params:
         out["params"] = [take(rr * cc).reshape(rr, cc) for _, rr, cc in shapes]
     out["seconds"] = take(steps, np.float64)
+    if decode_steps:
+        out["decode_logits"] = take(decode_steps * cfg.vocab).reshape(decode_steps, cfg.vocab)
+    if generate:
+        n = int(take(1, np.int32)[0])
+        out["generated"] = take(n, np.int32)
     assert off == len(raw), (off, len(raw))
     return out
 
@@ -80,7 +91,8 @@ def run_binary(binary, cfg: go.GptConfig, params, micro_batches, extra_args=(), 
                **kw):
     """Runs `binary in.bin out.bin [extra_args]` on the run described by the keywords of write_input."""
     io_kw = dict(steps=kw["steps"], accum=kw.get("accum", 1), dump_grads=kw.get("dump_grads", False),
-                 dump_logits=kw.get("dump_logits", False), skip_params=kw.get("skip_params", False))
+                 dump_logits=kw.get("dump_logits", False), skip_params=kw.get("skip_params", False),
+                 decode_steps=kw.get("decode_steps", 0), generate=kw.get("generate", 0))
     with tempfile.TemporaryDirectory() as td:
         fin, fout = os.path.join(td, "in.bin"), os.path.join(td, "out.bin")
         write_input(fin, cfg, params, micro_batches, **kw)

@@ -122,6 +122,37 @@ def full_cases(only=None):
         print(name, "losses", ref["losses"], "s/step", ref["seconds"], flush=True)
 
 
+# Incremental inference with a key/value cache: GPTModel::forward_step over a token list (logits of every step) and
+# GPTModel::generate at temperature 0 (prompt 10 tokens, more new tokens than the window has room for, so the sliding
+# window rebuild runs).  Weights N(0, 0.2) so that the arg max of the logits is well separated.
+DECODE_CASES = {
+    "ln_gelu_learned": go.GptConfig(96, 48, 6, 2, 80, 16, 1, go.ACT_GELU, go.NORM_LAYER, go.POS_LEARNED),
+    "rms_swiglu_sin": go.GptConfig(96, 48, 6, 2, 80, 16, 1, go.ACT_SWIGLU, go.NORM_RMS, go.POS_SINUSOIDAL),
+    "rms_swiglu_alibi": go.GptConfig(128, 64, 4, 3, 96, 24, 1, go.ACT_SWIGLU, go.NORM_RMS, go.POS_ALIBI),
+    "rms_swiglu_rope": go.GptConfig(128, 64, 4, 2, 96, 24, 1, go.ACT_SWIGLU, go.NORM_RMS, go.POS_ROPE),
+}
+
+
+def decode_cases():
+    arrays = {}
+    for name, cfg in DECODE_CASES.items():
+        params = go.init_params(cfg, 42, std=0.2)
+        rng = np.random.default_rng(77)
+        tokens = rng.integers(0, cfg.vocab, cfg.seq).astype(np.int32)          # a full window of tokens, step by step
+        mbs = go.make_batches(cfg, 1, seed=1)
+        ref = rr.run_reference(cfg, params, mbs, steps=0, lr=1e-3, skip_params=True, decode_tokens=tokens,
+                               decode_steps=cfg.seq)
+        gen = rr.run_reference(cfg, params, mbs, steps=0, lr=1e-3, skip_params=True, decode_tokens=tokens[:10],
+                               generate=cfg.seq + 6)
+        arrays[name + "_cfg"] = np.array(list(vars(cfg).values()), np.int64)
+        arrays[name + "_tokens"] = tokens
+        arrays[name + "_logits"] = ref["decode_logits"]
+        arrays[name + "_generated"] = gen["generated"]
+        arrays[name + "_p0_checksum"] = np.array([float(sum(np.abs(p.astype(np.float64)).sum() for p in params))])
+        print("decode", name, gen["generated"][:8], "...")
+    np.savez_compressed(os.path.join(OUT, "decode.npz"), **arrays)
+
+
 def c1_case():
     params = go.init_params(C1, 42)
     mbs = go.make_batches(C1, 20, seed=1, dist="uniform")
@@ -172,7 +203,7 @@ def prim_case():
 
 
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["prims", "gpt", "c1"]
+    which = sys.argv[1:] or ["prims", "gpt", "c1", "decode"]
     if "prims" in which:
         prim_case()
     if "gpt" in which:
@@ -185,3 +216,5 @@ if __name__ == "__main__":
         full_cases(named or None)
     if "c1" in which:
         c1_case()
+    if "decode" in which:
+        decode_cases()

@@ -81,6 +81,23 @@ def test_cpp_host_save_model_is_the_reference_file():
         assert rel_err(again["losses"], ref["losses"]) < 1e-5
 
 
+def test_cpp_host_forward_step_and_generate_match_reference():
+    """B200GPTModel::forward_step / ::generate (key/value cache) through the C++ host against the reference's
+    GPTModel::forward_step / ::generate golden vectors."""
+    _need_binary()
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "decode.npz"))
+    for name in ("ln_gelu_learned", "rms_swiglu_alibi", "rms_swiglu_rope"):
+        cfg = go.GptConfig(*[int(v) for v in z[name + "_cfg"]])
+        params = go.init_params(cfg, 42, std=0.2)
+        mbs = go.make_batches(cfg, 1, seed=1)
+        out = rr.run_binary([FUSED, "run"], cfg, params, mbs, extra_args=["--precision", "0"], steps=0, lr=1e-3, skip_params=True,
+                            decode_tokens=z[name + "_tokens"], decode_steps=cfg.seq)
+        assert rel_err(out["decode_logits"], z[name + "_logits"]) < 1e-5
+        gen = rr.run_binary([FUSED, "run"], cfg, params, mbs, extra_args=["--precision", "0"], steps=0, lr=1e-3, skip_params=True,
+                            decode_tokens=z[name + "_tokens"][:10], generate=cfg.seq + 6)
+        assert np.array_equal(gen["generated"], z[name + "_generated"])
+
+
 def test_cpp_host_bench_mode_runs():
     """The benchmark loop of the C++ host on a shallow copy of the benchmark model: one JSON line, finite loss."""
     _need_binary()

@@ -87,7 +87,7 @@ def _full_case_or_skip(name):
     return load_full_case(name)
 
 
-def _check_full(case, got, tol, grad_tol, key_bias_tol):
+def _check_full(case, got, tol, grad_tol, key_bias_tol, logits_l2_tol=None):
     """Losses, the logits sample, gradient / parameter samples and per-tensor norms of a full-width case against the
     reference CPU engine's.  The key-bias gradient is analytically zero (softmax does not see a per-query shift of
     the scores): instead of leaving it out silently, its norm must be negligible beside the query bias's."""
@@ -97,7 +97,13 @@ def _check_full(case, got, tol, grad_tol, key_bias_tol):
     assert rel_err(losses, case["losses"]) < tol
     lg = logits.reshape(-1)
     lg = lg[sample_indices(lg.size, 4 * 4096)]
-    assert np.abs(lg - case["logits_sample"]).max() < tol * case["logits_absmax"]
+    if logits_l2_tol is None:
+        assert np.abs(lg - case["logits_sample"]).max() < tol * case["logits_absmax"]
+    else:
+        # bf16 mode: every logit is itself rounded to bf16 (4e-3 relative) after up to twelve layers of bf16 arithmetic,
+        # so single elements near zero are not held to a fraction of the largest logit; the sample as a whole is
+        assert global_rel_err([lg], [case["logits_sample"]]) < logits_l2_tol
+        assert np.abs(lg - case["logits_sample"]).max() < 5 * tol * case["logits_absmax"]
     names = [n for n, _, _ in go.param_shapes(cfg)]
     skip = key_bias_indices(cfg)
     assert global_rel_err(sample_tensors(grads), case["grads"], skip) < grad_tol
@@ -131,7 +137,7 @@ def test_full_width_bf16_mode_matches_reference(nnb, name):
     engine; the gradient of a single bf16 backward pass is held to 5e-2."""
     import torch
     case = _full_case_or_skip(name)
-    _check_full(case, _run(nnb, case, nnb.BF16, record_logits=True), 1e-2, 5e-2, 5e-2)
+    _check_full(case, _run(nnb, case, nnb.BF16, record_logits=True), 1e-2, 5e-2, 5e-2, logits_l2_tol=2e-2)
     torch.cuda.empty_cache()
 
 
