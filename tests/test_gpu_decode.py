@@ -37,7 +37,7 @@ def _trainer(nnb, c, params, precision):
 
 
 @pytest.mark.parametrize("name", CASES)
-@pytest.mark.parametrize("precision,tol", [(0, 1e-5), (1, 1e-2)])
+@pytest.mark.parametrize("precision,tol", [(0, 1e-5), (1, 2e-2)])     # bf16 weights N(0, 0.2): ten times the training init, largest-logit norm
 def test_forward_step_matches_reference(nnb, name, precision, tol):
     import torch
     c, params, tokens, want, _ = _load(name)
