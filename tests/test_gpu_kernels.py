@@ -228,7 +228,7 @@ def test_attention_matches_reference_primitives_golden(g):
 # ----------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [0, 1])
 @pytest.mark.parametrize("layer", [0, 1])
-@pytest.mark.parametrize("rows,d", [(37, 48), (300, 128), (1024, 768)])
+@pytest.mark.parametrize("rows,d", [(37, 48), (300, 128), (1024, 768), (600, 384), (520, 1024), (260, 4096)])
 def test_norm_forward_backward(g, dtype, layer, rows, d):
     import torch
     from oracle import gpt_oracle as go
@@ -400,7 +400,8 @@ def test_adamw_clip_match_oracle(g):
     assert np.array_equal(g.host(shadow), g.bf16_round(g.host(tp)))
 
 
-@pytest.mark.parametrize("precision,rows,cols", [(0, 24, 40), (0, 40, 24), (1, 64, 128), (1, 256, 64), (0, 16, 1)])
+@pytest.mark.parametrize("precision,rows,cols", [(0, 24, 40), (0, 40, 24), (1, 64, 128), (1, 256, 64), (0, 16, 1),
+                                                 (1, 1024, 1024), (1, 2816, 1024), (1, 1024, 2816)])   # the last three: the packed-document configuration's matrices
 def test_muon_step_matches_oracle(g, precision, rows, cols):
     import torch
     from oracle import gpt_oracle as go
@@ -422,6 +423,39 @@ def test_muon_step_matches_oracle(g, precision, rows, cols):
     upd = g.host(tp) - p0
     tol = 3e-2 if precision else 1e-4
     assert np.linalg.norm(upd - upd_ref) < tol * np.linalg.norm(upd_ref)
+
+
+def test_muon_step_many_equals_single_calls(g):
+    """The multi-stream form spreads the matrices over lanes; every matrix must come out bit-identical to its own
+    single call (the updates are independent)."""
+    import torch
+    r = _rng(99)
+    shapes = [(256, 256), (512, 256), (256, 768), (256, 256), (128, 384)]
+    ps = [(r.standard_normal(s) * 0.02).astype(np.float32) for s in shapes]
+    gs = [(r.standard_normal(s) * 0.01).astype(np.float32) for s in shapes]
+    worst = max(int(g.call("nnb200_muon_scratch_bytes", a, b, 1)) for a, b in shapes)
+    lane = (worst + 255) // 256 * 256
+    outs = []
+    for many in (False, True):
+        tp = [g.dev(p.copy()) for p in ps]
+        tg = [g.dev(x) for x in gs]
+        tv = [torch.zeros(*s, device="cuda") for s in shapes]
+        sh = [torch.zeros(*s, dtype=torch.bfloat16, device="cuda") for s in shapes]
+        scratch = torch.zeros(lane * 3, dtype=torch.uint8, device="cuda")
+        if many:
+            n = len(shapes)
+            PA, IA = C.c_void_p * n, C.c_int * n
+            arr = lambda ts: PA(*[t.data_ptr() for t in ts])
+            g.call("nnb200_muon_step_many", n, arr(tp), arr(tg), arr(tv), arr(sh), IA(*[a for a, _ in shapes]), IA(*[b for _, b in shapes]),
+                   C.c_float(0.02), C.c_float(0.95), 5, C.c_float(1e-7), 1, g.ptr(scratch), lane, 3, None, g.stream())
+        else:
+            for i, (a, b) in enumerate(shapes):
+                g.call("nnb200_muon_step", g.ptr(tp[i]), g.ptr(tg[i]), g.ptr(tv[i]), g.ptr(sh[i]), a, b, C.c_float(0.02), C.c_float(0.95),
+                       5, C.c_float(1e-7), 1, g.ptr(scratch), None, g.stream())
+        outs.append([g.host(t) for t in tp] + [g.host(t) for t in sh])
+    assert g.gemm_status() == 0
+    for x, y in zip(*outs):
+        assert np.array_equal(x, y)
 
 
 # ----------------------------------------------------------------------------------------------
