@@ -449,6 +449,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a
     }
 }
 
+}  // namespace nnb
+
+#include "attention_tc_fwd64.cuh"
+
+namespace nnb {
+
 // ---------------------------------------------------------------- document ranges
 // ranges[b * S/64 + blk] = (min, max) of the document ids of rows [64 blk, 64 blk + 64) of sequence b: one warp per block
 __global__ void doc_ranges_kernel(const int* __restrict__ doc, int2* __restrict__ ranges, int nblocks)
@@ -510,7 +516,14 @@ int attention_fwd_tc(const bf16* qkv, bf16* out, float* lse, const int* doc, con
         if (alibi) return launch_fwd_tc<DKV, false, true>(tm, a, tiles, s);                   \
         return launch_fwd_tc<DKV, false, false>(tm, a, tiles, s);                             \
     } while (0)
-    if (dk == 64) NNB_FWD(64);
+    if (dk == 64) {
+        CUtensorMap tkv;
+        NNB_TRY(tensor_map_2d(qkv, 3LL * d, static_cast<long long>(B) * S, 3LL * d, 64, Fwd64::KB, &tkv, 2));
+        if (doc && alibi) return launch_fwd_tc64<true, true>(tm, tkv, a, tiles, s);
+        if (doc) return launch_fwd_tc64<true, false>(tm, tkv, a, tiles, s);
+        if (alibi) return launch_fwd_tc64<false, true>(tm, tkv, a, tiles, s);
+        return launch_fwd_tc64<false, false>(tm, tkv, a, tiles, s);
+    }
     NNB_FWD(128);
 #undef NNB_FWD
 }
