@@ -10,8 +10,14 @@
 //     when the reference point of its exponentials has to move: the running maximum may run ahead of the reference by up
 //     to 2^8 before the row (sum and output) is rescaled, so after the first blocks of a tile that is rare;
 //   * Q, K, V, S and P are single-buffered: 55 KB of shared memory per CTA.
-// Six warps: TMA producer, MMA issuer, four softmax warps.  Work list, ALiBi-by-MMA, document block skipping, bounded
-// waits and the status word are those of the general kernel.
+// Five warps: a control warp whose lane 0 issues every TMA load and every MMA in the order the data dependencies give,
+// and four softmax warps.  The CTAs draw their (128-query tile, head, batch) items, longest first, from a counter in
+// global memory (work_counter.cu); the control thread passes each item on through a two-slot ring in shared memory.
+// The control thread treats the key blocks of successive tiles as one stream: while the softmax warps finish the last
+// block of a tile and write its output rows, the next tile's Q and first K / V tiles are loaded and its first score
+// MMA is issued.  The score columns are handed back (s_free) as soon as the second pass has read them, before the
+// exponentials are done, so the next score MMA overlaps the rest of the block.
+// ALiBi-by-MMA, document block skipping, bounded waits and the status word are those of the general kernel.
 #pragma once
 
 namespace nnb {
@@ -29,7 +35,8 @@ static_assert(Fwd64::OFF_BAR + 128 <= Fwd64::SMEM, "barriers do not fit");
 
 template <bool DOC, bool ALIBI>
 __global__ void __launch_bounds__(Fwd64::THREADS, Fwd64::CTAS_PER_SM)
-attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV, const AttnTcArgs a)
+attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV, const AttnTcArgs a,
+                     unsigned int* __restrict__ work)
 {
     using LY = Fwd64;
     constexpr int DK = 64, KB = LY::KB;
@@ -42,9 +49,11 @@ attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint8_t* sW = smem + LY::OFF_W;                // key position inside the block, constant
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + LY::OFF_BAR);
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t q_full = bar0, k_full = bar0 + 8, v_full = bar0 + 16, s_full = bar0 + 24, p_full = bar0 + 32, pv_done = bar0 + 40, o_empty = bar0 + 48;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+    const uint32_t q_full = bar0, k_full = bar0 + 8, v_full = bar0 + 16, s_full = bar0 + 24, p_full = bar0 + 32, pv_done = bar0 + 40, o_empty = bar0 + 48,
+                   s_free = bar0 + 56, t_full0 = bar0 + 64;     // t_full: two barriers
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* tile_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);      // two entries
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int d = a.H * DK;
@@ -54,6 +63,7 @@ attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(v_full, 1);
         mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(pv_done, 1); mbar_init(o_empty, 4);
+        mbar_init(s_free, 4); mbar_init(t_full0, 1); mbar_init(t_full0 + 8, 1);
         *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;        // the swizzled tiles need a 1024-byte aligned base
         if (*abort_flag) atomicCAS(&g_attn_error, 0, (9 << 16));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -97,94 +107,129 @@ attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     };
 
     if (warp == 0) {
-        // Control warp: lane 0 issues every TMA load and every MMA of the CTA, in the order the data dependencies give
-        // (the whole warp evaluates the block mask and writes the ALiBi slope tile).  s_full doubles as "the key tile and
-        // the query tile have been read", pv_done as "the value tile and P have been read".
-        int kv = 0, tn = 0;                                     // key blocks and tiles processed so far: barrier phases
-        bool ok = !*abort_flag;
-        const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), p_addr = smem_u32(sP), v_addr = smem_u32(sV);
-        auto wait1 = [&](uint32_t bar, uint32_t parity, int code) -> bool { return mbar_wait(bar, parity, abort_flag, code, &g_attn_error); };
-        auto load_k = [&](const AttnTile& t, int kb) {
-            mbar_expect_tx(k_full, LY::K_TILE);
-            tma_load_2d(k_addr, &tmKV, k_full, d + t.h * DK, t.b * a.S + kb * KB);
-        };
-        auto load_v = [&](const AttnTile& t, int kb) {
-            mbar_expect_tx(v_full, LY::K_TILE);
-            tma_load_2d(v_addr, &tmKV, v_full, 2 * d + t.h * DK, t.b * a.S + kb * KB);
-        };
-        auto issue_s = [&]() {
+        if (lane == 0) {
+            // Control thread.  s_full doubles as "the key tile, the query tile and the slope tile have been read", pv_done
+            // as "the value tile and P have been read".  kv counts key blocks, tn tiles: they give the barrier phases.
+            int kv = 0, tn = 0;
+            bool ok = !*abort_flag;
+            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), p_addr = smem_u32(sP), v_addr = smem_u32(sV);
+            auto wait1 = [&](uint32_t bar, uint32_t parity, int code) -> bool { return mbar_wait(bar, parity, abort_flag, code, &g_attn_error); };
+            auto issue_s = [&]() {
 #pragma unroll
-            for (int k = 0; k < DK / 16; ++k)
-                umma_bf16(tmem_base, smem_desc(q_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 32, 16, 1024), IDESC_S, k > 0 ? 1u : 0u);
-            if (ALIBI)       // + (slope / scale) * (key position inside the block)
-                umma_bf16(tmem_base, smem_desc_noswizzle(smem_u32(sU), 128, 256), smem_desc_noswizzle(smem_u32(sW), 128, 256), IDESC_S, 1u);
-            umma_commit(s_full);
-        };
-        auto issue_pv = [&](bool first) {                      // first block of a tile: the output columns start from zero
+                for (int k = 0; k < DK / 16; ++k)
+                    umma_bf16(tmem_base, smem_desc(q_addr + k * 32, 16, 1024), smem_desc(k_addr + k * 32, 16, 1024), IDESC_S, k > 0 ? 1u : 0u);
+                if (ALIBI)       // + (slope / scale) * (key position inside the block)
+                    umma_bf16(tmem_base, smem_desc_noswizzle(smem_u32(sU), 128, 256), smem_desc_noswizzle(smem_u32(sW), 128, 256), IDESC_S, 1u);
+                umma_commit(s_full);
+            };
+            auto issue_pv = [&](bool first) {                  // first block of a tile: the output columns start from zero
 #pragma unroll
-            for (int k = 0; k < KB / 16; ++k)
-                umma_bf16(tmem_O, smem_desc(p_addr + k * 32, 16, 1024), smem_desc(v_addr + k * 2048, A_TILE, 1024), IDESC_PV,
-                          (first && k == 0) ? 0u : 1u);
-            umma_commit(pv_done);
-        };
-        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
-            const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
-            const int nkb = 2 * (t.qb + 1);
-            const BlockMask bm = tile_mask(t, nkb);
-            // Everything of the tile before has been issued; its last score MMA (reader of Q, K and the slope tile) and its
-            // last P V (reader of V) must be complete before their buffers are loaded again.
-            if (lane == 0 && kv >= 1) ok = wait1(s_full, (kv - 1) & 1, 11) && wait1(pv_done, (kv - 1) & 1, 12);
-            ok = __shfl_sync(0xffffffffu, static_cast<int>(ok), 0) != 0;
-            if (ALIBI && ok) {
-                const float sv = exp2f(-8.0f * static_cast<float>(t.h) / static_cast<float>(a.H)) / a.scale;
-                const bf16 s0 = __float2bfloat16_rn(sv);
-                const float r1 = sv - __bfloat162float(s0);
-                const bf16 s1 = __float2bfloat16_rn(r1);
-                const bf16 s2 = __float2bfloat16_rn(r1 - __bfloat162float(s1));
-                const uint32_t w0 = static_cast<uint32_t>(__bfloat16_as_ushort(s0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(s1)) << 16);
-                const uint32_t w1 = static_cast<uint32_t>(__bfloat16_as_ushort(s2));
-                for (int r = lane; r < 128; r += 32)
-                    *reinterpret_cast<uint4*>(sU + (r >> 3) * 256 + (r & 7) * 16) = make_uint4(w0, w1, 0u, 0u);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-            }
-            if (lane == 0 && ok) {
-                int kb = 0;
-                while (!block_active(bm, kb)) ++kb;             // the diagonal blocks are always active
-                mbar_expect_tx(q_full, A_TILE);
-                tma_load_2d(q_addr, &tmQ, q_full, t.h * DK, t.b * a.S + t.qb * AQ);
-                load_k(t, kb);
-                load_v(t, kb);
-                ok = wait1(q_full, tn & 1, 2) && wait1(k_full, kv & 1, 5);
-                // the score columns are free: the softmax warps handed over P of the block before (previous tile's last)
-                if (ok && kv >= 1) ok = wait1(p_full, (kv - 1) & 1, 6);
-                if (ok) { tc_fence_after(); issue_s(); }
-                bool first = true;
-                while (ok) {
-                    int nb = kb + 1;                            // next active block of the tile, nkb if none
-                    while (nb < nkb && !block_active(bm, nb)) ++nb;
-                    const bool more = nb < nkb;
-                    // the next key tile as soon as the scores of this block are complete
-                    if (more) { ok = wait1(s_full, kv & 1, 1); if (!ok) break; load_k(t, nb); }
-                    ok = wait1(p_full, kv & 1, 3);              // softmax of this block done: S free, P written
-                    if (!ok) break;
-                    if (more) { ok = wait1(k_full, (kv + 1) & 1, 5); if (!ok) break; tc_fence_after(); issue_s(); }
-                    if (first && tn >= 1) { ok = wait1(o_empty, (tn - 1) & 1, 4); if (!ok) break; }
-                    ok = wait1(v_full, kv & 1, 13);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_pv(first);
-                    first = false;
-                    ++kv;
-                    if (!more) break;
-                    ok = wait1(pv_done, (kv - 1) & 1, 12);      // the value tile is free
-                    if (!ok) break;
-                    load_v(t, nb);
-                    kb = nb;
+                for (int k = 0; k < KB / 16; ++k)
+                    umma_bf16(tmem_O, smem_desc(p_addr + k * 32, 16, 1024), smem_desc(v_addr + k * 2048, A_TILE, 1024), IDESC_PV,
+                              (first && k == 0) ? 0u : 1u);
+                umma_commit(pv_done);
+            };
+            // position in the stream of key blocks: tile (w < 0: the list is exhausted), block, document range of the tile
+            struct Pos { int w, h, row_base, q0, nkb, kb, tmin, tmax; const int2* rng; };
+            // The next item is drawn when two blocks of the current tile are left (about the latency of the draw), not
+            // earlier: an item drawn is an item no other CTA can take.
+            unsigned int drawn = atomicAdd(work, 1u);
+            bool have_draw = true;
+            int tiles_out = 0;                                  // tiles handed to the softmax warps so far
+            auto active = [&](const Pos& p, int kb) -> bool {   // the same rule as doc_block_mask
+                if (!DOC || p.rng == nullptr || p.nkb > 128 || kb >= p.nkb - 2) return true;
+                const int2 r = p.rng[kb];
+                return !(r.y < p.tmin || r.x > p.tmax);
+            };
+            auto open_tile = [&](Pos& p) {                      // the next item of the list, handed to the softmax warps as well
+                if (!have_draw) drawn = atomicAdd(work, 1u);
+                have_draw = false;
+                p.w = drawn < static_cast<unsigned int>(total) ? static_cast<int>(drawn) : -1;
+                tile_slot[tiles_out & 1] = p.w;
+                mbar_arrive(t_full0 + 8 * (tiles_out & 1));
+                ++tiles_out;
+                if (p.w < 0) return;
+                const AttnTile t = attn_tile(p.w, nq, a.H, a.H * a.B);
+                p.h = t.h; p.row_base = t.b * a.S; p.q0 = t.qb * AQ; p.nkb = 2 * (t.qb + 1); p.kb = 0;
+                p.rng = nullptr;
+                if (DOC && a.ranges != nullptr) {
+                    p.rng = a.ranges + static_cast<size_t>(t.b) * (a.S / 64);
+                    const int2 ta = p.rng[2 * t.qb], tb = p.rng[2 * t.qb + 1];
+                    p.tmin = min(ta.x, tb.x); p.tmax = max(ta.y, tb.y);
                 }
+                while (!active(p, p.kb)) ++p.kb;                // the diagonal blocks are always active
+            };
+            auto load_q = [&](const Pos& p) {
+                if (ALIBI) {
+                    // this head's slope / scale as three bf16 terms, in every query row of the slope tile
+                    const float sv = exp2f(-8.0f * static_cast<float>(p.h) / static_cast<float>(a.H)) / a.scale;
+                    const bf16 s0 = __float2bfloat16_rn(sv);
+                    const float r1 = sv - __bfloat162float(s0);
+                    const bf16 s1 = __float2bfloat16_rn(r1);
+                    const bf16 s2 = __float2bfloat16_rn(r1 - __bfloat162float(s1));
+                    const uint32_t w0 = static_cast<uint32_t>(__bfloat16_as_ushort(s0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(s1)) << 16);
+                    const uint32_t w1 = static_cast<uint32_t>(__bfloat16_as_ushort(s2));
+#pragma unroll 4
+                    for (int r = 0; r < 128; ++r)
+                        *reinterpret_cast<uint4*>(sU + (r >> 3) * 256 + (r & 7) * 16) = make_uint4(w0, w1, 0u, 0u);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                mbar_expect_tx(q_full, A_TILE);
+                tma_load_2d(q_addr, &tmQ, q_full, p.h * DK, p.row_base + p.q0);
+            };
+            auto load_k = [&](const Pos& p) {
+                mbar_expect_tx(k_full, LY::K_TILE);
+                tma_load_2d(k_addr, &tmKV, k_full, d + p.h * DK, p.row_base + p.kb * KB);
+            };
+            auto load_v = [&](const Pos& p) {
+                mbar_expect_tx(v_full, LY::K_TILE);
+                tma_load_2d(v_addr, &tmKV, v_full, 2 * d + p.h * DK, p.row_base + p.kb * KB);
+            };
+
+            Pos cur;
+            open_tile(cur);
+            if (ok && cur.w >= 0) {
+                load_q(cur); load_k(cur); load_v(cur);
+                ok = wait1(q_full, 0, 2) && wait1(k_full, 0, 5);
+                if (ok) { tc_fence_after(); issue_s(); }
             }
-            kv = __shfl_sync(0xffffffffu, kv, 0);
-            ok = __shfl_sync(0xffffffffu, static_cast<int>(ok), 0) != 0;
+            bool first = true;                                  // cur is the first block of its tile
+            while (ok && cur.w >= 0) {
+                // the block after cur in the stream: the next active block of the tile, or the first of the next tile
+                Pos nxt = cur;
+                bool new_tile = false;
+                if (!have_draw && cur.kb >= cur.nkb - 3) { drawn = atomicAdd(work, 1u); have_draw = true; }
+                ++nxt.kb;
+                while (nxt.kb < nxt.nkb && !active(nxt, nxt.kb)) ++nxt.kb;
+                if (nxt.kb >= nxt.nkb) { open_tile(nxt); new_tile = true; }
+                const bool more = nxt.w >= 0;
+                if (more) {
+                    // the score MMA of cur is complete: K (and, at a tile's end, Q and the slope tile) may be overwritten
+                    if (!(ok = wait1(s_full, kv & 1, 1))) break;
+                    if (new_tile) load_q(nxt);
+                    load_k(nxt);
+                    // the softmax warps have read the scores of cur: the next score MMA may overwrite them
+                    if (!(ok = wait1(s_free, kv & 1, 6))) break;
+                    if (new_tile && !(ok = wait1(q_full, (tn + 1) & 1, 2))) break;
+                    if (!(ok = wait1(k_full, (kv + 1) & 1, 5))) break;
+                    tc_fence_after();
+                    issue_s();
+                }
+                if (!(ok = wait1(p_full, kv & 1, 3))) break;    // P of cur is written
+                if (first && tn >= 1 && !(ok = wait1(o_empty, (tn - 1) & 1, 4))) break;   // the output rows of the tile before are read out
+                if (!(ok = wait1(v_full, kv & 1, 13))) break;
+                tc_fence_after();
+                issue_pv(first);
+                ++kv;
+                if (!more) break;
+                if (!(ok = wait1(pv_done, (kv - 1) & 1, 12))) break;     // the value tile is free
+                load_v(nxt);
+                first = new_tile;
+                if (new_tile) ++tn;
+                cur = nxt;
+            }
+            // every CTA ends with one failed draw; the CTA that leaves last puts the counter pair back to zero
+            if (atomicAdd(work + 1, 1u) == gridDim.x - 1u) { work[0] = 0u; work[1] = 0u; }
         }
     } else {
         const int q = warp & 3;                                // TMEM lane quadrant
@@ -202,7 +247,10 @@ attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             return __all_sync(0xffffffffu, got);
         };
 
-        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
+        for (; ok; ++tn) {
+            if (!wait_all(t_full0 + 8 * (tn & 1), (tn >> 1) & 1, 14)) break;
+            const int w = tile_slot[tn & 1];
+            if (w < 0) break;
             const AttnTile t = attn_tile(w, nq, a.H, a.H * a.B);
             const int h = t.h, b = t.b, q0 = t.qb * AQ, nkb = 2 * (t.qb + 1), row_base = b * a.S;
             const BlockMask bm = tile_mask(t, nkb);
@@ -247,6 +295,7 @@ attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 float mxr = -INFINITY;
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
+                    if (lim0 + 31 < 32 * c) continue;           // past the diagonal for every row of the warp (uniform)
                     uint32_t r[32];
                     tmem_ld32(tmem_base + lane_addr + c * 32, r);
                     tmem_ld_wait();
@@ -286,9 +335,22 @@ attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 uint64_t rs2 = 0ull;
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
+                    const bool none = lim0 + 31 < 32 * c;       // past the diagonal for every row of the warp (uniform): P = 0
                     uint32_t r[32];
-                    tmem_ld32(tmem_base + lane_addr + c * 32, r);
-                    tmem_ld_wait();
+                    if (!none) {
+                        tmem_ld32(tmem_base + lane_addr + c * 32, r);
+                        tmem_ld_wait();
+                    }
+                    if (c == 1) {                               // the scores are in registers: the columns go back to the tensor core
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(s_free);
+                    }
+                    if (none) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(prow + (((c * 4 + g) ^ sw) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                        continue;
+                    }
                     const bool plain = !DOC && lim0 >= 32 * c + 31;   // uniform over the warp
                     const uint32_t vis = plain ? 0xffffffffu : (c == 0 ? vis_lo : vis_hi);
 #pragma unroll
@@ -371,8 +433,10 @@ static int launch_fwd_tc64(const CUtensorMap& tq, const CUtensorMap& tkv, const 
     static PerDeviceOnce once;
     NNB_TRY(once.run([] { return cudaFuncSetAttribute(attn_fwd_tc64_kernel<DOC, ALIBI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd64::SMEM); }));
     const long long slots = static_cast<long long>(device_sm_count()) * Fwd64::CTAS_PER_SM;
-    const dim3 grid(static_cast<unsigned>(tiles < slots ? tiles : slots));     // persistent: each CTA walks the tile list
-    attn_fwd_tc64_kernel<DOC, ALIBI><<<grid, Fwd64::THREADS, Fwd64::SMEM, s>>>(tq, tkv, a);
+    const dim3 grid(static_cast<unsigned>(tiles < slots ? tiles : slots));     // persistent: each CTA draws tiles until none is left
+    unsigned int* work = nullptr;
+    NNB_TRY(work_counter_pair(s, &work));
+    attn_fwd_tc64_kernel<DOC, ALIBI><<<grid, Fwd64::THREADS, Fwd64::SMEM, s>>>(tq, tkv, a, work);
     NNB_LAUNCH_CHECK();
     return 0;
 }

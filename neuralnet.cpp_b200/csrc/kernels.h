@@ -25,6 +25,8 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
               cudaStream_t stream);
 int gemm_device_error(int* code);
 int gemm_pair_capacity();
+// {next item, CTAs that have left} of (current device, stream), zero between launches (work_counter.cu)
+int work_counter_pair(cudaStream_t s, unsigned int** out);
 int gemm_clear_device_error();
 int gemm_profile_enable(int enable);
 int gemm_profile_read(double* total_ms, double* total_flops, int* launches);
