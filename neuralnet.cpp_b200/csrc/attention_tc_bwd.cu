@@ -85,12 +85,39 @@ __device__ __forceinline__ void init_position_tiles(uint8_t* pos_tile, uint8_t* 
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// Both kernels are persistent: the CTAs resident on an SM walk a list of (tile, head, batch) work items, heaviest
-// tiles first, in snake order.  The rings, score buffers and barrier phases run on across tiles, so the loads and
+// Both kernels are persistent: the CTAs resident on an SM draw (tile, head, batch) work items, heaviest tiles first,
+// from a counter in global memory (work_counter.cu; the producer warp draws and passes the item on to the other
+// roles through a two-slot ring in shared memory), so that a CTA whose tiles ran slowly takes fewer of them.  The rings, score buffers and barrier phases run on across tiles, so the loads and
 // first MMAs of the next tile overlap the tail and the write-out of the current one.  Every resource is
 // single-buffered (block ring of 2); at head size 64 two CTAs share an SM (256 TMEM columns, 80 / 97 KB of shared
 // memory, 96 registers each), so that while the workers of one CTA are in their dependency chain (scores ready ->
 // tcgen05.ld -> exp -> dS tile -> next MMA) the other CTA's MMAs run; at head size 128 one CTA fills the SM.
+// Producer side of the work list (whole warp): lane 0 draws the next item and publishes it (or -1 when the list is
+// exhausted) in slot n & 1; everybody gets the value.  A slot is reused two tiles later, when its readers are long past it.
+__device__ __forceinline__ int draw_tile(unsigned int* work, int total, volatile int* slots, uint32_t t_full0, int n, int lane)
+{
+    int w = 0;
+    if (lane == 0) {
+        const unsigned int v = atomicAdd(work, 1u);
+        w = v < static_cast<unsigned int>(total) ? static_cast<int>(v) : -1;
+        slots[n & 1] = w;
+        mbar_arrive(t_full0 + 8 * (n & 1));
+    }
+    return __shfl_sync(0xffffffffu, w, 0);
+}
+// The producer's last act: the CTA that leaves last puts the counter pair back to zero for the next launch.
+__device__ __forceinline__ void leave_work_list(unsigned int* work, int lane)
+{
+    if (lane == 0 && atomicAdd(work + 1, 1u) == gridDim.x - 1u) { work[0] = 0u; work[1] = 0u; }
+}
+// Consumer side (whole warp): the item of round n, -1 at the end or when the wait gave up.
+__device__ __forceinline__ int read_tile(volatile int* slots, uint32_t t_full0, int n, volatile int* abort_flag, int* error_word)
+{
+    const bool got = mbar_wait(t_full0 + 8 * (n & 1), (n >> 1) & 1, abort_flag, 14, error_word);
+    if (!__all_sync(0xffffffffu, got)) return -1;
+    return slots[n & 1];
+}
+
 struct BwdTile { int t, h, b; };
 __device__ __forceinline__ BwdTile bwd_tile(int w, int H, int HB)
 {
@@ -108,7 +135,7 @@ __device__ __forceinline__ BwdTile bwd_tile(int w, int H, int HB)
 // shared memory: Q | dO | ring of two (K, V) 64-key tiles | dS | barriers
 template <int DK> struct DqLayout {
     static constexpr int NS = DK / 64;                              // 64-column sub-tiles per operand tile
-    static constexpr int ST = 2;                                    // (K, V) ring stages
+    static constexpr int ST = 3;                                    // (K, V) ring stages: a stage is free only when its dQ MMA is complete
     static constexpr int OFF_DO = NS * BT, OFF_RING = 2 * NS * BT, OFF_DS = OFF_RING + ST * 2 * NS * HT, OFF_U = OFF_DS + BT,
                          OFF_W = OFF_U + XT, OFF_BAR = OFF_W + XT, SMEM = OFF_BAR + 256;
     static constexpr uint32_t TMEM_COLS = 256u;                     // S [0, 64) | dP [64, 128) | dQ [128, 128 + DK)
@@ -118,7 +145,7 @@ template <int DK> struct DqLayout {
 template <int DK, bool DOC, bool ALIBI>
 __global__ void __launch_bounds__(320, DqLayout<DK>::CTAS_PER_SM)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_constant__ CUtensorMap tmKV64,
-                      const __grid_constant__ CUtensorMap tmDO128, const AttnBwdArgs a)
+                      const __grid_constant__ CUtensorMap tmDO128, const AttnBwdArgs a, unsigned int* __restrict__ work)
 {
     using LY = DqLayout<DK>;
     constexpr int ST = LY::ST, NS = LY::NS, STAGE = 2 * NS * HT;
@@ -129,10 +156,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
     uint8_t* sDS = smem + LY::OFF_DS;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + LY::OFF_BAR);
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t q_full = bar0, q_empty = bar0 + 8, kv_full0 = bar0 + 16, kv_empty0 = bar0 + 32, sp_full = bar0 + 48,
-                   sp_empty = bar0 + 56, ds_full = bar0 + 64, ds_empty = bar0 + 72, done = bar0 + 80, acc_empty = bar0 + 88;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    const uint32_t q_full = bar0, q_empty = bar0 + 8, kv_full0 = bar0 + 16, kv_empty0 = kv_full0 + 8 * ST, sp_full = kv_empty0 + 8 * ST,
+                   sp_empty = sp_full + 8, ds_full = sp_full + 16, ds_empty = sp_full + 24, done = sp_full + 32, acc_empty = sp_full + 40,
+                   t_full0 = sp_full + 48;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10 + 2 * ST);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* tile_slots = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int d = a.H * DK;
@@ -144,6 +173,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
         mbar_init(sp_full, 1); mbar_init(sp_empty, 8);
         mbar_init(ds_full, 8); mbar_init(ds_empty, 1);
         mbar_init(done, 1); mbar_init(acc_empty, 8);
+        mbar_init(t_full0, 1); mbar_init(t_full0 + 8, 1);
         *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;
         if (*abort_flag) atomicCAS(&g_attn_bwd_error, 0, (9 << 16));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -175,7 +205,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
     if (warp == 0) {
         int kv = 0, tn = 0;
         bool ok = !*abort_flag;
-        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
+        for (int w; ok && (w = draw_tile(work, total, tile_slots, t_full0, tn, lane)) >= 0; ++tn) {
             const BwdTile t = bwd_tile(w, a.H, HB);
             const int qb = nt - 1 - t.t, q0 = qb * 128, nkb = 2 * (qb + 1), row_base = t.b * a.S;
             const BlockMask bm = tile_mask(t.b, qb, nkb);
@@ -208,18 +238,17 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
             kv = __shfl_sync(0xffffffffu, kv, 0);
             ok = __shfl_sync(0xffffffffu, static_cast<int>(ok), 0) != 0;
         }
+        leave_work_list(work, lane);
     } else if (warp == 1) {
         int kv0 = 0, tn = 0;
         bool ok = !*abort_flag;
-        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
+        for (int w; ok && (w = read_tile(tile_slots, t_full0, tn, abort_flag, &g_attn_bwd_error)) >= 0; ++tn) {
             const BwdTile t = bwd_tile(w, a.H, HB);
             const int qb = nt - 1 - t.t, nkb = 2 * (qb + 1);
             const BlockMask bm = tile_mask(t.b, qb, nkb);
             if (lane == 0) {
                 const int nact = block_count(bm, nkb);
                 ok = mbar_wait(q_full, tn & 1, abort_flag, 2, &g_attn_bwd_error);
-                // the accumulator this tile writes was read out by the workers at the end of the previous tile
-                if (ok && tn >= 1) ok = mbar_wait(acc_empty, (tn - 1) & 1, abort_flag, 12, &g_attn_bwd_error);
                 const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
                 auto issue_sdp = [&](int gj) -> bool {
                     const int st = gj % ST;
@@ -243,6 +272,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
                 auto issue_dq = [&](int gj, bool first) -> bool {
                     const int st = gj % ST;
                     if (!mbar_wait(ds_full, gj & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
+                    // the accumulator this tile writes was read out by the workers at the end of the previous tile
+                    if (first && tn >= 1 && !mbar_wait(acc_empty, (tn - 1) & 1, abort_flag, 12, &g_attn_bwd_error)) return false;
                     tc_fence_after();
                     const uint32_t ds_addr = smem_u32(sDS), k_addr = smem_u32(sRing + st * STAGE);
 #pragma unroll
@@ -252,12 +283,18 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
                     umma_commit(kv_empty0 + 8 * st);
                     return true;
                 };
+                // Q and dO are read by the score MMAs only: they are handed back with the last of those, so that the next
+                // tile's loads overlap the last block's worker pass, its dQ MMA and the write-out
                 if (ok) ok = issue_sdp(kv0);
+                if (ok && nact == 1) umma_commit(q_empty);
                 for (int j = 0; ok && j < nact; ++j) {
-                    if (j + 1 < nact) ok = issue_sdp(kv0 + j + 1);
+                    if (j + 1 < nact) {
+                        ok = issue_sdp(kv0 + j + 1);
+                        if (ok && j + 2 == nact) umma_commit(q_empty);
+                    }
                     if (ok) ok = issue_dq(kv0 + j, j == 0);
                 }
-                if (ok) { umma_commit(done); umma_commit(q_empty); }
+                if (ok) umma_commit(done);
                 kv0 += nact;
             }
             kv0 = __shfl_sync(0xffffffffu, kv0, 0);
@@ -273,7 +310,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
         bool ok = !*abort_flag;
         int kv0 = 0, tn = 0;
 
-        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
+        for (int w; ok && (w = read_tile(tile_slots, t_full0, tn, abort_flag, &g_attn_bwd_error)) >= 0; ++tn) {
             const BwdTile t = bwd_tile(w, a.H, HB);
             const int h = t.h, b = t.b, qb = nt - 1 - t.t, q0 = qb * 128, nkb = 2 * (qb + 1), row_base = b * a.S;
             const BlockMask bm = tile_mask(b, qb, nkb);
@@ -381,7 +418,7 @@ template <int DK> struct KvLayout {
 template <int DK, bool DOC, bool ALIBI>
 __global__ void __launch_bounds__(320, KvLayout<DK>::CTAS_PER_SM)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid_constant__ CUtensorMap tmQ64,
-                       const __grid_constant__ CUtensorMap tmDO64, const AttnBwdArgs a)
+                       const __grid_constant__ CUtensorMap tmDO64, const AttnBwdArgs a, unsigned int* __restrict__ work)
 {
     using LY = KvLayout<DK>;
     constexpr int ST = LY::ST, NS = LY::NS, STAGE = 2 * NS * HT;
@@ -395,9 +432,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + LY::OFF_BAR);
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t kv_full = bar0, kv_empty = bar0 + 8, q_full0 = bar0 + 16, q_empty0 = bar0 + 32, sp_full = bar0 + 48,
-                   sp_empty = bar0 + 56, pd_full = bar0 + 64, pd_empty = bar0 + 72, done = bar0 + 80, acc_empty = bar0 + 88;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+                   sp_empty = bar0 + 56, pd_full = bar0 + 64, pd_empty = bar0 + 72, done = bar0 + 80, acc_empty = bar0 + 88,
+                   t_full0 = bar0 + 96;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* tile_slots = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int d = a.H * DK;
@@ -409,6 +448,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
         mbar_init(sp_full, 1); mbar_init(sp_empty, 8);
         mbar_init(pd_full, 8); mbar_init(pd_empty, 1);
         mbar_init(done, 1); mbar_init(acc_empty, 8);
+        mbar_init(t_full0, 1); mbar_init(t_full0 + 8, 1);
         *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;
         if (*abort_flag) atomicCAS(&g_attn_bwd_error, 0, (9 << 16));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -440,7 +480,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
     if (warp == 0) {
         int qc = 0, tn = 0;                                    // query-block counter across tiles, tile counter
         bool ok = !*abort_flag;
-        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
+        for (int w; ok && (w = draw_tile(work, total, tile_slots, t_full0, tn, lane)) >= 0; ++tn) {
             const BwdTile t = bwd_tile(w, a.H, HB);
             const int kt = t.t, k0 = kt * 128, qi0 = kt * 2, nit = a.S / 64 - qi0, row_base = t.b * a.S;
             const BlockMask bm = tile_mask(t.b, kt, nit);
@@ -476,17 +516,17 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
             qc = __shfl_sync(0xffffffffu, qc, 0);
             ok = __shfl_sync(0xffffffffu, static_cast<int>(ok), 0) != 0;
         }
+        leave_work_list(work, lane);
     } else if (warp == 1) {
         int qc0 = 0, tn = 0;
         bool ok = !*abort_flag;
-        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
+        for (int w; ok && (w = read_tile(tile_slots, t_full0, tn, abort_flag, &g_attn_bwd_error)) >= 0; ++tn) {
             const BwdTile t = bwd_tile(w, a.H, HB);
             const int nit = a.S / 64 - t.t * 2;
             const BlockMask bm = tile_mask(t.b, t.t, nit);
             if (lane == 0) {
                 const int nact = block_count(bm, nit);
                 ok = mbar_wait(kv_full, tn & 1, abort_flag, 2, &g_attn_bwd_error);
-                if (ok && tn >= 1) ok = mbar_wait(acc_empty, (tn - 1) & 1, abort_flag, 12, &g_attn_bwd_error);
                 const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
                 auto issue_st = [&](int gi) -> bool {
                     const int st = gi % ST;
@@ -510,6 +550,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                 auto issue_dkv = [&](int gi, bool first) -> bool {
                     const int st = gi % ST;
                     if (!mbar_wait(pd_full, gi & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
+                    // the accumulators this tile writes were read out by the workers at the end of the previous tile
+                    if (first && tn >= 1 && !mbar_wait(acc_empty, (tn - 1) & 1, abort_flag, 12, &g_attn_bwd_error)) return false;
                     tc_fence_after();
                     const uint32_t pt_addr = smem_u32(sPT), dst_addr = smem_u32(sDST);
                     const uint32_t q_addr = smem_u32(sRing + st * STAGE), do_addr = q_addr + NS * HT;
@@ -523,12 +565,17 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                     umma_commit(q_empty0 + 8 * st);
                     return true;
                 };
+                // K and V are read by the score MMAs only: handed back with the last of those (see the dQ kernel)
                 if (ok) ok = issue_st(qc0);
+                if (ok && nact == 1) umma_commit(kv_empty);
                 for (int j = 0; ok && j < nact; ++j) {
-                    if (j + 1 < nact) ok = issue_st(qc0 + j + 1);
+                    if (j + 1 < nact) {
+                        ok = issue_st(qc0 + j + 1);
+                        if (ok && j + 2 == nact) umma_commit(kv_empty);
+                    }
                     if (ok) ok = issue_dkv(qc0 + j, j == 0);
                 }
-                if (ok) { umma_commit(done); umma_commit(kv_empty); }
+                if (ok) umma_commit(done);
                 qc0 += nact;
             }
             qc0 = __shfl_sync(0xffffffffu, qc0, 0);
@@ -544,7 +591,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
         bool ok = !*abort_flag;
         int qc0 = 0, tn = 0;
 
-        for (int ps = 0, w; ok && (w = snake_tile(ps)) < total; ++ps, ++tn) {
+        for (int w; ok && (w = read_tile(tile_slots, t_full0, tn, abort_flag, &g_attn_bwd_error)) >= 0; ++tn) {
             const BwdTile t = bwd_tile(w, a.H, HB);
             const int h = t.h, b = t.b, kt = t.t, k0 = kt * 128, qi0 = kt * 2, nit = a.S / 64 - qi0, row_base = b * a.S;
             const BlockMask bm = tile_mask(b, kt, nit);
@@ -668,9 +715,11 @@ static int launch_bwd_tc(const CUtensorMap& q128, const CUtensorMap& q64, const 
     }));
     const long long cap = static_cast<long long>(device_sm_count()) * DqLayout<DK>::CTAS_PER_SM;   // persistent kernels
     const dim3 grid(static_cast<unsigned>(tiles < cap ? tiles : cap));
-    attn_bwd_dq_tc_kernel<DK, DOC, ALIBI><<<grid, 320, DqLayout<DK>::SMEM, s>>>(q128, q64, do128, a);
+    unsigned int* work = nullptr;                   // both kernels find the pair at zero and leave it at zero
+    NNB_TRY(work_counter_pair(s, &work));
+    attn_bwd_dq_tc_kernel<DK, DOC, ALIBI><<<grid, 320, DqLayout<DK>::SMEM, s>>>(q128, q64, do128, a, work);
     NNB_LAUNCH_CHECK();
-    attn_bwd_dkv_tc_kernel<DK, DOC, ALIBI><<<grid, 320, KvLayout<DK>::SMEM, s>>>(q128, q64, do64, a);
+    attn_bwd_dkv_tc_kernel<DK, DOC, ALIBI><<<grid, 320, KvLayout<DK>::SMEM, s>>>(q128, q64, do64, a, work);
     NNB_LAUNCH_CHECK();
     return 0;
 }
