@@ -12,9 +12,10 @@
 // MN-major (second MMAs) from the same shared-memory tile.  Recomputing S in both kernels keeps the
 // gradients deterministic (the reference's backward_q / backward_kv split, cpu_engine.hpp:702-915).
 // K-major operands wider than 64 values are kept as sub-tiles of 64 columns (one 128-byte swizzle atom per row).
-// ALiBi: the bias -slope_h (i - j) is linear in both positions, so the tensor core adds its in-block part: one more
-// MMA step per score block multiplies a 16-deep tile holding slope_h / scale (three bf16 terms) in every row by a
-// constant tile holding the position inside the block of the other side; the workers add one constant per row.
+// ALiBi: the bias -slope_h (i - j) is linear in both positions.  In the dQ kernel the tensor core adds its in-block
+// part: one more MMA step per score block multiplies a 16-deep tile holding slope_h / scale (three bf16 terms) in
+// every row by a constant tile holding the key's position inside the block; the workers add one constant per row.
+// The dK/dV kernel spends that shared memory on the third ring stage and steps the bias in registers instead.
 // With a table of per-64-row document-id ranges (attention_doc_ranges) every role skips the blocks a document mask
 // leaves nothing of; a skipped block would have contributed exact zeros, so no result bit changes.
 #include <type_traits>
@@ -87,21 +88,29 @@ __device__ __forceinline__ void init_position_tiles(uint8_t* pos_tile, uint8_t* 
 
 // Both kernels are persistent: the CTAs resident on an SM draw (tile, head, batch) work items, heaviest tiles first,
 // from a counter in global memory (work_counter.cu; the producer warp draws and passes the item on to the other
-// roles through a two-slot ring in shared memory), so that a CTA whose tiles ran slowly takes fewer of them.  The rings, score buffers and barrier phases run on across tiles, so the loads and
-// first MMAs of the next tile overlap the tail and the write-out of the current one.  Every resource is
-// single-buffered (block ring of 2); at head size 64 two CTAs share an SM (256 TMEM columns, 80 / 97 KB of shared
-// memory, 96 registers each), so that while the workers of one CTA are in their dependency chain (scores ready ->
-// tcgen05.ld -> exp -> dS tile -> next MMA) the other CTA's MMAs run; at head size 128 one CTA fills the SM.
+// roles through a two-slot ring in shared memory), so that a CTA whose tiles ran slowly takes fewer of them.  The
+// rings, score buffers and barrier phases run on across tiles, and the tile that stays resident (Q and dO, resp. K
+// and V) is handed back with the last score MMA that reads it, so the loads and first MMAs of the next tile overlap
+// the tail and the write-out of the current one.  The block ring is three deep: a stage is free only when the
+// gradient MMAs of its block are complete, and with two stages the load of block j + 2 (issued when block j retires)
+// arrived after the workers had finished block j + 1, a third of every block period.  Score and gradient-tile
+// buffers are single; at head size 64 two CTAs share an SM (256 TMEM columns, 102 / 111 KB of shared memory, 96
+// registers each), so that while the workers of one CTA are in their dependency chain (scores ready -> tcgen05.ld
+// -> exp -> dS tile -> next MMA) the other CTA's MMAs run; at head size 128 one CTA fills the SM.
 // Producer side of the work list (whole warp): lane 0 draws the next item and publishes it (or -1 when the list is
-// exhausted) in slot n & 1; everybody gets the value.  A slot is reused two tiles later, when its readers are long past it.
+// exhausted) in slot n & 3; everybody gets the value.  An item is drawn when the producer is ready to load it, not
+// earlier (an item drawn is an item no other CTA can take; drawing one tile ahead, with an L2 prefetch of its first
+// operands, was measured slower: the prefetch bought nothing and the balance at the list's end got worse).  When item
+// n is published the producer has issued the loads of item n - 1 and the other roles may still be in item n - 2: a
+// ring of four slots keeps everything that may still be read.
 __device__ __forceinline__ int draw_tile(unsigned int* work, int total, volatile int* slots, uint32_t t_full0, int n, int lane)
 {
     int w = 0;
     if (lane == 0) {
         const unsigned int v = atomicAdd(work, 1u);
         w = v < static_cast<unsigned int>(total) ? static_cast<int>(v) : -1;
-        slots[n & 1] = w;
-        mbar_arrive(t_full0 + 8 * (n & 1));
+        slots[n & 3] = w;
+        mbar_arrive(t_full0 + 8 * (n & 3));
     }
     return __shfl_sync(0xffffffffu, w, 0);
 }
@@ -113,9 +122,9 @@ __device__ __forceinline__ void leave_work_list(unsigned int* work, int lane)
 // Consumer side (whole warp): the item of round n, -1 at the end or when the wait gave up.
 __device__ __forceinline__ int read_tile(volatile int* slots, uint32_t t_full0, int n, volatile int* abort_flag, int* error_word)
 {
-    const bool got = mbar_wait(t_full0 + 8 * (n & 1), (n >> 1) & 1, abort_flag, 14, error_word);
+    const bool got = mbar_wait(t_full0 + 8 * (n & 3), (n >> 2) & 1, abort_flag, 14, error_word);
     if (!__all_sync(0xffffffffu, got)) return -1;
-    return slots[n & 1];
+    return slots[n & 3];
 }
 
 struct BwdTile { int t, h, b; };
@@ -132,7 +141,7 @@ __device__ __forceinline__ BwdTile bwd_tile(int w, int H, int HB)
 // ======================================================================================
 // dQ
 // ======================================================================================
-// shared memory: Q | dO | ring of two (K, V) 64-key tiles | dS | barriers
+// shared memory: Q | dO | ring of three (K, V) 64-key tiles | dS | ALiBi operand tiles | barriers
 template <int DK> struct DqLayout {
     static constexpr int NS = DK / 64;                              // 64-column sub-tiles per operand tile
     static constexpr int ST = 3;                                    // (K, V) ring stages: a stage is free only when its dQ MMA is complete
@@ -159,7 +168,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
     const uint32_t q_full = bar0, q_empty = bar0 + 8, kv_full0 = bar0 + 16, kv_empty0 = kv_full0 + 8 * ST, sp_full = kv_empty0 + 8 * ST,
                    sp_empty = sp_full + 8, ds_full = sp_full + 16, ds_empty = sp_full + 24, done = sp_full + 32, acc_empty = sp_full + 40,
                    t_full0 = sp_full + 48;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10 + 2 * ST);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12 + 2 * ST);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* tile_slots = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -173,7 +182,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
         mbar_init(sp_full, 1); mbar_init(sp_empty, 8);
         mbar_init(ds_full, 8); mbar_init(ds_empty, 1);
         mbar_init(done, 1); mbar_init(acc_empty, 8);
-        mbar_init(t_full0, 1); mbar_init(t_full0 + 8, 1);
+        for (int k = 0; k < 4; ++k) mbar_init(t_full0 + 8 * k, 1);
         *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;
         if (*abort_flag) atomicCAS(&g_attn_bwd_error, 0, (9 << 16));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -404,13 +413,16 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
 // ======================================================================================
 // dK, dV
 // ======================================================================================
-// shared memory: K | V | ring of two (Q, dO) 64-query tiles | P^T | dS^T | lse, D per stage | barriers
+// shared memory: K | V | ring of three Q tiles (64 queries) | ring of two dO tiles | P^T | dS^T | lse per Q stage, D per
+// dO stage | barriers.  A stage is free only when the dK / dV MMAs of its block are complete, so with two stages the
+// load of block i + 2 would arrive after the workers have finished block i + 1.  Shared memory has room for one more
+// 8 KB tile per CTA, not two: Q, which the first MMA of a block needs (and with it the exponentials), gets it, and
+// S^T and dP^T are handed to the workers separately so that dP^T of a block may come half a block later.
 template <int DK> struct KvLayout {
     static constexpr int NS = DK / 64;
-    static constexpr int ST = 2;                                    // (Q, dO) ring stages
-    static constexpr int OFF_V = NS * BT, OFF_RING = 2 * NS * BT, OFF_PT = OFF_RING + ST * 2 * NS * HT, OFF_DST = OFF_PT + BT,
-                         OFF_STAT = OFF_DST + BT, OFF_U = OFF_STAT + ST * 512, OFF_W = OFF_U + XT, OFF_BAR = OFF_W + XT,
-                         SMEM = OFF_BAR + 256;
+    static constexpr int QST = 3, DST = 2;                          // Q and dO ring stages
+    static constexpr int OFF_V = NS * BT, OFF_QR = 2 * NS * BT, OFF_DOR = OFF_QR + QST * NS * HT, OFF_PT = OFF_DOR + DST * NS * HT,
+                         OFF_DST = OFF_PT + BT, OFF_STAT = OFF_DST + BT, OFF_BAR = OFF_STAT + (QST + DST) * 256, SMEM = OFF_BAR + 256;
     static constexpr uint32_t TMEM_COLS = DK == 64 ? 256u : 512u;   // S^T [0, 64) | dP^T [64, 128) | dV [128, 128 + DK) | dK after it
     static constexpr int CTAS_PER_SM = DK == 64 ? 2 : 1;
 };
@@ -421,20 +433,23 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                        const __grid_constant__ CUtensorMap tmDO64, const AttnBwdArgs a, unsigned int* __restrict__ work)
 {
     using LY = KvLayout<DK>;
-    constexpr int ST = LY::ST, NS = LY::NS, STAGE = 2 * NS * HT;
+    constexpr int QST = LY::QST, DST = LY::DST, NS = LY::NS, QSTAGE = NS * HT;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sK = smem;
     uint8_t* sV = smem + LY::OFF_V;
-    uint8_t* sRing = smem + LY::OFF_RING;           // stage s: Q at +s*STAGE, dO right after
+    uint8_t* sQR = smem + LY::OFF_QR;               // Q ring
+    uint8_t* sDOR = smem + LY::OFF_DOR;             // dO ring
     uint8_t* sPT = smem + LY::OFF_PT;
     uint8_t* sDST = smem + LY::OFF_DST;
-    float* sStat = reinterpret_cast<float*>(smem + LY::OFF_STAT);   // [stage][lse(64) | D(64)]
+    float* sLse = reinterpret_cast<float*>(smem + LY::OFF_STAT);    // [Q stage][64]
+    float* sD = sLse + QST * 64;                                    // [dO stage][64]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + LY::OFF_BAR);
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t kv_full = bar0, kv_empty = bar0 + 8, q_full0 = bar0 + 16, q_empty0 = bar0 + 32, sp_full = bar0 + 48,
-                   sp_empty = bar0 + 56, pd_full = bar0 + 64, pd_empty = bar0 + 72, done = bar0 + 80, acc_empty = bar0 + 88,
-                   t_full0 = bar0 + 96;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    const uint32_t kv_full = bar0, kv_empty = bar0 + 8, q_full0 = bar0 + 16, q_empty0 = q_full0 + 8 * QST, do_full0 = q_empty0 + 8 * QST,
+                   do_empty0 = do_full0 + 8 * DST, s_full = do_empty0 + 8 * DST, s_empty = s_full + 8, dp_full = s_full + 16,
+                   dp_empty = s_full + 24, pd_full = s_full + 32, pd_empty = s_full + 40, done = s_full + 48, acc_empty = s_full + 56,
+                   t_full0 = s_full + 64;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14 + 2 * QST + 2 * DST);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* tile_slots = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -444,11 +459,12 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
 
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1); mbar_init(kv_empty, 1);
-        for (int s = 0; s < ST; ++s) { mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1); }
-        mbar_init(sp_full, 1); mbar_init(sp_empty, 8);
+        for (int s = 0; s < QST; ++s) { mbar_init(q_full0 + 8 * s, 1); mbar_init(q_empty0 + 8 * s, 1); }
+        for (int s = 0; s < DST; ++s) { mbar_init(do_full0 + 8 * s, 1); mbar_init(do_empty0 + 8 * s, 1); }
+        mbar_init(s_full, 1); mbar_init(s_empty, 8); mbar_init(dp_full, 1); mbar_init(dp_empty, 8);
         mbar_init(pd_full, 8); mbar_init(pd_empty, 1);
         mbar_init(done, 1); mbar_init(acc_empty, 8);
-        mbar_init(t_full0, 1); mbar_init(t_full0 + 8, 1);
+        for (int k = 0; k < 4; ++k) mbar_init(t_full0 + 8 * k, 1);
         *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;
         if (*abort_flag) atomicCAS(&g_attn_bwd_error, 0, (9 << 16));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -463,12 +479,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_ST = tmem_base, tmem_dPT = tmem_base + 64, tmem_dV = tmem_base + 128, tmem_dK = tmem_base + 128 + DK;
-    uint8_t* sU = smem + LY::OFF_U;                 // slope_h / scale in every key row (rewritten per tile by warp 0)
-    uint8_t* sW = smem + LY::OFF_W;                 // minus the query position inside the 64-query block, constant
-    if (ALIBI) {
-        init_position_tiles(sW, sU, 64, -1.0f);
-        __syncthreads();
-    }
 
     // query blocks (64 queries each, from the diagonal on) of a key tile that the document mask leaves anything of
     auto tile_mask = [&](int b, int kt, int nit) -> BlockMask {
@@ -486,7 +496,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
             const BlockMask bm = tile_mask(t.b, kt, nit);
             if (lane == 0) ok = mbar_wait(kv_empty, (tn & 1) ^ 1, abort_flag, 11, &g_attn_bwd_error);   // the previous tile's MMAs are done
             ok = __shfl_sync(0xffffffffu, static_cast<int>(ok), 0) != 0;
-            if (ALIBI && ok) write_slope_tile(sU, t.h, a.H, a.scale, lane);
             if (lane == 0) {
                 const size_t stat_base = (static_cast<size_t>(t.b) * a.H + t.h) * a.S;
                 if (ok) {
@@ -499,17 +508,21 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                 }
                 for (int it = 0; ok && it < nit; ++it) {
                     if (!block_active(bm, it)) continue;
-                    const int st = qc % ST, qs = (qi0 + it) * 64;
-                    if (!mbar_wait(q_empty0 + 8 * st, ((qc / ST) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) { ok = false; break; }
-                    mbar_expect_tx(q_full0 + 8 * st, STAGE + 512);
-                    const uint32_t dst = smem_u32(sRing + st * STAGE);
+                    // Both rings are released by the gradient MMAs of a block; the Q ring is one stage deeper, so when
+                    // block qc - 2 retires this thread loads dO of block qc and, at once, Q of block qc + 1.
+                    const int qst = qc % QST, dst = qc % DST, qs = (qi0 + it) * 64;
+                    if (!mbar_wait(q_empty0 + 8 * qst, ((qc / QST) & 1) ^ 1, abort_flag, 1, &g_attn_bwd_error)) { ok = false; break; }
+                    mbar_expect_tx(q_full0 + 8 * qst, QSTAGE + 256);
 #pragma unroll
-                    for (int j = 0; j < NS; ++j) {
-                        tma_load_2d(dst + j * HT, &tmQ64, q_full0 + 8 * st, t.h * DK + j * 64, row_base + qs);
-                        tma_load_2d(dst + NS * HT + j * HT, &tmDO64, q_full0 + 8 * st, t.h * DK + j * 64, row_base + qs);
-                    }
-                    bulk_load_1d(smem_u32(sStat + st * 128), a.lse + stat_base + qs, 256, q_full0 + 8 * st);
-                    bulk_load_1d(smem_u32(sStat + st * 128 + 64), a.dvec + stat_base + qs, 256, q_full0 + 8 * st);
+                    for (int j = 0; j < NS; ++j)
+                        tma_load_2d(smem_u32(sQR + qst * QSTAGE + j * HT), &tmQ64, q_full0 + 8 * qst, t.h * DK + j * 64, row_base + qs);
+                    bulk_load_1d(smem_u32(sLse + qst * 64), a.lse + stat_base + qs, 256, q_full0 + 8 * qst);
+                    if (!mbar_wait(do_empty0 + 8 * dst, ((qc / DST) & 1) ^ 1, abort_flag, 15, &g_attn_bwd_error)) { ok = false; break; }
+                    mbar_expect_tx(do_full0 + 8 * dst, QSTAGE + 256);
+#pragma unroll
+                    for (int j = 0; j < NS; ++j)
+                        tma_load_2d(smem_u32(sDOR + dst * QSTAGE + j * HT), &tmDO64, do_full0 + 8 * dst, t.h * DK + j * 64, row_base + qs);
+                    bulk_load_1d(smem_u32(sD + dst * 64), a.dvec + stat_base + qs, 256, do_full0 + 8 * dst);
                     ++qc;
                 }
             }
@@ -528,33 +541,40 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                 const int nact = block_count(bm, nit);
                 ok = mbar_wait(kv_full, tn & 1, abort_flag, 2, &g_attn_bwd_error);
                 const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-                auto issue_st = [&](int gi) -> bool {
-                    const int st = gi % ST;
-                    if (!mbar_wait(q_full0 + 8 * st, (gi / ST) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
-                    if (gi >= 1 && !mbar_wait(sp_empty, (gi - 1) & 1, abort_flag, 4, &g_attn_bwd_error)) return false;
+                auto issue_s = [&](int gi) -> bool {               // S^T = K Q^T: needs Q of the block and the score columns
+                    const int st = gi % QST;
+                    if (!mbar_wait(q_full0 + 8 * st, (gi / QST) & 1, abort_flag, 3, &g_attn_bwd_error)) return false;
+                    if (gi >= 1 && !mbar_wait(s_empty, (gi - 1) & 1, abort_flag, 4, &g_attn_bwd_error)) return false;
                     tc_fence_after();
-                    const uint32_t q_addr = smem_u32(sRing + st * STAGE), do_addr = q_addr + NS * HT;
+                    const uint32_t q_addr = smem_u32(sQR + st * QSTAGE);
 #pragma unroll
                     for (int k = 0; k < DK / 16; ++k)
                         umma_bf16(tmem_ST, smem_desc(k_addr + (k >> 2) * BT + (k & 3) * 32, 16, 1024),
                                   smem_desc(q_addr + (k >> 2) * HT + (k & 3) * 32, 16, 1024), IDESC_KK, k > 0);
-                    if (ALIBI)       // - (slope / scale) * (query position inside the block)
-                        umma_bf16(tmem_ST, smem_desc_noswizzle(smem_u32(sU), 128, 256), smem_desc_noswizzle(smem_u32(sW), 128, 256), IDESC_KK, 1u);
+                    umma_commit(s_full);
+                    return true;
+                };
+                auto issue_dp = [&](int gi) -> bool {              // dP^T = V dO^T: needs dO of the block and the dP columns
+                    const int st = gi % DST;
+                    if (!mbar_wait(do_full0 + 8 * st, (gi / DST) & 1, abort_flag, 16, &g_attn_bwd_error)) return false;
+                    if (gi >= 1 && !mbar_wait(dp_empty, (gi - 1) & 1, abort_flag, 17, &g_attn_bwd_error)) return false;
+                    tc_fence_after();
+                    const uint32_t do_addr = smem_u32(sDOR + st * QSTAGE);
 #pragma unroll
                     for (int k = 0; k < DK / 16; ++k)
                         umma_bf16(tmem_dPT, smem_desc(v_addr + (k >> 2) * BT + (k & 3) * 32, 16, 1024),
                                   smem_desc(do_addr + (k >> 2) * HT + (k & 3) * 32, 16, 1024), IDESC_KK, k > 0);
-                    umma_commit(sp_full);
+                    umma_commit(dp_full);
                     return true;
                 };
                 auto issue_dkv = [&](int gi, bool first) -> bool {
-                    const int st = gi % ST;
+                    const int qst = gi % QST, dst = gi % DST;
                     if (!mbar_wait(pd_full, gi & 1, abort_flag, 5, &g_attn_bwd_error)) return false;
                     // the accumulators this tile writes were read out by the workers at the end of the previous tile
                     if (first && tn >= 1 && !mbar_wait(acc_empty, (tn - 1) & 1, abort_flag, 12, &g_attn_bwd_error)) return false;
                     tc_fence_after();
                     const uint32_t pt_addr = smem_u32(sPT), dst_addr = smem_u32(sDST);
-                    const uint32_t q_addr = smem_u32(sRing + st * STAGE), do_addr = q_addr + NS * HT;
+                    const uint32_t q_addr = smem_u32(sQR + qst * QSTAGE), do_addr = smem_u32(sDOR + dst * QSTAGE);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         umma_bf16(tmem_dV, smem_desc(pt_addr + k * 32, 16, 1024), smem_desc(do_addr + k * 2048, HT, 1024), idesc_km<DK>(), (!first || k > 0));
@@ -562,15 +582,16 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                     for (int k = 0; k < 4; ++k)
                         umma_bf16(tmem_dK, smem_desc(dst_addr + k * 32, 16, 1024), smem_desc(q_addr + k * 2048, HT, 1024), idesc_km<DK>(), (!first || k > 0));
                     umma_commit(pd_empty);
-                    umma_commit(q_empty0 + 8 * st);
+                    umma_commit(q_empty0 + 8 * qst);
+                    umma_commit(do_empty0 + 8 * dst);
                     return true;
                 };
                 // K and V are read by the score MMAs only: handed back with the last of those (see the dQ kernel)
-                if (ok) ok = issue_st(qc0);
+                if (ok) ok = issue_s(qc0) && issue_dp(qc0);
                 if (ok && nact == 1) umma_commit(kv_empty);
                 for (int j = 0; ok && j < nact; ++j) {
                     if (j + 1 < nact) {
-                        ok = issue_st(qc0 + j + 1);
+                        ok = issue_s(qc0 + j + 1) && issue_dp(qc0 + j + 1);
                         if (ok && j + 2 == nact) umma_commit(kv_empty);
                     }
                     if (ok) ok = issue_dkv(qc0 + j, j == 0);
@@ -601,44 +622,68 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
 
             auto block = [&](auto diag_tag, int it, int cnt) -> bool {
                 constexpr bool DIAG = decltype(diag_tag)::value;
-                const int gi = qc0 + cnt, st = gi % ST;
-                if (!mbar_wait(sp_full, gi & 1, abort_flag, 6, &g_attn_bwd_error)) return false;
+                const int gi = qc0 + cnt;
+                if (!mbar_wait(s_full, gi & 1, abort_flag, 6, &g_attn_bwd_error)) return false;
                 tc_fence_after();
                 const int qs = (qi0 + it) * 64 + hf * 32;              // first query of this thread's 32 columns
                 uint32_t rs[32], rp[32];
                 tmem_ld32(tmem_ST + lane_addr + hf * 32, rs);
-                tmem_ld32(tmem_dPT + lane_addr + hf * 32, rp);
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sp_empty);
-                const float4* lse4 = reinterpret_cast<const float4*>(sStat + st * 128 + hf * 32);
-                const float4* dv4 = reinterpret_cast<const float4*>(sStat + st * 128 + 64 + hf * 32);
+                if (lane == 0) mbar_arrive(s_empty);
+                const float4* lse4 = reinterpret_cast<const float4*>(sLse + (gi % QST) * 64 + hf * 32);
+                const float4* dv4 = reinterpret_cast<const float4*>(sD + (gi % DST) * 64 + hf * 32);
                 const int* dq_ptr = DOC ? a.doc + row_base + qs : nullptr;
-                // base-2 exponent of P^T: raw * scale2 + base - lse2 of the column's query; the -slope2 * (query position
-                // inside the block) part of the ALiBi bias is in raw already
-                const float base = ALIBI ? -slope2 * static_cast<float>((qi0 + it) * 64 - j) : 0.f;
-                const uint64_t base2 = pack2(base, base), scale2x2 = pack2(scale2, scale2), negl2e = pack2(-kL2e, -kL2e),
+                // base-2 exponent of P^T: raw * scale2 - slope2 * (query - key) - lse2 of the column's query; the bias of a
+                // pair of columns is carried along and stepped by -2 slope2 (this kernel has no shared memory left for the
+                // operand tiles with which the other kernels let the tensor core add the bias)
+                const float base = ALIBI ? -slope2 * static_cast<float>(qs - j) : 0.f;
+                uint64_t base2 = pack2(base, base - slope2);
+                const uint64_t step2 = pack2(-2.f * slope2, -2.f * slope2), scale2x2 = pack2(scale2, scale2), negl2e = pack2(-kL2e, -kL2e),
                                neg1 = pack2(-1.f, -1.f);
+                // first the exponentials (they need S^T and the log-sum-exp only); P stays in rs as fp32 for the second half
                 uint32_t pk[16], dk[16];
 #pragma unroll
                 for (int c4 = 0; c4 < 8; ++c4) {
-                    const float4 l4 = lse4[c4], d4 = dv4[c4];
-                    const uint64_t lsp[2] = {pack2(l4.x, l4.y), pack2(l4.z, l4.w)}, ddp[2] = {pack2(d4.x, d4.y), pack2(d4.z, d4.w)};
+                    const float4 l4 = lse4[c4];
+                    const uint64_t lsp[2] = {pack2(l4.x, l4.y), pack2(l4.z, l4.w)};
 #pragma unroll
                     for (int e2 = 0; e2 < 2; ++e2) {
                         const int c = c4 * 4 + e2 * 2;
                         float x0, x1;
                         unpack2(fma2(lsp[e2], negl2e, fma2(pack2(__uint_as_float(rs[c]), __uint_as_float(rs[c + 1])), scale2x2, base2)), x0, x1);
+                        if (ALIBI) base2 = add2(base2, step2);
                         float p0 = ex2a(x0), p1 = ex2a(x1);
                         if (DIAG && j > qs + c) p0 = 0.f;
                         if (DIAG && j > qs + c + 1) p1 = 0.f;
                         if (DOC && dq_ptr[c] != my_doc) p0 = 0.f;
                         if (DOC && dq_ptr[c + 1] != my_doc) p1 = 0.f;
-                        float d0, d1;
-                        unpack2(mul2(pack2(p0, p1), fma2(ddp[e2], neg1, pack2(__uint_as_float(rp[c]), __uint_as_float(rp[c + 1])))), d0, d1);
-                        __nv_bfloat162 tp = __floats2bfloat162_rn(p0, p1), td = __floats2bfloat162_rn(d0, d1);
+                        rs[c] = __float_as_uint(p0);
+                        rs[c + 1] = __float_as_uint(p1);
+                        __nv_bfloat162 tp = __floats2bfloat162_rn(p0, p1);
                         pk[c4 * 2 + e2] = *reinterpret_cast<uint32_t*>(&tp);
+                    }
+                }
+                // then dS^T = P^T o (dP^T - D): dP^T of this block may arrive later than S^T (its ring is one stage shorter)
+                if (!mbar_wait(dp_full, gi & 1, abort_flag, 18, &g_attn_bwd_error)) return false;
+                tc_fence_after();
+                tmem_ld32(tmem_dPT + lane_addr + hf * 32, rp);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dp_empty);
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const float4 d4 = dv4[c4];
+                    const uint64_t ddp[2] = {pack2(d4.x, d4.y), pack2(d4.z, d4.w)};
+#pragma unroll
+                    for (int e2 = 0; e2 < 2; ++e2) {
+                        const int c = c4 * 4 + e2 * 2;
+                        float d0, d1;
+                        unpack2(mul2(pack2(__uint_as_float(rs[c]), __uint_as_float(rs[c + 1])),
+                                     fma2(ddp[e2], neg1, pack2(__uint_as_float(rp[c]), __uint_as_float(rp[c + 1])))), d0, d1);
+                        __nv_bfloat162 td = __floats2bfloat162_rn(d0, d1);
                         dk[c4 * 2 + e2] = *reinterpret_cast<uint32_t*>(&td);
                     }
                 }
