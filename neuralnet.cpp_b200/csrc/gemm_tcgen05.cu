@@ -437,7 +437,9 @@ static int max_pairs(Kernel kernel, int smem)
 }
 
 constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_STAGES_RES = 5;                          // the residual staging tiles take one operand stage's room
 constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + 2 * C_STAGE_BYTES + 256 * 4 + 1024 + 256;
+static_assert(PAIR_STAGES_RES * PAIR_STAGE_BYTES + 4 * C_STAGE_BYTES + 256 * 4 + 1024 + 256 <= PAIR_SMEM, "the residual variant must fit the same shared memory");
 static_assert(PAIR_SMEM <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 
 // number of CTA pairs the current device runs at once; 0 = the pair kernel cannot be used there
@@ -447,19 +449,20 @@ static int pair_capacity()
     const int dev = current_device_slot();
     int n = cache[dev].load(std::memory_order_relaxed);
     if (n == 0) {
-        if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<false, false, PAIR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM) != cudaSuccess) { cudaGetLastError(); n = -1; }
-        else n = max_pairs(gemm_bf16_pair_kernel<false, false, PAIR_STAGES>, PAIR_SMEM);
+        if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<false, false, PAIR_STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM) != cudaSuccess) { cudaGetLastError(); n = -1; }
+        else n = max_pairs(gemm_bf16_pair_kernel<false, false, PAIR_STAGES, false>, PAIR_SMEM);
         if (n <= 0) n = -1;
         cache[dev].store(n, std::memory_order_relaxed);
     }
     return n > 0 ? n : 0;
 }
 
-template <bool A_MN, bool B_MN>
-static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tcm, const GemmParams& p, cudaStream_t s)
+template <bool A_MN, bool B_MN, bool RES = false>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tcm, const CUtensorMap& tr, const GemmParams& p, cudaStream_t s)
 {
+    constexpr int STAGES = RES ? PAIR_STAGES_RES : PAIR_STAGES;
     static PerDeviceOnce once;
-    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, PAIR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
+    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
     const int units = p.tiles_m * p.tiles_n * p.splits;
     const int pairs = units < pair_capacity() ? units : pair_capacity();
     cudaLaunchConfig_t cfg = {};
@@ -472,7 +475,7 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
     if (g_prof.on) prof_event(s);
-    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, PAIR_STAGES>, ta, tb, tcm, p));
+    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES>, ta, tb, tcm, tr, p));
     if (g_prof.on) { prof_event(s); g_prof.flops += 2.0 * p.M * p.N * p.K; }
     NNB_LAUNCH_CHECK();
     return 0;
@@ -526,10 +529,16 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
     if (p.tma_store) NNB_TRY(tensor_map_2d(C, N, M, ldc, c_bf16 ? 64 : 32, BM, &tcm, esz));
 
     if (pair) {
-        if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(ta, tb, tcm, p, stream);
-        if (!a_mn && b_mn) return launch_gemm_pair<false, true>(ta, tb, tcm, p, stream);
-        if (a_mn && !b_mn) return launch_gemm_pair<true, false>(ta, tb, tcm, p, stream);
-        return launch_gemm_pair<true, true>(ta, tb, tcm, p, stream);
+        // a bf16 residual of a forward projection (both operands K-major) goes through its own staging tiles
+        if (!a_mn && !b_mn && residual && c_bf16) {
+            CUtensorMap tr;
+            NNB_TRY(tensor_map_2d(residual, N, M, ldc, 64, BM, &tr, 2));
+            return launch_gemm_pair<false, false, true>(ta, tb, tcm, tr, p, stream);
+        }
+        if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(ta, tb, tcm, tcm, p, stream);
+        if (!a_mn && b_mn) return launch_gemm_pair<false, true>(ta, tb, tcm, tcm, p, stream);
+        if (a_mn && !b_mn) return launch_gemm_pair<true, false>(ta, tb, tcm, tcm, p, stream);
+        return launch_gemm_pair<true, true>(ta, tb, tcm, tcm, p, stream);
     }
 #define GO(bn, am, bm) return launch_gemm<bn, am, bm>(ta, tb, tcm, p, stream)
     if (BN == 256) {

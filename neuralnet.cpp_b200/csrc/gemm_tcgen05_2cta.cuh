@@ -16,6 +16,14 @@
 // the sixteen epilogue warps of the pair.  All TMA loads are plain (no cluster multicast).  Every wait is
 // bounded as in the one-CTA kernel; a CTA that gives up still joins the cluster barrier at the end, so its
 // shared memory and TMEM outlive anything the peer may still send to them.
+//
+// RES: a bf16 residual (same shape and leading dimension as the output) is added in the epilogue.  Read straight from
+// global memory by the thread that owns the row it is a round trip to L2 or HBM per column block inside the drain (the
+// out-projection of the benchmark model took 40 us against 24 us for the same product without residual), and fetched
+// ahead into registers it cost the kernel its register budget.  In this form each epilogue group has a second staging
+// tile into which its elected thread TMA-loads the residual tile of the group's next column block (of this unit or
+// the next) as soon as the group has consumed the previous one, a whole block period ahead; the threads read it with
+// the swizzle they write the output with.  The 32 KB come out of the operand ring (five stages instead of six).
 #pragma once
 
 namespace nnb {
@@ -23,10 +31,10 @@ namespace nnb {
 constexpr int PAIR_BN_HALF = 128;                                // rows of B each CTA stages per k-block
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_BN_HALF * BK * 2;
 
-template <bool A_MN, bool B_MN, int STAGES>
+template <bool A_MN, bool B_MN, int STAGES, bool RES>
 __global__ void __launch_bounds__(320, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const __grid_constant__ CUtensorMap tmC, const GemmParams p)
+                      const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR, const GemmParams p)
 {
     constexpr int BN = 256;                                      // accumulator columns per CTA
     constexpr int B_STAGE_BYTES = PAIR_BN_HALF * BK * 2;
@@ -41,11 +49,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
     uint8_t* sC = sB + STAGES * B_STAGE_BYTES;
-    float* sBias = reinterpret_cast<float*>(sC + 2 * C_STAGE_BYTES);
+    uint8_t* sR = sC + 2 * C_STAGE_BYTES;                                 // RES: one residual tile per epilogue group
+    float* sBias = reinterpret_cast<float*>(sR + (RES ? 2 * C_STAGE_BYTES : 0));
     uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + BN);             // each epilogue group keeps the bias of its own 128 columns
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
-    const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16, drain_bar = tempty0 + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+    const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16, drain_bar = tempty0 + 16, res_full0 = drain_bar + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 7);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -56,6 +65,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 16); }
         mbar_init(drain_bar, 1);
+        mbar_init(res_full0, 1); mbar_init(res_full0 + 8, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -149,6 +159,28 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         uint8_t* stage = sC + grp * C_STAGE_BYTES;
         uint8_t* srow = stage + r_local * 128;
         float* bias_s = sBias + grp * (BN / 2);
+        uint8_t* rstage = sR + grp * C_STAGE_BYTES;
+        const uint8_t* rrow = rstage + r_local * 128;
+        const uint32_t res_full = res_full0 + 8 * grp;
+        int res_uses = 0;                                            // residual tiles of this group consumed so far (barrier phase)
+        // The elected thread requests the residual tiles in the order the group drains column blocks, always one ahead:
+        // (ru, rcb) is the block requested last.  A block the drain loop skips (beyond N or M) is skipped here too.
+        int ru = pair, rcb = grp - 2;
+        auto request_next_residual = [&]() {
+            for (;;) {
+                rcb += 2;
+                if (rcb * 64 >= BN) { ru += pairs; rcb = grp; }
+                if (ru >= units) return;
+                const int t = ru % tiles;
+                const int tile_n = t / p.tiles_m, tile_m = t - tile_n * p.tiles_m;
+                const int n0 = tile_n * BN + rcb * 64, m0 = tile_m * 256 + static_cast<int>(rank) * 128;
+                if (n0 >= p.N || m0 >= p.M) continue;
+                mbar_expect_tx(res_full, C_STAGE_BYTES);
+                tma_load_2d(smem_u32(rstage), &tmR, res_full, n0, m0);
+                return;
+            }
+        };
+        if (RES && elected) request_next_residual();
         int tc = 0;
         for (int u = pair; u < units; u += pairs, ++tc) {
             const int split = u / tiles, t = u - split * tiles;
@@ -202,10 +234,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     }
                     const int nh = n0 + half * 32;
                     if (p.c_bf16) {
-                        const bf16* rp = (p.residual && add_extra && row_ok) ? static_cast<const bf16*>(p.residual) + row_off + nh : nullptr;
+                        const bf16* rp = (!RES && p.residual && add_extra && row_ok) ? static_cast<const bf16*>(p.residual) + row_off + nh : nullptr;
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
-                            if (rp && nh + j + 8 <= p.N) { const Vec16<bf16> rr = ld16(rp + j);
+                            if (RES) {                            // rows and columns beyond the matrix were filled with zeros by the load
+                                const Vec16<bf16> rr = *reinterpret_cast<const Vec16<bf16>*>(rrow + (((half * 4 + (j >> 3)) ^ (r_local & 7)) << 4));
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) v[j + k] += __bfloat162float(rr.v[k]);
+                            } else if (rp && nh + j + 8 <= p.N) { const Vec16<bf16> rr = ld16(rp + j);
 #pragma unroll
                                 for (int k = 0; k < 8; ++k) v[j + k] += __bfloat162float(rr.v[k]); }
                             else if (rp) { for (int k = 0; k < 8; ++k) if (nh + j + k < p.N) v[j + k] += __bfloat162float(rp[j + k]); }
@@ -227,6 +263,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         }
                     }
                 };
+                if (RES) {                                       // this block's residual tile, requested a block period ago
+                    const bool got = mbar_wait(res_full, res_uses & 1, abort_flag, 11, &g_gemm_error);
+                    ++res_uses;
+                    if (group_any(bar_id, !got)) break;
+                }
                 emit(ra, 0);
                 if (piped) tmem_ld_wait();                       // second half
                 if (CB == 64) emit(rb, 1);
@@ -236,6 +277,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     if (p.accumulate) tma_reduce_add_2d(&tmC, smem_u32(stage), n0, m0);
                     else tma_store_2d(&tmC, smem_u32(stage), n0, m0);
                     tma_commit();
+                    if (RES) request_next_residual();            // the group is past its reads of the residual tile
                 }
             }
             }

@@ -66,11 +66,13 @@ def test_gemm_bf16_ragged_shapes(g, M, N, K):
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
-@pytest.mark.parametrize("M,N,K", [(640, 768, 512), (304, 520, 136), (1000, 264, 1032), (8192, 2304, 64), (4096, 2560, 192)])
+@pytest.mark.parametrize("M,N,K", [(640, 768, 512), (304, 520, 136), (1000, 264, 1032), (8192, 2304, 64), (4096, 2560, 192),
+                                   (2000, 840, 256), (20000, 768, 128)])
 def test_gemm_bf16_cta_pair_tiles(g, a_mn, b_mn, M, N, K):
     """Outputs larger than one 128 x 128 block run 256 x 256 tiles on CTA pairs: ragged rows where the second
-    CTA of a pair has nothing to store (304, 1000), ragged columns, several tiles per pair (both TMEM
-    accumulator buffers and every pipeline stage wrap around), all operand layouts."""
+    CTA of a pair has nothing to store (304, 1000), ragged columns (840: the last column tile holds one full and one
+    8-column block, two more are skipped), several tiles per pair (both TMEM accumulator buffers, every pipeline stage
+    and the residual staging tiles wrap around), all operand layouts."""
     _gemm_case(g, M, N, K, a_mn, b_mn, c_bf16=True, bias=True, residual=True, accumulate=False, seed=M + a_mn)
     _gemm_case(g, M, N, K, a_mn, b_mn, c_bf16=False, bias=True, residual=False, accumulate=False, seed=N + b_mn)
 
