@@ -275,6 +275,8 @@ def main():
     ap.add_argument("--config", type=int, default=3, choices=[2, 3, 4], help="BASELINE training configuration (default 3, the headline)")
     ap.add_argument("--host", default="python", choices=["python", "cpp"], help="cpp: the C++ Layer/Optimizer host (configuration 3, 1 GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (rank 0, N=1 only)")
+    ap.add_argument("--grad-buckets", default="fp32", choices=["fp32", "bf16"],
+                    help="dtype the gradient buckets are all-reduced in at N > 1 (bf16: half the bytes, gradients rounded once per rank)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -303,7 +305,8 @@ def main():
     pos = {"learned": nnb.POS_LEARNED, "sinusoidal": nnb.POS_SINUSOIDAL, "alibi": nnb.POS_ALIBI}[w["pos"]]
     cfg = nnb.GptConfig(w["vocab"], w["d_model"], w["heads"], w["layers"], w["d_ff"], w["seq"], w["batch"],
                         nnb.ACT_SWIGLU, nnb.NORM_RMS, pos, nnb.BF16)
-    tr = nnb.GptTrainer(cfg, lr=BASE_LR, weight_decay=WEIGHT_DECAY, muon=w["muon"], muon_lr=MUON_LR, process_group=pg)
+    tr = nnb.GptTrainer(cfg, lr=BASE_LR, weight_decay=WEIGHT_DECAY, muon=w["muon"], muon_lr=MUON_LR, process_group=pg,
+                        grad_reduce_dtype=args.grad_buckets)
     tr.init_params_normal(seed=42, std=0.02)
     ntok, accum = w["batch"] * w["seq"], w["accum"]
 
