@@ -103,6 +103,9 @@ int nnb200_gemm_status(int* host_code)
     int attn_b = 0;
     NNB_TRY(attention_bwd_device_error(&attn_b));
     if (!*host_code && attn_b) *host_code = attn_b | 0x20000000;   // bit 29: attention backward kernels
+    int fused = 0;
+    NNB_TRY(fused_device_error(&fused));
+    if (!*host_code && fused) *host_code = fused | 0x10000000;    // bit 28: norm backward (bulk-copy waits)
     return 0;
 }
 

@@ -45,11 +45,6 @@ __device__ __forceinline__ float ex2a(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
 
 // fp32 accumulate, bf16 operands, M = 128; score MMAs: N = 64, both operands K-major; gradient MMAs: N = head size,
 // B operand MN-major

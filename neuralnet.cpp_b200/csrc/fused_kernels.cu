@@ -8,6 +8,7 @@
 //   softmax cross-entropy    compute_loss.hpp:229-309 + cpu_engine.hpp:948-1006
 //   AdamW / clip / Muon      compute_optimizer.hpp:90-140, 252-304, 388-412, 517-590
 #include "kernels.h"
+#include "tc_ptx.cuh"
 
 namespace nnb {
 
@@ -255,6 +256,13 @@ norm_bwd_dx_reg_kernel(const T* __restrict__ g, const T* __restrict__ x, const f
 // of the produced dx — the bias gradient of the Linear layer that fed this point — accumulate in
 // registers.  Warps fold through shared memory, blocks write partials, and the block that finishes
 // last adds the partials up in fixed order: deterministic, no extra pass over the activations.
+// The rows reach the warps through shared memory: each warp owns a ring of two row slots ([g | x | residual-gradient]
+// row, 3 * D * sizeof(T) bytes each) that its lane 0 fills with bulk copies counted on an mbarrier, two rows ahead of
+// the one being worked on (the fold buffer of the kernel's end lies over the rings: every copy has landed by then).
+// Three slots were measured slower (25.9 against 22.4 us at 16384 x 768): they cost the second block per SM.  Loading a row into registers only when its turn came left the memory system idle while a
+// warp reduced and stored (the kernel ran at 0.57 of the copy bandwidth), and prefetching into registers does not fit
+// beside the three per-column accumulators.
+__device__ int g_fused_error = 0;        // 0 ok; otherwise (code << 16 | block) of the first wait that gave up
 constexpr int kNormFusedBlocks = 296;   // two per SM
 constexpr int kNormFoldGroup = 17;      // blocks per first-level fold group: about the square root of the block count, so both levels read as many rows
 constexpr int kNormFoldCounters = 64;   // ints at the end of the counter array: one per group, the last for the groups
@@ -267,9 +275,23 @@ norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const fl
                       float* __restrict__ dgamma, float* __restrict__ dbeta, float* __restrict__ osum, int rows, int defer)
 {
     constexpr int VN = Vec16<T>::N, D = 32 * NV * VN, NQ = 3;
-    __shared__ float red[8][D];
+    constexpr int ROW_BYTES = D * static_cast<int>(sizeof(T)), SLOT = 3 * ROW_BYTES;
+    extern __shared__ __align__(128) uint8_t nb_smem[];
+    constexpr int RING = 2;
+    static_assert(8 * RING * SLOT >= 8 * D * static_cast<int>(sizeof(float)), "the fold buffer lies over the rings");
+    float (*red)[D] = reinterpret_cast<float (*)[D]>(nb_smem);                      // [8][D], used after the row loop
+    uint8_t* ring = nb_smem;                                                        // [warp][RING][SLOT]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + 8 * RING * SLOT);           // [warp][RING]
     __shared__ int is_last;
+    __shared__ int abort_word;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    volatile int* abort_flag = &abort_word;
+    if (threadIdx.x == 0) abort_word = 0;
+    if (lane == 0) {
+        for (int k = 0; k < RING; ++k) mbar_init(smem_u32(bars + RING * warp + k), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
     float gm[NV][VN], a_dg[NV][VN], a_db[NV][VN], a_os[NV][VN];
 #pragma unroll
     for (int v = 0; v < NV; ++v)
@@ -278,26 +300,42 @@ norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const fl
 #pragma unroll
     for (int v = 0; v < NV; ++v) ld_f32x<VN>(gamma + (v * 32 + lane) * VN, gm[v]);
     const float inv_d = 1.0f / static_cast<float>(D);
-    for (int r = blockIdx.x * wpb + warp; r < rows; r += gridDim.x * wpb) {
+    const int r0 = blockIdx.x * wpb + warp, rstep = gridDim.x * wpb;
+    uint8_t* my_ring = ring + warp * RING * SLOT;
+    auto request = [&](int r, int slot) {                      // lane 0: the three rows of row r into a slot
+        const uint32_t bar = smem_u32(bars + RING * warp + slot), dst = smem_u32(my_ring + slot * SLOT);
         const size_t off = static_cast<size_t>(r) * D;
-        const float rinv = rinv_in[r], mean = LAYER ? mean_in[r] : 0.f;
-        float gg[NV][VN], nn[NV][VN];
+        mbar_expect_tx(bar, add ? 3 * ROW_BYTES : 2 * ROW_BYTES);
+        bulk_load_1d(dst, g + off, ROW_BYTES, bar);
+        bulk_load_1d(dst + ROW_BYTES, x + off, ROW_BYTES, bar);
+        if (add) bulk_load_1d(dst + 2 * ROW_BYTES, add + off, ROW_BYTES, bar);
+    };
+    if (lane == 0)
+        for (int k = 0; k < RING; ++k)
+            if (r0 + k * rstep < rows) request(r0 + k * rstep, k);
+    float rinv_next = r0 < rows ? rinv_in[r0] : 0.f, mean_next = (LAYER && r0 < rows) ? mean_in[r0] : 0.f;
+    int it = 0;
+    for (int r = r0; r < rows; r += rstep, ++it) {
+        const size_t off = static_cast<size_t>(r) * D;
+        const int slot = it % RING;
+        const float rinv = rinv_next, mean = mean_next;
+        if (r + rstep < rows) { rinv_next = rinv_in[r + rstep]; if (LAYER) mean_next = mean_in[r + rstep]; }
+        const bool got = mbar_wait(smem_u32(bars + RING * warp + slot), (it / RING) & 1, abort_flag, 1, &g_fused_error);
+        if (!__all_sync(0xffffffffu, got)) break;
+        const uint8_t* sl = my_ring + slot * SLOT;
+        // two passes over the slot (it is shared memory: cheaper than holding g * gamma and the normalised row in
+        // registers beside the three per-column accumulators)
         float s_g = 0.f, s_gn = 0.f;
-        Vec16<T> av[NV];
-        if (add) {
-#pragma unroll
-            for (int v = 0; v < NV; ++v) av[v] = ld16(add + off + (v * 32 + lane) * VN);
-        }
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-            const Vec16<T> gv = ld16(g + off + (v * 32 + lane) * VN), xv = ld16(x + off + (v * 32 + lane) * VN);
+            const Vec16<T> gv = *reinterpret_cast<const Vec16<T>*>(sl + (v * 32 + lane) * 16);
+            const Vec16<T> xv = *reinterpret_cast<const Vec16<T>*>(sl + ROW_BYTES + (v * 32 + lane) * 16);
 #pragma unroll
             for (int k = 0; k < VN; ++k) {
                 const float graw = to_f32(gv.v[k]);
-                gg[v][k] = graw * gm[v][k];
-                nn[v][k] = (to_f32(xv.v[k]) - mean) * rinv;
-                s_g += gg[v][k]; s_gn += gg[v][k] * nn[v][k];
-                a_dg[v][k] += gg[v][k] * nn[v][k];
+                const float ggk = graw * gm[v][k], nnk = (to_f32(xv.v[k]) - mean) * rinv;
+                s_g += ggk; s_gn += ggk * nnk;
+                a_dg[v][k] += ggk * nnk;
                 if (LAYER) a_db[v][k] += graw;
             }
         }
@@ -305,16 +343,23 @@ norm_bwd_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const fl
         const float m_g = LAYER ? warp_sum(s_g) * inv_d : 0.f;
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
+            const Vec16<T> gv = *reinterpret_cast<const Vec16<T>*>(sl + (v * 32 + lane) * 16);
+            const Vec16<T> xv = *reinterpret_cast<const Vec16<T>*>(sl + ROW_BYTES + (v * 32 + lane) * 16);
+            Vec16<T> av;
+            if (add) av = *reinterpret_cast<const Vec16<T>*>(sl + 2 * ROW_BYTES + (v * 32 + lane) * 16);
             Vec16<T> o;
 #pragma unroll
             for (int k = 0; k < VN; ++k) {
-                float t = (gg[v][k] - m_g - nn[v][k] * m_gn) * rinv;
-                if (add) t += to_f32(av[v].v[k]);
+                const float ggk = to_f32(gv.v[k]) * gm[v][k], nnk = (to_f32(xv.v[k]) - mean) * rinv;
+                float t = (ggk - m_g - nnk * m_gn) * rinv;
+                if (add) t += to_f32(av.v[k]);
                 o.v[k] = from_f32<T>(t);
                 a_os[v][k] += to_f32(o.v[k]);             // the rounded value: what the next kernel reads
             }
             st16(dx + off + (v * 32 + lane) * VN, o);
         }
+        __syncwarp();                                           // every lane is done with the slot
+        if (lane == 0 && r + RING * rstep < rows) request(r + RING * rstep, slot);
     }
     // block fold, one quantity at a time, then this block's partial row
     const size_t pstride = static_cast<size_t>(gridDim.x) * D;
@@ -768,6 +813,101 @@ ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const 
 }
 
 // loss = -(sum loss_vec) / num_valid (compute_loss.hpp:300-307); single block, fixed order
+// The same computation with the rows staged in shared memory: persistent blocks, each with a ring of row slots that
+// thread 0 fills with bulk copies (counted on an mbarrier) ahead of the row being worked on; the three passes (maximum,
+// sum of exponentials, gradient) read and overwrite the slot, and the finished row leaves as one bulk store while the
+// next is computed.  The register-cached kernel above does load -> reduce -> reduce -> store per row with nothing
+// overlapping inside a block (0.39 of the copy bandwidth at 16384 x 32768; this kernel: 0.50, the two exponentials per
+// element being the next limit: 4096 XU clocks per 64 KB row).  A thread handles the same vectors of a row in the same
+// order as there, so the results are bit-identical.  Used for rows above 32 KB.
+template <typename T>
+__global__ void __launch_bounds__(512)
+ce_staged_kernel(T* __restrict__ logits, const int* __restrict__ labels, const float* __restrict__ mask,
+                 const float* __restrict__ stats, float grad_scale, float* __restrict__ loss_vec, int rows, int V, int vocab,
+                 int slots)
+{
+    constexpr int VN = Vec16<T>::N;
+    extern __shared__ __align__(128) uint8_t ce_smem[];
+    __shared__ float red[32];
+    __shared__ int abort_word;
+    const uint32_t row_bytes = static_cast<uint32_t>(V) * sizeof(T);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ce_smem + static_cast<size_t>(slots) * row_bytes);
+    volatile int* abort_flag = &abort_word;
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        for (int k = 0; k < slots; ++k) mbar_init(smem_u32(bars + k), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int nvec = V / VN;
+    const int first = blockIdx.x, step = gridDim.x;
+    auto request = [&](int r, int slot) {
+        mbar_expect_tx(smem_u32(bars + slot), row_bytes);
+        bulk_load_1d(smem_u32(ce_smem + static_cast<size_t>(slot) * row_bytes), logits + static_cast<size_t>(r) * V, row_bytes, smem_u32(bars + slot));
+    };
+    if (threadIdx.x == 0)
+        for (int k = 0; k < slots; ++k)
+            if (first + k * step < rows) request(first + k * step, k);
+    const float inv_nv = stats[1] * grad_scale;   // inv_num_valid, times the accumulation scale (text_train.cpp:1253-1258)
+    int it = 0;
+    for (int r = first; r < rows; r += step, ++it) {
+        const int slot = it % slots;
+        T* row = reinterpret_cast<T*>(ce_smem + static_cast<size_t>(slot) * row_bytes);
+        const int lbl = labels[r];
+        const bool valid = (!mask || mask[r] >= 0.5f) && lbl >= 0 && lbl < vocab;
+        const bool got = mbar_wait(smem_u32(bars + slot), (it / slots) & 1, abort_flag, 2, &g_fused_error);
+        if (__syncthreads_or(!got)) break;
+        if (!valid) {
+            Vec16<T> z;
+#pragma unroll
+            for (int k = 0; k < VN; ++k) z.v[k] = from_f32<T>(0.f);
+            for (int i = threadIdx.x; i < nvec; i += blockDim.x) *reinterpret_cast<Vec16<T>*>(row + i * VN) = z;
+            if (threadIdx.x == 0) loss_vec[r] = 0.f;
+        } else {
+            float mx = -INFINITY;
+            for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+                const Vec16<T> v = *reinterpret_cast<const Vec16<T>*>(row + i * VN);
+#pragma unroll
+                for (int k = 0; k < VN; ++k) mx = fmaxf(mx, to_f32(v.v[k]));
+            }
+            mx = block_max(mx, red);
+            float den = 0.f;
+            for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+                const Vec16<T> v = *reinterpret_cast<const Vec16<T>*>(row + i * VN);
+#pragma unroll
+                for (int k = 0; k < VN; ++k) den += exp_t<T>(to_f32(v.v[k]) - mx);
+            }
+            den = block_sum(den, red);
+            const float ll = to_f32(row[lbl]);
+            __syncthreads();                              // everyone has read row[lbl] before it is overwritten
+            if (threadIdx.x == 0) loss_vec[r] = ll - mx - logf(den);
+            const float inv_den = inv_nv / den;
+            for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+                const Vec16<T> v = *reinterpret_cast<const Vec16<T>*>(row + i * VN);
+                Vec16<T> o;
+#pragma unroll
+                for (int k = 0; k < VN; ++k) {
+                    float gv = exp_t<T>(to_f32(v.v[k]) - mx) * inv_den;
+                    if (i * VN + k == lbl) gv -= inv_nv;
+                    o.v[k] = from_f32<T>(gv);
+                }
+                *reinterpret_cast<Vec16<T>*>(row + i * VN) = o;
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the slot as the bulk store will read it
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            bulk_store_1d(logits + static_cast<size_t>(r) * V, smem_u32(row), row_bytes);
+            tma_commit();
+            if (r + slots * step < rows) {                // the slot is loaded again once the store has read it
+                tma_wait_read0();
+                request(r + slots * step, slot);
+            }
+        }
+    }
+    if (threadIdx.x == 0) tma_wait_all();                 // shared memory outlives the stores in flight
+}
+
 __global__ void ce_loss_kernel(const float* __restrict__ loss_vec, const float* __restrict__ stats, int rows,
                                float* __restrict__ loss_out)
 {
@@ -889,6 +1029,13 @@ __global__ void bf16_to_f32_kernel(const bf16* __restrict__ in, float* __restric
 // host launchers
 // ======================================================================================
 #define LAUNCH_CHECK() NNB_LAUNCH_CHECK()
+
+int fused_device_error(int* code)
+{
+    NNB_CUDA_CHECK(cudaMemcpyFromSymbol(code, g_fused_error, sizeof(int)));
+    if (*code) { const int z = 0; NNB_CUDA_CHECK(cudaMemcpyToSymbol(g_fused_error, &z, sizeof(int))); }
+    return 0;
+}
 
 template <typename T>
 int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rinv, float* mean, int rows, int d,
@@ -1047,10 +1194,17 @@ int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, cons
     if (counters && aligned && out_ok && d == 32 * VN * nv) {                                                         \
         const bool defer = defer_partial != nullptr && deferred != nullptr;                                           \
         float* part = defer ? defer_partial : scratch;                                                                \
-        if (layer) norm_bwd_fused_kernel<T, true, nv><<<kNormFusedBlocks, 256, 0, s>>>(                                \
-            g, x, gamma, rinv, mean, add, dx, part, counters + kColsumCounters - kNormFoldCounters, dgamma, dbeta, out_colsum, rows, defer ? 1 : 0); \
-        else norm_bwd_fused_kernel<T, false, nv><<<kNormFusedBlocks, 256, 0, s>>>(                                     \
-            g, x, gamma, rinv, mean, add, dx, part, counters + kColsumCounters - kNormFoldCounters, dgamma, dbeta, out_colsum, rows, defer ? 1 : 0); \
+        constexpr int smem = 8 * 2 * 3 * 32 * VN * nv * static_cast<int>(sizeof(T)) + 8 * 2 * 8;                                       \
+        static PerDeviceOnce once_layer, once_rms;                                                                    \
+        if (layer) {                                                                                                  \
+            NNB_TRY(once_layer.run([] { return cudaFuncSetAttribute(norm_bwd_fused_kernel<T, true, nv>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); })); \
+            norm_bwd_fused_kernel<T, true, nv><<<kNormFusedBlocks, 256, smem, s>>>(                                   \
+                g, x, gamma, rinv, mean, add, dx, part, counters + kColsumCounters - kNormFoldCounters, dgamma, dbeta, out_colsum, rows, defer ? 1 : 0); \
+        } else {                                                                                                      \
+            NNB_TRY(once_rms.run([] { return cudaFuncSetAttribute(norm_bwd_fused_kernel<T, false, nv>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); })); \
+            norm_bwd_fused_kernel<T, false, nv><<<kNormFusedBlocks, 256, smem, s>>>(                                  \
+                g, x, gamma, rinv, mean, add, dx, part, counters + kColsumCounters - kNormFoldCounters, dgamma, dbeta, out_colsum, rows, defer ? 1 : 0); \
+        }                                                                                                             \
         LAUNCH_CHECK();                                                                                               \
         if (defer) *deferred = true;                                                                                  \
         return 0;                                                                                                     \
@@ -1115,6 +1269,27 @@ int cross_entropy(T* logits, const int* labels, const float* mask, float grad_sc
     constexpr int VN = Vec16<T>::N;
     const bool vec_ok = (V % VN) == 0;
     const int nvec = V / VN;
+    // Rows above 32 KB (up to 72 KB) go through the staged kernel, three slots per block.  Shorter rows stay with the
+    // register-cached kernel: there the per-row barriers weigh more than the overlap buys (16384 x 8192: 192 us staged
+    // against 153 us; 16384 x 32768: 661 against 843 us).
+    const size_t row_bytes = static_cast<size_t>(V) * sizeof(T);
+    if (vec_ok && (row_bytes % 16) == 0 && row_bytes > 32 * 1024 && row_bytes <= 72 * 1024 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        const int slots = 3;
+        const int smem = static_cast<int>(slots * row_bytes) + 64;
+        static PerDeviceOnce once;
+        NNB_TRY(once.run([] { return cudaFuncSetAttribute(ce_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 512); }));
+        int per_sm = 0;
+        NNB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ce_staged_kernel<T>, 512, smem));
+        if (per_sm > 0) {
+            const long long cap = static_cast<long long>(device_sm_count()) * per_sm;
+            const int grid = static_cast<int>(rows < cap ? rows : cap);
+            ce_staged_kernel<T><<<grid, 512, smem, s>>>(logits, labels, mask, stats, grad_scale, loss_vec, rows, V, vocab, slots);
+            LAUNCH_CHECK();
+            ce_loss_kernel<<<1, 1024, 0, s>>>(loss_vec, stats, rows, loss_out);
+            LAUNCH_CHECK();
+            return 0;
+        }
+    }
     if (vec_ok && nvec <= 512 * 2) ce_fwd_bwd_kernel<T, 2><<<rows, 512, 0, s>>>(logits, labels, mask, stats, grad_scale, loss_vec, rows, V, vocab);
     else if (vec_ok && nvec <= 512 * 4) ce_fwd_bwd_kernel<T, 4><<<rows, 512, 0, s>>>(logits, labels, mask, stats, grad_scale, loss_vec, rows, V, vocab);
     else if (vec_ok && nvec <= 512 * 8) ce_fwd_bwd_kernel<T, 8><<<rows, 512, 0, s>>>(logits, labels, mask, stats, grad_scale, loss_vec, rows, V, vocab);

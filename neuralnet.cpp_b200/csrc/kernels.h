@@ -110,6 +110,8 @@ int attention_device_error(int* code);
 int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const float* lse, float* dvec, bf16* dqkv,
                      const int* doc, const int* doc_ranges, int B, int S, int H, int dk, int alibi, cudaStream_t s);
 int attention_bwd_device_error(int* code);
+// status word of the fused elementwise kernels that wait on bulk copies (reads and clears)
+int fused_device_error(int* code);
 int attention_fwd_mma(const bf16* qkv, bf16* out, float* lse, const int* doc, int B, int S, int H, int dk, int alibi,
                       cudaStream_t s);
 int attention_bwd_mma(const bf16* qkv, const bf16* out, const bf16* dout, const float* lse, float* dvec, bf16* dqkv,

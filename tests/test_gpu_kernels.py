@@ -313,7 +313,7 @@ def test_cross_entropy_matches_reference_golden(g):
 
 
 @pytest.mark.parametrize("dtype", [0, 1])
-@pytest.mark.parametrize("rows,V", [(64, 8192), (16, 32768), (50, 1000), (9, 70)])
+@pytest.mark.parametrize("rows,V", [(64, 8192), (16, 32768), (50, 1000), (9, 70), (700, 20000), (300, 12000)])
 def test_cross_entropy_sizes_and_properties(g, dtype, rows, V):
     import torch
     from oracle import gpt_oracle as go
@@ -332,7 +332,10 @@ def test_cross_entropy_sizes_and_properties(g, dtype, rows, V):
            g.ptr(loss), rows, V, V, dtype, g.stream())
     got = g.host(t)
     assert np.isclose(g.host(loss)[0], loss_ref, rtol=1e-2 if dtype else 1e-5)
-    assert np.abs(got - 0.5 * grad_ref.T).max() < (1e-2 if dtype else 1e-5) * np.abs(grad_ref).max()
+    # fp32: 1e-5 of the largest gradient; the denominators of the two long-row cases are sums of 12000 / 20000 fp32 terms
+    # in an order of their own (measured 1.5e-5 and 1.7e-5 with either kernel)
+    tol32 = 1e-5 if V < 10000 else 3e-5
+    assert np.abs(got - 0.5 * grad_ref.T).max() < (1e-2 if dtype else tol32) * np.abs(grad_ref).max()
     assert np.all(got[0] == 0) and np.all(got[1] == 0)                 # invalid rows have zero gradient
     if dtype == 0:
         assert np.abs(got[2:].sum(axis=1)).max() < 1e-6                # softmax - onehot sums to zero
