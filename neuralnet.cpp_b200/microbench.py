@@ -6,6 +6,7 @@
   python neuralnet.cpp_b200/microbench.py --only train_step --shape 2,16 --iters 2 --no-time
                                                              training steps of a shallow copy of the benchmark model (layers,
                                                              micro-batch): every kernel of the step on ~2 GB, for profiler captures
+  python neuralnet.cpp_b200/microbench.py --only decode      incremental decoding (forward_step) of the benchmark model
   python neuralnet.cpp_b200/microbench.py --only gemm --shape 16384,4096,768 --iters 3 --no-time
                                                              a few launches of one shape (for an ncu capture)
 
@@ -175,6 +176,28 @@ def run_rmsnorm(rows, d, args):
              peak_source=src)
 
 
+def run_decode(context, args):
+    """Incremental decoding of the benchmark model (d 768, 12 layers, vocab 8192, bf16 weights): `forward_step` with
+    `context` tokens already in the key / value cache.  Bound: every weight is read once per token (2 bytes each)."""
+    cfg = nnb.GptConfig(8192, 768, 12, 12, 2048, 1024, 1, nnb.ACT_SWIGLU, nnb.NORM_RMS, nnb.POS_ALIBI, nnb.BF16)
+    tr = nnb.GptTrainer(cfg, lr=1e-3)
+    tr.init_params_normal(seed=42, std=0.02)
+    for t in range(context):                       # fill the cache
+        tr.forward_step(t % 8192, t, t)
+    fn = lambda: tr.forward_step(17, context, context)
+    if args.no_time:
+        for _ in range(args.iters):
+            fn()
+        torch.cuda.synchronize()
+        return
+    hbm, tf, src = peaks()
+    ms = timed(fn, args.iters, args.flush_l2)
+    nbytes = 2.0 * tr.arena_elems                  # the bf16 copy of every parameter (learned positions and padding included)
+    ach = nbytes / ms / 1e6
+    emit(kernel="decode_forward_step", context=context, us=ms * 1e3, tokens_per_s=1e3 / ms, bound="hbm", achieved=ach, peak=hbm,
+         unit="GB/s", frac=ach / hbm, peak_source=src)
+
+
 def run_train_step(layers, batch, args):
     """The benchmark model (d 768, 12 heads, SwiGLU 2048, RMSNorm, ALiBi, vocab 8192, seq 1024, bf16) with `layers` layers:
     forward + loss + backward + AdamW per step, token ids from a seed."""
@@ -225,6 +248,9 @@ def main():
         run_ce(*(shape or (16384, 32768)), args)
     if fam == "train_step":
         run_train_step(*(shape or (2, 16)), args)
+    if fam == "decode":
+        for ctx in ([shape[0]] if shape else [16, 512, 1000]):
+            run_decode(ctx, args)
     if fam in ("all", "rmsnorm"):
         run_rmsnorm(*(shape or (65536, 4096)), args)
     code = C.c_int(0)
