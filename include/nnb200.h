@@ -302,6 +302,15 @@ long long nnb200_gpt_decode_workspace_bytes(const nnb200_gpt_config* cfg);
 int nnb200_gpt_decode_init(const nnb200_gpt_config* cfg, void* workspace, void* stream);
 int nnb200_gpt_forward_step(const nnb200_gpt_config* cfg, const float* params, const void* params_bf16, void* workspace, int token_id,
                             int pos, int cur_len, float* logits_out, void* stream);
+/* The same step with the token id, the position and the cache length read from device memory (three int32 at
+ * step_dev, which the caller fills before the call; they are not validated: 0 <= position, cache length < seq).  Every
+ * launch of this call is the same whatever the three values are, so a caller may capture it in a CUDA graph once and
+ * replay it per token after updating step_dev.  No counterpart in the reference, which builds its step on the host. */
+int nnb200_gpt_forward_step_dev(const nnb200_gpt_config* cfg, const float* params, const void* params_bf16, void* workspace,
+                                const int32_t* step_dev, float* logits_out, void* stream);
+/* Writes the three values nnb200_gpt_forward_step_dev reads (a one-thread kernel on `stream`: ordered with the step
+ * without pinned host memory).  Helper, no counterpart in the reference. */
+int nnb200_gpt_decode_set_step(int32_t* step_dev, int token_id, int pos, int cur_len, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Engine primitives in the reference's own layouts (fp32; matrices row-major, batch blocks stacked

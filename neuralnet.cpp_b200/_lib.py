@@ -65,6 +65,8 @@ SIGNATURES = {
     "nnb200_gpt_decode_workspace_bytes": [_cfgp],
     "nnb200_gpt_decode_init": [_cfgp, _p, _p],
     "nnb200_gpt_forward_step": [_cfgp, _p, _p, _p, _i, _i, _i, _p, _p],
+    "nnb200_gpt_forward_step_dev": [_cfgp, _p, _p, _p, _p, _p, _p],
+    "nnb200_gpt_decode_set_step": [_p, _i, _i, _i, _p],
     "nnb200_ids_from_float": [_p, _p, _i, _i, _p],
     "nnb200_logits_to_reference": [_p, _p, _i, _i, _i, _p],
     "nnb200_zero_f32": [_p, _sz, _p],

@@ -299,13 +299,36 @@ class GptTrainer:
             self._decode_logits = torch.empty(self.cfg.vocab, dtype=torch.float32, device=self.device)
         return self._decode_ws, self._decode_logits
 
-    def forward_step(self, token_id: int, pos: int, cur_len: int) -> torch.Tensor:
+    def forward_step(self, token_id: int, pos: int, cur_len: int, graph: bool = True) -> torch.Tensor:
         """One token through the model with the key/value cache (GPTModel::forward_step, compute_layer.hpp:2906-2950):
         writes the token's keys and values at cache row cur_len, attends over rows [0, cur_len] and returns the
-        (vocab,) fp32 logits (a device tensor that the next call overwrites)."""
+        (vocab,) fp32 logits (a device tensor that the next call overwrites).
+
+        A token is about sixty small launches, which the host cannot issue as fast as the GPU runs them.  With `graph`
+        the launches are captured once as a CUDA graph (nnb200_gpt_forward_step_dev reads the token id, the position
+        and the cache length from device memory, so they are the same for every token) and replayed per token after a
+        one-thread kernel has written the three integers."""
         ws, logits = self._decode_state()
-        call("nnb200_gpt_forward_step", C.byref(self._c), _ptr(self.params), _ptr(self.shadow), _ptr(ws), int(token_id), int(pos),
-             int(cur_len), _ptr(logits), _stream())
+        if not (0 <= int(cur_len) < self.cfg.seq and 0 <= int(pos) < self.cfg.seq):
+            raise ValueError("pos and cur_len must be in [0, seq)")
+        if not graph:
+            call("nnb200_gpt_forward_step", C.byref(self._c), _ptr(self.params), _ptr(self.shadow), _ptr(ws), int(token_id), int(pos),
+                 int(cur_len), _ptr(logits), _stream())
+            return logits
+        if getattr(self, "_decode_graph", None) is None:
+            self._step_dev = torch.zeros(4, dtype=torch.int32, device=self.device)
+            args = (C.byref(self._c), _ptr(self.params), _ptr(self.shadow), _ptr(ws), _ptr(self._step_dev), _ptr(logits))
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):                      # one plain run first: per-device launch attributes are set there
+                call("nnb200_gpt_forward_step_dev", *args, _stream())
+            torch.cuda.current_stream().wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                call("nnb200_gpt_forward_step_dev", *args, _stream())
+            self._decode_graph = g
+        call("nnb200_gpt_decode_set_step", _ptr(self._step_dev), int(token_id), int(pos), int(cur_len), _stream())
+        self._decode_graph.replay()
         return logits
 
     def generate(self, prompt: Sequence[int], max_new_tokens: int, temperature: float = 1.0, eos_token_id: int = -1,

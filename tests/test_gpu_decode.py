@@ -82,3 +82,22 @@ def test_generate_sampling_and_eos(nnb):
     greedy = tr.generate([1, 2, 3], 8, temperature=0.0)
     cut = tr.generate([1, 2, 3], 8, temperature=0.0, eos_token_id=greedy[3])
     assert cut == greedy[:greedy.index(greedy[3])]           # stops before the first occurrence of the end token
+
+
+@pytest.mark.parametrize("pos", [0, 2, 3])                  # learned, ALiBi, rotary
+def test_forward_step_long_context_crosses_attention_chunks(nnb, pos):
+    """The decode attention splits the cache into chunks of 32 rows and merges the partial softmaxes: 300 steps in a
+    320-token window (ten chunks) against the full causal forward pass of the same tokens (check mode, 1e-5), with
+    the CUDA-graph replay and with plain launches."""
+    import torch
+    c = go.GptConfig(64, 64, 2, 2, 96, 320, 1, 1, 1, pos)       # vocab, d, heads, layers, ff, seq, batch, SwiGLU, RMSNorm
+    params = go.init_params(c, 7, std=0.2)
+    tokens = np.random.default_rng(11).integers(0, c.vocab, c.seq).astype(np.int32)
+    tr = _trainer(nnb, c, params, nnb.FP32)
+    tr.forward(tokens)
+    torch.cuda.synchronize()
+    full = tr.logits().float().cpu().numpy().copy()[:300]
+    graph = torch.stack([tr.forward_step(int(tok), t, t).clone() for t, tok in enumerate(tokens[:300])]).cpu().numpy()
+    assert rel_err(graph, full) < 1e-5
+    plain = torch.stack([tr.forward_step(int(tok), t, t, graph=False).clone() for t, tok in enumerate(tokens[:300])]).cpu().numpy()
+    assert np.array_equal(plain, graph)
