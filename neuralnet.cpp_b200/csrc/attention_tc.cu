@@ -1,8 +1,9 @@
-// Fused causal / document-masked / ALiBi attention forward on the 5th-generation tensor cores, head sizes 64 and 128.
+// Fused causal / document-masked / ALiBi attention forward on the 5th-generation tensor cores.  Head size 64 runs the
+// kernel of attention_tc_fwd64.cuh (four one-chain CTAs per SM); this file holds the kernel for head size 128, the
+// per-64-row document ranges, and the host entry point for both.
 //
-// Persistent: the CTAs resident on an SM (two for head size 64: 98 KB of shared memory and 256 TMEM columns each; one
-// for head size 128) walk the list of (128-query tile, head, batch) work items, longest tiles first, in snake order
-// (snake_tile in tc_ptx.cuh).  Ten warps:
+// Head size 128.  Persistent: one CTA per SM walks the list of (128-query tile, head, batch) work items, longest tiles
+// first, in snake order (snake_tile in tc_ptx.cuh).  Ten warps:
 //   warp 0      TMA producer: the tile's Q, then per 128-key block one K tile and one V tile (ring of two)
 //   warp 1      MMA issuer:   S = Q K^T   (128 x 128 x head)  into TMEM columns [0, 128)
 //                             O' = P V    (128 x head x 128)  into TMEM columns [128, 128 + head)
@@ -12,11 +13,11 @@
 //               exchanges the row maximum with its partner through shared memory; writes P as bf16 into a K-major
 //               128B-swizzled shared tile (the A operand of the second MMA) and folds its half of the columns of O'
 //               into registers; at the end of a tile it normalises and stores its output row.
-// Q, K, S and P are single-buffered (the key tile is released as soon as Q K^T has read it): with two CTAs per SM the
-// softmax chain of one CTA is covered by the other CTA's MMAs.  All ring positions and barrier phases are counted
-// across tiles, so the first loads and MMAs of the next tile overlap the write-out of this one.
+// Q, K, S and P are single-buffered (the key tile is released as soon as Q K^T has read it).  All ring positions and
+// barrier phases are counted across tiles, so the first loads and MMAs of the next tile overlap the write-out of this one.
 // K-major operands wider than 64 values are kept as sub-tiles of 64 columns (one 128-byte swizzle atom per row);
 // V is consumed as an MN-major B operand straight from its (key, head) tile.  Nothing of size (S, S) reaches memory.
+// (The kernel is a template over the head size; only 128 is instantiated.)
 //
 // ALiBi: the bias -slope_h (i - j) is linear in the key position, so the tensor core adds it: one more MMA step per
 // block multiplies a (128 x 16) tile that holds slope_h / scale, split into three bf16 terms (24 bits), in every query
