@@ -178,11 +178,14 @@ def test_attention_forward_backward(g, dtype, B, S, H, dk, alibi, docs, mean_len
         assert np.abs(got - want).max() < tol * scale(want) * 3, name
 
 
-@pytest.mark.parametrize("B,S,H,alibi,docs", [(13, 512, 4, 1, False), (7, 768, 8, 1, True), (5, 1024, 8, 0, False)])
+@pytest.mark.parametrize("B,S,H,alibi,docs", [(13, 512, 4, 1, False), (7, 768, 8, 1, True), (5, 1024, 8, 0, False),
+                                              (40, 512, 8, 1, False), (24, 768, 8, 0, True)])
 def test_attention_persistent_tile_loop(g, B, S, H, alibi, docs):
-    """More (tile, head, batch) work items than SMs: every persistent CTA of the tcgen05 kernels walks two or
-    three tiles, so the rings, the double-buffered resident tiles / TMEM accumulators and all barrier phases
-    carry over from one tile to the next (208, 336 and 320 tiles on 148 SMs)."""
+    """More (tile, head, batch) work items than resident CTAs: every persistent CTA of the tcgen05 kernels takes several
+    tiles, so the rings, the tile slots, the TMEM accumulators and all barrier phases carry over from one tile to the
+    next.  208, 336 and 320 tiles are more than the 296 CTAs of the backward kernels hold at once; 1280 and 1152 are
+    more than twice the 592 CTAs of the head-64 forward kernel, whose control thread streams the key blocks of
+    successive tiles."""
     test_attention_forward_backward(g, 1, B, S, H, 64, alibi, docs)
 
 
