@@ -295,7 +295,8 @@ attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 float mxr = -INFINITY;
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                    if (lim0 + 31 < 32 * c) continue;           // past the diagonal for every row of the warp (uniform)
+                    // nothing of the chunk is visible to any row of the warp: past the diagonal, or other documents only
+                    if (lim0 + 31 < 32 * c || (DOC && __all_sync(0xffffffffu, (c == 0 ? vis_lo : vis_hi) == 0u))) continue;
                     uint32_t r[32];
                     tmem_ld32(tmem_base + lane_addr + c * 32, r);
                     tmem_ld_wait();
@@ -335,7 +336,8 @@ attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 uint64_t rs2 = 0ull;
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                    const bool none = lim0 + 31 < 32 * c;       // past the diagonal for every row of the warp (uniform): P = 0
+                    // nothing of the chunk is visible to any row of the warp (uniform): P = 0
+                    const bool none = lim0 + 31 < 32 * c || (DOC && __all_sync(0xffffffffu, (c == 0 ? vis_lo : vis_hi) == 0u));
                     uint32_t r[32];
                     if (!none) {
                         tmem_ld32(tmem_base + lane_addr + c * 32, r);
