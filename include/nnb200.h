@@ -89,6 +89,14 @@ int cuda_scatter_add(float* dst, const float* indices, const float* grad, unsign
 int nnb200_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
                      long long ldc, int a_mn_major, int b_mn_major, int c_bf16, float alpha, const float* bias_n,
                      const void* residual, int accumulate, void* stream);
+/* First projection of a SwiGLU feed-forward block with its activation, one launch: h1[M, 2 ff] = x[M, K] W[2 ff, K]^T
+ * + bias (rows of W: gate, then up) and h2[M, ff] = gate * sigmoid(gate) * up from the bf16-rounded h1, the values
+ * nnb200_gemm_bf16 followed by nnb200_activation_forward(swiglu = 1) give, bit for bit.  All operands bf16, bias fp32
+ * or NULL.  Needs M > 128, ff a multiple of 128, K a multiple of 8 (nnb200_linear_swiglu_supported: 1 or 0); -1
+ * otherwise.  Replaces Linear::forward + SwiGLU::forward inside FeedForward (compute_layer.hpp:151-195, 375-404). */
+int nnb200_linear_swiglu_supported(int M, int ff, int K);
+int nnb200_linear_swiglu_forward(const void* x, const void* W, const float* bias, void* h1, void* h2, int M, int ff, int K,
+                                 void* stream);
 /* Same contract, fp32 operands and fp32 SIMT arithmetic (the check mode). */
 int nnb200_gemm_f32(const float* A, const float* B, float* D, int M, int N, int K, long long lda, long long ldb,
                     long long ldc, int a_mn_major, int b_mn_major, float alpha, const float* bias_n,

@@ -91,6 +91,14 @@ int nnb200_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K,
                      b_mn_major, c_bf16, alpha, bias_n, residual, accumulate, to_stream(stream));
 }
 
+int nnb200_linear_swiglu_supported(int M, int ff, int K) { return gemm_swiglu_supported(M, ff, K) ? 1 : 0; }
+int nnb200_linear_swiglu_forward(const void* x, const void* W, const float* bias, void* h1, void* h2, int M, int ff, int K,
+                                 void* stream)
+{
+    return gemm_bf16_swiglu(static_cast<const bf16*>(x), static_cast<const bf16*>(W), bias, static_cast<bf16*>(h1),
+                            static_cast<bf16*>(h2), M, ff, K, to_stream(stream));
+}
+
 int nnb200_gemm_pair_capacity(void) { return nnb::gemm_pair_capacity(); }
 int nnb200_gemm_status(int* host_code)
 {

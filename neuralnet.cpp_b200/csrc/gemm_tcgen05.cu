@@ -41,6 +41,7 @@ struct GemmParams {
     const float* bias_n;
     const void* residual;
     float alpha;
+    int glu_ff;                 // SwiGLU variant of the pair kernel: rows of B per half (gate rows, then up rows); 0 otherwise
 };
 
 // ---------------------------------------------------------------- kernel
@@ -457,12 +458,12 @@ static int pair_capacity()
     return n > 0 ? n : 0;
 }
 
-template <bool A_MN, bool B_MN, bool RES = false>
+template <bool A_MN, bool B_MN, bool RES = false, bool GLU = false>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tcm, const CUtensorMap& tr, const GemmParams& p, cudaStream_t s)
 {
-    constexpr int STAGES = RES ? PAIR_STAGES_RES : PAIR_STAGES;
+    constexpr int STAGES = (RES || GLU) ? PAIR_STAGES_RES : PAIR_STAGES;
     static PerDeviceOnce once;
-    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
+    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
     const int units = p.tiles_m * p.tiles_n * p.splits;
     const int pairs = units < pair_capacity() ? units : pair_capacity();
     cudaLaunchConfig_t cfg = {};
@@ -475,7 +476,7 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
     if (g_prof.on) prof_event(s);
-    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES>, ta, tb, tcm, tr, p));
+    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU>, ta, tb, tcm, tr, p));
     if (g_prof.on) { prof_event(s); g_prof.flops += 2.0 * p.M * p.N * p.K; }
     NNB_LAUNCH_CHECK();
     return 0;
@@ -553,6 +554,38 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
         GO(128, true, true);
     }
 #undef GO
+}
+
+// H1[M, 2 ff] = X[M, K] W[2 ff, K]^T + bias and H2[M, ff] = gate * sigmoid(gate) * up in one launch (the pair kernel's
+// SwiGLU epilogue).  gemm_swiglu_supported says whether the shape can take this path; the caller otherwise runs the
+// projection and the activation as two kernels, with the same results bit for bit.
+bool gemm_swiglu_supported(int M, int ff, int K)
+{
+    return M > 128 && ff >= 128 && (ff % 128) == 0 && K > 0 && (K % 8) == 0 && pair_capacity() > 0;
+}
+int gemm_bf16_swiglu(const bf16* X, const bf16* W, const float* bias, bf16* H1, bf16* H2, int M, int ff, int K, cudaStream_t stream)
+{
+    NNB_ARG_CHECK(gemm_swiglu_supported(M, ff, K), "shape not supported by the fused SwiGLU projection");
+    NNB_ARG_CHECK(((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(H1) |
+                    reinterpret_cast<uintptr_t>(H2)) & 15) == 0, "operands must be 16-byte aligned");
+    GemmParams p{};
+    p.M = M; p.N = ff; p.K = K;
+    p.C = H1; p.ldc = 2LL * ff; p.c_bf16 = 1; p.accumulate = 0;
+    p.bias_n = bias; p.residual = nullptr; p.alpha = 1.0f;
+    p.vec_ok = 1; p.tma_store = 1; p.glu_ff = ff;
+    p.tiles_m = static_cast<int>(ceil_div(M, 256));
+    p.tiles_n = ff / 128;
+    p.kb_total = static_cast<int>(ceil_div(K, BK));
+    p.splits = 1;
+    p.kb_per_split = p.kb_total;
+    CUtensorMap ta, tb, t1, t2;
+    NNB_TRY(tensor_map_2d(X, K, M, K, BK, BM, &ta, 2));
+    NNB_TRY(tensor_map_2d(W, K, 2 * ff, K, BK, PAIR_BN_HALF, &tb, 2));
+    NNB_TRY(tensor_map_2d(H1, 2 * ff, M, 2LL * ff, 64, BM, &t1, 2));
+    NNB_TRY(tensor_map_2d(H2, ff, M, ff, 64, BM, &t2, 2));
+    const int rc = launch_gemm_pair<false, false, false, true>(ta, tb, t1, t2, p, stream);
+    if (g_prof.on) g_prof.flops += 2.0 * M * ff * K;            // the launcher counted p.N = ff columns; the product has 2 ff
+    return rc;
 }
 
 int gemm_pair_capacity() { return pair_capacity(); }

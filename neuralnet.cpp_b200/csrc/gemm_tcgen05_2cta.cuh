@@ -24,6 +24,13 @@
 // tile into which its elected thread TMA-loads the residual tile of the group's next column block (of this unit or
 // the next) as soon as the group has consumed the previous one, a whole block period ahead; the threads read it with
 // the swizzle they write the output with.  The 32 KB come out of the operand ring (five stages instead of six).
+//
+// GLU: the product is the first projection of a SwiGLU feed-forward block (compute_layer.hpp:395-445): B holds the
+// gate rows [0, ff) and then the up rows [ff, 2 ff).  The leader stages 128 gate rows and its peer the 128 up rows of
+// the same columns, so every CTA's accumulator has gate in columns [0, 128) and up in [128, 256) of one 128-column
+// slice, and an epilogue group owns a matching pair of 64-column blocks.  It stores both (the backward pass reads
+// them) and, through the map in the residual slot, gate * sigmoid(gate) * up computed from the values as rounded to
+// bf16, which is bit for bit what a separate pass over the stored projection gives.  Each group has two staging tiles.
 #pragma once
 
 namespace nnb {
@@ -31,7 +38,7 @@ namespace nnb {
 constexpr int PAIR_BN_HALF = 128;                                // rows of B each CTA stages per k-block
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_BN_HALF * BK * 2;
 
-template <bool A_MN, bool B_MN, int STAGES, bool RES>
+template <bool A_MN, bool B_MN, int STAGES, bool RES, bool GLU = false>
 __global__ void __launch_bounds__(320, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR, const GemmParams p)
@@ -50,7 +57,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
     uint8_t* sC = sB + STAGES * B_STAGE_BYTES;
     uint8_t* sR = sC + 2 * C_STAGE_BYTES;                                 // RES: one residual tile per epilogue group
-    float* sBias = reinterpret_cast<float*>(sR + (RES ? 2 * C_STAGE_BYTES : 0));
+    float* sBias = reinterpret_cast<float*>(sR + ((RES || GLU) ? 2 * C_STAGE_BYTES : 0));
     uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + BN);             // each epilogue group keeps the bias of its own 128 columns
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
     const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16, drain_bar = tempty0 + 16, res_full0 = drain_bar + 8;
@@ -92,7 +99,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 const int tile_n = t / p.tiles_m, tile_m = t - tile_n * p.tiles_m;
                 const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 const int row_a = tile_m * 256 + static_cast<int>(rank) * 128;      // this CTA's rows of A (and of D)
-                const int row_b = tile_n * 256 + static_cast<int>(rank) * 128;      // this CTA's rows of B (columns of D)
+                const int row_b = GLU ? static_cast<int>(rank) * p.glu_ff + tile_n * 128  // gate rows in the leader, up rows in the peer
+                                       : tile_n * 256 + static_cast<int>(rank) * 128;     // this CTA's rows of B (columns of D)
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -190,7 +198,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const bool add_extra = (split == 0);
             const bool use_bias = p.bias_n && add_extra;
             float bias_reg = 0.f;                                // fetched while the accumulators are still being computed
-            if (use_bias) {                                      // slot j of the group: column block 2*(j/CB)+grp, column j%CB of it
+            if (GLU) {                                           // slots [0, 64): gate columns of the group, [64, 128): up columns
+                if (use_bias) bias_reg = p.bias_n[(grp_tid >> 6) * p.glu_ff + tile_n * 128 + grp * 64 + (grp_tid & 63)];
+            } else if (use_bias) {                               // slot j of the group: column block 2*(j/CB)+grp, column j%CB of it
                 const int col = tile_n * BN + (2 * (grp_tid / CB) + grp) * CB + grp_tid % CB;
                 if (col < p.N) bias_reg = p.bias_n[col];
             }
@@ -202,7 +212,81 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const int m = m0 + r_local;
             const bool row_ok = m < p.M;
             const long long row_off = static_cast<long long>(m) * p.ldc;
-            if (m0 < p.M) {
+            if (GLU) {
+                if (m0 < p.M) {
+                    const uint32_t tg = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + grp * 64;   // gate; up is 128 columns on
+                    const int n0 = tile_n * 128 + grp * 64;
+                    uint8_t* xrow = srow;                            // staging tile X: gate, then up
+                    uint8_t* yrow = rstage + r_local * 128;          // staging tile Y: the activation
+                    uint32_t ra[32], rb[32];
+                    uint32_t upk[32];                                // the up block as packed bf16 pairs, stored in pass 2
+                    // 32 accumulator columns + bias, rounded to bf16: packed pairs (what is stored) and the rounded values
+                    auto round_bias = [&](const uint32_t (&r)[32], const float* b, uint32_t* pk, float (&v)[32]) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                        if (use_bias) {
+                            const float4* b4 = reinterpret_cast<const float4*>(b);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) { const float4 t4 = b4[j]; v[4 * j] += t4.x; v[4 * j + 1] += t4.y; v[4 * j + 2] += t4.z; v[4 * j + 3] += t4.w; }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const uint32_t w = pack_bf16x2(v[j], v[j + 1]);
+                            pk[j >> 1] = w;
+                            v[j] = __uint_as_float(w << 16);
+                            v[j + 1] = __uint_as_float(w & 0xffff0000u);
+                        }
+                    };
+                    auto put = [&](uint8_t* row, const uint32_t* pk, int half) {     // 16 packed pairs = 32 columns
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            *reinterpret_cast<uint4*>(row + (((half * 4 + j) ^ (r_local & 7)) << 4)) =
+                                make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+                    };
+                    // pass 1: gate into X, the activation into Y.  Both tiles were handed to the store queue a pass or more ago.
+                    tmem_ld32(tg, ra);
+                    tmem_ld32(tg + 128, rb);
+                    tmem_ld_wait();
+                    if (elected) tma_wait_read0();
+                    group_bar(bar_id);                               // also orders the bias slots written above
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        if (half == 1) {
+                            tmem_ld32(tg + 32, ra);
+                            tmem_ld32(tg + 128 + 32, rb);
+                            tmem_ld_wait();
+                        }
+                        float g[32], u[32];
+                        uint32_t pk[16];
+                        round_bias(ra, bias_s + half * 32, pk, g);
+                        put(xrow, pk, half);
+                        round_bias(rb, bias_s + 64 + half * 32, upk + half * 16, u);
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2)
+                            pk[j >> 1] = pack_bf16x2(g[j] * __fdividef(1.0f, 1.0f + __expf(-g[j])) * u[j],
+                                                     g[j + 1] * __fdividef(1.0f, 1.0f + __expf(-g[j + 1])) * u[j + 1]);
+                        put(yrow, pk, half);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    group_bar(bar_id);
+                    if (elected) {
+                        tma_store_2d(&tmC, smem_u32(stage), n0, m0);
+                        tma_commit();
+                        tma_store_2d(&tmR, smem_u32(rstage), n0, m0);
+                        tma_commit();
+                        tma_wait_read1();                            // pass 2: up into X once the gate store has read it
+                    }
+                    group_bar(bar_id);
+                    put(xrow, upk, 0);
+                    put(xrow, upk + 16, 1);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    group_bar(bar_id);
+                    if (elected) {
+                        tma_store_2d(&tmC, smem_u32(stage), p.glu_ff + n0, m0);
+                        tma_commit();
+                    }
+                }
+            } else if (m0 < p.M) {
             // In the bf16 case (two 32-column halves per block) the second half is fetched from TMEM while the first
             // is converted.  Nothing is fetched across loop iterations: a register written by tcgen05.ld must not be
             // touched, not even moved by the compiler at a loop edge, before the wait that follows it.

@@ -219,8 +219,14 @@ static int forward_t(const nnb200_gpt_config& c, const float* P, const bf16* H, 
         NNB_TRY(attention_fwd<T>(A(a.qkv), A(a.attn), F(a.lse), doc, ranges, c, s));
         NNB_TRY(linear_fwd<T>(A(a.attn), P + lp.wo, H ? H + lp.wo : nullptr, P + lp.bo, A(a.x_in), A(a.x_mid), N, d, d, s));
         NNB_TRY(norm_fwd<T>(A(a.x_mid), P + lp.g2, PB(lp.be2), A(a.xn2), F(a.rinv2), F(a.mean2), N, d, ln, s));
-        NNB_TRY(linear_fwd<T>(A(a.xn2), P + lp.w1, H ? H + lp.w1 : nullptr, P + lp.b1, nullptr, A(a.h1), N, d, fc1, s));
-        NNB_TRY(act_fwd<T>(A(a.h1), A(a.h2), N, ff, swiglu, s));
+        if (Mode<T>::bf && swiglu && gemm_swiglu_supported(N, ff, d)) {
+            // projection and activation in one launch (the SwiGLU epilogue of the pair GEMM); same values as the two below
+            NNB_TRY(gemm_bf16_swiglu(reinterpret_cast<const bf16*>(A(a.xn2)), H + lp.w1, P + lp.b1, reinterpret_cast<bf16*>(A(a.h1)),
+                                     reinterpret_cast<bf16*>(A(a.h2)), N, ff, d, s));
+        } else {
+            NNB_TRY(linear_fwd<T>(A(a.xn2), P + lp.w1, H ? H + lp.w1 : nullptr, P + lp.b1, nullptr, A(a.h1), N, d, fc1, s));
+            NNB_TRY(act_fwd<T>(A(a.h1), A(a.h2), N, ff, swiglu, s));
+        }
         NNB_TRY(linear_fwd<T>(A(a.h2), P + lp.w2, H ? H + lp.w2 : nullptr, P + lp.b2, A(a.x_mid), x_next, N, ff, d, s));
     }
     NNB_TRY(norm_fwd<T>(A(W.x_final), P + L.lnf_g, PB(L.lnf_b), A(W.xnf), F(W.rinvf), F(W.meanf), N, d, ln, s));

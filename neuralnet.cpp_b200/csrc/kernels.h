@@ -23,6 +23,10 @@ int sgemm_strided(const float* A, const float* B, float* C, int M, int N, int K,
 int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
               int a_mn, int b_mn, int c_bf16, float alpha, const float* bias_n, const void* residual, int accumulate,
               cudaStream_t stream);
+// first projection of a SwiGLU feed-forward block and its activation in one launch: H1[M, 2 ff] = X W^T + bias (W rows:
+// gate, then up), H2[M, ff] = gate * sigmoid(gate) * up, bit-identical to gemm_bf16 followed by act_fwd
+bool gemm_swiglu_supported(int M, int ff, int K);
+int gemm_bf16_swiglu(const bf16* X, const bf16* W, const float* bias, bf16* H1, bf16* H2, int M, int ff, int K, cudaStream_t stream);
 int gemm_device_error(int* code);
 int gemm_pair_capacity();
 // {next item, CTAs that have left} of (current device, stream), zero between launches (work_counter.cu)

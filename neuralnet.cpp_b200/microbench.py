@@ -2,7 +2,7 @@
 """Kernel microbenchmarks through the C ABI (BASELINE configuration 5): bf16 inputs, values N(0,1) from a seed.
 
   python neuralnet.cpp_b200/microbench.py                   the whole sweep, one JSON line per case
-  python neuralnet.cpp_b200/microbench.py --only gemm        one family: gemm | attention | ce | rmsnorm | step_gemms
+  python neuralnet.cpp_b200/microbench.py --only gemm        one family: gemm | attention | ce | rmsnorm | step_gemms | linear_swiglu
   python neuralnet.cpp_b200/microbench.py --only train_step --shape 2,16 --iters 2 --no-time
                                                              training steps of a shallow copy of the benchmark model (layers,
                                                              micro-batch): every kernel of the step on ~2 GB, for profiler captures
@@ -128,6 +128,32 @@ def run_attention(B, S_, H, dk, args):
              unit="TFLOP/s", frac=ach / tf, peak_source=src)
 
 
+def run_linear_swiglu(M, ff, K, args):
+    """First feed-forward projection + SwiGLU: one launch (the GEMM's SwiGLU epilogue) against GEMM + activation kernel."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * ff, K, device="cuda", generator=g) * 0.05).bfloat16()
+    b = torch.randn(2 * ff, device="cuda", generator=g)
+    h1 = torch.empty(M, 2 * ff, device="cuda", dtype=torch.bfloat16)
+    h2 = torch.empty(M, ff, device="cuda", dtype=torch.bfloat16)
+    fused = lambda: call("nnb200_linear_swiglu_forward", P(x), P(w), P(b), P(h1), P(h2), M, ff, K, S())
+
+    def two():
+        call("nnb200_gemm_bf16", P(x), P(w), P(h1), M, 2 * ff, K, K, K, 2 * ff, 0, 0, 1, C.c_float(1.0), P(b), None, 0, S())
+        call("nnb200_activation_forward", P(h1), P(h2), M, ff, 1, 1, S())
+    if args.no_time:
+        for _ in range(args.iters):
+            fused()
+        torch.cuda.synchronize()
+        return
+    hbm, tf, src = peaks()
+    for name, fn in (("linear_swiglu.fused", fused), ("linear_swiglu.two_kernels", two)):
+        ms = timed(fn, args.iters, args.flush_l2)
+        ach = 4.0 * M * ff * K / ms / 1e9
+        emit(kernel=name, M=M, ff=ff, K=K, us=ms * 1e3, bound="tensor", achieved=ach, peak=tf, unit="TFLOP/s", frac=ach / tf,
+             peak_source=src)
+
+
 def run_ce(rows, V, args):
     g = torch.Generator(device="cuda").manual_seed(5)
     logits = torch.randn(rows, V, device="cuda", generator=g).bfloat16()
@@ -224,7 +250,7 @@ def run_train_step(layers, batch, args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="all")
-    ap.add_argument("--shape", default=None, help="comma-separated override: gemm M,N,K | attention B,S,H,dk | ce rows,V | rmsnorm rows,d")
+    ap.add_argument("--shape", default=None, help="comma-separated override: gemm M,N,K | attention B,S,H,dk | ce rows,V | rmsnorm rows,d | linear_swiglu M,ff,K")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--no-time", action="store_true", help="just launch --iters times (for profiler captures)")
@@ -241,6 +267,9 @@ def main():
             run_gemm(T, n, k, args, bias=True, tag=tag + ".fwd")
             run_gemm(T, k, n, args, b_mn=1, tag=tag + ".dx")
             run_gemm(n, k, T, args, a_mn=1, b_mn=1, c_bf16=0, acc=1, tag=tag + ".dw")
+    if fam in ("all", "linear_swiglu"):
+        for s in ([shape] if shape else [(16384, 2048, 768), (8192, 2816, 1024)]):
+            run_linear_swiglu(*s, args)
     if fam in ("all", "attention"):
         for s in ([shape] if shape else [(4, sq, 16, dk) for dk in (64, 128) for sq in (512, 1024, 2048, 4096, 8192)]):
             run_attention(*s, args)

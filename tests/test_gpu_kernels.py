@@ -87,6 +87,44 @@ def test_gemm_bf16_split_k_weight_gradient_shape(g):
     _gemm_case(g, 384, 256, 8192, 1, 1, c_bf16=False, bias=False, residual=False, accumulate=True)
 
 
+@pytest.mark.parametrize("bias", [True, False])
+@pytest.mark.parametrize("M,ff,K", [(300, 128, 64), (1000, 384, 200), (2048, 2048, 768), (20000, 256, 128), (4096, 2816, 1024)])
+def test_linear_swiglu_forward_equals_two_kernels(g, M, ff, K, bias):
+    """The projection with the SwiGLU epilogue against the plain projection followed by the activation kernel: both
+    outputs bit for bit (ragged rows, one and many tiles per CTA pair, both staging tiles of a group wrapping), and the
+    projection against float64."""
+    import torch
+    r = _rng(M + ff)
+    X = g.bf16_round(r.standard_normal((M, K)))
+    W = g.bf16_round(r.standard_normal((2 * ff, K)) * 0.1)
+    bv = r.standard_normal(2 * ff).astype(np.float32) if bias else None
+    x, w, b = g.dev(X, torch.bfloat16), g.dev(W, torch.bfloat16), (g.dev(bv) if bias else None)
+    assert g.call("nnb200_linear_swiglu_supported", M, ff, K) == 1
+    h1 = torch.full((M, 2 * ff), 7.0, dtype=torch.bfloat16, device="cuda")
+    h2 = torch.full((M, ff), 7.0, dtype=torch.bfloat16, device="cuda")
+    g.call("nnb200_linear_swiglu_forward", g.ptr(x), g.ptr(w), g.ptr(b), g.ptr(h1), g.ptr(h2), M, ff, K, g.stream())
+    r1 = torch.zeros_like(h1)
+    r2 = torch.zeros_like(h2)
+    g.call("nnb200_gemm_bf16", g.ptr(x), g.ptr(w), g.ptr(r1), M, 2 * ff, K, K, K, 2 * ff, 0, 0, 1, C.c_float(1.0), g.ptr(b),
+           None, 0, g.stream())
+    g.call("nnb200_activation_forward", g.ptr(r1), g.ptr(r2), M, ff, 1, 1, g.stream())
+    torch.cuda.synchronize()
+    assert g.gemm_status() == 0
+    assert torch.equal(h1, r1)
+    assert torch.equal(h2, r2)
+    want = X.astype(np.float64) @ W.astype(np.float64).T + (bv[None, :] if bias else 0.0)
+    assert np.abs(g.host(h1) - want).max() < 2e-2 * np.sqrt(K)
+
+
+def test_linear_swiglu_forward_rejects_unsupported_shapes(g):
+    import torch
+    assert g.call("nnb200_linear_swiglu_supported", 128, 256, 64) == 0      # a single 128-row block
+    assert g.call("nnb200_linear_swiglu_supported", 1024, 200, 64) == 0     # ff not a multiple of 128
+    t = torch.zeros(1024, 512, dtype=torch.bfloat16, device="cuda")
+    rc = g.nnb.lib.nnb200_linear_swiglu_forward(g.ptr(t), g.ptr(t), None, g.ptr(t), g.ptr(t), 1024, 200, 64, g.stream())
+    assert rc == -1
+
+
 def test_gemm_bf16_rejects_bad_leading_dimension(g):
     import torch
     a = torch.zeros(64, 60, dtype=torch.bfloat16, device="cuda")
