@@ -104,7 +104,8 @@ int nnb200_gemm_f32(const float* A, const float* B, float* D, int M, int N, int 
 /* Per-launch timing of the tcgen05 GEMM: enable=1 starts recording a CUDA event pair around every
  * GEMM kernel on its launching stream (and resets the totals), enable=0 stops.  _read synchronises
  * on the recorded events and returns (host) the summed kernel time, the summed algorithmic FLOPs
- * (2*M*N*K per launch) and the number of launches. */
+ * (2*M*N*K per launch) and the number of launches.  Only launches on the stream of the first GEMM after enabling
+ * are recorded: pairs of launches that overlap on other streams would add up to more than the time that passed. */
 int nnb200_gemm_profile(int enable);
 int nnb200_gemm_profile_read(double* host_total_ms, double* host_total_flops, int* host_launches);
 /* CTA pairs (two SMs running one 256 x 256 tile with tcgen05.mma.cta_group::2) the device keeps resident at once;

@@ -387,9 +387,19 @@ struct GemmProfile {
     std::vector<cudaEvent_t> events;     // pairs: start, stop
     size_t used = 0;
     double flops = 0.0;
+    // Only the launches of one stream are recorded, that of the first GEMM after enabling: event pairs of launches that
+    // overlap on other streams (the Newton-Schulz lanes of Muon) would add up to more than the time that passed.
+    bool have_stream = false;
+    cudaStream_t stream = nullptr;
 };
 static GemmProfile g_prof;
 
+static bool prof_takes(cudaStream_t s)
+{
+    if (!g_prof.on) return false;
+    if (!g_prof.have_stream) { g_prof.have_stream = true; g_prof.stream = s; }
+    return g_prof.stream == s;
+}
 static cudaEvent_t prof_event(cudaStream_t s)
 {
     if (g_prof.used == g_prof.events.size()) {
@@ -412,9 +422,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_kernel<BN, A_MN, B_MN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); }));
     const int units = p.tiles_m * p.tiles_n * p.splits;
     const int grid = units < sm_count() ? units : sm_count();
-    if (g_prof.on) prof_event(s);
+    const bool rec = prof_takes(s);
+    if (rec) prof_event(s);
     gemm_bf16_kernel<BN, A_MN, B_MN, STAGES><<<grid, 192, SMEM, s>>>(ta, tb, tcm, p);
-    if (g_prof.on) { prof_event(s); g_prof.flops += 2.0 * p.M * p.N * p.K; }
+    if (rec) { prof_event(s); g_prof.flops += 2.0 * p.M * p.N * p.K; }
     NNB_LAUNCH_CHECK();
     return 0;
 }
@@ -475,9 +486,10 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    if (g_prof.on) prof_event(s);
+    const bool rec = prof_takes(s);
+    if (rec) prof_event(s);
     NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU>, ta, tb, tcm, tr, p));
-    if (g_prof.on) { prof_event(s); g_prof.flops += 2.0 * p.M * p.N * p.K; }
+    if (rec) { prof_event(s); g_prof.flops += (GLU ? 4.0 : 2.0) * p.M * p.N * p.K; }     // GLU: p.N is half the product's width
     NNB_LAUNCH_CHECK();
     return 0;
 }
@@ -583,9 +595,7 @@ int gemm_bf16_swiglu(const bf16* X, const bf16* W, const float* bias, bf16* H1, 
     NNB_TRY(tensor_map_2d(W, K, 2 * ff, K, BK, PAIR_BN_HALF, &tb, 2));
     NNB_TRY(tensor_map_2d(H1, 2 * ff, M, 2LL * ff, 64, BM, &t1, 2));
     NNB_TRY(tensor_map_2d(H2, ff, M, ff, 64, BM, &t2, 2));
-    const int rc = launch_gemm_pair<false, false, false, true>(ta, tb, t1, t2, p, stream);
-    if (g_prof.on) g_prof.flops += 2.0 * M * ff * K;            // the launcher counted p.N = ff columns; the product has 2 ff
-    return rc;
+    return launch_gemm_pair<false, false, false, true>(ta, tb, t1, t2, p, stream);
 }
 
 int gemm_pair_capacity() { return pair_capacity(); }
@@ -593,7 +603,7 @@ int gemm_pair_capacity() { return pair_capacity(); }
 int gemm_profile_enable(int enable)
 {
     g_prof.on = enable != 0;
-    if (g_prof.on) { g_prof.used = 0; g_prof.flops = 0.0; }
+    if (g_prof.on) { g_prof.used = 0; g_prof.flops = 0.0; g_prof.have_stream = false; }
     return 0;
 }
 int gemm_profile_read(double* total_ms, double* total_flops, int* launches)
