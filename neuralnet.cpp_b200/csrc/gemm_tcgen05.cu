@@ -469,12 +469,12 @@ static int pair_capacity()
     return n > 0 ? n : 0;
 }
 
-template <bool A_MN, bool B_MN, bool RES = false, bool GLU = false>
+template <bool A_MN, bool B_MN, bool RES = false, bool GLU = false, bool DB = false>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tcm, const CUtensorMap& tr, const GemmParams& p, cudaStream_t s)
 {
-    constexpr int STAGES = (RES || GLU) ? PAIR_STAGES_RES : PAIR_STAGES;
+    constexpr int STAGES = (RES || GLU || DB) ? PAIR_STAGES_RES : PAIR_STAGES;
     static PerDeviceOnce once;
-    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
+    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU, DB>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
     const int units = p.tiles_m * p.tiles_n * p.splits;
     const int pairs = units < pair_capacity() ? units : pair_capacity();
     cudaLaunchConfig_t cfg = {};
@@ -488,7 +488,7 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     cfg.attrs = at; cfg.numAttrs = 1;
     const bool rec = prof_takes(s);
     if (rec) prof_event(s);
-    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU>, ta, tb, tcm, tr, p));
+    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU, DB>, ta, tb, tcm, tr, p));
     if (rec) { prof_event(s); g_prof.flops += (GLU ? 4.0 : 2.0) * p.M * p.N * p.K; }     // GLU: p.N is half the product's width
     NNB_LAUNCH_CHECK();
     return 0;
@@ -548,10 +548,15 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
             NNB_TRY(tensor_map_2d(residual, N, M, ldc, 64, BM, &tr, 2));
             return launch_gemm_pair<false, false, true>(ta, tb, tcm, tr, p, stream);
         }
+        // Two staging tiles per epilogue group (and five operand stages instead of six) where it was measured faster:
+        // short main loops of the forward projections (K <= 1024: 16384 x 2304 x 768 55.3 -> 51.2 us, 16384 x 8192 x 768
+        // 170.0 -> 161.6) and the split-K weight gradients (768 x 768 x 16384 23.4 -> 22.0 us); the input-gradient
+        // products (B read MN-major) lose 1-2 % with five stages and keep six.
+        if (!a_mn && !b_mn && p.kb_per_split <= 16) return launch_gemm_pair<false, false, false, false, true>(ta, tb, tcm, tcm, p, stream);
+        if (a_mn && b_mn) return launch_gemm_pair<true, true, false, false, true>(ta, tb, tcm, tcm, p, stream);
         if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(ta, tb, tcm, tcm, p, stream);
         if (!a_mn && b_mn) return launch_gemm_pair<false, true>(ta, tb, tcm, tcm, p, stream);
-        if (a_mn && !b_mn) return launch_gemm_pair<true, false>(ta, tb, tcm, tcm, p, stream);
-        return launch_gemm_pair<true, true>(ta, tb, tcm, tcm, p, stream);
+        return launch_gemm_pair<true, false>(ta, tb, tcm, tcm, p, stream);
     }
 #define GO(bn, am, bm) return launch_gemm<bn, am, bm>(ta, tb, tcm, p, stream)
     if (BN == 256) {

@@ -25,6 +25,9 @@
 // the next) as soon as the group has consumed the previous one, a whole block period ahead; the threads read it with
 // the swizzle they write the output with.  The 32 KB come out of the operand ring (five stages instead of six).
 //
+// DB: each epilogue group has two staging tiles and uses them in turn, so a block's conversion does not wait for the
+// previous block's store to have read its tile; the 32 KB come out of the operand ring as in the RES form.
+//
 // GLU: the product is the first projection of a SwiGLU feed-forward block (compute_layer.hpp:395-445): B holds the
 // gate rows [0, ff) and then the up rows [ff, 2 ff).  The leader stages 128 gate rows and its peer the 128 up rows of
 // the same columns, so every CTA's accumulator has gate in columns [0, 128) and up in [128, 256) of one 128-column
@@ -38,7 +41,7 @@ namespace nnb {
 constexpr int PAIR_BN_HALF = 128;                                // rows of B each CTA stages per k-block
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_BN_HALF * BK * 2;
 
-template <bool A_MN, bool B_MN, int STAGES, bool RES, bool GLU = false>
+template <bool A_MN, bool B_MN, int STAGES, bool RES, bool GLU = false, bool DB = false>
 __global__ void __launch_bounds__(320, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR, const GemmParams p)
@@ -57,7 +60,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
     uint8_t* sC = sB + STAGES * B_STAGE_BYTES;
     uint8_t* sR = sC + 2 * C_STAGE_BYTES;                                 // RES: one residual tile per epilogue group
-    float* sBias = reinterpret_cast<float*>(sR + ((RES || GLU) ? 2 * C_STAGE_BYTES : 0));
+    float* sBias = reinterpret_cast<float*>(sR + ((RES || GLU || DB) ? 2 * C_STAGE_BYTES : 0));
     uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + BN);             // each epilogue group keeps the bias of its own 128 columns
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
     const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16, drain_bar = tempty0 + 16, res_full0 = drain_bar + 8;
@@ -189,7 +192,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             }
         };
         if (RES && elected) request_next_residual();
-        int tc = 0;
+        int tc = 0, blk = 0;
         for (int u = pair; u < units; u += pairs, ++tc) {
             const int split = u / tiles, t = u - split * tiles;
             const int tile_n = t / p.tiles_m, tile_m = t - tile_n * p.tiles_m;
@@ -297,7 +300,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             for (int cb = grp; cb * CB < BN; cb += 2) {
                 const int n0 = tile_n * BN + cb * CB;
                 if (n0 >= p.N) break;
-                if (elected) tma_wait_read0();                   // the group's previous store has read the staging tile
+                if (DB) {                                        // two staging tiles per group, used in turn
+                    stage = ((blk & 1) ? sR : sC) + grp * C_STAGE_BYTES;
+                    srow = stage + r_local * 128;
+                    ++blk;
+                    if (elected) tma_wait_read1();               // the store before the group's previous one has read this tile
+                } else if (elected) tma_wait_read0();            // the group's previous store has read the staging tile
                 group_bar(bar_id);
                 if (piped) {
                     tmem_ld32(tbase + cb * CB, ra);
