@@ -97,6 +97,17 @@ int nnb200_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K,
 int nnb200_linear_swiglu_supported(int M, int ff, int K);
 int nnb200_linear_swiglu_forward(const void* x, const void* W, const float* bias, void* h1, void* h2, int M, int ff, int K,
                                  void* stream);
+/* Input gradient of a projection with a row term, one launch: dX[M, N] = dY[M, K] W[K, N] (W stored (K, N), N
+ * contiguous: the (out, in) weight of Linear) and dot[(m / S * H + h) * S + m % S] = sum over the 64 columns of block
+ * h of dX (as stored, bf16) * other[m, .], H = N / 64.  With dY the gradient of the attention out-projection's output
+ * and other the attention output (heads of 64) this leaves rowsum(dO * O) per (batch, head, row) in the layout
+ * nnb200_attention_backward keeps its dvec in.  All matrices bf16, dot fp32.  Needs M > 128, N = 64 H > 128, S | M,
+ * K a multiple of 8 (nnb200_gemm_bf16_rowdot_supported: 1 or 0); -1 otherwise.  Replaces Linear::backward's input
+ * gradient (compute_layer.hpp:176-195) plus a pass the reference does not have as such: its attention backward forms
+ * sum_j P_ij dP_ij inside softmax_backward_q / _kv (compute_layer.hpp:1317-1346). */
+int nnb200_gemm_bf16_rowdot_supported(int M, int N, int K, int S, int H);
+int nnb200_gemm_bf16_rowdot(const void* dY, const void* W, void* dX, const void* other, float* dot, int M, int N, int K,
+                            int S, int H, void* stream);
 /* Same contract, fp32 operands and fp32 SIMT arithmetic (the check mode). */
 int nnb200_gemm_f32(const float* A, const float* B, float* D, int M, int N, int K, long long lda, long long ldb,
                     long long ldc, int a_mn_major, int b_mn_major, float alpha, const float* bias_n,

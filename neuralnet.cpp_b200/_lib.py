@@ -79,6 +79,8 @@ SIGNATURES = {
     "nnb200_bias_grad_static": [_p, _ll, _p, _i, _i, _i, _p],
     "nnb200_activation_forward": [_p, _p, _i, _i, _i, _i, _p],
     "nnb200_linear_swiglu_supported": [_i, _i, _i],
+    "nnb200_gemm_bf16_rowdot_supported": [_i, _i, _i, _i, _i],
+    "nnb200_gemm_bf16_rowdot": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
     "nnb200_linear_swiglu_forward": [_p, _p, _p, _p, _p, _i, _i, _i, _p],
     "nnb200_activation_backward": [_p, _p, _p, _i, _i, _i, _i, _p],
     "nnb200_cross_entropy": [_p, _p, _p, _f, _p, _p, _p, _i, _i, _i, _i, _p],
@@ -140,7 +142,7 @@ _RET = {
 # functions whose int return value is a count, not a status
 _COUNT = {"nnb200_gpt_param_table"}
 # functions that return a plain value (negative values are answers, not errors)
-_VALUE = {"nnb200_gemm_pair_capacity", "nnb200_linear_swiglu_supported", "nnb200_expr_reduce_axis", "nnb200_rt_device", "nnb200_rt_stream"}
+_VALUE = {"nnb200_gemm_pair_capacity", "nnb200_linear_swiglu_supported", "nnb200_gemm_bf16_rowdot_supported", "nnb200_expr_reduce_axis", "nnb200_rt_device", "nnb200_rt_stream"}
 
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)

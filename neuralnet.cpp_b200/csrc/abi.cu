@@ -99,6 +99,14 @@ int nnb200_linear_swiglu_forward(const void* x, const void* W, const float* bias
                             static_cast<bf16*>(h2), M, ff, K, to_stream(stream));
 }
 
+int nnb200_gemm_bf16_rowdot_supported(int M, int N, int K, int S, int H) { return gemm_rowdot_supported(M, N, K, S, H) ? 1 : 0; }
+int nnb200_gemm_bf16_rowdot(const void* dY, const void* W, void* dX, const void* other, float* dot, int M, int N, int K,
+                            int S, int H, void* stream)
+{
+    return gemm_bf16_dx_rowdot(static_cast<const bf16*>(dY), static_cast<const bf16*>(W), static_cast<bf16*>(dX),
+                               static_cast<const bf16*>(other), dot, M, N, K, S, H, to_stream(stream));
+}
+
 int nnb200_gemm_pair_capacity(void) { return nnb::gemm_pair_capacity(); }
 int nnb200_gemm_status(int* host_code)
 {

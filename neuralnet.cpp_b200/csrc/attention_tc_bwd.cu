@@ -765,11 +765,11 @@ static int launch_bwd_tc(const CUtensorMap& q128, const CUtensorMap& q64, const 
 }
 
 int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const float* lse, float* dvec, bf16* dqkv,
-                     const int* doc, const int* doc_ranges, int B, int S, int H, int dk, int alibi, cudaStream_t s)
+                     const int* doc, const int* doc_ranges, int B, int S, int H, int dk, int alibi, cudaStream_t s, bool have_dvec)
 {
     if (static_cast<long long>(B) * S * H == 0) return 0;
     NNB_ARG_CHECK(attention_tc_supported(dk, S, H * dk), "shape not supported by the tcgen05 attention kernels");
-    NNB_TRY(attention_dvec_bf16(out, dout, dvec, B, S, H, dk, s));
+    if (!have_dvec) NNB_TRY(attention_dvec_bf16(out, dout, dvec, B, S, H, dk, s));
     const int d = H * dk;
     const long long rows = static_cast<long long>(B) * S;
     CUtensorMap q128, q64, do128, do64;

@@ -42,6 +42,8 @@ struct GemmParams {
     const void* residual;
     float alpha;
     int glu_ff;                 // SwiGLU variant of the pair kernel: rows of B per half (gate rows, then up rows); 0 otherwise
+    float* dot_out;             // row-dot variant: sums per (row, 64-column block), laid out [row / dot_S][block][row % dot_S]
+    int dot_S, dot_H;
 };
 
 // ---------------------------------------------------------------- kernel
@@ -469,12 +471,12 @@ static int pair_capacity()
     return n > 0 ? n : 0;
 }
 
-template <bool A_MN, bool B_MN, bool RES = false, bool GLU = false, bool DB = false>
+template <bool A_MN, bool B_MN, bool RES = false, bool GLU = false, bool DB = false, bool DOT = false>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tcm, const CUtensorMap& tr, const GemmParams& p, cudaStream_t s)
 {
-    constexpr int STAGES = (RES || GLU || DB) ? PAIR_STAGES_RES : PAIR_STAGES;
+    constexpr int STAGES = (RES || GLU || DB || DOT) ? PAIR_STAGES_RES : PAIR_STAGES;
     static PerDeviceOnce once;
-    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU, DB>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
+    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU, DB, DOT>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
     const int units = p.tiles_m * p.tiles_n * p.splits;
     const int pairs = units < pair_capacity() ? units : pair_capacity();
     cudaLaunchConfig_t cfg = {};
@@ -488,7 +490,7 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     cfg.attrs = at; cfg.numAttrs = 1;
     const bool rec = prof_takes(s);
     if (rec) prof_event(s);
-    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU, DB>, ta, tb, tcm, tr, p));
+    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU, DB, DOT>, ta, tb, tcm, tr, p));
     if (rec) { prof_event(s); g_prof.flops += (GLU ? 4.0 : 2.0) * p.M * p.N * p.K; }     // GLU: p.N is half the product's width
     NNB_LAUNCH_CHECK();
     return 0;
@@ -601,6 +603,36 @@ int gemm_bf16_swiglu(const bf16* X, const bf16* W, const float* bias, bf16* H1, 
     NNB_TRY(tensor_map_2d(H1, 2 * ff, M, 2LL * ff, 64, BM, &t1, 2));
     NNB_TRY(tensor_map_2d(H2, ff, M, ff, 64, BM, &t2, 2));
     return launch_gemm_pair<false, false, false, true>(ta, tb, t1, t2, p, stream);
+}
+
+// dX[M, N] = dY[M, K] W[K, N] (W stored (K, N), N contiguous) and, from the same epilogue, the sums over each 64-column
+// block of dX (as stored in bf16) times `other` (M, N): dot_out[(m / S * H + block) * S + m % S], H = N / 64 blocks.
+bool gemm_rowdot_supported(int M, int N, int K, int S, int H)
+{
+    return M > 128 && N > 128 && N == 64 * H && S > 0 && (M % S) == 0 && K > 0 && (K % 8) == 0 && pair_capacity() > 0;
+}
+int gemm_bf16_dx_rowdot(const bf16* dY, const bf16* W, bf16* dX, const bf16* other, float* dot_out, int M, int N, int K, int S, int H,
+                        cudaStream_t stream)
+{
+    NNB_ARG_CHECK(gemm_rowdot_supported(M, N, K, S, H), "shape not supported by the row-dot epilogue");
+    NNB_ARG_CHECK(((reinterpret_cast<uintptr_t>(dY) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(dX) |
+                    reinterpret_cast<uintptr_t>(other)) & 15) == 0 && dot_out, "operands must be 16-byte aligned");
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K;
+    p.C = dX; p.ldc = N; p.c_bf16 = 1; p.accumulate = 0;
+    p.alpha = 1.0f; p.vec_ok = 1; p.tma_store = 1;
+    p.dot_out = dot_out; p.dot_S = S; p.dot_H = H;
+    p.tiles_m = static_cast<int>(ceil_div(M, 256));
+    p.tiles_n = static_cast<int>(ceil_div(N, 256));
+    p.kb_total = static_cast<int>(ceil_div(K, BK));
+    p.splits = 1;
+    p.kb_per_split = p.kb_total;
+    CUtensorMap ta, tb, tcm, tr;
+    NNB_TRY(tensor_map_2d(dY, K, M, K, BK, BM, &ta, 2));
+    NNB_TRY(tensor_map_2d(W, N, K, N, 64, BK, &tb, 2));
+    NNB_TRY(tensor_map_2d(dX, N, M, N, 64, BM, &tcm, 2));
+    NNB_TRY(tensor_map_2d(other, N, M, N, 64, BM, &tr, 2));
+    return launch_gemm_pair<false, true, false, false, false, true>(ta, tb, tcm, tr, p, stream);
 }
 
 int gemm_pair_capacity() { return pair_capacity(); }

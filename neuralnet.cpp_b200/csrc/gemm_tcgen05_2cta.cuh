@@ -25,6 +25,12 @@
 // the next) as soon as the group has consumed the previous one, a whole block period ahead; the threads read it with
 // the swizzle they write the output with.  The 32 KB come out of the operand ring (five stages instead of six).
 //
+// DOT: the tile in the residual slot is not added but multiplied in: every thread sums, over the 64 columns of a
+// block, the product of the bf16 value it stores and the element of the other matrix at the same place, and writes the
+// sum to dot_out[(m / dot_S * dot_H + block) * dot_S + m % dot_S].  With the output gradient of the attention
+// out-projection as the product and the attention output as the other matrix this is the row term
+// D = rowsum(dO * O) of the attention backward pass (64 columns = one head), which then needs no pass of its own.
+//
 // DB: each epilogue group has two staging tiles and uses them in turn, so a block's conversion does not wait for the
 // previous block's store to have read its tile; the 32 KB come out of the operand ring as in the RES form.
 //
@@ -41,7 +47,7 @@ namespace nnb {
 constexpr int PAIR_BN_HALF = 128;                                // rows of B each CTA stages per k-block
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_BN_HALF * BK * 2;
 
-template <bool A_MN, bool B_MN, int STAGES, bool RES, bool GLU = false, bool DB = false>
+template <bool A_MN, bool B_MN, int STAGES, bool RES, bool GLU = false, bool DB = false, bool DOT = false>
 __global__ void __launch_bounds__(320, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR, const GemmParams p)
@@ -60,7 +66,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
     uint8_t* sC = sB + STAGES * B_STAGE_BYTES;
     uint8_t* sR = sC + 2 * C_STAGE_BYTES;                                 // RES: one residual tile per epilogue group
-    float* sBias = reinterpret_cast<float*>(sR + ((RES || GLU || DB) ? 2 * C_STAGE_BYTES : 0));
+    constexpr bool RT = RES || DOT;                                       // a second tile comes in through the residual slot
+    float* sBias = reinterpret_cast<float*>(sR + ((RT || GLU || DB) ? 2 * C_STAGE_BYTES : 0));
     uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + BN);             // each epilogue group keeps the bias of its own 128 columns
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
     const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16, drain_bar = tempty0 + 16, res_full0 = drain_bar + 8;
@@ -191,7 +198,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 return;
             }
         };
-        if (RES && elected) request_next_residual();
+        if (RT && elected) request_next_residual();
         int tc = 0, blk = 0;
         for (int u = pair; u < units; u += pairs, ++tc) {
             const int split = u / tiles, t = u - split * tiles;
@@ -214,6 +221,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const int m0 = tile_m * 256 + static_cast<int>(rank) * 128;
             const int m = m0 + r_local;
             const bool row_ok = m < p.M;
+            const int dot_b = DOT ? m / p.dot_S : 0;
             const long long row_off = static_cast<long long>(m) * p.ldc;
             if (GLU) {
                 if (m0 < p.M) {
@@ -315,6 +323,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     tmem_ld32(tbase + cb * CB, ra);
                     tmem_ld_wait();
                 }
+                float dot = 0.f;
                 auto emit = [&](const uint32_t (&r)[32], int half) {
                     float v[32];
 #pragma unroll
@@ -340,6 +349,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                             Vec16<bf16> o;
 #pragma unroll
                             for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(v[j + k]);
+                            if (DOT) {                            // zeros beyond the matrix, as above
+                                const Vec16<bf16> rr = *reinterpret_cast<const Vec16<bf16>*>(rrow + (((half * 4 + (j >> 3)) ^ (r_local & 7)) << 4));
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) dot = fmaf(__bfloat162float(o.v[k]), __bfloat162float(rr.v[k]), dot);
+                            }
                             const int chunk = half * 4 + (j >> 3);
                             *reinterpret_cast<uint4*>(srow + ((chunk ^ (r_local & 7)) << 4)) = *reinterpret_cast<const uint4*>(&o);
                         }
@@ -355,7 +369,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         }
                     }
                 };
-                if (RES) {                                       // this block's residual tile, requested a block period ago
+                if (RT) {                                        // this block's residual tile, requested a block period ago
                     const bool got = mbar_wait(res_full, res_uses & 1, abort_flag, 11, &g_gemm_error);
                     ++res_uses;
                     if (group_any(bar_id, !got)) break;
@@ -363,13 +377,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 emit(ra, 0);
                 if (piped) tmem_ld_wait();                       // second half
                 if (CB == 64) emit(rb, 1);
+                if (DOT && row_ok)
+                    p.dot_out[(static_cast<size_t>(dot_b) * p.dot_H + (n0 >> 6)) * p.dot_S + (m - dot_b * p.dot_S)] = dot;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 group_bar(bar_id);
                 if (elected) {
                     if (p.accumulate) tma_reduce_add_2d(&tmC, smem_u32(stage), n0, m0);
                     else tma_store_2d(&tmC, smem_u32(stage), n0, m0);
                     tma_commit();
-                    if (RES) request_next_residual();            // the group is past its reads of the residual tile
+                    if (RT) request_next_residual();             // the group is past its reads of the residual tile
                 }
             }
             }

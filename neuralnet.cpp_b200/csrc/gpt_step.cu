@@ -174,12 +174,12 @@ static int attention_fwd(const T* qkv, T* out, float* lse, const int* doc, const
 }
 template <typename T>
 static int attention_bwd(const T* qkv, const T* out, const T* dout, const float* lse, float* dvec, T* dqkv, const int* doc,
-                         const int* ranges, const nnb200_gpt_config& c, cudaStream_t s)
+                         const int* ranges, const nnb200_gpt_config& c, cudaStream_t s, bool have_dvec = false)
 {
     const int dk = c.d_model / c.heads, alibi = c.pos == 2;
     if constexpr (Mode<T>::bf) {
         if (attention_tc_supported(dk, c.seq, c.d_model))
-            return attention_bwd_tc(qkv, out, dout, lse, dvec, dqkv, doc, ranges, c.batch, c.seq, c.heads, dk, alibi, s);
+            return attention_bwd_tc(qkv, out, dout, lse, dvec, dqkv, doc, ranges, c.batch, c.seq, c.heads, dk, alibi, s, have_dvec);
         if (attention_mma_supported(dk, c.d_model))
             return attention_bwd_mma(qkv, out, dout, lse, dvec, dqkv, doc, c.batch, c.seq, c.heads, dk, alibi, s);
     }
@@ -313,8 +313,18 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         std::swap(g, g_other);
         // AttentionBase::backward (compute_layer.hpp:1271-1412)
         NNB_TRY(linear_bwd_params<T>(g, A(a.attn), G + lp.wo, nullptr, cs, cn, N, d, d, s));
-        NNB_TRY(linear_bwd_input<T>(g, P + lp.wo, Hh(lp.wo), A(W.d_attn), N, d, d, s));
-        NNB_TRY(attention_bwd<T>(A(a.qkv), A(a.attn), A(W.d_attn), F(a.lse), F(W.dvec), A(W.d_qkv), doc, ranges, c, s));
+        // with 64-wide heads on the tcgen05 kernels, the out-projection's input-gradient GEMM also leaves
+        // rowsum(dO * O) per head and row, which the attention backward pass would otherwise compute in a pass of its own
+        bool have_dvec = false;
+        if constexpr (Mode<T>::bf) {
+            if (d / c.heads == 64 && attention_tc_supported(64, c.seq, d) && gemm_rowdot_supported(N, d, d, c.seq, c.heads)) {
+                NNB_TRY(gemm_bf16_dx_rowdot(reinterpret_cast<const bf16*>(g), Hh(lp.wo), reinterpret_cast<bf16*>(A(W.d_attn)),
+                                            reinterpret_cast<const bf16*>(A(a.attn)), F(W.dvec), N, d, d, c.seq, c.heads, s));
+                have_dvec = true;
+            }
+        }
+        if (!have_dvec) NNB_TRY(linear_bwd_input<T>(g, P + lp.wo, Hh(lp.wo), A(W.d_attn), N, d, d, s));
+        NNB_TRY(attention_bwd<T>(A(a.qkv), A(a.attn), A(W.d_attn), F(a.lse), F(W.dvec), A(W.d_qkv), doc, ranges, c, s, have_dvec));
         // the gradients of the rotated Q and K go back through the inverse rotation (compute_layer.hpp:1365-1372)
         if (c.pos == 3) NNB_TRY(rope_apply<T>(A(W.d_qkv), F(W.sin_table), N, c.seq, c.heads, d / c.heads, 3 * d, true, s));
         NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, cn, N, d, 3 * d, s, cs_begin()));

@@ -27,6 +27,11 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
 // gate, then up), H2[M, ff] = gate * sigmoid(gate) * up, bit-identical to gemm_bf16 followed by act_fwd
 bool gemm_swiglu_supported(int M, int ff, int K);
 int gemm_bf16_swiglu(const bf16* X, const bf16* W, const float* bias, bf16* H1, bf16* H2, int M, int ff, int K, cudaStream_t stream);
+// input gradient of a projection, dX = dY W, and the sums over each 64-column block of dX * other in the same launch
+// (the row term of the attention backward pass when dX is the gradient of the attention output and other that output)
+bool gemm_rowdot_supported(int M, int N, int K, int S, int H);
+int gemm_bf16_dx_rowdot(const bf16* dY, const bf16* W, bf16* dX, const bf16* other, float* dot_out, int M, int N, int K, int S, int H,
+                        cudaStream_t stream);
 int gemm_device_error(int* code);
 int gemm_pair_capacity();
 // {next item, CTAs that have left} of (current device, stream), zero between launches (work_counter.cu)
@@ -111,8 +116,10 @@ int attention_fwd_tc(const bf16* qkv, bf16* out, float* lse, const int* doc, con
                      int alibi, cudaStream_t s);
 int attention_device_error(int* code);
 // attention_tc_bwd.cu : tcgen05 backward (same shape limits)
+// have_dvec: dvec already holds rowsum(dout * out) per (batch, head, row) (written by gemm_bf16_dx_rowdot)
 int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const float* lse, float* dvec, bf16* dqkv,
-                     const int* doc, const int* doc_ranges, int B, int S, int H, int dk, int alibi, cudaStream_t s);
+                     const int* doc, const int* doc_ranges, int B, int S, int H, int dk, int alibi, cudaStream_t s,
+                     bool have_dvec = false);
 int attention_bwd_device_error(int* code);
 // status word of the fused elementwise kernels that wait on bulk copies (reads and clears)
 int fused_device_error(int* code);

@@ -116,6 +116,31 @@ def test_linear_swiglu_forward_equals_two_kernels(g, M, ff, K, bias):
     assert np.abs(g.host(h1) - want).max() < 2e-2 * np.sqrt(K)
 
 
+@pytest.mark.parametrize("B,S,H,K", [(2, 128, 3, 64), (3, 256, 12, 768), (16, 1024, 12, 768), (5, 384, 16, 200)])
+def test_gemm_bf16_rowdot_equals_gemm_and_row_sums(g, B, S, H, K):
+    """Input-gradient GEMM with the row-dot epilogue: dX bit for bit what the plain GEMM stores, and the per-head sums of
+    dX * other against float64 over the stored bf16 values (ragged last row tile, several tiles per CTA pair)."""
+    import torch
+    M, N = B * S, 64 * H
+    r = _rng(M + H)
+    dY = g.bf16_round(r.standard_normal((M, K)))
+    W = g.bf16_round(r.standard_normal((K, N)) * 0.1)
+    O = g.bf16_round(r.standard_normal((M, N)))
+    dy, w, o = g.dev(dY, torch.bfloat16), g.dev(W, torch.bfloat16), g.dev(O, torch.bfloat16)
+    assert g.call("nnb200_gemm_bf16_rowdot_supported", M, N, K, S, H) == 1
+    dx = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    dot = torch.full((B * H * S,), 7.0, dtype=torch.float32, device="cuda")
+    g.call("nnb200_gemm_bf16_rowdot", g.ptr(dy), g.ptr(w), g.ptr(dx), g.ptr(o), g.ptr(dot), M, N, K, S, H, g.stream())
+    ref = torch.zeros_like(dx)
+    g.call("nnb200_gemm_bf16", g.ptr(dy), g.ptr(w), g.ptr(ref), M, N, K, K, N, N, 0, 1, 1, C.c_float(1.0), None, None, 0, g.stream())
+    torch.cuda.synchronize()
+    assert g.gemm_status() == 0
+    assert torch.equal(dx, ref)
+    want = (g.host(dx).astype(np.float64) * O).reshape(B, S, H, 64).sum(-1).transpose(0, 2, 1).reshape(-1)
+    got = g.host(dot)
+    assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max())
+
+
 def test_linear_swiglu_forward_rejects_unsupported_shapes(g):
     import torch
     assert g.call("nnb200_linear_swiglu_supported", 128, 256, 64) == 0      # a single 128-row block
