@@ -391,6 +391,9 @@ def main():
     nnb.call("nnb200_gemm_profile", 0)
     tms, tfl, nl = C.c_double(0), C.c_double(0), C.c_int(0)
     nnb.call("nnb200_gemm_profile_read", C.byref(tms), C.byref(tfl), C.byref(nl))
+    # the GEMM launches whose epilogue also runs the SwiGLU activation (forward: fc1, backward: fc2's input gradient)
+    fms, ffl, fnl = C.c_double(0), C.c_double(0), C.c_int(0)
+    nnb.call("nnb200_gemm_profile_read_fused", C.byref(fms), C.byref(ffl), C.byref(fnl))
     torch.cuda.synchronize()
     muon_ms = tr.muon_ms() if w["muon"] else None
     tr.check_device_status()
@@ -440,6 +443,14 @@ def main():
                      "peak_source": peaks["source"] + " cuBLAS bf16, sustained (kernel timed inside a long step)",
                      "launches_timed": nl.value, "share_of_step": tms.value / (ms_resident / K) if ms_resident else None},
     }
+    if fnl.value:
+        # not in `achieved`: these launches also do the work of the activation kernels they replace, and their epilogue
+        # outlasts the main loop; with them the GEMM family's rate is `all_gemm_launches_tflops`
+        line["roofline"]["with_activation_epilogue"] = {
+            "launches": fnl.value, "ms_per_step": fms.value,
+            "tflops": (ffl.value / (fms.value * 1e-3)) / 1e12 if fms.value > 0 else None,
+            "all_gemm_launches_tflops": ((tfl.value + ffl.value) / ((tms.value + fms.value) * 1e-3)) / 1e12,
+            "share_of_step": fms.value / (ms_resident / K) if ms_resident else None}
     if w["muon"]:
         mf = muon_flops_per_step(w)
         line["muon"] = {"ms_per_step": muon_ms, "newton_schulz_flops_per_step": mf,

@@ -97,6 +97,14 @@ int nnb200_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K,
 int nnb200_linear_swiglu_supported(int M, int ff, int K);
 int nnb200_linear_swiglu_forward(const void* x, const void* W, const float* bias, void* h1, void* h2, int M, int ff, int K,
                                  void* stream);
+/* Input gradient of a SwiGLU block's second projection taken through the activation, one launch:
+ * dh1[M, 2 ff] = (dgate | dup) from the product dY[M, K] W[K, ff] (W stored (K, ff), ff contiguous: the (out, in) weight
+ * of Linear) and h1[M, 2 ff] = (gate | up); the product is rounded to bf16 and not stored.  The values
+ * nnb200_gemm_bf16 followed by nnb200_activation_backward(swiglu = 1) give, bit for bit.  All matrices bf16.  Needs
+ * M > 128, ff > 128 a multiple of 64, K a multiple of 8 (nnb200_linear_swiglu_backward_supported: 1 or 0); -1 otherwise.
+ * Replaces the input gradient of Linear::backward + SwiGLU::backward (compute_layer.hpp:176-195, 436-445). */
+int nnb200_linear_swiglu_backward_supported(int M, int ff, int K);
+int nnb200_linear_swiglu_backward(const void* dY, const void* W, const void* h1, void* dh1, int M, int ff, int K, void* stream);
 /* Input gradient of a projection with a row term, one launch: dX[M, N] = dY[M, K] W[K, N] (W stored (K, N), N
  * contiguous: the (out, in) weight of Linear) and dot[(m / S * H + h) * S + m % S] = sum over the 64 columns of block
  * h of dX (as stored, bf16) * other[m, .], H = N / 64.  With dY the gradient of the attention out-projection's output
@@ -119,6 +127,9 @@ int nnb200_gemm_f32(const float* A, const float* B, float* D, int M, int N, int 
  * are recorded: pairs of launches that overlap on other streams would add up to more than the time that passed. */
 int nnb200_gemm_profile(int enable);
 int nnb200_gemm_profile_read(double* host_total_ms, double* host_total_flops, int* host_launches);
+/* The launches whose epilogue also runs an activation (nnb200_linear_swiglu_forward / _backward) are kept apart from
+ * the figures above, because that epilogue outlasts a short main loop: their totals. */
+int nnb200_gemm_profile_read_fused(double* host_total_ms, double* host_total_flops, int* host_launches);
 /* CTA pairs (two SMs running one 256 x 256 tile with tcgen05.mma.cta_group::2) the device keeps resident at once;
  * 0 when the pair kernel is unavailable or switched off (environment NNB200_GEMM_PAIR=0). */
 int nnb200_gemm_pair_capacity(void);

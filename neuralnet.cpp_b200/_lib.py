@@ -57,6 +57,7 @@ SIGNATURES = {
     "nnb200_gemm_status": [C.POINTER(C.c_int)],
     "nnb200_gemm_profile": [_i],
     "nnb200_gemm_profile_read": [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)],
+    "nnb200_gemm_profile_read_fused": [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)],
     "nnb200_launch_count": [_i],
     "nnb200_attention_forward": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "nnb200_attention_backward": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
@@ -80,6 +81,8 @@ SIGNATURES = {
     "nnb200_activation_forward": [_p, _p, _i, _i, _i, _i, _p],
     "nnb200_linear_swiglu_supported": [_i, _i, _i],
     "nnb200_gemm_bf16_rowdot_supported": [_i, _i, _i, _i, _i],
+    "nnb200_linear_swiglu_backward_supported": [_i, _i, _i],
+    "nnb200_linear_swiglu_backward": [_p, _p, _p, _p, _i, _i, _i, _p],
     "nnb200_gemm_bf16_rowdot": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
     "nnb200_linear_swiglu_forward": [_p, _p, _p, _p, _p, _i, _i, _i, _p],
     "nnb200_activation_backward": [_p, _p, _p, _i, _i, _i, _i, _p],
@@ -142,7 +145,7 @@ _RET = {
 # functions whose int return value is a count, not a status
 _COUNT = {"nnb200_gpt_param_table"}
 # functions that return a plain value (negative values are answers, not errors)
-_VALUE = {"nnb200_gemm_pair_capacity", "nnb200_linear_swiglu_supported", "nnb200_gemm_bf16_rowdot_supported", "nnb200_expr_reduce_axis", "nnb200_rt_device", "nnb200_rt_stream"}
+_VALUE = {"nnb200_gemm_pair_capacity", "nnb200_linear_swiglu_supported", "nnb200_gemm_bf16_rowdot_supported", "nnb200_linear_swiglu_backward_supported", "nnb200_expr_reduce_axis", "nnb200_rt_device", "nnb200_rt_stream"}
 
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)

@@ -99,6 +99,12 @@ int nnb200_linear_swiglu_forward(const void* x, const void* W, const float* bias
                             static_cast<bf16*>(h2), M, ff, K, to_stream(stream));
 }
 
+int nnb200_linear_swiglu_backward_supported(int M, int ff, int K) { return gemm_swiglu_bwd_supported(M, ff, K) ? 1 : 0; }
+int nnb200_linear_swiglu_backward(const void* dY, const void* W, const void* h1, void* dh1, int M, int ff, int K, void* stream)
+{
+    return gemm_bf16_swiglu_bwd(static_cast<const bf16*>(dY), static_cast<const bf16*>(W), static_cast<const bf16*>(h1),
+                                static_cast<bf16*>(dh1), M, ff, K, to_stream(stream));
+}
 int nnb200_gemm_bf16_rowdot_supported(int M, int N, int K, int S, int H) { return gemm_rowdot_supported(M, N, K, S, H) ? 1 : 0; }
 int nnb200_gemm_bf16_rowdot(const void* dY, const void* W, void* dX, const void* other, float* dot, int M, int N, int K,
                             int S, int H, void* stream)
@@ -362,7 +368,12 @@ int nnb200_gemm_profile(int enable) { return gemm_profile_enable(enable); }
 int nnb200_gemm_profile_read(double* host_total_ms, double* host_total_flops, int* host_launches)
 {
     NNB_ARG_CHECK(host_total_ms && host_total_flops && host_launches, "null output");
-    return gemm_profile_read(host_total_ms, host_total_flops, host_launches);
+    return gemm_profile_read(0, host_total_ms, host_total_flops, host_launches);
+}
+int nnb200_gemm_profile_read_fused(double* host_total_ms, double* host_total_flops, int* host_launches)
+{
+    NNB_ARG_CHECK(host_total_ms && host_total_flops && host_launches, "null output");
+    return gemm_profile_read(1, host_total_ms, host_total_flops, host_launches);
 }
 
 int nnb200_f32_to_bf16(const float* in, void* out, size_t n, void* stream) { return f32_to_bf16(in, static_cast<bf16*>(out), n, to_stream(stream)); }

@@ -54,6 +54,19 @@ constexpr int kSmCount = 148;   // B200: 2 dies x 74 SMs; grids are sized in mul
 
 __host__ __device__ constexpr inline long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 
+#ifdef __CUDACC__
+// 1 / (1 + e^-x) for the bf16 paths: one exponential and one reciprocal instruction, both flushing denormals (the
+// non-flushing forms of __expf and __fdividef cost several range-fixing instructions each); 0 for x < -88, 1 for x > 88.
+// The activation kernels and the GEMM epilogues that replace them use this one function, so they agree bit for bit.
+__device__ __forceinline__ float sigmoid_fast(float x)
+{
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return r;
+}
+#endif
+
 // Per-device caches.  A process may drive several GPUs (one after the other or from several threads), and function
 // attributes, SM counts and occupancy figures belong to the device that is current when they are set or read.
 inline int current_device_slot()

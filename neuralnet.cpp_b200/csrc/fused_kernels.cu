@@ -19,7 +19,7 @@ __device__ __forceinline__ float sigmoidf_ref(float x) { return 1.0f / (1.0f + e
 // bf16 mode rounds every activation to 8 mantissa bits anyway: use the fast exp / reciprocal there
 template <typename T> __device__ __forceinline__ float sigmoid_t(float x)
 {
-    if constexpr (sizeof(T) == 2) return __fdividef(1.0f, 1.0f + __expf(-x));   // one reciprocal instruction; 0 for x < -87
+    if constexpr (sizeof(T) == 2) return sigmoid_fast(x);
     else return sigmoidf_ref(x);
 }
 template <typename T> __device__ __forceinline__ float exp_t(float x)

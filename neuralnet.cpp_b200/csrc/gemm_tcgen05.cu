@@ -388,7 +388,10 @@ struct GemmProfile {
     bool on = false;
     std::vector<cudaEvent_t> events;     // pairs: start, stop
     size_t used = 0;
-    double flops = 0.0;
+    // Two classes: 0 = the product with bias / residual / row-dot epilogues, 1 = launches whose epilogue also runs an
+    // activation (SwiGLU forward or backward), which outlasts a short main loop and would blur the GEMM's own figure.
+    std::vector<unsigned char> cls;      // per pair
+    double flops[2] = {0.0, 0.0};
     // Only the launches of one stream are recorded, that of the first GEMM after enabling: event pairs of launches that
     // overlap on other streams (the Newton-Schulz lanes of Muon) would add up to more than the time that passed.
     bool have_stream = false;
@@ -402,6 +405,7 @@ static bool prof_takes(cudaStream_t s)
     if (!g_prof.have_stream) { g_prof.have_stream = true; g_prof.stream = s; }
     return g_prof.stream == s;
 }
+static void prof_close(cudaStream_t s, int cls, double flops);
 static cudaEvent_t prof_event(cudaStream_t s)
 {
     if (g_prof.used == g_prof.events.size()) {
@@ -412,6 +416,14 @@ static cudaEvent_t prof_event(cudaStream_t s)
     cudaEvent_t e = g_prof.events[g_prof.used++];
     cudaEventRecord(e, s);
     return e;
+}
+
+static void prof_close(cudaStream_t s, int cls, double flops)
+{
+    prof_event(s);
+    g_prof.cls.resize(g_prof.used / 2);
+    g_prof.cls[g_prof.used / 2 - 1] = static_cast<unsigned char>(cls);
+    g_prof.flops[cls] += flops;
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -427,7 +439,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     const bool rec = prof_takes(s);
     if (rec) prof_event(s);
     gemm_bf16_kernel<BN, A_MN, B_MN, STAGES><<<grid, 192, SMEM, s>>>(ta, tb, tcm, p);
-    if (rec) { prof_event(s); g_prof.flops += 2.0 * p.M * p.N * p.K; }
+    if (rec) prof_close(s, 0, 2.0 * p.M * p.N * p.K);
     NNB_LAUNCH_CHECK();
     return 0;
 }
@@ -471,12 +483,12 @@ static int pair_capacity()
     return n > 0 ? n : 0;
 }
 
-template <bool A_MN, bool B_MN, bool RES = false, bool GLU = false, bool DB = false, bool DOT = false>
+template <bool A_MN, bool B_MN, bool RES = false, bool GLU = false, bool DB = false, bool DOT = false, bool GLUB = false>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tcm, const CUtensorMap& tr, const GemmParams& p, cudaStream_t s)
 {
-    constexpr int STAGES = (RES || GLU || DB || DOT) ? PAIR_STAGES_RES : PAIR_STAGES;
+    constexpr int STAGES = (RES || GLU || DB || DOT || GLUB) ? PAIR_STAGES_RES : PAIR_STAGES;
     static PerDeviceOnce once;
-    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU, DB, DOT>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
+    NNB_TRY(once.run([] { return cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU, DB, DOT, GLUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM); }));
     const int units = p.tiles_m * p.tiles_n * p.splits;
     const int pairs = units < pair_capacity() ? units : pair_capacity();
     cudaLaunchConfig_t cfg = {};
@@ -490,8 +502,8 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     cfg.attrs = at; cfg.numAttrs = 1;
     const bool rec = prof_takes(s);
     if (rec) prof_event(s);
-    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU, DB, DOT>, ta, tb, tcm, tr, p));
-    if (rec) { prof_event(s); g_prof.flops += (GLU ? 4.0 : 2.0) * p.M * p.N * p.K; }     // GLU: p.N is half the product's width
+    NNB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<A_MN, B_MN, STAGES, RES, GLU, DB, DOT, GLUB>, ta, tb, tcm, tr, p));
+    if (rec) prof_close(s, (GLU || GLUB) ? 1 : 0, (GLU ? 4.0 : 2.0) * p.M * p.N * p.K);     // GLU: p.N is half the product's width
     NNB_LAUNCH_CHECK();
     return 0;
 }
@@ -605,6 +617,35 @@ int gemm_bf16_swiglu(const bf16* X, const bf16* W, const float* bias, bf16* H1, 
     return launch_gemm_pair<false, false, false, true>(ta, tb, t1, t2, p, stream);
 }
 
+// Input gradient of a SwiGLU block's second projection taken through the activation in one launch:
+// dH1[M, 2 ff] = (dgate | dup) of (dY[M, K] W[K, ff]) at H1[M, 2 ff] = (gate | up); W stored (K, ff), ff contiguous.
+// Bit-identical to gemm_bf16 into a (M, ff) buffer followed by act_bwd.
+bool gemm_swiglu_bwd_supported(int M, int ff, int K)
+{
+    return M > 128 && ff > 128 && (ff % 64) == 0 && K > 0 && (K % 8) == 0 && pair_capacity() > 0;
+}
+int gemm_bf16_swiglu_bwd(const bf16* dY, const bf16* W, const bf16* H1, bf16* dH1, int M, int ff, int K, cudaStream_t stream)
+{
+    NNB_ARG_CHECK(gemm_swiglu_bwd_supported(M, ff, K), "shape not supported by the fused SwiGLU input gradient");
+    NNB_ARG_CHECK(((reinterpret_cast<uintptr_t>(dY) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(H1) |
+                    reinterpret_cast<uintptr_t>(dH1)) & 15) == 0, "operands must be 16-byte aligned");
+    GemmParams p{};
+    p.M = M; p.N = ff; p.K = K;
+    p.C = dH1; p.ldc = 2LL * ff; p.c_bf16 = 1; p.accumulate = 0;
+    p.alpha = 1.0f; p.vec_ok = 1; p.tma_store = 1; p.glu_ff = ff;
+    p.tiles_m = static_cast<int>(ceil_div(M, 256));
+    p.tiles_n = static_cast<int>(ceil_div(ff, 256));
+    p.kb_total = static_cast<int>(ceil_div(K, BK));
+    p.splits = 1;
+    p.kb_per_split = p.kb_total;
+    CUtensorMap ta, tb, tcm, tr;
+    NNB_TRY(tensor_map_2d(dY, K, M, K, BK, BM, &ta, 2));
+    NNB_TRY(tensor_map_2d(W, ff, K, ff, 64, BK, &tb, 2));
+    NNB_TRY(tensor_map_2d(dH1, 2LL * ff, M, 2LL * ff, 64, BM, &tcm, 2));
+    NNB_TRY(tensor_map_2d(H1, 2LL * ff, M, 2LL * ff, 64, BM, &tr, 2));
+    return launch_gemm_pair<false, true, false, false, false, false, true>(ta, tb, tcm, tr, p, stream);
+}
+
 // dX[M, N] = dY[M, K] W[K, N] (W stored (K, N), N contiguous) and, from the same epilogue, the sums over each 64-column
 // block of dX (as stored in bf16) times `other` (M, N): dot_out[(m / S * H + block) * S + m % S], H = N / 64 blocks.
 bool gemm_rowdot_supported(int M, int N, int K, int S, int H)
@@ -640,19 +681,23 @@ int gemm_pair_capacity() { return pair_capacity(); }
 int gemm_profile_enable(int enable)
 {
     g_prof.on = enable != 0;
-    if (g_prof.on) { g_prof.used = 0; g_prof.flops = 0.0; g_prof.have_stream = false; }
+    if (g_prof.on) { g_prof.used = 0; g_prof.flops[0] = g_prof.flops[1] = 0.0; g_prof.have_stream = false; }
     return 0;
 }
-int gemm_profile_read(double* total_ms, double* total_flops, int* launches)
+int gemm_profile_read(int cls, double* total_ms, double* total_flops, int* launches)
 {
+    NNB_ARG_CHECK(cls == 0 || cls == 1, "class must be 0 or 1");
     double ms = 0.0;
+    int n = 0;
     for (size_t i = 0; i + 1 < g_prof.used; i += 2) {
+        if (g_prof.cls[i / 2] != cls) continue;
         NNB_CUDA_CHECK(cudaEventSynchronize(g_prof.events[i + 1]));
         float t = 0.f;
         NNB_CUDA_CHECK(cudaEventElapsedTime(&t, g_prof.events[i], g_prof.events[i + 1]));
         ms += t;
+        ++n;
     }
-    *total_ms = ms; *total_flops = g_prof.flops; *launches = static_cast<int>(g_prof.used / 2);
+    *total_ms = ms; *total_flops = g_prof.flops[cls]; *launches = n;
     return 0;
 }
 

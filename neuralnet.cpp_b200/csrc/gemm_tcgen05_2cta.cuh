@@ -31,6 +31,13 @@
 // out-projection as the product and the attention output as the other matrix this is the row term
 // D = rowsum(dO * O) of the attention backward pass (64 columns = one head), which then needs no pass of its own.
 //
+// GLUB: the product is the gradient of a SwiGLU block's activation (the input gradient of its second projection) and
+// is not stored: for every 64-column block the group TMA-loads the gate and up tiles of the first projection's output
+// (the map in the residual slot, up columns glu_ff further right) into its two tiles, turns them in place into the
+// gradients of gate and up (compute_layer.hpp:436-445; each thread rewrites the chunks of its own row) from the
+// product as rounded to bf16, and stores both through the output map, bit for bit what the activation's backward
+// kernel gives on the stored product.
+//
 // DB: each epilogue group has two staging tiles and uses them in turn, so a block's conversion does not wait for the
 // previous block's store to have read its tile; the 32 KB come out of the operand ring as in the RES form.
 //
@@ -47,7 +54,7 @@ namespace nnb {
 constexpr int PAIR_BN_HALF = 128;                                // rows of B each CTA stages per k-block
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_BN_HALF * BK * 2;
 
-template <bool A_MN, bool B_MN, int STAGES, bool RES, bool GLU = false, bool DB = false, bool DOT = false>
+template <bool A_MN, bool B_MN, int STAGES, bool RES, bool GLU = false, bool DB = false, bool DOT = false, bool GLUB = false>
 __global__ void __launch_bounds__(320, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR, const GemmParams p)
@@ -67,7 +74,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     uint8_t* sC = sB + STAGES * B_STAGE_BYTES;
     uint8_t* sR = sC + 2 * C_STAGE_BYTES;                                 // RES: one residual tile per epilogue group
     constexpr bool RT = RES || DOT;                                       // a second tile comes in through the residual slot
-    float* sBias = reinterpret_cast<float*>(sR + ((RT || GLU || DB) ? 2 * C_STAGE_BYTES : 0));
+    float* sBias = reinterpret_cast<float*>(sR + ((RT || GLU || DB || GLUB) ? 2 * C_STAGE_BYTES : 0));
     uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + BN);             // each epilogue group keeps the bias of its own 128 columns
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
     const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16, drain_bar = tempty0 + 16, res_full0 = drain_bar + 8;
@@ -199,6 +206,34 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             }
         };
         if (RT && elected) request_next_residual();
+        // GLUB: blocks in the order all eight warps take them; the elected thread keeps the loads one block ahead
+        const bool glub_elected = GLUB && threadIdx.x == 64;
+        int glub_blocks = 0, glub_requested = 0;
+        struct BlockCursor { int u, cb; } g_req{pair, -1};
+        // next block of this CTA in consumption order; false at the end of the list
+        auto glub_next = [&](BlockCursor& c, int& n0, int& m0) -> bool {
+            for (;;) {
+                if (++c.cb * 64 >= BN) { c.u += pairs; c.cb = 0; }
+                if (c.u >= units) return false;
+                const int t = c.u % tiles;
+                const int tile_n = t / p.tiles_m, tile_m = t - tile_n * p.tiles_m;
+                n0 = tile_n * BN + c.cb * 64; m0 = tile_m * 256 + static_cast<int>(rank) * 128;
+                if (n0 < p.N && m0 < p.M) return true;
+            }
+        };
+        bool glub_lost = false;
+        // loads of the next block into the set it will be turned in (an L2 prefetch of the tiles two blocks further on
+        // was measured slower: 93.8 against 86.5 us at 16384 x 2048 x 768)
+        auto glub_request = [&]() {
+            int n0, m0;
+            if (!glub_next(g_req, n0, m0)) return;
+            const int set = glub_requested & 1;
+            ++glub_requested;
+            mbar_expect_tx(res_full0 + 8 * set, 2 * C_STAGE_BYTES);
+            tma_load_2d(smem_u32(sC + set * C_STAGE_BYTES), &tmR, res_full0 + 8 * set, n0, m0);
+            tma_load_2d(smem_u32(sR + set * C_STAGE_BYTES), &tmR, res_full0 + 8 * set, p.glu_ff + n0, m0);
+        };
+        if (glub_elected) glub_request();
         int tc = 0, blk = 0;
         for (int u = pair; u < units; u += pairs, ++tc) {
             const int split = u / tiles, t = u - split * tiles;
@@ -274,8 +309,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         round_bias(rb, bias_s + 64 + half * 32, upk + half * 16, u);
 #pragma unroll
                         for (int j = 0; j < 32; j += 2)
-                            pk[j >> 1] = pack_bf16x2(g[j] * __fdividef(1.0f, 1.0f + __expf(-g[j])) * u[j],
-                                                     g[j + 1] * __fdividef(1.0f, 1.0f + __expf(-g[j + 1])) * u[j + 1]);
+                            pk[j >> 1] = pack_bf16x2(g[j] * sigmoid_fast(g[j]) * u[j], g[j + 1] * sigmoid_fast(g[j + 1]) * u[j + 1]);
                         put(yrow, pk, half);
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -296,6 +330,58 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         tma_store_2d(&tmC, smem_u32(stage), p.glu_ff + n0, m0);
                         tma_commit();
                     }
+                }
+            } else if (GLUB) {
+                // All eight warps work on one 64-column block at a time, the two warps of a TMEM lane quadrant on 32
+                // columns each, so that two sets of (gate, up) tiles can be used in turn: while a block is turned in
+                // place in one set, the loads of the next block arrive in the other.
+                if (m0 < p.M) {
+                    const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + grp * 32;
+                    uint32_t ra[32];
+#pragma unroll 1
+                    for (int cb = 0; cb * 64 < BN; ++cb) {
+                        const int n0 = tile_n * BN + cb * 64;
+                        if (n0 >= p.N) break;
+                        const int set = glub_blocks & 1;
+                        uint8_t* gtile = sC + set * C_STAGE_BYTES;
+                        uint8_t* utile = sR + set * C_STAGE_BYTES;
+                        if (glub_elected) {
+                            tma_wait_read0();                        // the other set's stores (the block before this one) have read it
+                            glub_request();
+                        }
+                        tmem_ld32(tbase + cb * 64, ra);
+                        tmem_ld_wait();
+                        const bool got = mbar_wait(res_full0 + 8 * set, (glub_blocks >> 1) & 1, abort_flag, 11, &g_gemm_error);
+                        ++glub_blocks;
+                        if (all_epilogue_any(!got)) { glub_lost = true; break; }
+                        uint8_t* grow = gtile + r_local * 128;
+                        uint8_t* urow = utile + r_local * 128;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            const int chunk = ((grp * 4 + (j >> 3)) ^ (r_local & 7)) << 4;
+                            const Vec16<bf16> gv = *reinterpret_cast<const Vec16<bf16>*>(grow + chunk);
+                            const Vec16<bf16> uv = *reinterpret_cast<const Vec16<bf16>*>(urow + chunk);
+                            Vec16<bf16> og, ou;
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) {
+                                const float go = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ra[j + k])));
+                                const float gt = __bfloat162float(gv.v[k]), up = __bfloat162float(uv.v[k]);
+                                const float sg = sigmoid_fast(gt);
+                                og.v[k] = __float2bfloat16_rn(go * up * (sg * (1.0f + gt * (1.0f - sg))));
+                                ou.v[k] = __float2bfloat16_rn(go * gt * sg);
+                            }
+                            *reinterpret_cast<uint4*>(grow + chunk) = *reinterpret_cast<const uint4*>(&og);
+                            *reinterpret_cast<uint4*>(urow + chunk) = *reinterpret_cast<const uint4*>(&ou);
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        all_epilogue_bar();
+                        if (glub_elected) {
+                            tma_store_2d(&tmC, smem_u32(gtile), n0, m0);
+                            tma_store_2d(&tmC, smem_u32(utile), p.glu_ff + n0, m0);
+                            tma_commit();
+                        }
+                    }
+                    if (glub_lost) break;
                 }
             } else if (m0 < p.M) {
             // In the bf16 case (two 32-column halves per block) the second half is fetched from TMEM while the first

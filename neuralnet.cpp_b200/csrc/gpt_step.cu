@@ -301,8 +301,20 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         const LayerActs& a = W.layers[l];
         // FeedForward::backward (compute_layer.hpp:1674-1688)
         NNB_TRY(linear_bwd_params<T>(g, A(a.h2), G + lp.w2, nullptr, cs, cn, N, ff, d, s));
-        NNB_TRY(linear_bwd_input<T>(g, P + lp.w2, Hh(lp.w2), A(W.d_h2), N, ff, d, s));
-        NNB_TRY(act_bwd<T>(A(W.d_h2), A(a.h1), A(W.d_h1), N, ff, swiglu, s, G + lp.b1, cs, cn, cs_begin()));   // also sums fc1's bias gradient
+        bool fused_act = false;
+        if constexpr (Mode<T>::bf) {
+            if (swiglu && gemm_swiglu_bwd_supported(N, ff, d)) {
+                // the activation's backward pass in the epilogue of fc2's input-gradient GEMM; fc1's bias gradient after it
+                NNB_TRY(gemm_bf16_swiglu_bwd(reinterpret_cast<const bf16*>(g), Hh(lp.w2), reinterpret_cast<const bf16*>(A(a.h1)),
+                                             reinterpret_cast<bf16*>(A(W.d_h1)), N, ff, d, s));
+                NNB_TRY(colsum_accumulate<T>(A(W.d_h1), fc1, nullptr, nullptr, nullptr, nullptr, 0, G + lp.b1, cs, N, fc1, s, cn, cs_begin()));
+                fused_act = true;
+            }
+        }
+        if (!fused_act) {
+            NNB_TRY(linear_bwd_input<T>(g, P + lp.w2, Hh(lp.w2), A(W.d_h2), N, ff, d, s));
+            NNB_TRY(act_bwd<T>(A(W.d_h2), A(a.h1), A(W.d_h1), N, ff, swiglu, s, G + lp.b1, cs, cn, cs_begin()));   // also sums fc1's bias gradient
+        }
         cs_done(lp.b1, fc1);
         NNB_TRY(linear_bwd_params<T>(A(W.d_h1), A(a.xn2), G + lp.w1, nullptr, cs, cn, N, d, fc1, s));
         NNB_TRY(linear_bwd_input<T>(A(W.d_h1), P + lp.w1, Hh(lp.w1), A(W.d_xn), N, d, fc1, s));

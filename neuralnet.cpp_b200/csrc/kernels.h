@@ -27,6 +27,10 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
 // gate, then up), H2[M, ff] = gate * sigmoid(gate) * up, bit-identical to gemm_bf16 followed by act_fwd
 bool gemm_swiglu_supported(int M, int ff, int K);
 int gemm_bf16_swiglu(const bf16* X, const bf16* W, const float* bias, bf16* H1, bf16* H2, int M, int ff, int K, cudaStream_t stream);
+// input gradient of a SwiGLU block's second projection taken through the activation: dH1 = SwiGLU'(H1) * (dY W), the
+// product itself not stored; bit-identical to gemm_bf16 followed by act_bwd
+bool gemm_swiglu_bwd_supported(int M, int ff, int K);
+int gemm_bf16_swiglu_bwd(const bf16* dY, const bf16* W, const bf16* H1, bf16* dH1, int M, int ff, int K, cudaStream_t stream);
 // input gradient of a projection, dX = dY W, and the sums over each 64-column block of dX * other in the same launch
 // (the row term of the attention backward pass when dX is the gradient of the attention output and other that output)
 bool gemm_rowdot_supported(int M, int N, int K, int S, int H);
@@ -38,7 +42,7 @@ int gemm_pair_capacity();
 int work_counter_pair(cudaStream_t s, unsigned int** out);
 int gemm_clear_device_error();
 int gemm_profile_enable(int enable);
-int gemm_profile_read(double* total_ms, double* total_flops, int* launches);
+int gemm_profile_read(int cls, double* total_ms, double* total_flops, int* launches);   // 0: products, 1: products with an activation in the epilogue
 
 // ---- fused_kernels.cu
 template <typename T> int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rinv, float* mean,

@@ -141,15 +141,27 @@ def run_linear_swiglu(M, ff, K, args):
     def two():
         call("nnb200_gemm_bf16", P(x), P(w), P(h1), M, 2 * ff, K, K, K, 2 * ff, 0, 0, 1, C.c_float(1.0), P(b), None, 0, S())
         call("nnb200_activation_forward", P(h1), P(h2), M, ff, 1, 1, S())
+    # backward: input gradient of the second projection taken through the activation (dY: (M, K), W2: (K, ff))
+    w2 = (torch.randn(K, ff, device="cuda", generator=g) * 0.05).bfloat16()
+    dh2 = torch.empty(M, ff, device="cuda", dtype=torch.bfloat16)
+    dh1 = torch.empty(M, 2 * ff, device="cuda", dtype=torch.bfloat16)
+    fused_b = lambda: call("nnb200_linear_swiglu_backward", P(x), P(w2), P(h1), P(dh1), M, ff, K, S())
+
+    def two_b():
+        call("nnb200_gemm_bf16", P(x), P(w2), P(dh2), M, ff, K, K, ff, ff, 0, 1, 1, C.c_float(1.0), None, None, 0, S())
+        call("nnb200_activation_backward", P(dh2), P(h1), P(dh1), M, ff, 1, 1, S())
+    fused()
     if args.no_time:
         for _ in range(args.iters):
             fused()
+            fused_b()
         torch.cuda.synchronize()
         return
     hbm, tf, src = peaks()
-    for name, fn in (("linear_swiglu.fused", fused), ("linear_swiglu.two_kernels", two)):
+    for name, fn, fl in (("linear_swiglu.fused", fused, 4.0), ("linear_swiglu.two_kernels", two, 4.0),
+                         ("linear_swiglu_backward.fused", fused_b, 2.0), ("linear_swiglu_backward.two_kernels", two_b, 2.0)):
         ms = timed(fn, args.iters, args.flush_l2)
-        ach = 4.0 * M * ff * K / ms / 1e9
+        ach = fl * M * ff * K / ms / 1e9
         emit(kernel=name, M=M, ff=ff, K=K, us=ms * 1e3, bound="tensor", achieved=ach, peak=tf, unit="TFLOP/s", frac=ach / tf,
              peak_source=src)
 

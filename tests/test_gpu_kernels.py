@@ -141,6 +141,31 @@ def test_gemm_bf16_rowdot_equals_gemm_and_row_sums(g, B, S, H, K):
     assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("M,ff,K", [(300, 192, 64), (1000, 384, 200), (2048, 2048, 768), (20000, 256, 128), (4096, 2816, 1024)])
+def test_linear_swiglu_backward_equals_two_kernels(g, M, ff, K):
+    """The input-gradient GEMM with the SwiGLU backward epilogue against the plain GEMM followed by the activation's
+    backward kernel: bit for bit (ragged rows, a ragged last column tile, many tiles per CTA pair)."""
+    import torch
+    r = _rng(M + ff)
+    dY = g.bf16_round(r.standard_normal((M, K)))
+    W = g.bf16_round(r.standard_normal((K, ff)) * 0.1)
+    H1 = g.bf16_round(r.standard_normal((M, 2 * ff)) * 2.0)
+    dy, w, h1 = g.dev(dY, torch.bfloat16), g.dev(W, torch.bfloat16), g.dev(H1, torch.bfloat16)
+    assert g.call("nnb200_linear_swiglu_backward_supported", M, ff, K) == 1
+    dh1 = torch.full((M, 2 * ff), 7.0, dtype=torch.bfloat16, device="cuda")
+    g.call("nnb200_linear_swiglu_backward", g.ptr(dy), g.ptr(w), g.ptr(h1), g.ptr(dh1), M, ff, K, g.stream())
+    dh2 = torch.zeros((M, ff), dtype=torch.bfloat16, device="cuda")
+    ref = torch.zeros_like(dh1)
+    g.call("nnb200_gemm_bf16", g.ptr(dy), g.ptr(w), g.ptr(dh2), M, ff, K, K, ff, ff, 0, 1, 1, C.c_float(1.0), None, None, 0, g.stream())
+    g.call("nnb200_activation_backward", g.ptr(dh2), g.ptr(h1), g.ptr(ref), M, ff, 1, 1, g.stream())
+    torch.cuda.synchronize()
+    assert g.gemm_status() == 0
+    assert torch.equal(dh1, ref)
+    # and the plain product against float64, so that the comparison above is not between two wrong results
+    want = dY.astype(np.float64) @ W.astype(np.float64)
+    assert np.abs(g.host(dh2) - want).max() < 2e-2 * np.sqrt(K)
+
+
 def test_linear_swiglu_forward_rejects_unsupported_shapes(g):
     import torch
     assert g.call("nnb200_linear_swiglu_supported", 128, 256, 64) == 0      # a single 128-row block
