@@ -221,7 +221,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 if (n0 < p.N && m0 < p.M) return true;
             }
         };
-        bool glub_lost = false;
         // loads of the next block into the set it will be turned in (an L2 prefetch of the tiles two blocks further on
         // was measured slower: 93.8 against 86.5 us at 16384 x 2048 x 768)
         auto glub_request = [&]() {
@@ -353,7 +352,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         tmem_ld_wait();
                         const bool got = mbar_wait(res_full0 + 8 * set, (glub_blocks >> 1) & 1, abort_flag, 11, &g_gemm_error);
                         ++glub_blocks;
-                        if (all_epilogue_any(!got)) { glub_lost = true; break; }
+                        // a wait that gave up has raised the abort flag: this thread goes on (on stale tiles, inside its own
+                        // rows) so that nobody is left alone at the barrier below, and all leave together at the next tile
+                        (void)got;
                         uint8_t* grow = gtile + r_local * 128;
                         uint8_t* urow = utile + r_local * 128;
 #pragma unroll
@@ -381,7 +382,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                             tma_commit();
                         }
                     }
-                    if (glub_lost) break;
                 }
             } else if (m0 < p.M) {
             // In the bf16 case (two 32-column halves per block) the second half is fetched from TMEM while the first

@@ -139,19 +139,8 @@ __device__ __forceinline__ bool group_any(int id, bool pred)
         : "=r"(r) : "r"(id), "r"(static_cast<uint32_t>(pred)) : "memory");
     return r != 0;
 }
-// the same two over all eight epilogue warps of a pair-GEMM CTA (barrier 3)
+// barrier over all eight epilogue warps of a pair-GEMM CTA (barrier 3)
 __device__ __forceinline__ void all_epilogue_bar() { asm volatile("bar.sync 3, 256;" ::: "memory"); }
-__device__ __forceinline__ bool all_epilogue_any(bool pred)
-{
-    uint32_t r;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.b32 q, %1, 0;\n\t"
-        "bar.red.or.pred p, 3, 256, q;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(r) : "r"(static_cast<uint32_t>(pred)) : "memory");
-    return r != 0;
-}
 __device__ __forceinline__ void tma_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
 // ---- CTA-pair (cta_group::2) forms: one thread of the leader CTA issues an MMA that spans both CTAs'
