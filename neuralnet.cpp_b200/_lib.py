@@ -82,7 +82,7 @@ SIGNATURES = {
     "nnb200_linear_swiglu_supported": [_i, _i, _i],
     "nnb200_gemm_bf16_rowdot_supported": [_i, _i, _i, _i, _i],
     "nnb200_linear_swiglu_backward_supported": [_i, _i, _i],
-    "nnb200_linear_swiglu_backward": [_p, _p, _p, _p, _i, _i, _i, _p],
+    "nnb200_linear_swiglu_backward": [_p, _p, _p, _p, _i, _i, _i, _p, _p],
     "nnb200_gemm_bf16_rowdot": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
     "nnb200_linear_swiglu_forward": [_p, _p, _p, _p, _p, _i, _i, _i, _p],
     "nnb200_activation_backward": [_p, _p, _p, _i, _i, _i, _i, _p],

@@ -100,10 +100,11 @@ int nnb200_linear_swiglu_forward(const void* x, const void* W, const float* bias
 }
 
 int nnb200_linear_swiglu_backward_supported(int M, int ff, int K) { return gemm_swiglu_bwd_supported(M, ff, K) ? 1 : 0; }
-int nnb200_linear_swiglu_backward(const void* dY, const void* W, const void* h1, void* dh1, int M, int ff, int K, void* stream)
+int nnb200_linear_swiglu_backward(const void* dY, const void* W, const void* h1, void* dh1, int M, int ff, int K,
+                                  float* colsum_partial, void* stream)
 {
     return gemm_bf16_swiglu_bwd(static_cast<const bf16*>(dY), static_cast<const bf16*>(W), static_cast<const bf16*>(h1),
-                                static_cast<bf16*>(dh1), M, ff, K, to_stream(stream));
+                                static_cast<bf16*>(dh1), M, ff, K, colsum_partial, to_stream(stream));
 }
 int nnb200_gemm_bf16_rowdot_supported(int M, int N, int K, int S, int H) { return gemm_rowdot_supported(M, N, K, S, H) ? 1 : 0; }
 int nnb200_gemm_bf16_rowdot(const void* dY, const void* W, void* dX, const void* other, float* dot, int M, int N, int K,

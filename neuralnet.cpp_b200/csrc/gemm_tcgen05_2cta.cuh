@@ -370,11 +370,41 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                                 const float sg = sigmoid_fast(gt);
                                 og.v[k] = __float2bfloat16_rn(go * up * (sg * (1.0f + gt * (1.0f - sg))));
                                 ou.v[k] = __float2bfloat16_rn(go * gt * sg);
+                                // the accumulator registers are free once read: keep the stored values for the column sums
+                                ra[j + k] = (static_cast<uint32_t>(__bfloat16_as_ushort(og.v[k])) << 16) | __bfloat16_as_ushort(ou.v[k]);
                             }
                             *reinterpret_cast<uint4*>(grow + chunk) = *reinterpret_cast<const uint4*>(&og);
                             *reinterpret_cast<uint4*>(urow + chunk) = *reinterpret_cast<const uint4*>(&ou);
                         }
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        if (p.colsum_part) {
+                            // Column sums of both gradient blocks over this warp's 32 rows (the bias gradient of the first
+                            // projection): a butterfly in which every lane sends half of what it holds and keeps the other
+                            // half, 31 exchanges for 32 columns, after which lane l holds column l.  Fixed order: the sums
+                            // are reproducible.  One partial row per 32 matrix rows; a later kernel folds them.
+                            float sg_[32], su_[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                sg_[j] = row_ok ? __uint_as_float(ra[j] & 0xffff0000u) : 0.f;
+                                su_[j] = row_ok ? __uint_as_float(ra[j] << 16) : 0.f;
+                            }
+#pragma unroll
+                            for (int st = 16; st >= 1; st >>= 1) {
+                                const bool upper = (lane & st) != 0;
+#pragma unroll
+                                for (int i = 0; i < st; ++i) {
+                                    const float send_g = upper ? sg_[i] : sg_[i + st], keep_g = upper ? sg_[i + st] : sg_[i];
+                                    const float send_u = upper ? su_[i] : su_[i + st], keep_u = upper ? su_[i + st] : su_[i];
+                                    sg_[i] = keep_g + __shfl_xor_sync(0xffffffffu, send_g, st);
+                                    su_[i] = keep_u + __shfl_xor_sync(0xffffffffu, send_u, st);
+                                }
+                            }
+                            if (m0 + q * 32 < p.M) {
+                                float* dst = p.colsum_part + static_cast<size_t>((m0 >> 5) + q) * (2 * p.glu_ff) + n0 + grp * 32 + lane;
+                                dst[0] = sg_[0];
+                                dst[p.glu_ff] = su_[0];
+                            }
+                        }
                         all_epilogue_bar();
                         if (glub_elected) {
                             tma_store_2d(&tmC, smem_u32(gtile), n0, m0);

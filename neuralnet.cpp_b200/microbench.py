@@ -145,11 +145,16 @@ def run_linear_swiglu(M, ff, K, args):
     w2 = (torch.randn(K, ff, device="cuda", generator=g) * 0.05).bfloat16()
     dh2 = torch.empty(M, ff, device="cuda", dtype=torch.bfloat16)
     dh1 = torch.empty(M, 2 * ff, device="cuda", dtype=torch.bfloat16)
-    fused_b = lambda: call("nnb200_linear_swiglu_backward", P(x), P(w2), P(h1), P(dh1), M, ff, K, S())
+    part = torch.empty((M + 31) // 32, 2 * ff, device="cuda")    # column sums per 32 rows, as the training step asks for them
+    fused_b = lambda: call("nnb200_linear_swiglu_backward", P(x), P(w2), P(h1), P(dh1), M, ff, K, P(part), S())
 
-    def two_b():
+    bsum = torch.zeros(2 * ff, device="cuda")
+    bscratch = torch.empty(int(nnb.lib.nnb200_colsum_scratch_floats(M, 2 * ff)), device="cuda")
+
+    def two_b():                                                   # GEMM, activation backward, bias-gradient column sums
         call("nnb200_gemm_bf16", P(x), P(w2), P(dh2), M, ff, K, K, ff, ff, 0, 1, 1, C.c_float(1.0), None, None, 0, S())
         call("nnb200_activation_backward", P(dh2), P(h1), P(dh1), M, ff, 1, 1, S())
+        call("nnb200_bias_grad", P(dh1), 2 * ff, P(bsum), P(bscratch), M, 2 * ff, 1, S())
     fused()
     if args.no_time:
         for _ in range(args.iters):
