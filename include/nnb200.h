@@ -162,6 +162,14 @@ int nnb200_attention_forward(const void* qkv, void* out, float* lse, const int32
 int nnb200_attention_backward(const void* qkv, const void* out, const void* dout, const float* lse, float* dvec,
                               void* dqkv, const int32_t* doc_ids, const int32_t* doc_ranges, int batch, int seq, int heads,
                               int head_dim, int alibi, int dtype, void* stream);
+/* The same on the tcgen05 kernels only (bf16, head size 64 or 128, seq a multiple of 128; -1 otherwise), which also
+ * leave the column sums of dqkv over each 32 token rows in colsum_partial ((batch*seq/32) x 3*d floats, every one
+ * written): summed over the rows they are the bias gradient of the QKV projection (Linear::backward's column sum,
+ * compute_layer.hpp:188-193), which then needs no pass over dqkv.  dqkv is bit-identical to nnb200_attention_backward's. */
+int nnb200_attention_backward_bias_partials(const void* qkv, const void* out, const void* dout, const float* lse, float* dvec,
+                                            void* dqkv, const int32_t* doc_ids, const int32_t* doc_ranges,
+                                            float* colsum_partial, int batch, int seq, int heads, int head_dim, int alibi,
+                                            void* stream);
 /* ranges[2*(b*seq/64 + k)], [.. + 1] = smallest and largest document id among rows [64k, 64k+64) of
  * sequence b; seq must be a multiple of 64; ranges holds 2*batch*seq/64 ints.  The device-side
  * counterpart of the per-step mask rebuild of CausalSelfAttention (compute_layer.hpp:2226-2246). */

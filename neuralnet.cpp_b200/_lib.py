@@ -61,6 +61,7 @@ SIGNATURES = {
     "nnb200_launch_count": [_i],
     "nnb200_attention_forward": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "nnb200_attention_backward": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "nnb200_attention_backward_bias_partials": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
     "nnb200_attention_doc_ranges": [_p, _i, _i, _p, _p],
     "nnb200_muon_step_many": [_i, _p, _p, _p, _p, _p, _p, _f, _f, _i, _f, _i, _p, _sz, _i, _p, _p],
     "nnb200_gpt_decode_workspace_bytes": [_cfgp],

@@ -168,6 +168,17 @@ int nnb200_attention_backward(const void* qkv, const void* out, const void* dout
     return attention_bwd_simt<float>(static_cast<const float*>(qkv), static_cast<const float*>(out), static_cast<const float*>(dout), lse, dvec, static_cast<float*>(dqkv), doc_ids, batch, seq, heads, head_dim, alibi, s);
 }
 
+int nnb200_attention_backward_bias_partials(const void* qkv, const void* out, const void* dout, const float* lse, float* dvec,
+                                            void* dqkv, const int32_t* doc_ids, const int32_t* doc_ranges,
+                                            float* colsum_partial, int batch, int seq, int heads, int head_dim, int alibi,
+                                            void* stream)
+{
+    NNB_ARG_CHECK(colsum_partial != nullptr, "null output");
+    return attention_bwd_tc(static_cast<const bf16*>(qkv), static_cast<const bf16*>(out), static_cast<const bf16*>(dout), lse, dvec,
+                            static_cast<bf16*>(dqkv), doc_ids, doc_ranges, batch, seq, heads, head_dim, alibi, to_stream(stream),
+                            false, colsum_partial);
+}
+
 int nnb200_ids_from_float(const float* ids_seq_major, int32_t* out_batch_major, int seq, int batch, void* stream)
 {
     NNB_ARG_CHECK(seq >= 0 && batch >= 0 && (static_cast<long long>(seq) * batch == 0 || (ids_seq_major && out_batch_major)), "bad arguments");

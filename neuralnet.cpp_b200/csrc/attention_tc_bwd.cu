@@ -35,6 +35,7 @@ constexpr float kL2e = 1.4426950408889634f;
 
 struct AttnBwdArgs {
     bf16* dqkv; const float* lse; const float* dvec; const int* doc; const int2* ranges;
+    float* colsum_part;      // null, or [rows / 32][3 d]: column sums of dqkv over each 32 token rows (the QKV bias gradient's partials)
     int B, S, H;
     float scale;
 };
@@ -386,8 +387,18 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_c
                     for (int c = 0; c < 32; c += 8) {
                         Vec16<bf16> o;
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(__uint_as_float(r[c + k]) * a.scale);
+                        for (int k = 0; k < 8; ++k) {
+                            o.v[k] = __float2bfloat16_rn(__uint_as_float(r[c + k]) * a.scale);
+                            r[c + k] = __float_as_uint(__bfloat162float(o.v[k]));        // what is stored, for the column sums
+                        }
                         st16(op + c0 + c, o);
+                    }
+                    if (a.colsum_part) {                                // this warp's 32 rows of 32 columns
+                        float v[32];
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(r[c]);
+                        const float sum = lane_sums32(v, lane);
+                        a.colsum_part[(static_cast<size_t>(row_base + q0) / 32 + q) * (3 * d) + h * DK + hf * OC + c0 + lane] = sum;
                     }
                 }
                 tc_fence_before();
@@ -720,9 +731,21 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKV128, const __grid
                         for (int k = 0; k < 8; ++k) {
                             ok8.v[k] = __float2bfloat16_rn(__uint_as_float(rk[c + k]) * a.scale);
                             ov8.v[k] = __float2bfloat16_rn(__uint_as_float(rv[c + k]));
+                            rk[c + k] = __float_as_uint(__bfloat162float(ok8.v[k]));     // what is stored, for the column sums
+                            rv[c + k] = __float_as_uint(__bfloat162float(ov8.v[k]));
                         }
                         st16(kp + c0 + c, ok8);
                         st16(kp + d + c0 + c, ov8);
+                    }
+                    if (a.colsum_part) {
+                        float v[32];
+                        float* dst = a.colsum_part + (static_cast<size_t>(row_base + k0) / 32 + q) * (3 * d) + d + h * DK + hf * OC + c0 + lane;
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(rk[c]);
+                        dst[0] = lane_sums32(v, lane);
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(rv[c]);
+                        dst[d] = lane_sums32(v, lane);
                     }
                 }
                 tc_fence_before();
@@ -765,7 +788,8 @@ static int launch_bwd_tc(const CUtensorMap& q128, const CUtensorMap& q64, const 
 }
 
 int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const float* lse, float* dvec, bf16* dqkv,
-                     const int* doc, const int* doc_ranges, int B, int S, int H, int dk, int alibi, cudaStream_t s, bool have_dvec)
+                     const int* doc, const int* doc_ranges, int B, int S, int H, int dk, int alibi, cudaStream_t s, bool have_dvec,
+                     float* colsum_part)
 {
     if (static_cast<long long>(B) * S * H == 0) return 0;
     NNB_ARG_CHECK(attention_tc_supported(dk, S, H * dk), "shape not supported by the tcgen05 attention kernels");
@@ -777,7 +801,7 @@ int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const f
     NNB_TRY(tensor_map_2d(qkv, 3LL * d, rows, 3LL * d, 64, 64, &q64, 2));
     NNB_TRY(tensor_map_2d(dout, d, rows, d, 64, 128, &do128, 2));
     NNB_TRY(tensor_map_2d(dout, d, rows, d, 64, 64, &do64, 2));
-    AttnBwdArgs a{dqkv, lse, dvec, doc, doc ? reinterpret_cast<const int2*>(doc_ranges) : nullptr, B, S, H, 1.0f / sqrtf(static_cast<float>(dk))};
+    AttnBwdArgs a{dqkv, lse, dvec, doc, doc ? reinterpret_cast<const int2*>(doc_ranges) : nullptr, colsum_part, B, S, H, 1.0f / sqrtf(static_cast<float>(dk))};
     const long long tiles = static_cast<long long>(S / 128) * H * B;
     NNB_ARG_CHECK(tiles < (1ll << 31), "too many attention tiles");
 #define NNB_BWD(DKV)                                                                                      \

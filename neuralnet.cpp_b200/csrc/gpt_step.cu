@@ -73,9 +73,10 @@ DecodeLayout decode_layout(const nnb200_gpt_config& c)
 
 // ---------------------------------------------------------------- workspace
 struct LayerActs { size_t x_in, xn1, qkv, attn, x_mid, xn2, h1, h2; size_t rinv1, mean1, rinv2, mean2, lse; };
-// floats of the deferred column-sum slot of fc1's bias gradient: one partial row per 32 token rows (what the
-// SwiGLU-backward epilogue of the GEMM leaves), which also holds the coarser partials of the column-sum kernel
-static size_t fc1_slot_floats(long long rows, long long cols) { return static_cast<size_t>(ceil_div(rows, 32) * cols); }
+// floats of the deferred column-sum slots of the fc1 and QKV bias gradients: one partial row per 32 token rows (what the
+// SwiGLU-backward epilogue of the GEMM and the write-outs of the attention backward kernels leave), which also holds
+// the coarser partials of the column-sum kernel
+static size_t wide_slot_floats(long long rows, long long cols) { return static_cast<size_t>(ceil_div(rows, 32) * cols); }
 
 struct Workspace {
     size_t sin_table, stats, loss, loss_vec;
@@ -117,8 +118,8 @@ static Workspace make_workspace(const nnb200_gpt_config& c)
     // and one per bias gradient that has a column-sum pass of its own: the LM head, and fc1 and qkv of every layer
     W.colsum_partials = take(2 * static_cast<size_t>(c.layers) + 1 <= kColsumFoldMaxSlots
                                  ? (colsum_scratch_floats(static_cast<int>(N), static_cast<int>(V)) +
-                                    c.layers * (fc1_slot_floats(static_cast<int>(N), static_cast<int>(fc1)) +
-                                                colsum_scratch_floats(static_cast<int>(N), static_cast<int>(3 * d)))) * 4
+                                    c.layers * (wide_slot_floats(static_cast<int>(N), static_cast<int>(fc1)) +
+                                                wide_slot_floats(static_cast<int>(N), static_cast<int>(3 * d)))) * 4
                                  : 0);
     W.embed_scratch = take(embed_bwd_scratch_bytes(static_cast<int>(N)));
     W.doc_ranges = take((N / 64 + 1) * 2 * sizeof(int));      // (min, max) document id per 64 token rows
@@ -178,12 +179,13 @@ static int attention_fwd(const T* qkv, T* out, float* lse, const int* doc, const
 }
 template <typename T>
 static int attention_bwd(const T* qkv, const T* out, const T* dout, const float* lse, float* dvec, T* dqkv, const int* doc,
-                         const int* ranges, const nnb200_gpt_config& c, cudaStream_t s, bool have_dvec = false)
+                         const int* ranges, const nnb200_gpt_config& c, cudaStream_t s, bool have_dvec = false,
+                         float* colsum_part = nullptr)          // the last two: honoured by the tcgen05 kernels only
 {
     const int dk = c.d_model / c.heads, alibi = c.pos == 2;
     if constexpr (Mode<T>::bf) {
         if (attention_tc_supported(dk, c.seq, c.d_model))
-            return attention_bwd_tc(qkv, out, dout, lse, dvec, dqkv, doc, ranges, c.batch, c.seq, c.heads, dk, alibi, s, have_dvec);
+            return attention_bwd_tc(qkv, out, dout, lse, dvec, dqkv, doc, ranges, c.batch, c.seq, c.heads, dk, alibi, s, have_dvec, colsum_part);
         if (attention_mma_supported(dk, c.d_model))
             return attention_bwd_mma(qkv, out, dout, lse, dvec, dqkv, doc, c.batch, c.seq, c.heads, dk, alibi, s);
     }
@@ -277,11 +279,11 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         cd.partial = F(W.colsum_partials) + cs_off; cd.chunks = 0; cd.deferred = false;
         return &cd;
     };
-    auto cs_done = [&](long long dst, int cols, bool fc1_slot = false) {
+    auto cs_done = [&](long long dst, int cols, bool wide = false) {
         if (!cd.deferred) return;
         csl.dst[ncs] = dst; csl.part[ncs] = static_cast<long long>(cs_off); csl.chunks[ncs] = cd.chunks; csl.cols[ncs] = cols;
         ++ncs;
-        cs_off += fc1_slot ? fc1_slot_floats(N, cols) : colsum_scratch_floats(N, cols);
+        cs_off += wide ? wide_slot_floats(N, cols) : colsum_scratch_floats(N, cols);
         cd.deferred = false;
     };
 
@@ -343,11 +345,23 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
             }
         }
         if (!have_dvec) NNB_TRY(linear_bwd_input<T>(g, P + lp.wo, Hh(lp.wo), A(W.d_attn), N, d, d, s));
-        NNB_TRY(attention_bwd<T>(A(a.qkv), A(a.attn), A(W.d_attn), F(a.lse), F(W.dvec), A(W.d_qkv), doc, ranges, c, s, have_dvec));
+        // On the tcgen05 kernels the write-outs of dQ, dK and dV also leave their column sums per 32 rows: the QKV bias
+        // gradient without a pass over d_qkv.  Not with rotary positions: there the bias sees the gradient rotated back.
+        ColsumDefer* qkv_dfr = nullptr;
+        if constexpr (Mode<T>::bf) {
+            if (c.pos != 3 && attention_tc_supported(d / c.heads, c.seq, d)) qkv_dfr = cs_begin();
+        }
+        NNB_TRY(attention_bwd<T>(A(a.qkv), A(a.attn), A(W.d_attn), F(a.lse), F(W.dvec), A(W.d_qkv), doc, ranges, c, s, have_dvec,
+                                 qkv_dfr ? qkv_dfr->partial : nullptr));
+        if (qkv_dfr) { qkv_dfr->chunks = static_cast<int>(N / 32); qkv_dfr->deferred = true; cs_done(lp.bqkv, 3 * d, true); }
         // the gradients of the rotated Q and K go back through the inverse rotation (compute_layer.hpp:1365-1372)
         if (c.pos == 3) NNB_TRY(rope_apply<T>(A(W.d_qkv), F(W.sin_table), N, c.seq, c.heads, d / c.heads, 3 * d, true, s));
-        NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, cn, N, d, 3 * d, s, cs_begin()));
-        cs_done(lp.bqkv, 3 * d);
+        if (qkv_dfr) {
+            NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, nullptr, cs, cn, N, d, 3 * d, s));
+        } else {
+            NNB_TRY(linear_bwd_params<T>(A(W.d_qkv), A(a.xn1), G + lp.wqkv, G + lp.bqkv, cs, cn, N, d, 3 * d, s, cs_begin()));
+            cs_done(lp.bqkv, 3 * d, true);
+        }
         NNB_TRY(linear_bwd_input<T>(A(W.d_qkv), P + lp.wqkv, Hh(lp.wqkv), A(W.d_xn), N, d, 3 * d, s));
         NNB_TRY(norm_bwd<T>(A(W.d_xn), A(a.x_in), P + lp.g1, F(a.rinv1), F(a.mean1), g, g_other, G + lp.g1, GB(lp.be1), cs, N,
                             d, ln, s, cn, l >= 1 ? G + L.layers[l - 1].b2 : nullptr, slot_ptr(), &was_deferred));

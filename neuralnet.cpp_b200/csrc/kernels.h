@@ -121,10 +121,12 @@ int attention_fwd_tc(const bf16* qkv, bf16* out, float* lse, const int* doc, con
                      int alibi, cudaStream_t s);
 int attention_device_error(int* code);
 // attention_tc_bwd.cu : tcgen05 backward (same shape limits)
-// have_dvec: dvec already holds rowsum(dout * out) per (batch, head, row) (written by gemm_bf16_dx_rowdot)
+// have_dvec: dvec already holds rowsum(dout * out) per (batch, head, row) (written by gemm_bf16_dx_rowdot).
+// colsum_part: null, or (B S / 32) x 3 d floats that receive the column sums of dqkv over each 32 token rows, every
+// element written (summed over the rows they are the bias gradient of the QKV projection)
 int attention_bwd_tc(const bf16* qkv, const bf16* out, const bf16* dout, const float* lse, float* dvec, bf16* dqkv,
                      const int* doc, const int* doc_ranges, int B, int S, int H, int dk, int alibi, cudaStream_t s,
-                     bool have_dvec = false);
+                     bool have_dvec = false, float* colsum_part = nullptr);
 int attention_bwd_device_error(int* code);
 // status word of the fused elementwise kernels that wait on bulk copies (reads and clears)
 int fused_device_error(int* code);

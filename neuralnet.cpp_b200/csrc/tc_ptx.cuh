@@ -139,6 +139,22 @@ __device__ __forceinline__ bool group_any(int id, bool pred)
         : "=r"(r) : "r"(id), "r"(static_cast<uint32_t>(pred)) : "memory");
     return r != 0;
 }
+// Sum over the 32 lanes of a warp of 32 values per lane: a butterfly in which every lane sends half of what it holds and
+// keeps the other half (31 exchanges instead of 160); on return lane l holds the sum of element l.  Fixed order, so the
+// result is reproducible.  v is destroyed.
+__device__ __forceinline__ float lane_sums32(float (&v)[32], int lane)
+{
+#pragma unroll
+    for (int st = 16; st >= 1; st >>= 1) {
+        const bool upper = (lane & st) != 0;
+#pragma unroll
+        for (int i = 0; i < st; ++i) {
+            const float send = upper ? v[i] : v[i + st], keep = upper ? v[i + st] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, st);
+        }
+    }
+    return v[0];
+}
 // barrier over all eight epilogue warps of a pair-GEMM CTA (barrier 3)
 __device__ __forceinline__ void all_epilogue_bar() { asm volatile("bar.sync 3, 256;" ::: "memory"); }
 __device__ __forceinline__ void tma_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

@@ -270,6 +270,17 @@ def test_attention_forward_backward(g, dtype, B, S, H, dk, alibi, docs, mean_len
                g.ptr(t_doc), g.ptr(ranges), B, S, H, dk, alibi, dtype, g.stream())
         torch.cuda.synchronize()
         assert torch.equal(t_out2, t_out) and torch.equal(lse2, lse) and torch.equal(t_dqkv2, t_dqkv)
+    if dtype == 1 and dk in (64, 128) and S % 128 == 0:
+        # the tcgen05 kernels with the QKV bias gradient's partial column sums: the same gradients bit for bit, and every
+        # partial row (32 token rows) against float64 sums of the stored values
+        part = torch.full((N // 32, 3 * d), 7.0, dtype=torch.float32, device="cuda")
+        t_dqkv3 = torch.zeros_like(t_dqkv)
+        g.call("nnb200_attention_backward_bias_partials", g.ptr(t_qkv), g.ptr(t_out), g.ptr(t_dout), g.ptr(lse), g.ptr(dvec),
+               g.ptr(t_dqkv3), g.ptr(t_doc), None, g.ptr(part), B, S, H, dk, alibi, g.stream())
+        torch.cuda.synchronize()
+        assert torch.equal(t_dqkv3, t_dqkv)
+        want_part = dqkv.astype(np.float64).reshape(N // 32, 32, 3 * d).sum(1)
+        assert np.abs(g.host(part) - want_part).max() < 1e-5 * max(1.0, np.abs(want_part).max())
     tol = 1e-2 if dtype == 1 else 1e-5        # the stated bars: bf16 tensor-core path / fp32 check mode
     scale = lambda x: np.abs(x).max()
     assert np.abs(out - o_ref).max() < tol * scale(o_ref) * 3
