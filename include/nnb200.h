@@ -102,8 +102,8 @@ int nnb200_linear_swiglu_forward(const void* x, const void* W, const float* bias
  * of Linear) and h1[M, 2 ff] = (gate | up); the product is rounded to bf16 and not stored.  The values
  * nnb200_gemm_bf16 followed by nnb200_activation_backward(swiglu = 1) give, bit for bit.  All matrices bf16.  Needs
  * M > 128, ff > 128 a multiple of 64, K a multiple of 8 (nnb200_linear_swiglu_backward_supported: 1 or 0); -1 otherwise.
- * colsum_partial (may be NULL): ceil(M / 32) rows of 2 ff floats, every one written, row r = the column sums of dh1 over
- * matrix rows [32 r, 32 r + 32): summed over r they are the bias gradient of the first projection
+ * colsum_partial (may be NULL; 16-byte aligned): ceil(M / 128) rows of 2 ff floats, every one written, row r = the column
+ * sums of dh1 over matrix rows [128 r, 128 r + 128): summed over r they are the bias gradient of the first projection
  * (Linear::backward's column sum, compute_layer.hpp:188-193), which then needs no pass over dh1.
  * Replaces the input gradient of Linear::backward + SwiGLU::backward (compute_layer.hpp:176-195, 436-445). */
 int nnb200_linear_swiglu_backward_supported(int M, int ff, int K);

@@ -42,7 +42,7 @@ struct GemmParams {
     const void* residual;
     float alpha;
     int glu_ff;                 // SwiGLU variant of the pair kernel: rows of B per half (gate rows, then up rows); 0 otherwise
-    float* colsum_part;         // SwiGLU-backward variant: column sums of the output per 32 rows, [ceil(M / 32)][2 glu_ff]; or null
+    float* colsum_part;         // SwiGLU-backward variant: column sums of the output per 128 rows, [ceil(M / 128)][2 glu_ff]; or null
     float* dot_out;             // row-dot variant: sums per (row, 64-column block), laid out [row / dot_S][block][row % dot_S]
     int dot_S, dot_H;
 };
@@ -445,7 +445,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     return 0;
 }
 
-constexpr int PAIR_THREADS = 320;
+constexpr int PAIR_THREADS = 384;     // producer, MMA, eight epilogue warps, and two warps that sum columns in the SwiGLU-backward form
 // CTA pairs that can be resident at once (GPCs with an odd SM count strand one SM each)
 template <typename Kernel>
 static int max_pairs(Kernel kernel, int smem)
@@ -620,9 +620,9 @@ int gemm_bf16_swiglu(const bf16* X, const bf16* W, const float* bias, bf16* H1, 
 
 // Input gradient of a SwiGLU block's second projection taken through the activation in one launch:
 // dH1[M, 2 ff] = (dgate | dup) of (dY[M, K] W[K, ff]) at H1[M, 2 ff] = (gate | up); W stored (K, ff), ff contiguous.
-// Bit-identical to gemm_bf16 into a (M, ff) buffer followed by act_bwd.  colsum_partial (may be null): ceil(M / 32) rows
-// of 2 ff floats that receive the column sums of dH1 over each 32 rows (what the bias gradient of the first projection
-// is folded from), every element written.
+// Bit-identical to gemm_bf16 into a (M, ff) buffer followed by act_bwd.  colsum_partial (may be null; 16-byte aligned):
+// ceil(M / 128) rows of 2 ff floats that receive the column sums of dH1 over each 128 rows (what the bias gradient of
+// the first projection is folded from), every element written.
 bool gemm_swiglu_bwd_supported(int M, int ff, int K)
 {
     return M > 128 && ff > 128 && (ff % 64) == 0 && K > 0 && (K % 8) == 0 && pair_capacity() > 0;
@@ -637,6 +637,7 @@ int gemm_bf16_swiglu_bwd(const bf16* dY, const bf16* W, const bf16* H1, bf16* dH
     p.M = M; p.N = ff; p.K = K;
     p.C = dH1; p.ldc = 2LL * ff; p.c_bf16 = 1; p.accumulate = 0;
     p.alpha = 1.0f; p.vec_ok = 1; p.tma_store = 1; p.glu_ff = ff;
+    NNB_ARG_CHECK((reinterpret_cast<uintptr_t>(colsum_partial) & 15) == 0, "the partial sums must be 16-byte aligned");
     p.colsum_part = colsum_partial;
     p.tiles_m = static_cast<int>(ceil_div(M, 256));
     p.tiles_n = static_cast<int>(ceil_div(ff, 256));

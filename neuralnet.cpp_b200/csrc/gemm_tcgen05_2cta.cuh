@@ -55,7 +55,7 @@ constexpr int PAIR_BN_HALF = 128;                                // rows of B ea
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_BN_HALF * BK * 2;
 
 template <bool A_MN, bool B_MN, int STAGES, bool RES, bool GLU = false, bool DB = false, bool DOT = false, bool GLUB = false>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(384, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR, const GemmParams p)
 {
@@ -78,7 +78,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + BN);             // each epilogue group keeps the bias of its own 128 columns
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
     const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16, drain_bar = tempty0 + 16, res_full0 = drain_bar + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 7);
+    const uint32_t tile_ready0 = res_full0 + 16, sums_done0 = tile_ready0 + 16;   // GLUB with column sums: hand-offs with warp 10
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -90,6 +91,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 16); }
         mbar_init(drain_bar, 1);
         mbar_init(res_full0, 1); mbar_init(res_full0 + 8, 1);
+        for (int k = 0; k < 2; ++k) { mbar_init(tile_ready0 + 8 * k, 1); mbar_init(sums_done0 + 8 * k, 2); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -106,6 +108,19 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
     const int tiles = p.tiles_m * p.tiles_n;
     const int units = tiles * p.splits;
+
+    // GLUB: the 64-column blocks of this CTA in the order its epilogue takes them; false at the end of the list
+    struct BlockCursor { int u, cb; };
+    auto glub_next = [&](BlockCursor& c, int& n0, int& m0) -> bool {
+        for (;;) {
+            if (++c.cb * 64 >= BN) { c.u += pairs; c.cb = 0; }
+            if (c.u >= units) return false;
+            const int t = c.u % tiles;
+            const int tile_n = t / p.tiles_m, tile_m = t - tile_n * p.tiles_m;
+            n0 = tile_n * BN + c.cb * 64; m0 = tile_m * 256 + static_cast<int>(rank) * 128;
+            if (n0 < p.N && m0 < p.M) return true;
+        }
+    };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -170,7 +185,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             umma_commit_pair(drain_bar, 1);
             mbar_wait(drain_bar, 0, abort_flag, 5, &g_gemm_error);
         }
-    } else {
+    } else if (warp < 10) {
         // Two epilogue groups of four warps; group g takes the column blocks cb with (cb & 1) == g, has its own
         // staging tile, bias copy, named barrier and bulk-store queue, and never synchronises with the other.
         const int q = warp & 3;                                  // TMEM lane quadrant this warp may read
@@ -209,18 +224,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         // GLUB: blocks in the order all eight warps take them; the elected thread keeps the loads one block ahead
         const bool glub_elected = GLUB && threadIdx.x == 64;
         int glub_blocks = 0, glub_requested = 0;
-        struct BlockCursor { int u, cb; } g_req{pair, -1};
-        // next block of this CTA in consumption order; false at the end of the list
-        auto glub_next = [&](BlockCursor& c, int& n0, int& m0) -> bool {
-            for (;;) {
-                if (++c.cb * 64 >= BN) { c.u += pairs; c.cb = 0; }
-                if (c.u >= units) return false;
-                const int t = c.u % tiles;
-                const int tile_n = t / p.tiles_m, tile_m = t - tile_n * p.tiles_m;
-                n0 = tile_n * BN + c.cb * 64; m0 = tile_m * 256 + static_cast<int>(rank) * 128;
-                if (n0 < p.N && m0 < p.M) return true;
-            }
-        };
+        BlockCursor g_req{pair, -1};
         // loads of the next block into the set it will be turned in (an L2 prefetch of the tiles two blocks further on
         // was measured slower: 93.8 against 86.5 us at 16384 x 2048 x 768)
         auto glub_request = [&]() {
@@ -346,6 +350,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         uint8_t* utile = sR + set * C_STAGE_BYTES;
                         if (glub_elected) {
                             tma_wait_read0();                        // the other set's stores (the block before this one) have read it
+                            // ... and so has the warp that sums its columns
+                            if (p.colsum_part && glub_blocks >= 1)
+                                mbar_wait(sums_done0 + 8 * (set ^ 1), ((glub_blocks - 1) >> 1) & 1, abort_flag, 13, &g_gemm_error);
                             glub_request();
                         }
                         tmem_ld32(tbase + cb * 64, ra);
@@ -370,46 +377,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                                 const float sg = sigmoid_fast(gt);
                                 og.v[k] = __float2bfloat16_rn(go * up * (sg * (1.0f + gt * (1.0f - sg))));
                                 ou.v[k] = __float2bfloat16_rn(go * gt * sg);
-                                // the accumulator registers are free once read: keep the stored values for the column sums
-                                ra[j + k] = (static_cast<uint32_t>(__bfloat16_as_ushort(og.v[k])) << 16) | __bfloat16_as_ushort(ou.v[k]);
                             }
                             *reinterpret_cast<uint4*>(grow + chunk) = *reinterpret_cast<const uint4*>(&og);
                             *reinterpret_cast<uint4*>(urow + chunk) = *reinterpret_cast<const uint4*>(&ou);
                         }
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        if (p.colsum_part) {
-                            // Column sums of both gradient blocks over this warp's 32 rows (the bias gradient of the first
-                            // projection): a butterfly in which every lane sends half of what it holds and keeps the other
-                            // half, 31 exchanges for 32 columns, after which lane l holds column l.  Fixed order: the sums
-                            // are reproducible.  One partial row per 32 matrix rows; a later kernel folds them.
-                            float sg_[32], su_[32];
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                sg_[j] = row_ok ? __uint_as_float(ra[j] & 0xffff0000u) : 0.f;
-                                su_[j] = row_ok ? __uint_as_float(ra[j] << 16) : 0.f;
-                            }
-#pragma unroll
-                            for (int st = 16; st >= 1; st >>= 1) {
-                                const bool upper = (lane & st) != 0;
-#pragma unroll
-                                for (int i = 0; i < st; ++i) {
-                                    const float send_g = upper ? sg_[i] : sg_[i + st], keep_g = upper ? sg_[i + st] : sg_[i];
-                                    const float send_u = upper ? su_[i] : su_[i + st], keep_u = upper ? su_[i + st] : su_[i];
-                                    sg_[i] = keep_g + __shfl_xor_sync(0xffffffffu, send_g, st);
-                                    su_[i] = keep_u + __shfl_xor_sync(0xffffffffu, send_u, st);
-                                }
-                            }
-                            if (m0 + q * 32 < p.M) {
-                                float* dst = p.colsum_part + static_cast<size_t>((m0 >> 5) + q) * (2 * p.glu_ff) + n0 + grp * 32 + lane;
-                                dst[0] = sg_[0];
-                                dst[p.glu_ff] = su_[0];
-                            }
-                        }
                         all_epilogue_bar();
                         if (glub_elected) {
                             tma_store_2d(&tmC, smem_u32(gtile), n0, m0);
                             tma_store_2d(&tmC, smem_u32(utile), p.glu_ff + n0, m0);
                             tma_commit();
+                            if (p.colsum_part) mbar_arrive(tile_ready0 + 8 * set);   // warp 10 may sum the set's columns
                         }
                     }
                 }
@@ -510,6 +488,44 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8 * acc);
         }
         if (elected) tma_wait_all();
+    } else if (GLUB && p.colsum_part != nullptr) {
+        // Warps 10 and 11 of the GLUB form: column sums of the gate-gradient tile (warp 10) and of the up-gradient tile
+        // (warp 11) of every block over the CTA's 128 rows (rows beyond the matrix hold zeros), read from the staging
+        // tiles while the eight epilogue warps are on the next block: fc1's bias gradient as one partial row per 128
+        // matrix rows, in a fixed order.  Lane (c, rs) takes 16-byte chunk c of rows [32 rs, 32 rs + 32).
+        BlockCursor cur{pair, -1};
+        int n0, m0;
+        const int c = lane & 7, rs = lane >> 3, which = warp - 10;
+        for (int k = 0; glub_next(cur, n0, m0); ++k) {
+            const int set = k & 1;
+            if (!mbar_wait(tile_ready0 + 8 * set, (k >> 1) & 1, abort_flag, 14, &g_gemm_error)) break;
+            const uint8_t* tile = (which ? sR : sC) + set * C_STAGE_BYTES;
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < 32; ++i) {
+                const int r = rs * 32 + i;
+                const uint4 v4 = *reinterpret_cast<const uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4));
+                const uint32_t w[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[2 * j] += __uint_as_float(w[j] << 16);
+                    acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sums_done0 + 8 * set);        // (with the other warp's arrival) the set may be loaded into again
+#pragma unroll
+            for (int st = 8; st <= 16; st <<= 1)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], st);
+            if (rs == 0) {
+                float* dst = p.colsum_part + static_cast<size_t>(m0 >> 7) * (2 * p.glu_ff) + which * p.glu_ff + n0 + c * 8;
+                *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            }
+        }
     }
 
     tc_fence_before();

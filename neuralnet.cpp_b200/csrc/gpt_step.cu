@@ -73,9 +73,8 @@ DecodeLayout decode_layout(const nnb200_gpt_config& c)
 
 // ---------------------------------------------------------------- workspace
 struct LayerActs { size_t x_in, xn1, qkv, attn, x_mid, xn2, h1, h2; size_t rinv1, mean1, rinv2, mean2, lse; };
-// floats of the deferred column-sum slots of the fc1 and QKV bias gradients: one partial row per 32 token rows (what the
-// SwiGLU-backward epilogue of the GEMM and the write-outs of the attention backward kernels leave), which also holds
-// the coarser partials of the column-sum kernel
+// floats of the deferred column-sum slot of the QKV bias gradient: one partial row per 32 token rows (what the write-outs
+// of the attention backward kernels leave), which also holds the coarser partials of the column-sum kernel
 static size_t wide_slot_floats(long long rows, long long cols) { return static_cast<size_t>(ceil_div(rows, 32) * cols); }
 
 struct Workspace {
@@ -118,7 +117,7 @@ static Workspace make_workspace(const nnb200_gpt_config& c)
     // and one per bias gradient that has a column-sum pass of its own: the LM head, and fc1 and qkv of every layer
     W.colsum_partials = take(2 * static_cast<size_t>(c.layers) + 1 <= kColsumFoldMaxSlots
                                  ? (colsum_scratch_floats(static_cast<int>(N), static_cast<int>(V)) +
-                                    c.layers * (wide_slot_floats(static_cast<int>(N), static_cast<int>(fc1)) +
+                                    c.layers * (colsum_scratch_floats(static_cast<int>(N), static_cast<int>(fc1)) +
                                                 wide_slot_floats(static_cast<int>(N), static_cast<int>(3 * d)))) * 4
                                  : 0);
     W.embed_scratch = take(embed_bwd_scratch_bytes(static_cast<int>(N)));
@@ -311,11 +310,11 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
         if constexpr (Mode<T>::bf) {
             if (swiglu && gemm_swiglu_bwd_supported(N, ff, d)) {
                 // the activation's backward pass in the epilogue of fc2's input-gradient GEMM; fc1's bias gradient after it
-                // (with the deferred fold its epilogue also leaves the column sums per 32 rows: no pass over d_h1 for them)
+                // (with the deferred fold its epilogue also leaves the column sums per 128 rows: no pass over d_h1 for them)
                 ColsumDefer* dfr = cs_begin();
                 NNB_TRY(gemm_bf16_swiglu_bwd(reinterpret_cast<const bf16*>(g), Hh(lp.w2), reinterpret_cast<const bf16*>(A(a.h1)),
                                              reinterpret_cast<bf16*>(A(W.d_h1)), N, ff, d, dfr ? dfr->partial : nullptr, s));
-                if (dfr) { dfr->chunks = static_cast<int>(ceil_div(N, 32)); dfr->deferred = true; }
+                if (dfr) { dfr->chunks = static_cast<int>(ceil_div(N, 128)); dfr->deferred = true; }
                 else NNB_TRY(colsum_accumulate<T>(A(W.d_h1), fc1, nullptr, nullptr, nullptr, nullptr, 0, G + lp.b1, cs, N, fc1, s, cn, nullptr));
                 fused_act = true;
             }
@@ -324,7 +323,7 @@ static int backward_t(const nnb200_gpt_config& c, const float* P, const bf16* H,
             NNB_TRY(linear_bwd_input<T>(g, P + lp.w2, Hh(lp.w2), A(W.d_h2), N, ff, d, s));
             NNB_TRY(act_bwd<T>(A(W.d_h2), A(a.h1), A(W.d_h1), N, ff, swiglu, s, G + lp.b1, cs, cn, cs_begin()));   // also sums fc1's bias gradient
         }
-        cs_done(lp.b1, fc1, true);
+        cs_done(lp.b1, fc1);
         NNB_TRY(linear_bwd_params<T>(A(W.d_h1), A(a.xn2), G + lp.w1, nullptr, cs, cn, N, d, fc1, s));
         NNB_TRY(linear_bwd_input<T>(A(W.d_h1), P + lp.w1, Hh(lp.w1), A(W.d_xn), N, d, fc1, s));
         // grad_r1 = grad_output + norm2.backward (GPTBlock::backward, compute_layer.hpp:2388-2404)

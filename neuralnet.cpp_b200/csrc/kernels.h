@@ -31,7 +31,7 @@ int gemm_bf16_swiglu(const bf16* X, const bf16* W, const float* bias, bf16* H1, 
 // product itself not stored; bit-identical to gemm_bf16 followed by act_bwd
 bool gemm_swiglu_bwd_supported(int M, int ff, int K);
 int gemm_bf16_swiglu_bwd(const bf16* dY, const bf16* W, const bf16* H1, bf16* dH1, int M, int ff, int K, float* colsum_partial,
-                         cudaStream_t stream);   // colsum_partial: null, or ceil(M / 32) x 2 ff floats for the column sums per 32 rows
+                         cudaStream_t stream);   // colsum_partial: null, or ceil(M / 128) x 2 ff floats for the column sums per 128 rows
 // input gradient of a projection, dX = dY W, and the sums over each 64-column block of dX * other in the same launch
 // (the row term of the attention backward pass when dX is the gradient of the attention output and other that output)
 bool gemm_rowdot_supported(int M, int N, int K, int S, int H);

@@ -145,7 +145,7 @@ def run_linear_swiglu(M, ff, K, args):
     w2 = (torch.randn(K, ff, device="cuda", generator=g) * 0.05).bfloat16()
     dh2 = torch.empty(M, ff, device="cuda", dtype=torch.bfloat16)
     dh1 = torch.empty(M, 2 * ff, device="cuda", dtype=torch.bfloat16)
-    part = torch.empty((M + 31) // 32, 2 * ff, device="cuda")    # column sums per 32 rows, as the training step asks for them
+    part = torch.empty((M + 127) // 128, 2 * ff, device="cuda")  # column sums per 128 rows, as the training step asks for them
     fused_b = lambda: call("nnb200_linear_swiglu_backward", P(x), P(w2), P(h1), P(dh1), M, ff, K, P(part), S())
 
     bsum = torch.zeros(2 * ff, device="cuda")

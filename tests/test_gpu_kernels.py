@@ -153,7 +153,7 @@ def test_linear_swiglu_backward_equals_two_kernels(g, M, ff, K):
     dy, w, h1 = g.dev(dY, torch.bfloat16), g.dev(W, torch.bfloat16), g.dev(H1, torch.bfloat16)
     assert g.call("nnb200_linear_swiglu_backward_supported", M, ff, K) == 1
     dh1 = torch.full((M, 2 * ff), 7.0, dtype=torch.bfloat16, device="cuda")
-    part = torch.full(((M + 31) // 32, 2 * ff), 7.0, dtype=torch.float32, device="cuda")
+    part = torch.full(((M + 127) // 128, 2 * ff), 7.0, dtype=torch.float32, device="cuda")
     g.call("nnb200_linear_swiglu_backward", g.ptr(dy), g.ptr(w), g.ptr(h1), g.ptr(dh1), M, ff, K, g.ptr(part), g.stream())
     twice = torch.zeros_like(dh1)          # without the column sums: same gradients
     g.call("nnb200_linear_swiglu_backward", g.ptr(dy), g.ptr(w), g.ptr(h1), g.ptr(twice), M, ff, K, None, g.stream())
@@ -165,11 +165,11 @@ def test_linear_swiglu_backward_equals_two_kernels(g, M, ff, K):
     assert g.gemm_status() == 0
     assert torch.equal(dh1, ref)
     assert torch.equal(twice, ref)
-    # column sums per 32 rows of the stored gradients (the last group ragged): every partial row against float64
+    # column sums per 128 rows of the stored gradients (the last group ragged): every partial row against float64
     d64 = g.host(dh1).astype(np.float64)
-    pad = np.zeros((part.shape[0] * 32, 2 * ff))
+    pad = np.zeros((part.shape[0] * 128, 2 * ff))
     pad[:M] = d64
-    want_part = pad.reshape(part.shape[0], 32, 2 * ff).sum(1)
+    want_part = pad.reshape(part.shape[0], 128, 2 * ff).sum(1)
     got_part = g.host(part).astype(np.float64)
     assert np.abs(got_part - want_part).max() < 1e-5 * max(1.0, np.abs(want_part).max())
     # and the plain product against float64, so that the comparison above is not between two wrong results
