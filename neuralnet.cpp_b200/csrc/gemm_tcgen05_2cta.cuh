@@ -10,6 +10,8 @@
 //                    memory -> TMA store / reduce-add) in two independent groups of four warps that take
 //                    alternate 128-byte column blocks, so the drain of a tile keeps pace with a main loop
 //                    that is as short as 12 k-blocks (K = 768)
+//   both             warps 10, 11: in the GLUB form with column sums, each sums the columns of one of the two
+//                    gradient tiles of a block; otherwise they go straight to the barrier at the end
 // Barriers: full[s] lives in the leader and counts the bytes of all four loads of a stage (the peer's loads
 // name it through its shared::cluster address); empty[s] and tfull[a] exist in both CTAs and are signalled
 // together by a multicast tcgen05.commit; tempty[a] lives in the leader and takes one arrival from each of
@@ -32,11 +34,14 @@
 // D = rowsum(dO * O) of the attention backward pass (64 columns = one head), which then needs no pass of its own.
 //
 // GLUB: the product is the gradient of a SwiGLU block's activation (the input gradient of its second projection) and
-// is not stored: for every 64-column block the group TMA-loads the gate and up tiles of the first projection's output
-// (the map in the residual slot, up columns glu_ff further right) into its two tiles, turns them in place into the
-// gradients of gate and up (compute_layer.hpp:436-445; each thread rewrites the chunks of its own row) from the
-// product as rounded to bf16, and stores both through the output map, bit for bit what the activation's backward
-// kernel gives on the stored product.
+// is not stored: all eight epilogue warps work on one 64-column block at a time; the elected thread TMA-loads the gate
+// and up tiles of the first projection's output (the map in the residual slot, up columns glu_ff further right) into
+// one of two sets of two tiles, a block ahead; the warps turn them in place into the gradients of gate and up
+// (compute_layer.hpp:436-445; each thread rewrites the chunks of its own row) from the product as rounded to bf16,
+// and both are stored through the output map, bit for bit what the activation's backward kernel gives on the stored
+// product.  With colsum_part, warps 10 and 11 then read the two tiles back and leave their column sums over the CTA's
+// 128 rows (the bias gradient of the first projection, one partial row per 128 matrix rows); the set is loaded into
+// again only when they are done with it.
 //
 // DB: each epilogue group has two staging tiles and uses them in turn, so a block's conversion does not wait for the
 // previous block's store to have read its tile; the 32 KB come out of the operand ring as in the RES form.
