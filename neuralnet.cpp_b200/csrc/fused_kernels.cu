@@ -37,6 +37,25 @@ template <int N> __device__ __forceinline__ void ld_f32x(const float* __restrict
     }
 }
 
+// the same from shared (or any generic) memory: ld_f32x reads through the read-only global path and must not be given
+// a shared-memory address
+template <int N> __device__ __forceinline__ void ld_f32x_generic(const float* p, float* out)
+{
+#pragma unroll
+    for (int k = 0; k < N; k += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p + k);
+        out[k] = t.x; out[k + 1] = t.y; out[k + 2] = t.z; out[k + 3] = t.w;
+    }
+}
+// tells the compiler that a 16-byte register vector may have changed: values derived from it before are not kept alive
+// across this point (a row held packed is converted again in a second pass instead of being kept twice)
+template <typename V> __device__ __forceinline__ void forget_derived(V& v)
+{
+    static_assert(sizeof(V) == 16, "16-byte vectors only");
+    uint4& w = reinterpret_cast<uint4&>(v);
+    asm volatile("" : "+r"(w.x), "+r"(w.y), "+r"(w.z), "+r"(w.w));
+}
+
 // ======================================================================================
 // normalisation: one warp per token row
 // ======================================================================================
@@ -203,6 +222,66 @@ norm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma, co
     }
 }
 
+// Wide rows (d = 32 * NV * elements per 16 bytes, NV up to 16: 4096 bf16 columns): a warp per row with the row held in
+// registers as fp32, all its loads in flight at once, and the parameters in shared memory; every activation is read
+// once.  Blocks of four warps, three per SM: twelve rows (96 KB at 4096 bf16 columns) in flight per SM.
+template <typename T, bool LAYER, int NV>
+__global__ void __launch_bounds__(128, 3)
+norm_fwd_wide_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                     T* __restrict__ y, float* __restrict__ rinv_out, float* __restrict__ mean_out, int rows)
+{
+    constexpr int VN = Vec16<T>::N, D = 32 * NV * VN;
+    extern __shared__ __align__(16) float norm_params[];            // gamma[D], then beta[D] for LayerNorm
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const int stride = gridDim.x * wpb;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) { norm_params[i] = gamma[i]; if (LAYER) norm_params[D + i] = beta[i]; }
+    __syncthreads();
+    const float inv_d = 1.0f / static_cast<float>(D);
+    for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += stride) {
+        float xv[NV][VN];
+        {
+            Vec16<T> xr[NV];
+#pragma unroll
+            for (int v = 0; v < NV; ++v) xr[v] = ld16(x + static_cast<size_t>(r) * D + (v * 32 + lane) * VN);
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+                for (int k = 0; k < VN; ++k) xv[v][k] = to_f32(xr[v].v[k]);
+        }
+        float mean = 0.f;
+        if (LAYER) {
+            float sm = 0.f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+                for (int k = 0; k < VN; ++k) sm += xv[v][k];
+            mean = warp_sum(sm) * inv_d;
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+            for (int k = 0; k < VN; ++k) { const float t = xv[v][k] - mean; ss += t * t; }
+        const float rinv = 1.0f / sqrtf(warp_sum(ss) * inv_d + kNormEps);
+        if (lane == 0) { rinv_out[r] = rinv; if (LAYER) mean_out[r] = mean; }
+        T* yr = y + static_cast<size_t>(r) * D;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            float gm[VN], bt[VN];
+            ld_f32x_generic<VN>(norm_params + (v * 32 + lane) * VN, gm);
+            if (LAYER) ld_f32x_generic<VN>(norm_params + D + (v * 32 + lane) * VN, bt);
+            Vec16<T> o;
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                float n = (xv[v][k] - mean) * rinv * gm[k];
+                if (LAYER) n += bt[k];
+                o.v[k] = from_f32<T>(n);
+            }
+            st16(yr + (v * 32 + lane) * VN, o);
+        }
+    }
+}
+
 template <typename T, bool LAYER, int NV>
 __global__ void __launch_bounds__(256)
 norm_bwd_dx_reg_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ gamma,
@@ -249,6 +328,161 @@ norm_bwd_dx_reg_kernel(const T* __restrict__ g, const T* __restrict__ x, const f
             st16(dx + off + (v * 32 + lane) * VN, o);
         }
     }
+}
+
+// The same for wide rows (NV up to 16: 4096 bf16 columns): g and x stay in registers as loaded (packed) and are
+// converted once for the two row sums and once for the output; gamma comes from shared memory.  Blocks of four warps,
+// two per SM (a row is 16 to 24 KB of loads in flight per warp).
+template <typename T, bool LAYER, int NV>
+__global__ void __launch_bounds__(128, 2)
+norm_bwd_dx_wide_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ gamma,
+                        const float* __restrict__ rinv_in, const float* __restrict__ mean_in, const T* __restrict__ add,
+                        T* __restrict__ dx, int rows)
+{
+    constexpr int VN = Vec16<T>::N, D = 32 * NV * VN;
+    extern __shared__ __align__(16) float norm_params[];
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) norm_params[i] = gamma[i];
+    __syncthreads();
+    const float inv_d = 1.0f / static_cast<float>(D);
+    for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
+        const size_t off = static_cast<size_t>(r) * D;
+        const float rinv = rinv_in[r], mean = LAYER ? mean_in[r] : 0.f;
+        Vec16<T> gv[NV], xv[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) { gv[v] = ld16(g + off + (v * 32 + lane) * VN); xv[v] = ld16(x + off + (v * 32 + lane) * VN); }
+        float s_g = 0.f, s_gn = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            float gm[VN];
+            ld_f32x_generic<VN>(norm_params + (v * 32 + lane) * VN, gm);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                const float gg = to_f32(gv[v].v[k]) * gm[k], nn = (to_f32(xv[v].v[k]) - mean) * rinv;
+                s_g += gg; s_gn += gg * nn;
+            }
+        }
+        const float m_gn = warp_sum(s_gn) * inv_d;
+        const float m_g = LAYER ? warp_sum(s_g) * inv_d : 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) { forget_derived(gv[v]); forget_derived(xv[v]); }
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            float gm[VN];
+            ld_f32x_generic<VN>(norm_params + (v * 32 + lane) * VN, gm);
+            Vec16<T> av;
+            if (add) av = ld16(add + off + (v * 32 + lane) * VN);
+            Vec16<T> o;
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                const float gg = to_f32(gv[v].v[k]) * gm[k], nn = (to_f32(xv[v].v[k]) - mean) * rinv;
+                float t = (gg - m_g - nn * m_gn) * rinv;
+                if (add) t += to_f32(av.v[k]);
+                o.v[k] = from_f32<T>(t);
+            }
+            st16(dx + off + (v * 32 + lane) * VN, o);
+        }
+    }
+}
+
+// Norm backward for wide rows with its parameter gradients fused in (d = 256 * NVT * elements per 16 bytes: 2048 and
+// 4096 bf16 columns).  A block works on two rows at a time, every thread on the same NVT 16-byte vectors of each row, so
+// dgamma += sum g*gamma*n, dbeta += sum g and the column sums of the produced dx accumulate in registers; the two row
+// sums go through shared memory (one barrier per row pair, buffers used in turn).  Every activation is read once.  Each
+// block leaves its partial sums in partial[quantity][block][d] (quantities: dgamma, dbeta for LayerNorm, the column sums
+// if asked for); colsum_final_kernel adds them up in block order.
+template <typename T, bool LAYER, int NVT>
+__global__ void __launch_bounds__(256, 2)
+norm_bwd_wide_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ gamma,
+                           const float* __restrict__ rinv_in, const float* __restrict__ mean_in, const T* __restrict__ add,
+                           T* __restrict__ dx, float* __restrict__ partial, int rows, int want_colsum)
+{
+    constexpr int VN = Vec16<T>::N, D = 256 * NVT * VN, RG = 2;
+    __shared__ float red[2][8][RG][2];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float gm[NVT][VN], a_dg[NVT][VN], a_db[NVT][VN], a_cs[NVT][VN];
+#pragma unroll
+    for (int j = 0; j < NVT; ++j) {
+        ld_f32x<VN>(gamma + (j * 256 + tid) * VN, gm[j]);
+#pragma unroll
+        for (int k = 0; k < VN; ++k) { a_dg[j][k] = 0.f; a_db[j][k] = 0.f; a_cs[j][k] = 0.f; }
+    }
+    const float inv_d = 1.0f / static_cast<float>(D);
+    int it = 0;
+    for (int r0 = blockIdx.x * RG; r0 < rows; r0 += gridDim.x * RG, ++it) {
+        Vec16<T> gv[RG][NVT], xv[RG][NVT];
+        float rinv[RG], mean[RG];
+#pragma unroll
+        for (int rr = 0; rr < RG; ++rr) {
+            const int r = r0 + rr;
+            const bool live = r < rows;
+            rinv[rr] = live ? rinv_in[r] : 0.f;
+            mean[rr] = (LAYER && live) ? mean_in[r] : 0.f;
+#pragma unroll
+            for (int j = 0; j < NVT; ++j) {
+                if (live) {
+                    gv[rr][j] = ld16(g + static_cast<size_t>(r) * D + (j * 256 + tid) * VN);
+                    xv[rr][j] = ld16(x + static_cast<size_t>(r) * D + (j * 256 + tid) * VN);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < VN; ++k) { gv[rr][j].v[k] = from_f32<T>(0.f); xv[rr][j].v[k] = from_f32<T>(0.f); }
+                }
+            }
+        }
+#pragma unroll
+        for (int rr = 0; rr < RG; ++rr) {
+            float s_g = 0.f, s_gn = 0.f;
+#pragma unroll
+            for (int j = 0; j < NVT; ++j)
+#pragma unroll
+                for (int k = 0; k < VN; ++k) {
+                    const float gg = to_f32(gv[rr][j].v[k]) * gm[j][k], nn = (to_f32(xv[rr][j].v[k]) - mean[rr]) * rinv[rr];
+                    s_g += gg; s_gn += gg * nn;
+                }
+            s_gn = warp_sum(s_gn);
+            if (LAYER) s_g = warp_sum(s_g);
+            if (lane == 0) { red[it & 1][warp][rr][0] = s_gn; red[it & 1][warp][rr][1] = s_g; }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int rr = 0; rr < RG; ++rr) {
+            const int r = r0 + rr;
+            if (r >= rows) break;
+            float m_gn = 0.f, m_g = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) { m_gn += red[it & 1][w][rr][0]; if (LAYER) m_g += red[it & 1][w][rr][1]; }
+            m_gn *= inv_d; m_g *= inv_d;
+#pragma unroll
+            for (int j = 0; j < NVT; ++j) {
+                const size_t off = static_cast<size_t>(r) * D + (j * 256 + tid) * VN;
+                Vec16<T> av;
+                if (add) av = ld16(add + off);
+                Vec16<T> o;
+#pragma unroll
+                for (int k = 0; k < VN; ++k) {
+                    const float gr = to_f32(gv[rr][j].v[k]);
+                    const float gg = gr * gm[j][k], nn = (to_f32(xv[rr][j].v[k]) - mean[rr]) * rinv[rr];
+                    float t = (gg - m_g - nn * m_gn) * rinv[rr];
+                    if (add) t += to_f32(av.v[k]);
+                    o.v[k] = from_f32<T>(t);
+                    a_dg[j][k] += gg * nn;
+                    if (LAYER) a_db[j][k] += gr;
+                    if (want_colsum) a_cs[j][k] += to_f32(o.v[k]);
+                }
+                st16(dx + off, o);
+            }
+        }
+    }
+    const size_t per = static_cast<size_t>(gridDim.x) * D;
+#pragma unroll
+    for (int j = 0; j < NVT; ++j)
+#pragma unroll
+        for (int k = 0; k < VN; ++k) {
+            const size_t at = static_cast<size_t>(blockIdx.x) * D + (j * 256 + tid) * VN + k;
+            partial[at] = a_dg[j][k];
+            if (LAYER) partial[per + at] = a_db[j][k];
+            if (want_colsum) partial[(LAYER ? 2 : 1) * per + at] = a_cs[j][k];
+        }
 }
 
 // norm backward with its parameter gradients fused in.  A lane owns the same columns for every row
@@ -1056,6 +1290,18 @@ int norm_fwd(const T* x, const float* gamma, const float* beta, T* y, float* rin
     }
     NNB_NORM_FWD_REG(1) NNB_NORM_FWD_REG(2) NNB_NORM_FWD_REG(3) NNB_NORM_FWD_REG(4)
 #undef NNB_NORM_FWD_REG
+    // wider rows (up to 4096 bf16 columns): the row in registers as loaded, the parameters in shared memory
+    const int grid_wide = grid_for(rows, 4, 3);
+#define NNB_NORM_FWD_WIDE(nv)                                                                                         \
+    if (aligned && d == 32 * VN * nv) {                                                                               \
+        const size_t smem = static_cast<size_t>(layer ? 2 : 1) * d * sizeof(float);                                   \
+        if (layer) norm_fwd_wide_kernel<T, true, nv><<<grid_wide, 128, smem, s>>>(x, gamma, beta, y, rinv, mean, rows); \
+        else norm_fwd_wide_kernel<T, false, nv><<<grid_wide, 128, smem, s>>>(x, gamma, beta, y, rinv, mean, rows);     \
+        LAUNCH_CHECK();                                                                                               \
+        return 0;                                                                                                     \
+    }
+    NNB_NORM_FWD_WIDE(6) NNB_NORM_FWD_WIDE(8) NNB_NORM_FWD_WIDE(12) NNB_NORM_FWD_WIDE(16)
+#undef NNB_NORM_FWD_WIDE
     if (layer) norm_fwd_kernel<T, true><<<grid, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows, d);
     else norm_fwd_kernel<T, false><<<grid, 256, 0, s>>>(x, gamma, beta, y, rinv, mean, rows, d);
     LAUNCH_CHECK();
@@ -1211,6 +1457,28 @@ int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, cons
     }
     NNB_NORM_BWD_FUSED(1) NNB_NORM_BWD_FUSED(2) NNB_NORM_BWD_FUSED(3) NNB_NORM_BWD_FUSED(4)
 #undef NNB_NORM_BWD_FUSED
+    // wide rows (2048 / 4096 bf16 columns): one pass with the parameter gradients accumulated per block, then their fold.
+    // The caller's scratch holds colsum_scratch_floats(rows, d) floats, one row of d per 128 matrix rows: that bounds the
+    // number of blocks (each leaves one row per quantity); below one block the passes that follow take over.
+    const long long wide_rows_of_scratch = static_cast<long long>(colsum_scratch_floats(rows, d) / static_cast<size_t>(d));
+    const int wide_blocks = static_cast<int>(std::min<long long>(std::min<long long>(kNormFusedBlocks, ceil_div(rows, 2)),
+                                                                 wide_rows_of_scratch / (1 + (layer ? 1 : 0) + (out_colsum ? 1 : 0))));
+#define NNB_NORM_BWD_WIDE_FUSED(nvt)                                                                                  \
+    if (aligned && scratch && d == 256 * VN * nvt && wide_blocks >= 1) {                                              \
+        const int blocks = wide_blocks;                                                                               \
+        if (layer) norm_bwd_wide_fused_kernel<T, true, nvt><<<blocks, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, scratch, rows, out_colsum ? 1 : 0); \
+        else norm_bwd_wide_fused_kernel<T, false, nvt><<<blocks, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, scratch, rows, out_colsum ? 1 : 0);      \
+        LAUNCH_CHECK();                                                                                               \
+        const unsigned fold_grid = static_cast<unsigned>(ceil_div(d, 128));                                           \
+        const size_t per = static_cast<size_t>(blocks) * d;                                                           \
+        colsum_final_kernel<<<fold_grid, 128, 0, s>>>(scratch, dgamma, blocks, d);                                    \
+        LAUNCH_CHECK();                                                                                               \
+        if (layer) { colsum_final_kernel<<<fold_grid, 128, 0, s>>>(scratch + per, dbeta, blocks, d); LAUNCH_CHECK(); } \
+        if (out_colsum) { colsum_final_kernel<<<fold_grid, 128, 0, s>>>(scratch + (layer ? 2 : 1) * per, out_colsum, blocks, d); LAUNCH_CHECK(); } \
+        return 0;                                                                                                     \
+    }
+    NNB_NORM_BWD_WIDE_FUSED(1) NNB_NORM_BWD_WIDE_FUSED(2)
+#undef NNB_NORM_BWD_WIDE_FUSED
     // parameter gradients first: dx may alias g
     NNB_TRY(colsum_accumulate<T>(g, d, x, gamma, rinv, layer ? mean : nullptr, 1, dgamma, scratch, rows, d, s, counters));
     if (layer) NNB_TRY(colsum_accumulate<T>(g, d, nullptr, nullptr, nullptr, nullptr, 0, dbeta, scratch, rows, d, s, counters));
@@ -1224,6 +1492,17 @@ int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, cons
     }
     NNB_NORM_BWD_REG(1) NNB_NORM_BWD_REG(2) NNB_NORM_BWD_REG(3) NNB_NORM_BWD_REG(4)
 #undef NNB_NORM_BWD_REG
+#define NNB_NORM_BWD_WIDE(nv)                                                                                         \
+    if (!done && aligned && d == 32 * VN * nv) {                                                                      \
+        const int grid_wide = grid_for(rows, 4, 2);                                                                   \
+        const size_t smem = static_cast<size_t>(d) * sizeof(float);                                                   \
+        if (layer) norm_bwd_dx_wide_kernel<T, true, nv><<<grid_wide, 128, smem, s>>>(g, x, gamma, rinv, mean, add, dx, rows);  \
+        else norm_bwd_dx_wide_kernel<T, false, nv><<<grid_wide, 128, smem, s>>>(g, x, gamma, rinv, mean, add, dx, rows);       \
+        LAUNCH_CHECK();                                                                                               \
+        done = true;                                                                                                  \
+    }
+    NNB_NORM_BWD_WIDE(6) NNB_NORM_BWD_WIDE(8) NNB_NORM_BWD_WIDE(12) NNB_NORM_BWD_WIDE(16)
+#undef NNB_NORM_BWD_WIDE
     if (!done) {
         if (layer) norm_bwd_dx_kernel<T, true><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);
         else norm_bwd_dx_kernel<T, false><<<grid, 256, 0, s>>>(g, x, gamma, rinv, mean, add, dx, rows, d);

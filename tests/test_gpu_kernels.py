@@ -343,7 +343,8 @@ def test_attention_matches_reference_primitives_golden(g):
 # ----------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [0, 1])
 @pytest.mark.parametrize("layer", [0, 1])
-@pytest.mark.parametrize("rows,d", [(37, 48), (300, 128), (1024, 768), (600, 384), (520, 1024), (260, 4096)])
+@pytest.mark.parametrize("rows,d", [(37, 48), (300, 128), (1024, 768), (600, 384), (520, 1024), (260, 4096), (130, 2048),
+                                    (70, 1536), (45, 3072)])
 def test_norm_forward_backward(g, dtype, layer, rows, d):
     import torch
     from oracle import gpt_oracle as go
