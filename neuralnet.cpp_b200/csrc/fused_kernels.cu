@@ -1051,8 +1051,9 @@ ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const 
 // thread 0 fills with bulk copies (counted on an mbarrier) ahead of the row being worked on; the three passes (maximum,
 // sum of exponentials, gradient) read and overwrite the slot, and the finished row leaves as one bulk store while the
 // next is computed.  The register-cached kernel above does load -> reduce -> reduce -> store per row with nothing
-// overlapping inside a block (0.39 of the copy bandwidth at 16384 x 32768; this kernel: 0.50, the two exponentials per
-// element being the next limit: 4096 XU clocks per 64 KB row).  A thread handles the same vectors of a row in the same
+// overlapping inside a block (0.39 of the copy bandwidth at 16384 x 32768; this kernel: 0.50 with three slots and one
+// block per SM, 0.60 with one slot and three blocks per SM, which is how it is launched; the two exponentials per
+// element are the next limit: 4096 XU clocks per 64 KB row).  A thread handles the same vectors of a row in the same
 // order as there, so the results are bit-identical.  Used for rows above 32 KB.
 template <typename T>
 __global__ void __launch_bounds__(512)
@@ -1548,12 +1549,13 @@ int cross_entropy(T* logits, const int* labels, const float* mask, float grad_sc
     constexpr int VN = Vec16<T>::N;
     const bool vec_ok = (V % VN) == 0;
     const int nvec = V / VN;
-    // Rows above 32 KB (up to 72 KB) go through the staged kernel, three slots per block.  Shorter rows stay with the
-    // register-cached kernel: there the per-row barriers weigh more than the overlap buys (16384 x 8192: 192 us staged
-    // against 153 us; 16384 x 32768: 661 against 843 us).
+    // Rows of 32 to 72 KB go through the staged kernel with one slot per block, so that three blocks (64 KB rows) or four
+    // share an SM and one block's reductions and stores hide behind the others' passes (16384 x 32768: 546 us, against
+    // 662 us with three slots in one block per SM and 843 us register-cached; 16384 x 16384: 300 against 348 us
+    // register-cached).  Shorter rows stay with the register-cached kernel (16384 x 8192: 148 us against 185-193 staged).
     const size_t row_bytes = static_cast<size_t>(V) * sizeof(T);
-    if (vec_ok && (row_bytes % 16) == 0 && row_bytes > 32 * 1024 && row_bytes <= 72 * 1024 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
-        const int slots = 3;
+    if (vec_ok && (row_bytes % 16) == 0 && row_bytes >= 32 * 1024 && row_bytes <= 72 * 1024 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        const int slots = 1;
         const int smem = static_cast<int>(slots * row_bytes) + 64;
         static PerDeviceOnce once;
         NNB_TRY(once.run([] { return cudaFuncSetAttribute(ce_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 512); }));
