@@ -1048,13 +1048,14 @@ ce_fwd_bwd_kernel(T* __restrict__ logits, const int* __restrict__ labels, const 
 
 // loss = -(sum loss_vec) / num_valid (compute_loss.hpp:300-307); single block, fixed order
 // The same computation with the rows staged in shared memory: persistent blocks, each with a ring of row slots that
-// thread 0 fills with bulk copies (counted on an mbarrier) ahead of the row being worked on; the three passes (maximum,
+// thread 0 fills with bulk copies (counted on an mbarrier) ahead of the row being worked on; the two passes (maximum with
 // sum of exponentials, gradient) read and overwrite the slot, and the finished row leaves as one bulk store while the
 // next is computed.  The register-cached kernel above does load -> reduce -> reduce -> store per row with nothing
 // overlapping inside a block (0.39 of the copy bandwidth at 16384 x 32768; this kernel: 0.50 with three slots and one
 // block per SM, 0.60 with one slot and three blocks per SM, which is how it is launched; the two exponentials per
-// element are the next limit: 4096 XU clocks per 64 KB row).  A thread handles the same vectors of a row in the same
-// order as there, so the results are bit-identical.  Used for rows above 32 KB.
+// element are the next limit: 4096 XU clocks per 64 KB row).  Maximum and sum of exponentials are taken in one pass
+// (a running maximum per thread), so the sums differ from the register-cached kernel's in the last bits.  Used for rows
+// of 32 KB and more.
 template <typename T>
 __global__ void __launch_bounds__(512)
 ce_staged_kernel(T* __restrict__ logits, const int* __restrict__ labels, const float* __restrict__ mask,
@@ -1099,20 +1100,20 @@ ce_staged_kernel(T* __restrict__ logits, const int* __restrict__ labels, const f
             for (int i = threadIdx.x; i < nvec; i += blockDim.x) *reinterpret_cast<Vec16<T>*>(row + i * VN) = z;
             if (threadIdx.x == 0) loss_vec[r] = 0.f;
         } else {
-            float mx = -INFINITY;
+            // maximum and sum of exponentials in one pass over the slot: a thread's sum is kept relative to its own
+            // running maximum (rescaled when a vector raises it) and brought to the row maximum at the end
+            float tm = -INFINITY, ts = 0.f;
             for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
                 const Vec16<T> v = *reinterpret_cast<const Vec16<T>*>(row + i * VN);
+                float vm = to_f32(v.v[0]);
 #pragma unroll
-                for (int k = 0; k < VN; ++k) mx = fmaxf(mx, to_f32(v.v[k]));
-            }
-            mx = block_max(mx, red);
-            float den = 0.f;
-            for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-                const Vec16<T> v = *reinterpret_cast<const Vec16<T>*>(row + i * VN);
+                for (int k = 1; k < VN; ++k) vm = fmaxf(vm, to_f32(v.v[k]));
+                if (vm > tm) { ts *= exp_t<T>(tm - vm); tm = vm; }      // exp(-inf) = 0 the first time
 #pragma unroll
-                for (int k = 0; k < VN; ++k) den += exp_t<T>(to_f32(v.v[k]) - mx);
+                for (int k = 0; k < VN; ++k) ts += exp_t<T>(to_f32(v.v[k]) - tm);
             }
-            den = block_sum(den, red);
+            const float mx = block_max(tm, red);
+            float den = block_sum(tm == -INFINITY ? 0.f : ts * exp_t<T>(tm - mx), red);
             const float ll = to_f32(row[lbl]);
             __syncthreads();                              // everyone has read row[lbl] before it is overwritten
             if (threadIdx.x == 0) loss_vec[r] = ll - mx - logf(den);
@@ -1550,7 +1551,7 @@ int cross_entropy(T* logits, const int* labels, const float* mask, float grad_sc
     const bool vec_ok = (V % VN) == 0;
     const int nvec = V / VN;
     // Rows of 32 to 72 KB go through the staged kernel with one slot per block, so that three blocks (64 KB rows) or four
-    // share an SM and one block's reductions and stores hide behind the others' passes (16384 x 32768: 546 us, against
+    // share an SM and one block's reductions and stores hide behind the others' passes (16384 x 32768: 532 us, against
     // 662 us with three slots in one block per SM and 843 us register-cached; 16384 x 16384: 300 against 348 us
     // register-cached).  Shorter rows stay with the register-cached kernel (16384 x 8192: 148 us against 185-193 staged).
     const size_t row_bytes = static_cast<size_t>(V) * sizeof(T);
