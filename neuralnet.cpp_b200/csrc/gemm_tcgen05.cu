@@ -527,10 +527,12 @@ int gemm_bf16(const bf16* A, const bf16* B, void* C, int M, int N, int K, long l
     const int esz = c_bf16 ? 2 : 4;
     p.vec_ok = ((ldc * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) &&
                (!residual || (reinterpret_cast<uintptr_t>(residual) & 15) == 0);
-    const int BN = (N > 128) ? 256 : 128;
     // 256 x 256 tiles on CTA pairs when the output has more than one 128-row and one 128-column block and
-    // the coalesced (TMA-store) epilogue applies
-    const bool pair = p.vec_ok && M > 128 && N > 128 && pair_capacity() > 0;
+    // the coalesced (TMA-store) epilogue applies; a product too small to give half the pairs a tile runs 128 x 128 tiles
+    // on single CTAs instead (1024^3: 64 tiles instead of 16)
+    const bool few_tiles = !accumulate && 2 * ceil_div(M, 256) * ceil_div(N, 256) <= pair_capacity();
+    const int BN = (N > 128 && !few_tiles) ? 256 : 128;
+    const bool pair = p.vec_ok && M > 128 && N > 128 && pair_capacity() > 0 && !few_tiles;
     p.tiles_m = static_cast<int>(ceil_div(M, pair ? 256 : BM));
     p.tiles_n = static_cast<int>(ceil_div(N, BN));
     p.kb_total = static_cast<int>(ceil_div(K, BK));
