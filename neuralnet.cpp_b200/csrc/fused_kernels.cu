@@ -386,9 +386,9 @@ norm_bwd_dx_wide_kernel(const T* __restrict__ g, const T* __restrict__ x, const 
 }
 
 // Norm backward for wide rows with its parameter gradients fused in (d = 256 * NVT * elements per 16 bytes: 2048 and
-// 4096 bf16 columns).  A block works on two rows at a time, every thread on the same NVT 16-byte vectors of each row, so
+// 4096 bf16 columns).  A block works on two rows at a time (four at the narrower width), every thread on the same NVT 16-byte vectors of each row, so
 // dgamma += sum g*gamma*n, dbeta += sum g and the column sums of the produced dx accumulate in registers; the two row
-// sums go through shared memory (one barrier per row pair, buffers used in turn).  Every activation is read once.  Each
+// sums go through shared memory (one barrier per row group, buffers used in turn).  Every activation is read once.  Each
 // block leaves its partial sums in partial[quantity][block][d] (quantities: dgamma, dbeta for LayerNorm, the column sums
 // if asked for); colsum_final_kernel adds them up in block order.
 template <typename T, bool LAYER, int NVT>
@@ -397,7 +397,7 @@ norm_bwd_wide_fused_kernel(const T* __restrict__ g, const T* __restrict__ x, con
                            const float* __restrict__ rinv_in, const float* __restrict__ mean_in, const T* __restrict__ add,
                            T* __restrict__ dx, float* __restrict__ partial, int rows, int want_colsum)
 {
-    constexpr int VN = Vec16<T>::N, D = 256 * NVT * VN, RG = 2;
+    constexpr int VN = Vec16<T>::N, D = 256 * NVT * VN, RG = NVT == 1 ? 4 : 2;     // rows per step: 32 KB of g and x in flight
     __shared__ float red[2][8][RG][2];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float gm[NVT][VN], a_dg[NVT][VN], a_db[NVT][VN], a_cs[NVT][VN];
@@ -1463,7 +1463,7 @@ int norm_bwd(const T* g, const T* x, const float* gamma, const float* rinv, cons
     // The caller's scratch holds colsum_scratch_floats(rows, d) floats, one row of d per 128 matrix rows: that bounds the
     // number of blocks (each leaves one row per quantity); below one block the passes that follow take over.
     const long long wide_rows_of_scratch = static_cast<long long>(colsum_scratch_floats(rows, d) / static_cast<size_t>(d));
-    const int wide_blocks = static_cast<int>(std::min<long long>(std::min<long long>(kNormFusedBlocks, ceil_div(rows, 2)),
+    const int wide_blocks = static_cast<int>(std::min<long long>(std::min<long long>(kNormFusedBlocks, ceil_div(rows, d == 256 * VN ? 4 : 2)),
                                                                  wide_rows_of_scratch / (1 + (layer ? 1 : 0) + (out_colsum ? 1 : 0))));
 #define NNB_NORM_BWD_WIDE_FUSED(nvt)                                                                                  \
     if (aligned && scratch && d == 256 * VN * nvt && wide_blocks >= 1) {                                              \
